@@ -1,0 +1,20 @@
+"""Argument prototypes of libgcow_cuda.so's C entry points."""
+import ctypes as C
+
+u64, u32, i32 = C.c_uint64, C.c_uint32, C.c_int
+ptr = C.c_void_p
+
+
+def declare(lib, proto):
+    def opt(name, restype, *args):
+        if hasattr(lib, name):
+            proto(lib, name, restype, *args)
+
+    # codec
+    opt("gcow_encode_1d_fixed", i32, ptr, u64, i32, ptr, ptr)
+    opt("gcow_decode_1d_fixed", i32, ptr, ptr, u64, i32, i32, ptr)
+    opt("gcow_encode_generic_scratch_bytes", u64, ptr, u64, i32)
+    opt("gcow_encode_generic", i32, ptr, u64, u64, ptr, ptr, u64, ptr, ptr, ptr)
+    opt("gcow_decode_generic", i32, ptr, ptr, u64, u64, ptr, ptr, i32, ptr)
+    opt("gcow_dbg_stage", i32, i32, i32, u64, ptr, ptr, ptr, i32, ptr)
+    opt("gcow_dbg_planes", i32, i32, u64, ptr, u32, u32, i32, u32, ptr, ptr, ptr)

@@ -1,0 +1,93 @@
+"""One configuration object for codec, collective and training front ends.
+
+Precedence: dataclass defaults < environment variables ``GCOW_<FIELD>`` < explicit
+keyword / CLI arguments. The reference spreads its settings over make variables
+(hw/Makefile:30-36), compile-time macros (hw/include/common.hpp:13-15), a
+tolerance hard-wired into the kernel (hw/src/gcow.cpp:44) and argparse flags
+(hw/models/train_imagenet.py:36-94); this replaces all of them.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import os
+from dataclasses import dataclass, fields
+
+
+@dataclass
+class GcowConfig:
+    # codec
+    dim: int = 1                    # 1: blocks of 4 (flat gradients); 2: blocks of 4x4
+    mode: str = "rate"              # rate | accuracy | precision
+    rate: float = 8.0               # bits per value (rate mode)
+    tolerance: float = 1e-3         # absolute error bound (accuracy mode)
+    precision: int = 16             # bit planes kept (precision mode)
+    # collective
+    variant: str = "auto"           # auto | oneshot | twoshot | nvls | nccl
+    oneshot_max_bytes: int = 1 << 20  # buckets up to this many fp32 bytes use one-shot
+    comm_ctas: int = 32             # CTAs of the persistent fused kernel
+    timeout_ms: int = 2000          # bound of every device-side wait
+    bucket_mb: int = 25             # DDP bucket size
+    average: bool = True            # divide by world size (DDP semantics)
+    error_feedback: bool = False    # keep the compression residual per bucket
+    fallback_nccl: bool = True      # on a collective time-out, redo the bucket with NCCL fp32
+    # runtime
+    log_path: str = ""              # JSONL metrics file ("" = off)
+    trace: bool = False             # NVTX ranges + device phase stamps
+
+    @classmethod
+    def from_env(cls, **overrides) -> "GcowConfig":
+        kw = {}
+        for f in fields(cls):
+            v = os.environ.get("GCOW_" + f.name.upper())
+            if v is None:
+                continue
+            if f.type in ("bool", bool):
+                kw[f.name] = v.lower() in ("1", "true", "yes", "on")
+            elif f.type in ("int", int):
+                kw[f.name] = int(v)
+            elif f.type in ("float", float):
+                kw[f.name] = float(v)
+            else:
+                kw[f.name] = v
+        kw.update({k: v for k, v in overrides.items() if v is not None})
+        cfg = cls(**kw)
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if self.dim not in (1, 2):
+            raise ValueError("dim must be 1 or 2")
+        if self.mode not in ("rate", "accuracy", "precision"):
+            raise ValueError("mode must be rate, accuracy or precision")
+        if self.variant not in ("auto", "oneshot", "twoshot", "nvls", "nccl"):
+            raise ValueError("unknown collective variant " + self.variant)
+        if self.timeout_ms <= 0:
+            raise ValueError("timeout_ms must be positive")
+
+    @classmethod
+    def add_cli(cls, parser: argparse.ArgumentParser) -> None:
+        g = parser.add_argument_group("gcow")
+        for f in fields(cls):
+            name = "--gcow-" + f.name.replace("_", "-")
+            if f.type in ("bool", bool):
+                g.add_argument(name, default=None, action=argparse.BooleanOptionalAction)
+            else:
+                typ = {"int": int, "float": float, "str": str}.get(f.type, f.type)
+                g.add_argument(name, default=None, type=typ)
+
+    @classmethod
+    def from_cli(cls, args: argparse.Namespace) -> "GcowConfig":
+        ov = {f.name: getattr(args, "gcow_" + f.name, None) for f in fields(cls)}
+        return cls.from_env(**ov)
+
+    def zfp_params(self):
+        from .codec import ZfpParams
+        if self.mode == "rate":
+            return ZfpParams.from_rate(self.rate, self.dim)
+        if self.mode == "accuracy":
+            return ZfpParams.from_accuracy(self.tolerance)
+        return ZfpParams.from_precision(self.precision)
+
+    def asdict(self) -> dict:
+        return dataclasses.asdict(self)

@@ -1,0 +1,512 @@
+// Per-block stages of the ZFP float32 codec as host+device inline functions.
+//
+// One CUDA thread (or one CPU loop iteration) owns one block of 4^DIM values
+// and runs every stage in registers: common exponent, block-floating-point
+// cast, decorrelating lift, negabinary reorder and the embedded bit-plane
+// coder. The same functions compile for the host, so the fast formulation used
+// by the kernels is checked on the CPU against the serial oracle.
+//
+// Stage semantics follow the reference CPU codec:
+//   sw/src/encode.c:41-88     gather and padding of partial blocks
+//   sw/src/encode.c:128-152   block exponent (frexp, subnormal clamp)
+//   sw/src/encode.c:162-187   cast: (int32)(2^(30-emax) * f), C truncation
+//   sw/src/encode.c:189-260   forward lift, rows then columns
+//   sw/src/encode.c:263-275   negabinary + coefficient order (sw/include/types.h:71-97)
+//   sw/src/encode.c:279-339   budgeted embedded coder (group test + unary runs)
+//   sw/src/encode.c:457-495   block header: flag bit + 8-bit biased exponent
+//   sw/src/decode.c:12-25,44-183,220-253  the inverses
+// The budgeted coder emits a prefix of the unbudgeted one (every emitted bit
+// depends only on the plane and on the running count n), so encoding is
+// "concatenate per-plane codes, cut at the budget".
+#pragma once
+#include <stdint.h>
+#include <string.h>
+#include "zfp_params.h"
+
+namespace gcow {
+
+// ---------------------------------------------------------------- bit casts
+GCOW_HD uint32_t f32_bits(float f) {
+#if defined(__CUDA_ARCH__)
+  return __float_as_uint(f);
+#else
+  uint32_t u; memcpy(&u, &f, 4); return u;
+#endif
+}
+GCOW_HD float bits_f32(uint32_t u) {
+#if defined(__CUDA_ARCH__)
+  return __uint_as_float(u);
+#else
+  float f; memcpy(&f, &u, 4); return f;
+#endif
+}
+GCOW_HD int ctz32(uint32_t x) {  // x != 0
+#if defined(__CUDA_ARCH__)
+  return __ffs((int)x) - 1;
+#else
+  return __builtin_ctz(x);
+#endif
+}
+GCOW_HD uint32_t low_mask32(uint32_t n) { return n >= 32 ? 0xffffffffu : ((1u << n) - 1u); }
+GCOW_HD uint64_t low_mask64(uint32_t n) { return n >= 64 ? ~0ull : ((1ull << n) - 1ull); }
+
+// 2^e as float32: exact for -149 <= e <= 127, +inf above, 0 below (what
+// ldexpf(1, e) returns).
+GCOW_HD float pow2f(int e) {
+  if (e > 127) return bits_f32(0x7f800000u);
+  if (e >= -126) return bits_f32((uint32_t)(e + 127) << 23);
+  if (e >= -149) return bits_f32(1u << (e + 149));
+  return 0.0f;
+}
+
+// float -> int32 with truncation; out-of-range and NaN give INT32_MIN, which
+// is what the x86 conversion the reference relies on produces.
+GCOW_HD int32_t trunc_to_i32(float v) {
+  float a = v < 0 ? -v : v;
+  if (!(a < 2147483648.0f)) return (int32_t)0x80000000u;
+#if defined(__CUDA_ARCH__)
+  return __float2int_rz(v);
+#else
+  return (int32_t)v;
+#endif
+}
+
+// ------------------------------------------------------------------ stages
+// Exponent e of m >= 0 with m = f * 2^e, 0.5 <= f < 1; -127 for zero, clamped
+// to -126 for subnormals. Non-finite input is clamped to the largest exponent.
+GCOW_HD int scalar_exponent(float m) {
+  if (!(m > 0)) return -kEBias;
+  uint32_t ex = (f32_bits(m) >> 23) & 0xffu;
+  if (ex == 0) return 1 - kEBias;
+  if (ex == 255) ex = 254;
+  return (int)ex - 126;
+}
+
+template <int N>
+GCOW_HD int block_emax(const float* f) {
+  float m = 0;
+#pragma unroll
+  for (int i = 0; i < N; i++) {
+    float a = f[i] < 0 ? -f[i] : f[i];
+    if (m < a) m = a;
+  }
+  return scalar_exponent(m);
+}
+
+template <int N>
+GCOW_HD void fwd_cast(int32_t* q, const float* f, int emax) {
+  float scale = pow2f(30 - emax);
+#pragma unroll
+  for (int i = 0; i < N; i++) q[i] = trunc_to_i32(scale * f[i]);
+}
+
+// `shift` folds an exact division by 2^shift into the scale (averaging over a
+// power-of-two number of ranks).
+template <int N>
+GCOW_HD void inv_cast(float* f, const int32_t* q, int emax, int shift = 0) {
+  float scale = pow2f(emax - 30 - shift);
+#pragma unroll
+  for (int i = 0; i < N; i++) f[i] = scale * (float)q[i];
+}
+
+GCOW_HD uint32_t asr1(uint32_t v) { return (uint32_t)((int32_t)v >> 1); }
+
+// Forward lift of one 4-vector; wrapping arithmetic, arithmetic shifts.
+GCOW_HD void fwd_lift(int32_t& x_, int32_t& y_, int32_t& z_, int32_t& w_) {
+  uint32_t x = (uint32_t)x_, y = (uint32_t)y_, z = (uint32_t)z_, w = (uint32_t)w_;
+  x += w; x = asr1(x); w -= x;
+  z += y; z = asr1(z); y -= z;
+  x += z; x = asr1(x); z -= x;
+  w += y; w = asr1(w); y -= w;
+  w += asr1(y); y -= asr1(w);
+  x_ = (int32_t)x; y_ = (int32_t)y; z_ = (int32_t)z; w_ = (int32_t)w;
+}
+
+GCOW_HD void inv_lift(int32_t& x_, int32_t& y_, int32_t& z_, int32_t& w_) {
+  uint32_t x = (uint32_t)x_, y = (uint32_t)y_, z = (uint32_t)z_, w = (uint32_t)w_;
+  y += asr1(w); w -= asr1(y);
+  y += w; w <<= 1; w -= y;
+  z += x; x <<= 1; x -= z;
+  y += z; z <<= 1; z -= y;
+  w += x; x <<= 1; x -= w;
+  x_ = (int32_t)x; y_ = (int32_t)y; z_ = (int32_t)z; w_ = (int32_t)w;
+}
+
+template <int DIM> struct Xform;
+template <> struct Xform<1> {
+  static GCOW_HD void fwd(int32_t* q) { fwd_lift(q[0], q[1], q[2], q[3]); }
+  static GCOW_HD void inv(int32_t* q) { inv_lift(q[0], q[1], q[2], q[3]); }
+  static GCOW_HD constexpr int perm(int i) { return i; }
+};
+template <> struct Xform<2> {
+  static GCOW_HD void fwd(int32_t* q) {
+#pragma unroll
+    for (int y = 0; y < 4; y++) fwd_lift(q[4 * y], q[4 * y + 1], q[4 * y + 2], q[4 * y + 3]);
+#pragma unroll
+    for (int x = 0; x < 4; x++) fwd_lift(q[x], q[x + 4], q[x + 8], q[x + 12]);
+  }
+  static GCOW_HD void inv(int32_t* q) {
+#pragma unroll
+    for (int x = 0; x < 4; x++) inv_lift(q[x], q[x + 4], q[x + 8], q[x + 12]);
+#pragma unroll
+    for (int y = 0; y < 4; y++) inv_lift(q[4 * y], q[4 * y + 1], q[4 * y + 2], q[4 * y + 3]);
+  }
+  // Coefficients ordered by total degree i+j, then i^2+j^2.
+  static GCOW_HD constexpr int perm(int i) {
+    constexpr int P[16] = {0, 1, 4, 5, 2, 8, 6, 9, 3, 12, 10, 7, 13, 11, 14, 15};
+    return P[i];
+  }
+};
+
+GCOW_HD uint32_t int2nb(int32_t x) { return ((uint32_t)x + kNbMask) ^ kNbMask; }
+GCOW_HD int32_t nb2int(uint32_t u) { return (int32_t)((u ^ kNbMask) - kNbMask); }
+
+template <int DIM>
+GCOW_HD void fwd_reorder(uint32_t* u, const int32_t* q) {
+#pragma unroll
+  for (int i = 0; i < (1 << (2 * DIM)); i++) u[i] = int2nb(q[Xform<DIM>::perm(i)]);
+}
+template <int DIM>
+GCOW_HD void inv_reorder(int32_t* q, const uint32_t* u) {
+#pragma unroll
+  for (int i = 0; i < (1 << (2 * DIM)); i++) q[Xform<DIM>::perm(i)] = nb2int(u[i]);
+}
+
+// Fill positions n..3 of a 4-vector with stride s: 0 -> zeros, 1 -> a a a a,
+// 2 -> a b b a, 3 -> a b c a.
+GCOW_HD void pad_partial(float* b, uint32_t n, int s) {
+  if (n == 0) b[0] = 0;
+  if (n <= 1) b[s] = b[0];
+  if (n <= 2) b[2 * s] = b[s];
+  if (n <= 3) b[3 * s] = b[0];
+}
+
+// --------------------------------------------------------- plane transposes
+template <int N>
+GCOW_HD uint32_t extract_plane(const uint32_t* u, int k) {
+  uint32_t x = 0;
+#pragma unroll
+  for (int i = 0; i < N; i++) x |= ((u[i] >> k) & 1u) << i;
+  return x;
+}
+template <int N>
+GCOW_HD void deposit_plane(uint32_t* u, uint32_t x, int k) {
+#pragma unroll
+  for (int i = 0; i < N; i++) u[i] |= ((x >> i) & 1u) << k;
+}
+
+// ------------------------------------------------------ embedded plane coder
+// Code of one bit plane `x` (N bits) given that the first `n` coefficients are
+// already significant: n verbatim bits, then group tests and unary runs. `n`
+// is advanced. Runs of zeros are skipped with a count-trailing-zeros.
+template <int N>
+GCOW_HD void encode_plane(uint32_t x, uint32_t& n, uint64_t& code, uint32_t& len) {
+  code = x & low_mask32(n);
+  len = n;
+  x = n >= 32 ? 0 : x >> n;
+  while (n < (uint32_t)N) {
+    if (!x) { len++; break; }            // negative group test: one 0 bit
+    code |= 1ull << len; len++;          // positive group test
+    uint32_t z = (uint32_t)ctz32(x);     // z zeros precede the next one-bit
+    if (n + z < (uint32_t)N - 1) { code |= 1ull << (len + z); len += z + 1; }
+    else len += z;                       // last position: the one-bit is implied
+    x >>= z; x >>= 1;
+    n += z + 1;
+  }
+}
+
+// Encode planes 31..kmin into `sink` until `budget` bits are used.
+template <int N, class Sink>
+GCOW_HD uint32_t encode_planes(const uint32_t* u, uint32_t budget, uint32_t prec, Sink& sink) {
+  uint32_t kmin = prec < 32 ? 32 - prec : 0;
+  uint32_t bits = budget, n = 0;
+  for (uint32_t k = 32; bits && k-- > kmin;) {
+    uint32_t x = extract_plane<N>(u, (int)k);
+    uint64_t code; uint32_t len;
+    encode_plane<N>(x, n, code, len);
+    if (len > bits) { len = bits; code &= low_mask64(len); }
+    sink.put(code, len);
+    bits -= len;
+  }
+  return budget - bits;
+}
+
+// Decode planes k-1..kmin from `src` with `bits` of budget, starting with `n`
+// significant coefficients; `u` accumulates. When the budget ends inside a
+// unary run the pending one-bit is still placed at the position reached, which
+// is what the serial decoder of the reference does.
+template <int N, class Src>
+GCOW_HD uint32_t decode_planes_from(uint32_t* u, uint32_t bits, uint32_t kmin, uint32_t k,
+                                    uint32_t n, Src& src) {
+  uint32_t start = bits;
+  while (bits && k-- > kmin) {
+    uint32_t m = n < bits ? n : bits;
+    bits -= m;
+    uint32_t x = (uint32_t)src.get(m);
+    for (; bits && n < (uint32_t)N; n++) {
+      bits--;
+      if (src.get(1)) {
+        for (; bits && n < (uint32_t)N - 1; n++) {
+          bits--;
+          if (src.get(1)) break;
+        }
+        x += 1u << n;
+      } else {
+        break;
+      }
+    }
+    deposit_plane<N>(u, x, (int)k);
+  }
+  return start - bits;
+}
+
+template <int N, class Src>
+GCOW_HD uint32_t decode_planes(uint32_t* u, uint32_t budget, uint32_t prec, Src& src) {
+#pragma unroll
+  for (int i = 0; i < N; i++) u[i] = 0;
+  uint32_t kmin = prec < 32 ? 32 - prec : 0;
+  return decode_planes_from<N>(u, budget, kmin, 32, 0, src);
+}
+
+// ------------------------------------------------------- memory bit streams
+// LSB-first packer into 64-bit words (sw/src/stream.c:61-138 semantics).
+struct WordSink {
+  uint64_t* out;
+  uint64_t acc;
+  uint32_t fill;
+  uint32_t nw;
+  GCOW_HD explicit WordSink(uint64_t* o) : out(o), acc(0), fill(0), nw(0) {}
+  GCOW_HD void put(uint64_t v, uint32_t n) {  // 0 <= n <= 64, v < 2^n
+    if (!n) return;
+    acc |= v << fill;
+    uint32_t tot = fill + n;
+    if (tot >= 64) {
+      out[nw++] = acc;
+      acc = fill ? (v >> (64 - fill)) : 0;
+      tot -= 64;
+    }
+    fill = tot;
+  }
+  GCOW_HD void pad(uint32_t n) {
+    while (n) { uint32_t c = n < 64 ? n : 64; put(0, c); n -= c; }
+  }
+  GCOW_HD uint64_t bit_count() const { return (uint64_t)nw * 64 + fill; }
+  GCOW_HD void finish() { if (fill) { out[nw++] = acc; acc = 0; fill = 0; } }
+};
+
+// Random-access LSB-first reader over 64-bit words.
+struct WordSrc {
+  const uint64_t* in;
+  uint64_t pos;
+  GCOW_HD WordSrc(const uint64_t* i, uint64_t p) : in(i), pos(p) {}
+  GCOW_HD uint64_t get(uint32_t n) {  // 0 <= n <= 32
+    if (!n) return 0;
+    uint32_t o = (uint32_t)(pos & 63);
+    uint64_t w = in[pos >> 6] >> o;
+    if (o + n > 64) w |= in[(pos >> 6) + 1] << (64 - o);
+    pos += n;
+    return w & low_mask64(n);
+  }
+  GCOW_HD void skip(uint64_t n) { pos += n; }
+};
+
+// ------------------------------------------------------ generic block codec
+// Encode one block of 4^DIM floats. Returns the number of bits emitted,
+// including zero padding up to minbits.
+template <int DIM, class Sink>
+GCOW_HD uint32_t encode_block(const float* f, const ZfpParams& p, Sink& sink) {
+  constexpr int N = 1 << (2 * DIM);
+  int emax = block_emax<N>(f);
+  uint32_t prec = block_precision(emax, p.maxprec, p.minexp, DIM);
+  uint32_t biased = prec ? (uint32_t)(emax + kEBias) : 0;
+  uint32_t bits;
+  if (biased) {
+    sink.put(2 * biased + 1, kHeaderBits);
+    int32_t q[N];
+    uint32_t u[N];
+    fwd_cast<N>(q, f, emax);
+    Xform<DIM>::fwd(q);
+    fwd_reorder<DIM>(u, q);
+    bits = kHeaderBits + encode_planes<N>(u, p.maxbits - kHeaderBits, prec, sink);
+  } else {
+    sink.put(0, 1);
+    bits = 1;
+  }
+  if (bits < p.minbits) { sink.pad(p.minbits - bits); bits = p.minbits; }
+  return bits;
+}
+
+// Decode one block; the source is advanced by the block's full length
+// (including padding up to minbits). `shift` divides the result by 2^shift.
+template <int DIM, class Src>
+GCOW_HD uint32_t decode_block(float* f, const ZfpParams& p, Src& src, int shift = 0) {
+  constexpr int N = 1 << (2 * DIM);
+  uint32_t bits = 1;
+  if (src.get(1)) {
+    int emax = (int)src.get(kEBits) - kEBias;
+    bits += kEBits;
+    uint32_t prec = block_precision(emax, p.maxprec, p.minexp, DIM);
+    uint32_t u[N];
+    int32_t q[N];
+    bits += decode_planes<N>(u, p.maxbits - kHeaderBits, prec, src);
+    inv_reorder<DIM>(q, u);
+    Xform<DIM>::inv(q);
+    inv_cast<N>(f, q, emax, shift);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; i++) f[i] = 0;
+  }
+  if (bits < p.minbits) { src.skip(p.minbits - bits); bits = p.minbits; }
+  return bits;
+}
+
+// ------------------------------------------- table-driven 1-D block codec
+// For blocks of 4 a plane has 16 values and the running count n has 5, so one
+// plane is one table lookup. Encoder entry: code (7 bits) | len << 7 | n' << 10.
+// Decoder entry, indexed by (n, next 7 stream bits): plane | len << 4 | n' << 7.
+constexpr int kEncTabSize = 5 * 16;
+constexpr int kDecTabSize = 5 * 128;
+
+GCOW_HD uint16_t make_enc_entry(uint32_t n, uint32_t x) {
+  uint64_t code; uint32_t len;
+  encode_plane<4>(x, n, code, len);
+  return (uint16_t)(code | (len << 7) | (n << 10));
+}
+
+struct TinySrc {  // reads from a small integer
+  uint32_t v, used;
+  GCOW_HD uint64_t get(uint32_t n) {
+    uint32_t r = n ? (v & low_mask32(n)) : 0;
+    v = n >= 32 ? 0 : v >> n;
+    used += n;
+    return r;
+  }
+};
+
+GCOW_HD uint16_t make_dec_entry(uint32_t n, uint32_t peek) {
+  uint32_t u[4] = {0, 0, 0, 0};
+  TinySrc s{peek, 0};
+  // one plane (k = 1 -> plane 0), effectively unlimited budget
+  uint32_t m = n;
+  uint32_t x = (uint32_t)s.get(m);
+  for (; n < 4; n++) {
+    if (s.get(1)) {
+      for (; n < 3; n++) if (s.get(1)) break;
+      x += 1u << n;
+    } else break;
+  }
+  (void)u;
+  return (uint16_t)(x | (s.used << 4) | (n << 7));
+}
+
+// Append `len` (<= 9) low bits of v at bit `pos` of a little-endian array of
+// NW 32-bit words; bits past the array fall off.
+template <int NW>
+GCOW_HD void reg_put(uint32_t (&w)[NW], uint32_t pos, uint32_t v) {
+#pragma unroll
+  for (int i = 0; i < NW; i++) {
+    int lo = (int)pos - 32 * i;
+    if (lo >= 0 && lo < 32) w[i] |= v << lo;
+    else if (lo < 0 && lo > -32) w[i] |= v >> (-lo);
+  }
+}
+// At least 7 valid bits starting at bit `pos`.
+template <int NW>
+GCOW_HD uint32_t reg_peek(const uint32_t (&w)[NW], uint32_t pos) {
+  uint32_t r = 0;
+#pragma unroll
+  for (int i = 0; i < NW; i++) {
+    int lo = (int)pos - 32 * i;
+    if (lo >= 0 && lo < 32) r |= w[i] >> lo;
+    else if (lo < 0 && lo > -32) r |= w[i] << (-lo);
+  }
+  return r;
+}
+template <int NW>
+struct RegSrc {
+  const uint32_t (&w)[NW];
+  uint32_t pos;
+  GCOW_HD uint64_t get(uint32_t n) {  // n <= 7 here
+    if (!n) return 0;
+    uint32_t r = reg_peek<NW>(w, pos) & low_mask32(n);
+    pos += n;
+    return r;
+  }
+};
+
+// Encode one block of 4 into NW 32-bit words (maxbits <= 32*NW). Returns the
+// bit count including padding to minbits.
+template <int NW>
+GCOW_HD uint32_t encode_block_1d_fast(const float* f, const ZfpParams& p, const uint16_t* etab,
+                                      uint32_t (&w)[NW]) {
+#pragma unroll
+  for (int i = 0; i < NW; i++) w[i] = 0;
+  int emax = block_emax<4>(f);
+  uint32_t prec = block_precision(emax, p.maxprec, p.minexp, 1);
+  uint32_t pos;
+  if (prec && emax + kEBias) {
+    w[0] = 2u * (uint32_t)(emax + kEBias) + 1u;
+    pos = kHeaderBits;
+    int32_t q[4];
+    uint32_t u[4];
+    fwd_cast<4>(q, f, emax);
+    fwd_lift(q[0], q[1], q[2], q[3]);
+#pragma unroll
+    for (int i = 0; i < 4; i++) u[i] = int2nb(q[i]);
+    uint32_t kmin = prec < 32 ? 32 - prec : 0;
+    uint32_t n = 0;
+    const uint32_t end = p.maxbits;
+    for (uint32_t k = 32; pos < end && k-- > kmin;) {
+      uint32_t x = extract_plane<4>(u, (int)k);
+      uint32_t e = etab[n * 16 + x];
+      reg_put<NW>(w, pos, e & 0x7fu);
+      pos += (e >> 7) & 7u;
+      n = e >> 10;
+    }
+    if (pos > end) {  // cut the last code at the budget
+#pragma unroll
+      for (int i = 0; i < NW; i++) {
+        if (end <= 32u * i) w[i] = 0;
+        else if (end < 32u * (i + 1)) w[i] &= low_mask32(end - 32u * i);
+      }
+      pos = end;
+    }
+  } else {
+    pos = 1;
+  }
+  return pos < p.minbits ? p.minbits : pos;
+}
+
+// Decode one block of 4 held in NW 32-bit words.
+template <int NW>
+GCOW_HD void decode_block_1d_fast(float* f, const ZfpParams& p, const uint16_t* dtab,
+                                  const uint32_t (&w)[NW], int shift = 0) {
+  if (!(w[0] & 1u)) {
+    f[0] = f[1] = f[2] = f[3] = 0;
+    return;
+  }
+  int emax = (int)((w[0] >> 1) & 0xffu) - kEBias;
+  uint32_t prec = block_precision(emax, p.maxprec, p.minexp, 1);
+  uint32_t kmin = prec < 32 ? 32 - prec : 0;
+  uint32_t u[4] = {0, 0, 0, 0};
+  uint32_t pos = kHeaderBits, n = 0, k = 32;
+  const uint32_t end = p.maxbits;
+  // whole codes: at least 7 bits left, so any plane code fits the budget
+  while (end - pos >= 7 && k > kmin) {
+    k--;
+    uint32_t e = dtab[n * 128 + (reg_peek<NW>(w, pos) & 127u)];
+    deposit_plane<4>(u, e & 15u, (int)k);
+    pos += (e >> 4) & 7u;
+    n = e >> 7;
+  }
+  // last few bits: exact serial semantics at the budget edge
+  RegSrc<NW> src{w, pos};
+  decode_planes_from<4>(u, end - pos, kmin, k, n, src);
+  int32_t q[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) q[i] = nb2int(u[i]);
+  inv_lift(q[0], q[1], q[2], q[3]);
+  inv_cast<4>(f, q, emax, shift);
+}
+
+}  // namespace gcow
