@@ -18,3 +18,31 @@ def declare(lib, proto):
     opt("gcow_decode_generic", i32, ptr, ptr, u64, u64, ptr, ptr, i32, ptr)
     opt("gcow_dbg_stage", i32, i32, i32, u64, ptr, ptr, ptr, i32, ptr)
     opt("gcow_dbg_planes", i32, i32, u64, ptr, u32, u32, i32, u32, ptr, ptr, ptr)
+
+
+def _declare_comm(lib, proto):
+    def opt(name, restype, *args):
+        if hasattr(lib, name):
+            proto(lib, name, restype, *args)
+    f32 = C.c_float
+    opt("gcow_ar_arena_bytes", u64, u64)
+    opt("gcow_ar_flag_bytes", u64)
+    opt("gcow_ar_region_bytes", u64, u64, i32, i32, i32, i32)
+    opt("gcow_ar_max_ctas", i32, i32)
+    opt("gcow_ar_launch", i32, ptr, ptr, u64, i32, i32, i32, i32, i32, i32, f32, ptr, ptr, u64, u32, u64,
+        ptr, ptr, ptr, ptr)
+    opt("gcow_ar_wait_probe", i32, ptr, u32, u64, ptr, ptr, ptr)
+    opt("gcow_ipc_alloc", i32, u64, ptr)
+    opt("gcow_ipc_free", i32, ptr)
+    opt("gcow_ipc_export", i32, ptr, ptr)
+    opt("gcow_ipc_open", i32, ptr, ptr)
+    opt("gcow_ipc_close", i32, ptr)
+    opt("gcow_device_sync", i32)
+
+
+_declare_codec = declare
+
+
+def declare(lib, proto):  # noqa: F811
+    _declare_codec(lib, proto)
+    _declare_comm(lib, proto)

@@ -54,6 +54,8 @@ def cpu() -> C.CDLL:
             _proto(lib, "gcow_stage_stream_write", u64, ptr, ptr, i32, ptr, i32)
             _proto(lib, "gcow_stage_gather", None, ptr, u64, u64, u64, ptr)
             _proto(lib, "gcow_oracle_allreduce", None, ptr, i32, u64, ptr, i32, i32, ptr, i32)
+            _proto(lib, "gcow_protocol_model", i32, ptr, ptr, i32, u64, i32, i32, i32, i32, i32, i32, i32,
+                   i32, i32, i32, i32, i32, i32, i32, ptr)
             _cpu = lib
     return _cpu
 

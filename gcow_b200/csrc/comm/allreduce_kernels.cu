@@ -1,0 +1,458 @@
+// Fused compressed all-reduce over NVLink peer memory (sm_100a).
+//
+// One persistent kernel per rank does the whole collective; there is no NCCL
+// call and no separate codec launch. With P ranks, rank r:
+//   phase 1  encodes its bucket block by block in registers and stores every
+//            compressed block straight into the owner's receive slot over
+//            NVLink (plain peer st.global), then releases one flag per
+//            (destination, CTA);
+//   phase 2  (owner of shard r) waits for the P flags of its slice, decodes the
+//            P copies of each block, adds them in ascending rank order in fp32,
+//            re-encodes and stores the result into every rank's gather slot -
+//            P peer stores, or one multimem.st through the NVSwitch multicast
+//            mapping in the NVLS variant - then releases the gather flags;
+//   phase 3  waits for each shard's gather flag and decodes into the fp32
+//            output, folding the division by P into the block exponent.
+// The one-shot variant pushes every block to every rank in phase 1 and sums the
+// P decoded copies locally (no re-encode, one network hop).
+//
+// Every wait is bounded by a globaltimer deadline and an iteration count; a CTA
+// that gives up records {code, phase, peer, cta, expected, seen}, raises the
+// abort flag for its siblings and returns. Nothing traps and nothing spins
+// forever, so a missing peer costs a time-out, not the GPU.
+//
+// Replaces the reference's "NCCL all-reduce, then copy the whole gradient to
+// the host, zfpy round trip, copy back" (hw/models/train_imagenet.py:219,449-475).
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "zfp_block.cuh"
+#include "ar_layout.h"
+
+namespace gcow {
+
+constexpr int kArThreads = 256;
+
+struct ArArgs {
+  const float* in;
+  float* out;
+  uint64_t n;
+  int rank, world, variant, shift;
+  float postscale;
+  uint8_t* arena[kMaxRanks];  // every rank's arena as mapped here; arena[rank] is local memory
+  uint8_t* mc_arena;          // multicast mapping of all arenas (NVLS) or nullptr
+  uint64_t region_off;        // byte offset of this call's data region
+  int parity;
+  uint32_t epoch;
+  uint64_t timeout_ns;
+  uint32_t* status;           // 8 words, see record_failure
+  uint32_t* abort_flag;       // local device word
+  unsigned long long* stamps; // optional [gridDim.x][4] globaltimer stamps, or nullptr
+  ArLayout L;
+};
+
+// ------------------------------------------------------------- primitives
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st_release_u32(uint32_t* p, uint32_t v) {
+  asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+template <int BYTES> struct McStore;
+template <> struct McStore<2> {  // two 16-bit codes are paired by the caller into 32 bits
+  static __device__ __forceinline__ void st(void* p, const uint32_t* w) {
+    asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(w[0]) : "memory");
+  }
+};
+template <> struct McStore<4> {
+  static __device__ __forceinline__ void st(void* p, const uint32_t* w) {
+    asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(w[0]) : "memory");
+  }
+};
+template <> struct McStore<8> {
+  static __device__ __forceinline__ void st(void* p, const uint32_t* w) {
+    uint64_t v = (uint64_t)w[0] | ((uint64_t)w[1] << 32);
+    asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+  }
+};
+template <> struct McStore<16> {
+  static __device__ __forceinline__ void st(void* p, const uint32_t* w) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p),
+                 "f"(__uint_as_float(w[0])), "f"(__uint_as_float(w[1])), "f"(__uint_as_float(w[2])),
+                 "f"(__uint_as_float(w[3]))
+                 : "memory");
+  }
+};
+
+// First failure wins the status record; everyone learns through abort_flag.
+__device__ __forceinline__ void record_failure(const ArArgs& a, uint32_t code, int phase, int peer,
+                                               uint32_t expected, uint32_t seen) {
+  if (atomicCAS(a.status, 0u, code) == 0u) {
+    a.status[1] = (uint32_t)phase;
+    a.status[2] = (uint32_t)peer;
+    a.status[3] = blockIdx.x;
+    a.status[4] = expected;
+    a.status[5] = seen;
+    a.status[6] = a.epoch;
+    __threadfence_system();
+  }
+  atomicExch(a.abort_flag, 1u);
+}
+
+// Bounded wait until *flag reaches `epoch`. Returns false on time-out / abort.
+__device__ __forceinline__ bool wait_flag(const ArArgs& a, const uint32_t* flag, int phase, int peer) {
+  const uint64_t deadline = global_ns() + a.timeout_ns;
+  const uint64_t max_iters = a.timeout_ns / 8 + 4096;
+  uint32_t seen = 0;
+  for (uint64_t it = 0; it < max_iters; it++) {
+    seen = ld_acquire_sys(flag);
+    if ((int32_t)(seen - a.epoch) >= 0) return true;
+    if ((it & 63) == 63) {
+      if (ld_volatile_u32(a.abort_flag)) { record_failure(a, kArAborted, phase, peer, a.epoch, seen); return false; }
+      if (global_ns() > deadline) break;
+    }
+    __nanosleep(40);
+  }
+  record_failure(a, kArTimeout, phase, peer, a.epoch, seen);
+  return false;
+}
+
+__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* arena, int parity, int phase, int src, int cta) {
+  return reinterpret_cast<uint32_t*>(arena + flag_offset(parity, phase, src, cta));
+}
+
+template <int BITS> struct Code;
+template <> struct Code<16> {
+  static constexpr int NW = 1, BYTES = 2;
+  static __device__ __forceinline__ void st(void* base, uint64_t b, const uint32_t (&w)[1]) { ((uint16_t*)base)[b] = (uint16_t)w[0]; }
+  static __device__ __forceinline__ void ld(const void* base, uint64_t b, uint32_t (&w)[1]) { w[0] = ((const volatile uint16_t*)base)[b]; }
+};
+template <> struct Code<32> {
+  static constexpr int NW = 1, BYTES = 4;
+  static __device__ __forceinline__ void st(void* base, uint64_t b, const uint32_t (&w)[1]) { ((uint32_t*)base)[b] = w[0]; }
+  static __device__ __forceinline__ void ld(const void* base, uint64_t b, uint32_t (&w)[1]) { w[0] = __ldcg((const uint32_t*)base + b); }
+};
+template <> struct Code<64> {
+  static constexpr int NW = 2, BYTES = 8;
+  static __device__ __forceinline__ void st(void* base, uint64_t b, const uint32_t (&w)[2]) { ((uint2*)base)[b] = make_uint2(w[0], w[1]); }
+  static __device__ __forceinline__ void ld(const void* base, uint64_t b, uint32_t (&w)[2]) { uint2 v = __ldcg((const uint2*)base + b); w[0] = v.x; w[1] = v.y; }
+};
+template <> struct Code<128> {
+  static constexpr int NW = 4, BYTES = 16;
+  static __device__ __forceinline__ void st(void* base, uint64_t b, const uint32_t (&w)[4]) { ((uint4*)base)[b] = make_uint4(w[0], w[1], w[2], w[3]); }
+  static __device__ __forceinline__ void ld(const void* base, uint64_t b, uint32_t (&w)[4]) { uint4 v = __ldcg((const uint4*)base + b); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+};
+
+__device__ __forceinline__ void load_block(float* f, const float* __restrict__ in, uint64_t n, uint64_t gb, bool aligned) {
+  uint64_t x0 = 4 * gb;
+  if (x0 + 4 <= n) {
+    if (aligned) { float4 v = reinterpret_cast<const float4*>(in)[gb]; f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }
+    else { f[0] = in[x0]; f[1] = in[x0 + 1]; f[2] = in[x0 + 2]; f[3] = in[x0 + 3]; }
+  } else {
+    uint32_t c = (uint32_t)(n - x0);
+    f[0] = f[1] = f[2] = f[3] = 0;
+    for (uint32_t i = 0; i < c; i++) f[i] = in[x0 + i];
+    pad_partial(f, c, 1);
+  }
+}
+__device__ __forceinline__ void store_block(const float* f, float* __restrict__ out, uint64_t n, uint64_t gb, bool aligned) {
+  uint64_t x0 = 4 * gb;
+  if (x0 + 4 <= n) {
+    if (aligned) reinterpret_cast<float4*>(out)[gb] = make_float4(f[0], f[1], f[2], f[3]);
+    else { out[x0] = f[0]; out[x0 + 1] = f[1]; out[x0 + 2] = f[2]; out[x0 + 3] = f[3]; }
+  } else {
+    for (uint64_t i = 0; x0 + i < n; i++) out[x0 + i] = f[i];
+  }
+}
+
+__device__ __forceinline__ void stamp(const ArArgs& a, int slot) {
+  if (a.stamps && threadIdx.x == 0) a.stamps[(uint64_t)blockIdx.x * 4 + slot] = global_ns();
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kArThreads)
+allreduce_fused_kernel(const ArArgs a) {
+  using C = Code<BITS>;
+  constexpr int NW = C::NW;
+  __shared__ uint16_t etab[kEncTabSize];
+  __shared__ uint16_t dtab[kDecTabSize];
+  __shared__ int s_ok;
+  for (int i = threadIdx.x; i < kEncTabSize; i += blockDim.x) etab[i] = make_enc_entry(i >> 4, i & 15);
+  for (int i = threadIdx.x; i < kDecTabSize; i += blockDim.x) dtab[i] = make_dec_entry(i >> 7, i & 127);
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+
+  ZfpParams p = default_params();
+  p.minbits = p.maxbits = BITS;
+  const int P = a.world, r = a.rank, cta = blockIdx.x, tid = threadIdx.x;
+  const ArLayout& L = a.L;
+  const uint64_t SB = L.shard_blocks, NB = L.blocks;
+  const uint64_t s0 = (uint64_t)cta * L.slice_blocks;
+  const uint64_t s1 = s0 + L.slice_blocks < SB ? s0 + L.slice_blocks : SB;
+  const bool in_al = ((uintptr_t)a.in & 15) == 0, out_al = ((uintptr_t)a.out & 15) == 0;
+  uint8_t* const local = a.arena[r];
+  stamp(a, 0);
+
+  if (a.variant == kOneShot) {
+    // ---- phase 1: encode once, store to every rank's slot for this source
+    for (int k = 0; k < P; k++) {
+      for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+        uint64_t gb = (uint64_t)k * SB + b;
+        if (gb >= NB) break;
+        float f[4];
+        load_block(f, a.in, a.n, gb, in_al);
+        uint32_t w[NW];
+        encode_block_1d_fast<NW>(f, p, etab, w);
+        for (int step = 0; step < P; step++) {
+          int j = (r + 1 + step) % P;
+          C::st(a.arena[j] + a.region_off + (uint64_t)r * L.slot_bytes, gb, w);
+        }
+      }
+    }
+    __syncthreads();
+    if (tid < P) {
+      __threadfence_system();
+      st_release_sys(flag_ptr(a.arena[tid], a.parity, 0, r, cta), a.epoch);
+    }
+    stamp(a, 1);
+    // ---- phase 2: wait for every source, decode P copies, sum, write fp32
+    if (tid < P) {
+      if (!wait_flag(a, flag_ptr(local, a.parity, 0, tid, cta), 1, tid)) s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    stamp(a, 2);
+    for (int k = 0; k < P; k++) {
+      for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+        uint64_t gb = (uint64_t)k * SB + b;
+        if (gb >= NB) break;
+        float acc[4];
+        for (int s = 0; s < P; s++) {
+          uint32_t w[NW];
+          C::ld(local + a.region_off + (uint64_t)s * L.slot_bytes, gb, w);
+          float d[4];
+          decode_block_1d_fast<NW>(d, p, dtab, w, 0);
+          if (s == 0) { acc[0] = d[0]; acc[1] = d[1]; acc[2] = d[2]; acc[3] = d[3]; }
+          else { acc[0] += d[0]; acc[1] += d[1]; acc[2] += d[2]; acc[3] += d[3]; }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[i] *= a.postscale;
+        store_block(acc, a.out, a.n, gb, out_al);
+      }
+    }
+    stamp(a, 3);
+    return;
+  }
+
+  // ------------------------------------------------------------- two-shot
+  const uint64_t shard_bytes = SB * C::BYTES;
+  // ---- phase 1: encode shard j, store into owner j's slot for source r
+  for (int step = 0; step < P; step++) {
+    const int j = (r + 1 + step) % P;  // peers first, own shard last
+    uint8_t* dst = a.arena[j] + a.region_off + (uint64_t)r * L.slot_bytes;
+    for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+      uint64_t gb = (uint64_t)j * SB + b;
+      if (gb >= NB) break;
+      float f[4];
+      load_block(f, a.in, a.n, gb, in_al);
+      uint32_t w[NW];
+      encode_block_1d_fast<NW>(f, p, etab, w);
+      C::st(dst, b, w);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence_system();
+      st_release_sys(flag_ptr(a.arena[j], a.parity, 0, r, cta), a.epoch);
+    }
+  }
+  stamp(a, 1);
+
+  // ---- phase 2: reduce my shard's slice, broadcast the re-encoded result
+  if (tid < P) {
+    if (!wait_flag(a, flag_ptr(local, a.parity, 0, tid, cta), 1, tid)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  {
+    const uint64_t gather_off = a.region_off + L.recv_bytes + (uint64_t)r * shard_bytes;
+    // slice bounds are multiples of 32, so a warp enters and leaves this loop
+    // together; blocks past the end of the bucket are skipped by predicate
+    for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+      const uint64_t gb = (uint64_t)r * SB + b;
+      const bool valid = gb < NB;
+      uint32_t w[NW];
+#pragma unroll
+      for (int i = 0; i < NW; i++) w[i] = 0;
+      if (valid) {
+        float acc[4];
+        for (int s = 0; s < P; s++) {
+          uint32_t c[NW];
+          C::ld(local + a.region_off + (uint64_t)s * L.slot_bytes, b, c);
+          float d[4];
+          decode_block_1d_fast<NW>(d, p, dtab, c, 0);
+          if (s == 0) { acc[0] = d[0]; acc[1] = d[1]; acc[2] = d[2]; acc[3] = d[3]; }
+          else { acc[0] += d[0]; acc[1] += d[1]; acc[2] += d[2]; acc[3] += d[3]; }
+        }
+        encode_block_1d_fast<NW>(acc, p, etab, w);
+      }
+      if (a.variant == kTwoShotNvls) {
+        if (BITS == 16) {
+          // pair two 16-bit codes so the multicast store is 32 bits wide
+          uint32_t other = __shfl_down_sync(0xffffffffu, w[0], 1);
+          if ((tid & 1) == 0 && valid) {
+            uint32_t pair[1] = {(w[0] & 0xffffu) | (other << 16)};
+            McStore<4>::st(a.mc_arena + gather_off + b * 2, pair);
+          }
+        } else if (valid) {
+          McStore<C::BYTES>::st(a.mc_arena + gather_off + b * C::BYTES, w);
+        }
+      } else if (valid) {
+        for (int step = 0; step < P; step++) {
+          int j = (r + 1 + step) % P;
+          C::st(a.arena[j] + gather_off, b, w);
+        }
+      }
+    }
+    __syncthreads();
+    if (a.variant == kTwoShotNvls) {
+      if (tid == 0) {
+        __threadfence_system();
+        mc_st_release_u32(flag_ptr(a.mc_arena, a.parity, 1, r, cta), a.epoch);
+      }
+    } else if (tid < P) {
+      __threadfence_system();
+      st_release_sys(flag_ptr(a.arena[tid], a.parity, 1, r, cta), a.epoch);
+    }
+  }
+  stamp(a, 2);
+
+  // ---- phase 3: decode every shard's slice into the output. All P flags are
+  // awaited before the first write, so a CTA that gives up leaves `out` alone.
+  if (tid < P) {
+    if (!wait_flag(a, flag_ptr(local, a.parity, 1, tid, cta), 2, tid)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  for (int step = 0; step < P; step++) {
+    const int j = (r + step) % P;
+    const uint8_t* src = local + a.region_off + L.recv_bytes + (uint64_t)j * shard_bytes;
+    for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+      uint64_t gb = (uint64_t)j * SB + b;
+      if (gb >= NB) break;
+      uint32_t w[NW];
+      C::ld(src, b, w);
+      float d[4];
+      decode_block_1d_fast<NW>(d, p, dtab, w, a.shift);
+      if (a.postscale != 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) d[i] *= a.postscale;
+      }
+      store_block(d, a.out, a.n, gb, out_al);
+    }
+  }
+  stamp(a, 3);
+}
+
+// A flag wait on its own: lets the host-visible time-out path be exercised
+// without a peer (the flag is one that nothing sets).
+__global__ void wait_probe_kernel(const ArArgs a, const uint32_t* flag) {
+  if (threadIdx.x == 0) wait_flag(a, flag, 9, 0);
+}
+
+template <int BITS>
+int max_coresident_ctas(int device) {
+  int per_sm = 0, sms = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_fused_kernel<BITS>, kArThreads, 0);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  return per_sm * sms;
+}
+
+}  // namespace gcow
+
+using namespace gcow;
+
+extern "C" {
+
+uint64_t gcow_ar_arena_bytes(uint64_t region_bytes) { return arena_bytes_for(region_bytes); }
+uint64_t gcow_ar_flag_bytes() { return kFlagBytes; }
+
+// Bytes of data region one call needs (to be checked against the arena's capacity).
+uint64_t gcow_ar_region_bytes(uint64_t n, int world, int ctas, int bits, int variant) {
+  return ar_layout(n, world, ctas, bits, variant).region_bytes;
+}
+
+// Largest grid that is guaranteed co-resident (the flag protocol needs it).
+int gcow_ar_max_ctas(int bits) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int m = 0;
+  switch (bits) {
+    case 16: m = max_coresident_ctas<16>(dev); break;
+    case 32: m = max_coresident_ctas<32>(dev); break;
+    case 64: m = max_coresident_ctas<64>(dev); break;
+    case 128: m = max_coresident_ctas<128>(dev); break;
+    default: return -1;
+  }
+  return m < kMaxCtas ? m : kMaxCtas;
+}
+
+// Launch the fused all-reduce on `stream`.
+//   arenas: `world` device pointers (every rank's arena as mapped in this process)
+//   mc_arena: multicast mapping or null; region_cap: bytes of one parity's data region
+//   status: 8 u32 (device-visible); abort_flag: 1 u32; stamps: optional ctas*4 u64
+// Returns 0, a CUDA error code, or -1 / -2 for bad arguments / insufficient arena.
+int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world, int variant, int bits,
+                   int ctas, int shift, float postscale, void* const* arenas, void* mc_arena,
+                   uint64_t region_cap, uint32_t epoch, uint64_t timeout_ns, uint32_t* status,
+                   uint32_t* abort_flag, unsigned long long* stamps, void* stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || ctas < 1 || ctas > kMaxCtas) return -1;
+  if (variant == kTwoShotNvls && !mc_arena) return -1;
+  ArArgs a;
+  a.in = in; a.out = out; a.n = n;
+  a.rank = rank; a.world = world; a.variant = variant; a.shift = shift; a.postscale = postscale;
+  for (int i = 0; i < kMaxRanks; i++) a.arena[i] = i < world ? (uint8_t*)arenas[i] : nullptr;
+  a.mc_arena = (uint8_t*)mc_arena;
+  a.parity = (int)(epoch & 1);
+  a.region_off = region_offset(a.parity, region_cap);
+  a.epoch = epoch;
+  a.timeout_ns = timeout_ns;
+  a.status = status; a.abort_flag = abort_flag; a.stamps = stamps;
+  a.L = ar_layout(n, world, ctas, bits, variant);
+  if (a.L.region_bytes > region_cap) return -2;
+  if (n == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (bits) {
+    case 16: allreduce_fused_kernel<16><<<ctas, kArThreads, 0, s>>>(a); break;
+    case 32: allreduce_fused_kernel<32><<<ctas, kArThreads, 0, s>>>(a); break;
+    case 64: allreduce_fused_kernel<64><<<ctas, kArThreads, 0, s>>>(a); break;
+    case 128: allreduce_fused_kernel<128><<<ctas, kArThreads, 0, s>>>(a); break;
+    default: return -1;
+  }
+  return (int)cudaGetLastError();
+}
+
+// Wait (bounded) on one flag word that the caller chooses; used to test that a
+// wait that is never satisfied ends with a status record instead of a hang.
+int gcow_ar_wait_probe(const uint32_t* flag, uint32_t epoch, uint64_t timeout_ns, uint32_t* status,
+                       uint32_t* abort_flag, void* stream) {
+  ArArgs a = {};
+  a.epoch = epoch; a.timeout_ns = timeout_ns; a.status = status; a.abort_flag = abort_flag;
+  wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a, flag);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

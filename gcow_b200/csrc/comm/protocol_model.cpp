@@ -1,0 +1,247 @@
+// CPU thread model of the fused all-reduce's flag protocol.
+//
+// P host threads play the ranks and G "CTAs" per rank are played in sequence by
+// that thread, running the same three phases, the same arena layout
+// (ar_layout.h) and the same block codec (zfp_block.cuh, host build) as the
+// CUDA kernel. Flags are std::atomic<uint32_t> with release/acquire ordering
+// and every wait has a deadline. The model exists to test what must never be
+// tested by faulting a GPU: a rank that never joins, a late rank, a dropped
+// flag, a stale epoch left in a flag, parity reuse across calls. It is also
+// what runs under ThreadSanitizer (build.py: sanitize="thread").
+//
+// The reference has no distributed failure handling to mirror (its host code
+// exits on any OpenCL error, hw/include/host.hpp:18-24).
+#include <stdint.h>
+#include <string.h>
+#include <atomic>
+#include <chrono>
+#include <thread>
+#include <vector>
+
+#include "../codec/zfp_block.cuh"
+#include "ar_layout.h"
+
+namespace {
+
+using namespace gcow;
+using Clock = std::chrono::steady_clock;
+
+struct Fault {
+  int skip_rank;        // this rank never runs (-1: none)
+  int delay_rank;       // this rank starts late (-1: none)
+  int delay_ms;
+  int drop_src, drop_dst, drop_phase;  // flag (src -> dst, phase) is never written (-1: none)
+};
+
+struct Model {
+  int P, G, bits, variant, shift;
+  uint64_t n, region_cap;
+  ArLayout L;
+  std::vector<std::vector<uint8_t>> arena;  // one per rank
+  std::vector<uint16_t> etab, dtab;
+};
+
+std::atomic<uint32_t>* flag_at(Model& m, int rank, int parity, int phase, int src, int cta) {
+  return reinterpret_cast<std::atomic<uint32_t>*>(m.arena[rank].data() + flag_offset(parity, phase, src, cta));
+}
+
+bool wait_flag(std::atomic<uint32_t>* f, uint32_t epoch, int timeout_ms, uint32_t* seen) {
+  auto deadline = Clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (;;) {
+    uint32_t v = f->load(std::memory_order_acquire);
+    *seen = v;
+    if ((int32_t)(v - epoch) >= 0) return true;
+    if (Clock::now() > deadline) return false;
+    std::this_thread::yield();
+  }
+}
+
+template <int NW>
+void put_code(uint8_t* base, uint64_t b, const uint32_t (&w)[NW], int bytes) {
+  memcpy(base + b * bytes, w, bytes);
+}
+template <int NW>
+void get_code(const uint8_t* base, uint64_t b, uint32_t (&w)[NW], int bytes) {
+  for (int i = 0; i < NW; i++) w[i] = 0;
+  memcpy(w, base + b * bytes, bytes);
+}
+
+void load_block(float* f, const float* in, uint64_t n, uint64_t gb) {
+  uint64_t x0 = 4 * gb;
+  uint32_t c = (uint32_t)(n - x0 < 4 ? n - x0 : 4);
+  f[0] = f[1] = f[2] = f[3] = 0;
+  for (uint32_t i = 0; i < c; i++) f[i] = in[x0 + i];
+  if (c < 4) pad_partial(f, c, 1);
+}
+void store_block(const float* f, float* out, uint64_t n, uint64_t gb) {
+  uint64_t x0 = 4 * gb;
+  for (uint64_t i = 0; i < 4 && x0 + i < n; i++) out[x0 + i] = f[i];
+}
+
+// status: [0] code, [1] phase, [2] peer, [3] cta, [4] expected, [5] seen
+template <int NW>
+void run_rank(Model& m, int r, const float* in, float* out, uint32_t epoch, int timeout_ms,
+              const Fault& ft, uint32_t* status) {
+  const int P = m.P, G = m.G, parity = (int)(epoch & 1), bytes = m.bits / 8;
+  const ArLayout& L = m.L;
+  const uint64_t SB = L.shard_blocks, NB = L.blocks;
+  const uint64_t roff = region_offset(parity, m.region_cap);
+  ZfpParams p = default_params();
+  p.minbits = p.maxbits = (uint32_t)m.bits;
+  auto fail = [&](int phase, int peer, int cta, uint32_t seen) {
+    if (status[0] == 0) { status[0] = kArTimeout; status[1] = phase; status[2] = peer; status[3] = cta; status[4] = epoch; status[5] = seen; }
+  };
+  auto signal = [&](int dst, int phase, int cta) {
+    if (ft.drop_src == r && ft.drop_dst == dst && ft.drop_phase == phase) return;
+    flag_at(m, dst, parity, phase, r, cta)->store(epoch, std::memory_order_release);
+  };
+  const uint64_t shard_bytes = SB * bytes;
+
+  // phase 1 for every CTA
+  for (int cta = 0; cta < G; cta++) {
+    uint64_t s0 = (uint64_t)cta * L.slice_blocks, s1 = std::min<uint64_t>(s0 + L.slice_blocks, SB);
+    if (m.variant == kOneShot) {
+      for (int k = 0; k < P; k++)
+        for (uint64_t b = s0; b < s1; b++) {
+          uint64_t gb = (uint64_t)k * SB + b;
+          if (gb >= NB) break;
+          float f[4]; uint32_t w[NW];
+          load_block(f, in, m.n, gb);
+          encode_block_1d_fast<NW>(f, p, m.etab.data(), w);
+          for (int j = 0; j < P; j++) put_code<NW>(m.arena[j].data() + roff + (uint64_t)r * L.slot_bytes, gb, w, bytes);
+        }
+      for (int j = 0; j < P; j++) signal(j, 0, cta);
+    } else {
+      for (int step = 0; step < P; step++) {
+        int j = (r + 1 + step) % P;
+        for (uint64_t b = s0; b < s1; b++) {
+          uint64_t gb = (uint64_t)j * SB + b;
+          if (gb >= NB) break;
+          float f[4]; uint32_t w[NW];
+          load_block(f, in, m.n, gb);
+          encode_block_1d_fast<NW>(f, p, m.etab.data(), w);
+          put_code<NW>(m.arena[j].data() + roff + (uint64_t)r * L.slot_bytes, b, w, bytes);
+        }
+        signal(j, 0, cta);
+      }
+    }
+  }
+  // phase 2
+  const float inv = 1.0f / (float)(1u << m.shift);
+  for (int cta = 0; cta < G; cta++) {
+    uint64_t s0 = (uint64_t)cta * L.slice_blocks, s1 = std::min<uint64_t>(s0 + L.slice_blocks, SB);
+    for (int s = 0; s < P; s++) {
+      uint32_t seen;
+      if (!wait_flag(flag_at(m, r, parity, 0, s, cta), epoch, timeout_ms, &seen)) { fail(1, s, cta, seen); return; }
+    }
+    const uint8_t* local = m.arena[r].data();
+    if (m.variant == kOneShot) {
+      for (int k = 0; k < P; k++)
+        for (uint64_t b = s0; b < s1; b++) {
+          uint64_t gb = (uint64_t)k * SB + b;
+          if (gb >= NB) break;
+          float acc[4] = {0, 0, 0, 0};
+          for (int s = 0; s < P; s++) {
+            uint32_t w[NW]; float d[4];
+            get_code<NW>(local + roff + (uint64_t)s * L.slot_bytes, gb, w, bytes);
+            decode_block_1d_fast<NW>(d, p, m.dtab.data(), w, 0);
+            for (int i = 0; i < 4; i++) acc[i] = s == 0 ? d[i] : acc[i] + d[i];
+          }
+          for (int i = 0; i < 4; i++) acc[i] *= inv;
+          store_block(acc, out, m.n, gb);
+        }
+      continue;
+    }
+    for (uint64_t b = s0; b < s1; b++) {
+      uint64_t gb = (uint64_t)r * SB + b;
+      if (gb >= NB) break;
+      float acc[4] = {0, 0, 0, 0};
+      for (int s = 0; s < P; s++) {
+        uint32_t w[NW]; float d[4];
+        get_code<NW>(local + roff + (uint64_t)s * L.slot_bytes, b, w, bytes);
+        decode_block_1d_fast<NW>(d, p, m.dtab.data(), w, 0);
+        for (int i = 0; i < 4; i++) acc[i] = s == 0 ? d[i] : acc[i] + d[i];
+      }
+      uint32_t w[NW];
+      encode_block_1d_fast<NW>(acc, p, m.etab.data(), w);
+      for (int j = 0; j < P; j++)
+        put_code<NW>(m.arena[j].data() + roff + L.recv_bytes + (uint64_t)r * shard_bytes, b, w, bytes);
+    }
+    for (int j = 0; j < P; j++) signal(j, 1, cta);
+  }
+  if (m.variant == kOneShot) return;
+  // phase 3
+  for (int cta = 0; cta < G; cta++) {
+    uint64_t s0 = (uint64_t)cta * L.slice_blocks, s1 = std::min<uint64_t>(s0 + L.slice_blocks, SB);
+    for (int j = 0; j < P; j++) {
+      uint32_t seen;
+      if (!wait_flag(flag_at(m, r, parity, 1, j, cta), epoch, timeout_ms, &seen)) { fail(2, j, cta, seen); return; }
+    }
+    for (int j = 0; j < P; j++) {
+      const uint8_t* src = m.arena[r].data() + roff + L.recv_bytes + (uint64_t)j * shard_bytes;
+      for (uint64_t b = s0; b < s1; b++) {
+        uint64_t gb = (uint64_t)j * SB + b;
+        if (gb >= NB) break;
+        uint32_t w[NW]; float d[4];
+        get_code<NW>(src, b, w, bytes);
+        decode_block_1d_fast<NW>(d, p, m.dtab.data(), w, m.shift);
+        store_block(d, out, m.n, gb);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// Run `calls` consecutive all-reduces of P ranks x n floats on host threads.
+// xs: [calls][P][n] inputs; outs: [calls][P][n] outputs; status: [P][8] words
+// (first failure per rank over all calls). The fault applies to call
+// `fault_call` only; stale_epoch >= 0 pre-seeds every flag with that value
+// before the first call. Returns the number of ranks that reported a failure.
+int gcow_protocol_model(const float* xs, float* outs, int P, uint64_t n, int G, int bits, int variant,
+                        int shift, int calls, int timeout_ms, int fault_call, int skip_rank,
+                        int delay_rank, int delay_ms, int drop_src, int drop_dst, int drop_phase,
+                        int stale_epoch, uint32_t* status) {
+  Model m;
+  m.P = P; m.G = G; m.bits = bits; m.variant = variant; m.shift = shift; m.n = n;
+  m.L = ar_layout(n, P, G, bits, variant);
+  m.region_cap = m.L.region_bytes;
+  m.arena.assign(P, std::vector<uint8_t>(arena_bytes_for(m.region_cap), 0));
+  m.etab.resize(kEncTabSize);
+  m.dtab.resize(kDecTabSize);
+  for (int i = 0; i < kEncTabSize; i++) m.etab[i] = make_enc_entry(i / 16, i % 16);
+  for (int i = 0; i < kDecTabSize; i++) m.dtab[i] = make_dec_entry(i / 128, i % 128);
+  if (stale_epoch >= 0)
+    for (int r = 0; r < P; r++)
+      for (uint64_t o = 0; o < kFlagBytes; o += 4) *reinterpret_cast<uint32_t*>(m.arena[r].data() + o) = (uint32_t)stale_epoch;
+  memset(status, 0, sizeof(uint32_t) * 8 * P);
+  uint32_t first_epoch = stale_epoch >= 0 ? (uint32_t)stale_epoch + 1 : 1;
+  for (int c = 0; c < calls; c++) {
+    Fault ft = {-1, -1, 0, -1, -1, -1};
+    if (c == fault_call) ft = {skip_rank, delay_rank, delay_ms, drop_src, drop_dst, drop_phase};
+    std::vector<std::thread> th;
+    for (int r = 0; r < P; r++) {
+      if (ft.skip_rank == r) continue;
+      th.emplace_back([&, r, c, ft] {
+        if (ft.delay_rank == r) std::this_thread::sleep_for(std::chrono::milliseconds(ft.delay_ms));
+        const float* in = xs + ((uint64_t)c * P + r) * n;
+        float* out = outs + ((uint64_t)c * P + r) * n;
+        uint32_t epoch = first_epoch + (uint32_t)c;
+        switch (bits) {
+          case 16: run_rank<1>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+          case 32: run_rank<1>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+          case 64: run_rank<2>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+          default: run_rank<4>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+        }
+      });
+    }
+    for (auto& t : th) t.join();
+  }
+  int failed = 0;
+  for (int r = 0; r < P; r++) failed += status[8 * r] != 0;
+  return failed;
+}
+
+}  // extern "C"

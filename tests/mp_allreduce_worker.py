@@ -1,0 +1,90 @@
+"""Worker of the multi-GPU all-reduce tests (one process per GPU, torchrun).
+Every rank regenerates all ranks' inputs from their seeds, computes the host
+oracle and compares its own device result bit for bit. Results go to the JSON
+file named by GCOW_TEST_OUT (rank 0) and to the exit code."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from gcow_b200.codec import ZfpParams  # noqa: E402
+from gcow_b200.comm import CompressedAllReduce, allreduce_oracle  # noqa: E402
+from gcow_b200.config import GcowConfig  # noqa: E402
+
+
+def gen(seed, n):
+    return (np.random.default_rng(seed).standard_normal(n) * 1e-3).astype(np.float32)
+
+
+def main():
+    rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    backend = os.environ.get("GCOW_COMM_BACKEND", "auto")
+    shift = {1: 0, 2: 1, 4: 2, 8: 3}.get(world, 0)
+    fails, ran = [], 0
+    info = {}
+    sizes = [5, 4099, (1 << 16) | 3, 1 << 21]
+    for rate in (8, 4, 16, 32):
+        cfg = GcowConfig(rate=rate, comm_ctas=int(os.environ.get("GCOW_TEST_CTAS", "24")), timeout_ms=5000,
+                         oneshot_max_bytes=1 << 20)
+        ar = CompressedAllReduce(1 << 21, cfg, device=dev, backend=backend)
+        info = {"backend": ar.arena.backend, "multicast": bool(ar.arena.mc_ptr), "ctas": ar.ctas,
+                "max_ctas": ar.max_ctas}
+        p = ZfpParams.from_rate(rate, 1)
+        variants = ["twoshot", "oneshot"] + (["nvls"] if ar.arena.mc_ptr else [])
+        for variant in variants:
+            for n in sizes:
+                if variant == "oneshot" and n > ar.oneshot_numel:
+                    continue
+                xs = np.stack([gen(1000 * n + 17 * rate + r, n) for r in range(world)])
+                ref = allreduce_oracle(xs, p, "oneshot" if variant == "oneshot" else "twoshot", shift)
+                x = torch.from_numpy(xs[rank]).to(dev)
+                # two back-to-back calls on fresh copies exercise both parities
+                y1 = ar(x.clone(), variant=variant)
+                y2 = ar(x.clone(), variant=variant)
+                ar.check()
+                ran += 1
+                for y in (y1, y2):
+                    if not np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32)):
+                        bad = int((y.cpu().numpy().view(np.uint32) != ref.view(np.uint32)).sum())
+                        fails.append(f"rate {rate} {variant} n {n}: {bad} words differ")
+                        break
+        # unaligned in-place view through the automatic variant choice
+        base = torch.zeros((1 << 16) + 8, device=dev)
+        n = (1 << 16) + 1
+        xs = np.stack([gen(99 + r, n) for r in range(world)])
+        base[1:1 + n] = torch.from_numpy(xs[rank]).to(dev)
+        v = ar.pick_variant(n)
+        ar(base[1:1 + n])
+        ar.check()
+        ref = allreduce_oracle(xs, p, "oneshot" if v == "oneshot" else "twoshot", shift)
+        if not np.array_equal(base[1:1 + n].cpu().numpy().view(np.uint32), ref.view(np.uint32)):
+            fails.append(f"rate {rate} unaligned view ({v}) differs")
+        if float(base[0]) != 0.0 or float(base[1 + n:].abs().sum()) != 0.0:
+            fails.append(f"rate {rate} unaligned view wrote outside its range")
+        ran += 1
+        del ar
+    allf = [None] * world
+    dist.all_gather_object(allf, fails)
+    if rank == 0:
+        out = os.environ.get("GCOW_TEST_OUT")
+        res = {"world": world, "cases": ran, "fails": allf, **info}
+        print(json.dumps(res))
+        if out:
+            with open(out, "w") as f:
+                json.dump(res, f)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(1 if any(allf) else 0)
+
+
+if __name__ == "__main__":
+    main()
