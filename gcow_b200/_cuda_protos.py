@@ -46,3 +46,21 @@ _declare_codec = declare
 def declare(lib, proto):  # noqa: F811
     _declare_codec(lib, proto)
     _declare_comm(lib, proto)
+
+
+def _declare_ops(lib, proto):
+    def opt(name, restype, *args):
+        if hasattr(lib, name):
+            proto(lib, name, restype, *args)
+    f32 = C.c_float
+    opt("gcow_opt_chunk_bytes", u32)
+    opt("gcow_sgd_step", i32, ptr, u32, f32, f32, f32, f32, i32, i32, f32, ptr)
+    opt("gcow_adamw_step", i32, ptr, u32, f32, f32, f32, f32, f32, f32, f32, f32, ptr)
+
+
+_declare_codec_comm = declare
+
+
+def declare(lib, proto):  # noqa: F811
+    _declare_codec_comm(lib, proto)
+    _declare_ops(lib, proto)

@@ -1,0 +1,66 @@
+"""nn modules and functions used by the model zoo.
+
+Each wrapper keeps PyTorch's parameter layout (so state dicts are
+interchangeable with torch / torchvision checkpoints) and dispatches its math to
+this library's sm_100a kernel when one exists for the case at hand, else to the
+PyTorch operator. The list of cases served by own kernels grows in
+``gcow_b200.ops.kernels``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import backend
+from . import kernels as K
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    if backend.get_backend() == "own" and K.gemm_usable(x, weight):
+        return K.linear(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
+class Linear(nn.Linear):
+    def forward(self, x):
+        return linear(x, self.weight, self.bias)
+
+
+class Conv2d(nn.Conv2d):
+    def forward(self, x):
+        if (backend.get_backend() == "own" and self.kernel_size == (1, 1) and self.stride == (1, 1)
+                and self.padding == (0, 0) and self.groups == 1 and K.conv1x1_usable(x, self.weight)):
+            return K.conv1x1(x, self.weight, self.bias)
+        return super().forward(x)
+
+
+class BatchNorm2d(nn.BatchNorm2d):
+    pass
+
+
+class LayerNorm(nn.LayerNorm):
+    def forward(self, x):
+        if backend.get_backend() == "own" and K.layernorm_usable(x, self):
+            return K.layernorm(x, self.weight, self.bias, self.eps)
+        return super().forward(x)
+
+
+class Embedding(nn.Embedding):
+    pass
+
+
+def gelu(x: torch.Tensor) -> torch.Tensor:
+    return F.gelu(x)
+
+
+def attention(qkv: torch.Tensor) -> torch.Tensor:
+    """qkv: [B, S, 3, heads, head_dim] -> context [B, S, heads*head_dim] (no mask, no dropout)."""
+    B, S, _, H, D = qkv.shape
+    q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))     # [B, H, S, D]
+    ctx = F.scaled_dot_product_attention(q, k, v)
+    return ctx.transpose(1, 2).reshape(B, S, H * D)
+
+
+def cross_entropy(logits: torch.Tensor, target: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    return F.cross_entropy(logits.float(), target, ignore_index=ignore_index)

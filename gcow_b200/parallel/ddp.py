@@ -1,0 +1,106 @@
+"""DistributedDataParallel integration: the gradient buckets of stock PyTorch DDP
+are all-reduced by the fused compressed kernel instead of NCCL.
+
+``wrap_ddp`` builds DDP with 25 MB buckets that alias the parameters' .grad
+(``gradient_as_bucket_view``), registers ``compressed_allreduce_hook`` and
+returns the hook state. For each bucket the hook makes the communication stream
+wait for the producer stream, launches ONE fused kernel there and completes a
+CUDA-aware future, so backward keeps running while earlier buckets travel.
+
+The reference runs stock DDP (NCCL fp32) and only afterwards round-trips the
+whole gradient through a host codec (hw/models/train_imagenet.py:219,449-475);
+at one GPU it still applies the codec round trip to the local gradient, which is
+what this hook does when the world size is 1.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+from torch.nn.parallel import DistributedDataParallel as DDP
+
+from ..comm.allreduce import CompressedAllReduce, CollectiveTimeout
+from ..config import GcowConfig
+
+
+@dataclass
+class GcowDDPState:
+    ar: CompressedAllReduce
+    cfg: GcowConfig
+    group: object = None
+    buckets_seen: int = 0
+    launches: int = 0
+    residual: dict = field(default_factory=dict)   # error-feedback memory per bucket index
+    last_buckets: list = field(default_factory=list)
+
+    def begin_step(self) -> None:
+        self.last_buckets.clear()
+
+    def finish_step(self) -> None:
+        """Call after backward, before the optimizer step: waits for the
+        communication stream and raises CollectiveTimeout if a bucket gave up."""
+        self.ar.check(self.ar.stream)
+
+    def state_dict(self) -> dict:
+        return {"cfg": self.cfg.asdict(), "residual": {k: v.cpu() for k, v in self.residual.items()}}
+
+    def load_state_dict(self, sd: dict) -> None:
+        dev = self.ar.device
+        self.residual = {int(k): v.to(dev) for k, v in sd.get("residual", {}).items()}
+
+
+def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> torch.futures.Future:
+    buf = bucket.buffer()
+    ar = state.ar
+    cur = torch.cuda.current_stream(buf.device)
+    ar.stream.wait_stream(cur)
+    with torch.cuda.stream(ar.stream):
+        if state.cfg.error_feedback:
+            idx = bucket.index()
+            res = state.residual.get(idx)
+            if res is None or res.numel() != buf.numel():
+                res = torch.zeros_like(buf)
+                state.residual[idx] = res
+            buf.add_(res)                      # re-inject what compression dropped last time
+            sent = buf.clone()
+        ar(buf, stream=ar.stream)
+        if state.cfg.error_feedback:
+            # residual = what this rank wanted to send minus what the codec kept of it
+            from ..codec import compress, decompress
+            kept = decompress(compress(sent, params=ar.params))
+            torch.sub(sent, kept, out=state.residual[bucket.index()])
+        buf.record_stream(ar.stream)
+        fut = torch.futures.Future(devices=[buf.device])
+        fut.set_result(buf)
+    state.buckets_seen += 1
+    state.launches += 1
+    state.last_buckets.append(buf.numel())
+    return fut
+
+
+def nccl_fp32_hook(state, bucket: dist.GradBucket) -> torch.futures.Future:
+    """Uncompressed baseline with the same averaging semantics."""
+    group = state.group if state is not None else None
+    buf = bucket.buffer()
+    world = dist.get_world_size(group)
+    fut = dist.all_reduce(buf, group=group, async_op=True).get_future()
+    return fut.then(lambda f: f.value()[0].div_(world))
+
+
+def wrap_ddp(model: torch.nn.Module, cfg: GcowConfig | None = None, device: torch.device | None = None,
+             group=None, max_bucket_numel: int | None = None):
+    """Returns (ddp_model, state). ``cfg.variant == 'nccl'`` gives the uncompressed baseline."""
+    cfg = cfg or GcowConfig.from_env()
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    ddp = DDP(model, device_ids=[device.index], bucket_cap_mb=cfg.bucket_mb, gradient_as_bucket_view=True,
+              process_group=group, broadcast_buffers=False)
+    if cfg.variant == "nccl":
+        return ddp, None
+    cap = max_bucket_numel or max(int(cfg.bucket_mb * (1 << 20) // 4 * 2), 1 << 20)
+    biggest = max((p.numel() for p in model.parameters()), default=1)
+    cap = max(cap, biggest)
+    ar = CompressedAllReduce(cap, cfg, group=group, device=device)
+    state = GcowDDPState(ar, cfg, group)
+    ddp.register_comm_hook(state, compressed_allreduce_hook)
+    return ddp, state
