@@ -1,0 +1,147 @@
+"""All-reduce sweep: fused compressed variants against NCCL fp32 and the roofline.
+
+    torchrun --nproc-per-node N -m gcow_b200.bench.allreduce_sweep \
+        [--sizes-kb 1 ... 1048576] [--rates 4 8 16] [--json out.json]
+
+For each message size x rate x variant the kernel is timed on the device (CUDA
+events around `iters` back-to-back calls on the launching stream, after warm-up)
+and the MAX over ranks is reported. Effective GB/s = fp32 message bytes / time.
+Roofline per call = the slower of (a) codec HBM traffic at the measured copy
+bandwidth and (b) compressed bytes leaving one GPU at the measured 770 GB/s
+per-direction NVLink peer bandwidth; `frac` = roofline time / measured time.
+Messages rotate through a pool larger than L2 (126 MB) when they are small.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from gcow_b200.comm import CompressedAllReduce
+from gcow_b200.config import GcowConfig
+
+NVLINK_GBS = 770.0   # measured peer copy, per direction per GPU
+
+
+def hbm_gbs():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text()).get("hbm_gbs", 6650.0), "measured"
+    return 6650.0, "fallback"
+
+
+def time_calls(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / iters], device="cuda", dtype=torch.float64)
+    if dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def roofline_ms(nbytes, rate, P, variant, hbm):
+    comp = nbytes * rate / 32.0
+    if variant == "oneshot":
+        link = comp * (P - 1)
+        mem = nbytes + comp * P + comp * P + nbytes          # read in, write P copies, read P copies, write out
+    else:
+        link = 2.0 * comp * (P - 1) / P
+        mem = nbytes + comp + comp + comp / P * P + comp + nbytes   # enc(read fp32, write comp), reduce(read P/P.., write), decode
+    return max(link / (NVLINK_GBS * 1e6), mem / (hbm * 1e6)) if P > 1 else mem / (hbm * 1e6)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sizes-kb", type=int, nargs="+",
+                    default=[1, 16, 256, 1024, 4096, 25600, 65536, 262144, 1048576])
+    ap.add_argument("--rates", type=float, nargs="+", default=[4, 8, 16])
+    ap.add_argument("--variants", nargs="+", default=["twoshot", "oneshot", "nvls"])
+    ap.add_argument("--ctas", type=int, default=0, help="0 = as many as are co-resident")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", default="")
+    args = ap.parse_args(argv)
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if "RANK" in os.environ:
+        dist.init_process_group("nccl", device_id=dev)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    P = dist.get_world_size() if dist.is_initialized() else 1
+    hbm, how = hbm_gbs()
+    max_numel = max(args.sizes_kb) * 256
+    rows = []
+    pool_bytes = 192 << 20
+
+    # NCCL fp32 baseline
+    for kb in args.sizes_kb:
+        n = kb * 256
+        copies = max(1, min(8, pool_bytes // (n * 4)))
+        bufs = [torch.randn(n, device=dev) * 1e-3 for _ in range(copies)]
+        k = {"i": 0}
+
+        def nccl():
+            if P > 1:
+                dist.all_reduce(bufs[k["i"] % copies])
+            k["i"] += 1
+        iters = args.iters if kb >= 1024 else args.iters * 10
+        ms = time_calls(nccl, iters) if P > 1 else float("nan")
+        rows.append({"impl": "nccl_fp32", "kb": kb, "ms": ms, "eff_gbs": n * 4 / ms / 1e6 if P > 1 else None, "P": P})
+        if rank == 0:
+            print(json.dumps(rows[-1]), flush=True)
+        del bufs
+
+    for rate in args.rates:
+        ctas = args.ctas or 4096
+        cfg = GcowConfig(rate=rate, comm_ctas=ctas, timeout_ms=10000, oneshot_max_bytes=4 << 20, average=True)
+        ar = CompressedAllReduce(max_numel, cfg, device=dev)
+        for kb in args.sizes_kb:
+            n = kb * 256
+            copies = max(1, min(8, pool_bytes // (n * 4)))
+            bufs = [torch.randn(n, device=dev) * 1e-3 for _ in range(copies)]
+            for variant in args.variants:
+                if variant == "nvls" and not ar.arena.mc_ptr:
+                    continue
+                if variant == "oneshot" and (n > ar.oneshot_numel or P == 1):
+                    continue
+                k = {"i": 0}
+
+                def call():
+                    ar(bufs[k["i"] % copies], variant=variant)
+                    k["i"] += 1
+                iters = args.iters if kb >= 1024 else args.iters * 10
+                ms = time_calls(call, iters)
+                ar.check()
+                roof = roofline_ms(n * 4, rate, P, variant, hbm)
+                rows.append({"impl": variant, "rate": rate, "kb": kb, "ms": ms, "eff_gbs": n * 4 / ms / 1e6,
+                             "roofline_ms": roof, "frac": roof / ms, "roofline": f"{how} HBM {hbm:.0f} GB/s, NVLink {NVLINK_GBS:.0f} GB/s",
+                             "P": P, "ctas": ar.ctas})
+                if rank == 0:
+                    print(json.dumps(rows[-1]), flush=True)
+            del bufs
+        del ar
+    if rank == 0 and args.json:
+        Path(args.json).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.json).write_text(json.dumps(rows, indent=1))
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -17,6 +17,14 @@ from .. import _native
 _CHUNK = 1 << 16
 
 
+def _dense(t: torch.Tensor) -> bool:
+    """Memory is one gap-free run (row-major or channels-last), so an elementwise
+    update may walk it linearly."""
+    if t.is_contiguous():
+        return True
+    return t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last)
+
+
 class _FusedBase(torch.optim.Optimizer):
     n_states = 1
 
@@ -41,8 +49,9 @@ class _FusedBase(torch.optim.Optimizer):
             return ent[1], ent[2], params
         rows = []
         for p in params:
-            if not (p.is_contiguous() and p.grad.is_contiguous() and p.dtype == torch.float32):
-                raise TypeError("fused optimizers need contiguous float32 parameters and gradients")
+            if not (_dense(p) and p.grad.stride() == p.stride() and p.dtype == torch.float32
+                    and p.grad.dtype == torch.float32):
+                raise TypeError("fused optimizers need dense float32 parameters whose gradients share their strides")
             st = self._ensure_state(p)
             n = p.numel()
             for lo in range(0, n, _CHUNK):

@@ -11,10 +11,12 @@ The reference runs stock DDP (NCCL fp32) and only afterwards round-trips the
 whole gradient through a host codec (hw/models/train_imagenet.py:219,449-475);
 at one GPU it still applies the codec round trip to the local gradient, which is
 what this hook does when the world size is 1.
-"""
-from __future__ import annotations
 
+(No postponed evaluation of annotations in this module: DDP inspects the hook's
+``bucket`` annotation and requires the class object itself.)
+"""
 from dataclasses import dataclass, field
+from typing import Optional
 
 import torch
 import torch.distributed as dist
@@ -50,7 +52,7 @@ class GcowDDPState:
         self.residual = {int(k): v.to(dev) for k, v in sd.get("residual", {}).items()}
 
 
-def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> torch.futures.Future:
+def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     buf = bucket.buffer()
     ar = state.ar
     cur = torch.cuda.current_stream(buf.device)
@@ -79,7 +81,7 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
     return fut
 
 
-def nccl_fp32_hook(state, bucket: dist.GradBucket) -> torch.futures.Future:
+def nccl_fp32_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """Uncompressed baseline with the same averaging semantics."""
     group = state.group if state is not None else None
     buf = bucket.buffer()
@@ -88,8 +90,8 @@ def nccl_fp32_hook(state, bucket: dist.GradBucket) -> torch.futures.Future:
     return fut.then(lambda f: f.value()[0].div_(world))
 
 
-def wrap_ddp(model: torch.nn.Module, cfg: GcowConfig | None = None, device: torch.device | None = None,
-             group=None, max_bucket_numel: int | None = None):
+def wrap_ddp(model: torch.nn.Module, cfg: Optional[GcowConfig] = None, device: Optional[torch.device] = None,
+             group=None, max_bucket_numel: Optional[int] = None):
     """Returns (ddp_model, state). ``cfg.variant == 'nccl'`` gives the uncompressed baseline."""
     cfg = cfg or GcowConfig.from_env()
     device = device or torch.device("cuda", torch.cuda.current_device())

@@ -61,7 +61,8 @@ def test_adamw_gpu_matches_torch_and_resumes():
     for x, y in zip(a, b):
         assert torch.allclose(x, y, rtol=1e-4, atol=1e-6)
     # state dict round trip keeps stepping identically
-    sd = fa.state_dict()
+    import copy
+    sd = copy.deepcopy(fa.state_dict())   # torch.save/load would give separate tensors too
     a2 = [t.detach().clone().requires_grad_(True) for t in a]
     fa2 = FusedAdamW(a2, lr=1e-3, weight_decay=0.01, eps=1e-6)
     fa2.load_state_dict(sd)
