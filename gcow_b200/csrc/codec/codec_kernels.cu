@@ -540,3 +540,102 @@ int gcow_dbg_planes(int dim, uint64_t nb, const uint32_t* u, uint32_t budget, ui
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of gcow_encode_generic (see gcow_static_api.h).
+// ---------------------------------------------------------------------------
+#include <mutex>
+#include <stdio.h>
+#include "gcow_static_api.h"
+
+namespace {
+
+constexpr uint64_t kStaticScratchBytes = 8ull << 20;
+
+// Scratch shared by every call on a device. In host code this name is only a
+// stand-in for the symbol, not a device address: the address handed to kernels
+// comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_addr[kMaxDevices] = {};
+thread_local char g_static_err[256] = "";
+
+int static_fail(int code, const char* fmt, unsigned long long a = 0, unsigned long long b = 0) {
+  snprintf(g_static_err, sizeof g_static_err, fmt, a, b);
+  return code;
+}
+
+// Device address of the scratch on the current device; looked up once per device.
+int static_scratch_ptr(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return static_fail(GCOW_STATIC_SETUP_FAILED, "cannot identify the current device (cuda error %llu)", (unsigned long long)e);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (e != cudaSuccess || !p)
+      return static_fail(GCOW_STATIC_SETUP_FAILED, "cudaGetSymbolAddress failed with cuda error %llu", (unsigned long long)e);
+    g_static_addr[dev] = p;
+  }
+  *out = g_static_addr[dev];
+  return GCOW_STATIC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint64_t gcow_encode_generic_static_capacity(void) { return kStaticScratchBytes; }
+
+const char* gcow_encode_generic_static_error(void) { return g_static_err; }
+
+int gcow_encode_generic_static(const float* in, uint64_t nx, uint64_t ny, const int32_t* params,
+                               uint64_t* out, uint64_t out_bytes, uint64_t* block_bits, void* stream) {
+  g_static_err[0] = 0;
+  if (!in || !params || !out || !block_bits)
+    return static_fail(GCOW_STATIC_BAD_ARGS, "null argument");
+  ZfpParams p = load_params(params);
+  const int dim = ny ? 2 : 1;
+  const uint64_t blocks = ny ? num_blocks_2d(nx, ny) : num_blocks_1d(nx);
+  if (!blocks) return GCOW_STATIC_OK;
+  const uint64_t need = gcow_encode_generic_scratch_bytes(params, blocks, dim);
+  if (need > kStaticScratchBytes)
+    return static_fail(GCOW_STATIC_TOO_LARGE,
+                       "request needs %llu bytes of scratch but the built-in array holds %llu; "
+                       "split the input or use gcow_encode_generic with your own scratch",
+                       (unsigned long long)need, (unsigned long long)kStaticScratchBytes);
+  if (out_bytes < max_output_bytes(p, blocks, dim))
+    return static_fail(GCOW_STATIC_BAD_ARGS, "output buffer of %llu bytes is smaller than the worst case %llu",
+                       (unsigned long long)out_bytes, (unsigned long long)max_output_bytes(p, blocks, dim));
+  void* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc != GCOW_STATIC_OK) return rc;
+
+  cudaStream_t s = (cudaStream_t)stream;
+  const uint64_t wpb = (max_block_bits(p, dim) + 63) / 64;
+  uint64_t* slots = (uint64_t*)scratch;
+  uint32_t* lens = (uint32_t*)(slots + wpb * blocks);
+  uint64_t* tile_sums = (uint64_t*)((char*)lens + ((blocks * 4 + 7) & ~7ull));
+  const uint64_t tiles = (blocks + kScanTile - 1) / kScanTile;
+  cudaMemsetAsync(out, 0, out_bytes, s);   // the scatter pass ORs into the stream
+  const int g = grid_for(blocks);
+  if (dim == 1) encode_slots_kernel<1><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, slots, lens);
+  else encode_slots_kernel<2><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, slots, lens);
+  if (is_fixed_rate(p)) {
+    fixed_offsets_kernel<<<grid_for(blocks + 1), kThreads, 0, s>>>(blocks, p.maxbits, block_bits);
+  } else {
+    scan_tile_sums_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums);
+    scan_tile_offsets_kernel<<<1, kThreads, 0, s>>>(tile_sums, tiles);
+    scan_apply_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums, block_bits);
+  }
+  scatter_slots_kernel<<<g, kThreads, 0, s>>>(slots, lens, block_bits, blocks, (unsigned long long*)out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_fail((int)e, "kernel launch failed with cuda error %llu", (unsigned long long)e);
+  return GCOW_STATIC_OK;
+}
+
+}  // extern "C"
