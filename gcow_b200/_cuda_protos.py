@@ -64,3 +64,18 @@ _declare_codec_comm = declare
 def declare(lib, proto):  # noqa: F811
     _declare_codec_comm(lib, proto)
     _declare_ops(lib, proto)
+
+
+def _declare_gemm(lib, proto):
+    def opt(name, restype, *args):
+        if hasattr(lib, name):
+            proto(lib, name, restype, *args)
+    opt("gcow_gemm_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, i32, ptr, i32, ptr)
+
+
+_declare_prev_gemm = declare
+
+
+def declare(lib, proto):  # noqa: F811
+    _declare_prev_gemm(lib, proto)
+    _declare_gemm(lib, proto)

@@ -50,6 +50,7 @@ def main(argv=None):
     ap.add_argument("--cpu-mb", type=int, default=16)
     ap.add_argument("--json", default="")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU reference / oracle timings")
     args = ap.parse_args(argv)
     res = {"mb": args.mb, "gpu": [], "cpu": []}
     hbm, how = peaks()
@@ -69,6 +70,8 @@ def main(argv=None):
                    "roofline": f"of {how} {hbm:.0f} GB/s copy"}
             res["gpu"].append(row)
             print(json.dumps(row), flush=True)
+    if args.no_cpu:
+        return res
     # CPU side: reference sw codec (1 thread) and this library's oracle
     sys.path.insert(0, str(Path(__file__).resolve().parents[2] / "tests"))
     try:

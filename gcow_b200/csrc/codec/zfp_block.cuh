@@ -399,8 +399,8 @@ GCOW_HD uint16_t make_dec_entry(uint32_t n, uint32_t peek) {
   return (uint16_t)(x | (s.used << 4) | (n << 7));
 }
 
-// Append `len` (<= 9) low bits of v at bit `pos` of a little-endian array of
-// NW 32-bit words; bits past the array fall off.
+// OR the bits of v (up to 32) in at bit `pos` of a little-endian array of NW
+// 32-bit words; bits past the array fall off.
 template <int NW>
 GCOW_HD void reg_put(uint32_t (&w)[NW], uint32_t pos, uint32_t v) {
 #pragma unroll
@@ -410,7 +410,7 @@ GCOW_HD void reg_put(uint32_t (&w)[NW], uint32_t pos, uint32_t v) {
     else if (lo < 0 && lo > -32) w[i] |= v >> (-lo);
   }
 }
-// At least 7 valid bits starting at bit `pos`.
+// The 32 bits starting at bit `pos` (zeros past the array).
 template <int NW>
 GCOW_HD uint32_t reg_peek(const uint32_t (&w)[NW], uint32_t pos) {
   uint32_t r = 0;
@@ -434,8 +434,60 @@ struct RegSrc {
   }
 };
 
+GCOW_HD uint32_t brev32(uint32_t x) {
+#if defined(__CUDA_ARCH__)
+  return __brev(x);
+#else
+  x = ((x >> 1) & 0x55555555u) | ((x & 0x55555555u) << 1);
+  x = ((x >> 2) & 0x33333333u) | ((x & 0x33333333u) << 2);
+  x = ((x >> 4) & 0x0f0f0f0fu) | ((x & 0x0f0f0f0fu) << 4);
+  x = ((x >> 8) & 0x00ff00ffu) | ((x & 0x00ff00ffu) << 8);
+  return (x >> 16) | (x << 16);
+#endif
+}
+GCOW_HD uint32_t clz32(uint32_t x) {  // x != 0
+#if defined(__CUDA_ARCH__)
+  return (uint32_t)__clz((int)x);
+#else
+  return (uint32_t)__builtin_clz(x);
+#endif
+}
+// low 8 bits -> every 4th bit, and back
+GCOW_HD uint32_t spread4(uint32_t x) {
+  x &= 0xffu;
+  x = (x | (x << 12)) & 0x000f000fu;
+  x = (x | (x << 6)) & 0x03030303u;
+  x = (x | (x << 3)) & 0x11111111u;
+  return x;
+}
+GCOW_HD uint32_t compact4(uint32_t x) {
+  x &= 0x11111111u;
+  x = (x | (x >> 3)) & 0x03030303u;
+  x = (x | (x >> 6)) & 0x000f000fu;
+  x = (x | (x >> 12)) & 0xffu;
+  return x;
+}
+// Bit planes k-1 .. k-8 of four values as eight nibbles in stream order
+// (plane k-1 in the low nibble, value i in bit i of a nibble); 1 <= k <= 32.
+GCOW_HD uint32_t plane_group(const uint32_t* u, uint32_t k) {
+  const uint32_t s = 32 - k;
+  return spread4(brev32(u[0] << s)) | (spread4(brev32(u[1] << s)) << 1) |
+         (spread4(brev32(u[2] << s)) << 2) | (spread4(brev32(u[3] << s)) << 3);
+}
+GCOW_HD void deposit_group(uint32_t* u, uint32_t T, uint32_t k) {
+  const uint32_t s = 32 - k;
+#pragma unroll
+  for (int i = 0; i < 4; i++) u[i] |= brev32(compact4(T >> i)) >> s;
+}
+
 // Encode one block of 4 into NW 32-bit words (maxbits <= 32*NW). Returns the
 // bit count including padding to minbits.
+//
+// Three shortcuts over the plane-by-plane loop, all bit-identical to it:
+// leading all-zero planes cost one 0 bit each and are skipped with a
+// count-leading-zeros; planes are transposed eight at a time (plane_group);
+// and once all four coefficients are significant every further plane is four
+// verbatim bits, i.e. the rest of the transposed group is appended as is.
 template <int NW>
 GCOW_HD uint32_t encode_block_1d_fast(const float* f, const ZfpParams& p, const uint16_t* etab,
                                       uint32_t (&w)[NW]) {
@@ -453,15 +505,31 @@ GCOW_HD uint32_t encode_block_1d_fast(const float* f, const ZfpParams& p, const 
     fwd_lift(q[0], q[1], q[2], q[3]);
 #pragma unroll
     for (int i = 0; i < 4; i++) u[i] = int2nb(q[i]);
-    uint32_t kmin = prec < 32 ? 32 - prec : 0;
-    uint32_t n = 0;
+    const uint32_t kmin = prec < 32 ? 32 - prec : 0;
     const uint32_t end = p.maxbits;
-    for (uint32_t k = 32; pos < end && k-- > kmin;) {
-      uint32_t x = extract_plane<4>(u, (int)k);
-      uint32_t e = etab[n * 16 + x];
-      reg_put<NW>(w, pos, e & 0x7fu);
-      pos += (e >> 7) & 7u;
-      n = e >> 10;
+    uint32_t n = 0, k = 32;
+    const uint32_t m = u[0] | u[1] | u[2] | u[3];
+    uint32_t z = m ? clz32(m) : 32u;
+    if (z > 32 - kmin) z = 32 - kmin;
+    pos += z;  // one 0 bit per all-zero plane
+    k -= z;
+    while (pos < end && k > kmin) {
+      const uint32_t T = plane_group(u, k);
+      const uint32_t cnt = k - kmin < 8 ? k - kmin : 8;
+      uint32_t j = 0;
+      while (n < 4 && j < cnt && pos < end) {
+        uint32_t e = etab[n * 16 + ((T >> (4 * j)) & 15u)];
+        reg_put<NW>(w, pos, e & 0x7fu);
+        pos += (e >> 7) & 7u;
+        n = e >> 10;
+        j++;
+      }
+      if (j < cnt && pos < end) {  // n == 4: the remaining planes of the group are verbatim
+        uint32_t nb = 4 * (cnt - j);
+        reg_put<NW>(w, pos, (T >> (4 * j)) & low_mask32(nb));
+        pos += nb;
+      }
+      k -= cnt;
     }
     if (pos > end) {  // cut the last code at the budget
 #pragma unroll
@@ -477,7 +545,10 @@ GCOW_HD uint32_t encode_block_1d_fast(const float* f, const ZfpParams& p, const 
   return pos < p.minbits ? p.minbits : pos;
 }
 
-// Decode one block of 4 held in NW 32-bit words.
+// Decode one block of 4 held in NW 32-bit words; mirror of the encoder's
+// shortcuts. Codes are looked up whole only while at least 7 bits of budget
+// remain; the last few bits before all coefficients are significant go through
+// the serial routine, which has the exact semantics at the budget edge.
 template <int NW>
 GCOW_HD void decode_block_1d_fast(float* f, const ZfpParams& p, const uint16_t* dtab,
                                   const uint32_t (&w)[NW], int shift = 0) {
@@ -487,21 +558,44 @@ GCOW_HD void decode_block_1d_fast(float* f, const ZfpParams& p, const uint16_t* 
   }
   int emax = (int)((w[0] >> 1) & 0xffu) - kEBias;
   uint32_t prec = block_precision(emax, p.maxprec, p.minexp, 1);
-  uint32_t kmin = prec < 32 ? 32 - prec : 0;
+  const uint32_t kmin = prec < 32 ? 32 - prec : 0;
   uint32_t u[4] = {0, 0, 0, 0};
   uint32_t pos = kHeaderBits, n = 0, k = 32;
   const uint32_t end = p.maxbits;
-  // whole codes: at least 7 bits left, so any plane code fits the budget
-  while (end - pos >= 7 && k > kmin) {
-    k--;
-    uint32_t e = dtab[n * 128 + (reg_peek<NW>(w, pos) & 127u)];
-    deposit_plane<4>(u, e & 15u, (int)k);
-    pos += (e >> 4) & 7u;
-    n = e >> 7;
+  {  // leading all-zero planes
+    uint32_t avail = end - pos;
+    uint32_t S = reg_peek<NW>(w, pos) & low_mask32(avail);
+    uint32_t z = S ? (uint32_t)ctz32(S) : 32u;
+    if (z > avail) z = avail;
+    if (z > 32 - kmin) z = 32 - kmin;
+    pos += z;
+    k -= z;
   }
-  // last few bits: exact serial semantics at the budget edge
-  RegSrc<NW> src{w, pos};
-  decode_planes_from<4>(u, end - pos, kmin, k, n, src);
+  while (pos < end && k > kmin) {
+    const uint32_t cnt = k - kmin < 8 ? k - kmin : 8;
+    uint32_t T = 0, j = 0;
+    while (n < 4 && j < cnt && end - pos >= 7) {
+      uint32_t e = dtab[n * 128 + (reg_peek<NW>(w, pos) & 127u)];
+      T |= (e & 15u) << (4 * j);
+      pos += (e >> 4) & 7u;
+      n = e >> 7;
+      j++;
+    }
+    if (n == 4 && j < cnt && pos < end) {  // verbatim planes
+      uint32_t nb = 4 * (cnt - j), avail = end - pos;
+      uint32_t take = nb < avail ? nb : avail;
+      T |= (reg_peek<NW>(w, pos) & low_mask32(take)) << (4 * j);
+      pos += take;
+      j = cnt;
+    }
+    if (T) deposit_group(u, T, k);
+    if (j < cnt) {  // budget nearly spent before all coefficients became significant
+      RegSrc<NW> src{w, pos};
+      decode_planes_from<4>(u, end - pos, kmin, k - j, n, src);
+      break;
+    }
+    k -= cnt;
+  }
   int32_t q[4];
 #pragma unroll
   for (int i = 0; i < 4; i++) q[i] = nb2int(u[i]);

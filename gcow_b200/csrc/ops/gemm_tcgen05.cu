@@ -1,0 +1,384 @@
+// bf16 GEMM on the 5th-generation tensor cores (sm_100a): C[M,N] = A[M,K] * B[N,K]^T
+// with fp32 accumulation in tensor memory and a fused epilogue.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles of A (128x64) and B (256x64),
+//               128-byte swizzle, into a 4-stage shared-memory ring (mbarrier tx counts);
+//   warp 1      allocates 512 TMEM columns (two 128x256 fp32 accumulators) and one
+//               elected thread issues tcgen05.mma (M128 N256 K16, kind::f16) from
+//               shared-memory descriptors; tcgen05.commit releases ring stages and
+//               publishes finished accumulators;
+//   warps 2-5   epilogue: tcgen05.ld their 32-lane quarter of the accumulator,
+//               add bias / residual, optional GELU, convert and store - while the
+//               MMA warp already works on the other accumulator.
+// Both operands are K-major (row-major A[M,K], row-major B[N,K]), which is the
+// layout of activations and of nn.Linear / 1x1-convolution weights. No TMA
+// multicast is used anywhere. Every mbarrier wait is bounded: after a fixed
+// number of polls the CTA raises an error word, all roles leave their loops,
+// outstanding MMAs are drained (bounded), TMEM is freed and the kernel returns.
+//
+// Replaces the cuBLAS GEMMs behind nn.Linear / 1x1 convolutions in the
+// reference's models (hw/models/resenet.py:11,17,90).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <mutex>
+
+namespace gcow {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+constexpr int THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t kSpinLimit = 1u << 26;   // polls before a wait gives up
+
+enum Flags : int { kOutF32 = 1, kBias = 2, kGelu = 4, kResidual = 8, kAccumulate = 16 };
+
+struct Params {
+  void* C;                 // bf16 or fp32 [M, ldc]
+  const float* bias;       // [N] fp32 or nullptr
+  const void* residual;    // same type/ld as C or nullptr
+  int M, N, K, ldc, flags;
+  uint32_t* error;         // device word, set non-zero when a wait gave up
+};
+
+struct Smem {
+  uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain;
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait. Returns false when the CTA is aborting (this or another role gave up).
+__device__ __forceinline__ bool mbar_wait(Smem* sm, uint64_t* bar, uint32_t parity, uint32_t* error, uint32_t code) {
+  for (uint32_t it = 0; it < kSpinLimit; it++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (sm->abort) return false;
+  }
+  sm->abort = 1;
+  atomicCAS(error, 0u, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes
+// with the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);        // start address
+  d |= (uint64_t)(1024u >> 4) << 32;               // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                          // layout: 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ float gelu_f(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smA = base;
+  uint8_t* smB = base + STAGES * A_BYTES;
+  Smem* sm = reinterpret_cast<Smem*>(base + STAGES * (A_BYTES + B_BYTES));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&sm->tmem_full[a], 1); mbar_init(&sm->tmem_empty[a], 128); }
+    mbar_init(&sm->drain, 1);
+    sm->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t s = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < kblocks; kb++) {
+          if (!(ok = mbar_wait(sm, &sm->empty[s], phase ^ 1, p.error, 1))) break;
+          mbar_expect_tx(&sm->full[s], A_BYTES + B_BYTES);
+          tma_load_2d(smem_u32(smA + s * A_BYTES), &tmap_a, smem_u32(&sm->full[s]), kb * BK, m0);
+          tma_load_2d(smem_u32(smB + s * B_BYTES), &tmap_b, smem_u32(&sm->full[s]), kb * BK, n0);
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // giving up: let copies already in flight land before the CTA's shared memory is released
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N256 M128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      uint32_t s = 0, phase = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+        const uint32_t a = t & 1, aphase = (t >> 1) & 1;
+        if (!(ok = mbar_wait(sm, &sm->tmem_empty[a], aphase ^ 1, p.error, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * BN;
+        for (int kb = 0; kb < kblocks; kb++) {
+          if (!(ok = mbar_wait(sm, &sm->full[s], phase, p.error, 3))) break;
+          tc_fence_after();
+          const uint64_t da = smem_desc_sw128(smem_u32(smA + s * A_BYTES));
+          const uint64_t db = smem_desc_sw128(smem_u32(smB + s * B_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++) {
+            // advance 16 elements = 32 bytes inside the swizzled 128-byte row
+            tc_mma(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+          }
+          tc_commit(&sm->empty[s]);
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&sm->tmem_full[a]);
+      }
+      // drain: everything issued by this thread has finished before TMEM is freed
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < kSpinLimit; it++) if (mbar_try_wait(&sm->drain, 0)) break;
+    }
+  } else {
+    // ----------------------------------------------------------------- epilogue
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    uint32_t t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const uint32_t a = t & 1, aphase = (t >> 1) & 1;
+      ok = mbar_wait(sm, &sm->tmem_full[a], aphase, p.error, 4);
+      ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below need the whole warp
+      if (!ok) break;
+      tc_fence_after();
+      const int m = m0 + row_in_tile;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        tc_ld32(taddr + c * 32, r);
+        tc_wait_ld();
+        const int n = n0 + c * 32;
+        if (m < p.M && n < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+          if (p.flags & kBias) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) if (n + j < p.N) v[j] += __ldg(p.bias + n + j);
+          }
+          if (p.flags & kGelu) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
+          }
+          const size_t off = (size_t)m * p.ldc + n;
+          if (p.flags & kOutF32) {
+            float* C = reinterpret_cast<float*>(p.C) + off;
+            const float* R = reinterpret_cast<const float*>(p.residual) + off;
+            if (n + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (p.flags & kResidual) { float4 x = *reinterpret_cast<const float4*>(R + j); o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w; }
+                if (p.flags & kAccumulate) { float4 x = *reinterpret_cast<const float4*>(C + j); o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w; }
+                *reinterpret_cast<float4*>(C + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && n + j < p.N; j++) {
+                float o = v[j];
+                if (p.flags & kResidual) o += R[j];
+                if (p.flags & kAccumulate) o += C[j];
+                C[j] = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
+            const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.residual) + off;
+            if (n + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (p.flags & kResidual) {
+                  uint4 x = *reinterpret_cast<const uint4*>(R + j);
+                  const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+                  for (int e = 0; e < 4; e++) { float2 f = __bfloat1622float2(xb[e]); v[j + 2 * e] += f.x; v[j + 2 * e + 1] += f.y; }
+                }
+                uint4 o;
+                __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                *reinterpret_cast<uint4*>(C + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && n + j < p.N; j++) {
+                float o = v[j];
+                if (p.flags & kResidual) o += __bfloat162float(R[j]);
+                C[j] = __float2bfloat16(o);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&sm->tmem_empty[a]);
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] with leading dimension ld (elements); box = 64 x box_rows.
+static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  if (((uintptr_t)ptr & 15) || (ld * 2) % 16) return -11;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+constexpr size_t kSmemBytes = STAGES * (A_BYTES + B_BYTES) + sizeof(Smem) + 1024;
+
+}  // namespace gemm
+}  // namespace gcow
+
+using namespace gcow::gemm;
+
+extern "C" {
+
+// C[M,N] (+)= A[M,K] * B[N,K]^T  (+ bias[N]) (GELU) (+ residual[M,N]).
+// A, B bf16 row-major with leading dimensions lda, ldb (multiples of 8, 16-byte
+// aligned bases); C bf16 or fp32 (flags & 1) with ldc a multiple of 8 (bf16) or
+// 4 (fp32). `error` is a device word that stays 0 unless a wait gave up.
+// Returns 0, a negative argument error, or a CUDA error code.
+int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                   const float* bias, const void* residual, int flags, uint32_t* error, int max_ctas,
+                   void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 || lda % 8 || ldb % 8) return -1;
+  if ((flags & kOutF32) ? (ldc % 4) : (ldc % 8)) return -1;
+  if ((uintptr_t)C & 15) return -1;
+  if ((flags & kBias) && !bias) return -1;
+  if ((flags & kResidual) && (!residual || ((uintptr_t)residual & 15))) return -1;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
+  if (rc) return rc;
+  static std::once_flag once;
+  static int sms = 148;
+  std::call_once(once, [] {
+    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  });
+  Params p;
+  p.C = C; p.bias = bias; p.residual = residual;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags; p.error = error;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = tiles < sms ? tiles : sms;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  gemm_bf16_kernel<<<grid, THREADS, kSmemBytes, (cudaStream_t)stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

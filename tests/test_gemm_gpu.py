@@ -1,0 +1,77 @@
+"""tcgen05 bf16 GEMM against an fp32 PyTorch reference of the same product."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, bias=None, residual=None, gelu=False):
+    y = a.float() @ b.float().t()
+    if bias is not None:
+        y = y + bias
+    if gelu:
+        y = torch.nn.functional.gelu(y)
+    if residual is not None:
+        y = y + residual.float()
+    return y
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 1024), (300, 520, 136),
+                                   (4096, 1000, 2048), (77, 40, 72), (1024, 3072, 1024)])
+def test_gemm_matches_fp32_reference(M, N, K):
+    from gcow_b200.ops import kernels as K_
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    ref = _ref(a, b)
+    for dt in (torch.float32, torch.bfloat16):
+        y = K_.gemm_bf16(a, b, out_dtype=dt)
+        K_.check_errors()
+        tol = 2e-2 if dt == torch.bfloat16 else 1e-3
+        err = (y.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+        assert err < tol, (dt, err)
+
+
+def test_gemm_epilogues():
+    from gcow_b200.ops import kernels as K_
+    torch.manual_seed(0)
+    M, N, K = 512, 768, 256
+    a = (torch.randn(M, K, device="cuda") * 0.3).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.3).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    y = K_.gemm_bf16(a, b, bias=bias, gelu=True, residual=res)
+    K_.check_errors()
+    ref = _ref(a, b, bias, res, True)
+    assert (y.float() - ref).abs().max().item() < 0.06
+    acc = torch.ones(M, N, device="cuda")
+    K_.gemm_bf16(a, b, out=acc, accumulate=True)
+    assert (acc - (_ref(a, b) + 1)).abs().max().item() < 2e-2
+
+
+def test_strided_operands_and_small_grid():
+    from gcow_b200.ops import kernels as K_
+    big = (torch.randn(640, 512, device="cuda") * 0.5).bfloat16()
+    a = big[:, :256]                      # leading dimension 512, K 256
+    b = (torch.randn(1024, 256, device="cuda") * 0.5).bfloat16()
+    y = K_.gemm_bf16(a, b, out_dtype=torch.float32, max_ctas=3)   # several tiles per CTA
+    K_.check_errors()
+    assert (y - _ref(a, b)).abs().max().item() < 2e-2
+
+
+def test_linear_autograd_matches_torch():
+    from gcow_b200.ops import kernels as K_
+    torch.manual_seed(1)
+    x = torch.randn(4, 64, 256, device="cuda", requires_grad=True)
+    w = (torch.randn(384, 256, device="cuda") * 0.05).requires_grad_(True)
+    b = torch.zeros(384, device="cuda", requires_grad=True)
+    y = K_.linear(x, w, b)
+    y.float().square().mean().backward()
+    K_.check_errors()
+    gx, gw, gb = x.grad.clone(), w.grad.clone(), b.grad.clone()
+    x.grad = w.grad = b.grad = None
+    yr = torch.nn.functional.linear(x, w, b)
+    yr.square().mean().backward()
+    assert (y.float() - yr).abs().max().item() < 0.05
+    for g, r in ((gx, x.grad), (gw, w.grad), (gb, b.grad)):
+        assert (g.float() - r).abs().max().item() <= 0.03 * r.abs().max().item() + 1e-6
