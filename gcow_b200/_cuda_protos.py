@@ -79,3 +79,27 @@ _declare_prev_gemm = declare
 def declare(lib, proto):  # noqa: F811
     _declare_prev_gemm(lib, proto)
     _declare_gemm(lib, proto)
+
+
+def _declare_norm(lib, proto):
+    def opt(name, restype, *args):
+        if hasattr(lib, name):
+            proto(lib, name, restype, *args)
+    f32 = C.c_float
+    opt("gcow_layernorm_fwd", i32, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, f32, ptr)
+    opt("gcow_layernorm_bwd_parts", i32, i32)
+    opt("gcow_layernorm_bwd", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, ptr)
+    opt("gcow_gelu_fwd", i32, ptr, ptr, u64, ptr)
+    opt("gcow_gelu_bwd", i32, ptr, ptr, ptr, u64, ptr)
+    opt("gcow_softmax_xent", i32, ptr, ptr, ptr, ptr, i32, i32, i32, i32, ptr)
+    opt("gcow_colsum_parts", i32, i32)
+    opt("gcow_colsum", i32, ptr, ptr, ptr, i32, i32, i32, ptr)
+    opt("gcow_u8_to_bf16_norm", i32, ptr, ptr, u64, i32, ptr, ptr, ptr)
+
+
+_declare_prev_norm = declare
+
+
+def declare(lib, proto):  # noqa: F811
+    _declare_prev_norm(lib, proto)
+    _declare_norm(lib, proto)

@@ -84,15 +84,13 @@ encode_1d_fixed_kernel(const float* __restrict__ in, uint64_t n, void* __restric
   __shared__ uint16_t etab[kEncTabSize];
   build_enc_table(etab);
   __syncthreads();
-  ZfpParams p = default_params();
-  p.minbits = p.maxbits = BITS;
   const uint64_t blocks = num_blocks_1d(n);
   for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
        b += (uint64_t)gridDim.x * blockDim.x) {
     float f[4];
     load_block_1d(f, in, n, b, aligned);
     uint32_t w[CodeIO<BITS>::NW];
-    encode_block_1d_fast<CodeIO<BITS>::NW>(f, p, etab, w);
+    encode_block_1d_rate<BITS>(f, etab, w);
     CodeIO<BITS>::store(out, b, w);
   }
 }
@@ -104,15 +102,13 @@ decode_1d_fixed_kernel(const void* __restrict__ in, float* __restrict__ out, uin
   __shared__ uint16_t dtab[kDecTabSize];
   build_dec_table(dtab);
   __syncthreads();
-  ZfpParams p = default_params();
-  p.minbits = p.maxbits = BITS;
   const uint64_t blocks = num_blocks_1d(n);
   for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
        b += (uint64_t)gridDim.x * blockDim.x) {
     uint32_t w[CodeIO<BITS>::NW];
     CodeIO<BITS>::load(in, b, w);
     float f[4];
-    decode_block_1d_fast<CodeIO<BITS>::NW>(f, p, dtab, w, shift);
+    decode_block_1d_rate<BITS>(f, dtab, w, shift);
     store_block_1d(f, out, n, b, aligned);
   }
 }

@@ -434,7 +434,8 @@ uint64_t gcow_header_decompress(const uint64_t* in, float* data, uint64_t nx, ui
   return src.pos;
 }
 
-// Table-driven 1-D fixed-rate path; maxbits must be 16, 32, 64 or 128.
+// Table-driven 1-D fixed-rate paths (rate-specialised and general); both are run
+// and must agree (-2 otherwise). maxbits must be 16, 32, 64 or 128.
 int gcow_fast1d_compress(const float* data, uint64_t n, const int32_t* params, void* out) {
   ZfpParams p = load_params(params);
   uint16_t etab[gcow::kEncTabSize];
@@ -444,10 +445,10 @@ int gcow_fast1d_compress(const float* data, uint64_t n, const int32_t* params, v
   for (uint64_t b = 0; b < blocks; b++) {
     o_gather(blk, data, n, 0, b);
     switch (p.maxbits) {
-      case 16: { uint32_t w[1]; gcow::encode_block_1d_fast<1>(blk, p, etab, w); ((uint16_t*)out)[b] = (uint16_t)w[0]; break; }
-      case 32: { uint32_t w[1]; gcow::encode_block_1d_fast<1>(blk, p, etab, w); ((uint32_t*)out)[b] = w[0]; break; }
-      case 64: { uint32_t w[2]; gcow::encode_block_1d_fast<2>(blk, p, etab, w); memcpy((uint32_t*)out + 2 * b, w, 8); break; }
-      case 128: { uint32_t w[4]; gcow::encode_block_1d_fast<4>(blk, p, etab, w); memcpy((uint32_t*)out + 4 * b, w, 16); break; }
+      case 16: { uint32_t w[1], v[1]; gcow::encode_block_1d_rate<16>(blk, etab, w); gcow::encode_block_1d_fast<1>(blk, p, etab, v); if (w[0] != v[0]) return -2; ((uint16_t*)out)[b] = (uint16_t)w[0]; break; }
+      case 32: { uint32_t w[1], v[1]; gcow::encode_block_1d_rate<32>(blk, etab, w); gcow::encode_block_1d_fast<1>(blk, p, etab, v); if (w[0] != v[0]) return -2; ((uint32_t*)out)[b] = w[0]; break; }
+      case 64: { uint32_t w[2], v[2]; gcow::encode_block_1d_rate<64>(blk, etab, w); gcow::encode_block_1d_fast<2>(blk, p, etab, v); if (memcmp(w, v, 8)) return -2; memcpy((uint32_t*)out + 2 * b, w, 8); break; }
+      case 128: { uint32_t w[4], v[4]; gcow::encode_block_1d_rate<128>(blk, etab, w); gcow::encode_block_1d_fast<4>(blk, p, etab, v); if (memcmp(w, v, 16)) return -2; memcpy((uint32_t*)out + 4 * b, w, 16); break; }
       default: return -1;
     }
   }
@@ -458,15 +459,16 @@ int gcow_fast1d_decompress(const void* in, float* data, uint64_t n, const int32_
   std::vector<uint16_t> dtab(gcow::kDecTabSize);
   for (uint32_t i = 0; i < (uint32_t)gcow::kDecTabSize; i++) dtab[i] = gcow::make_dec_entry(i / 128, i % 128);
   uint64_t blocks = gcow::num_blocks_1d(n);
-  float blk[4];
+  float blk[4], alt[4];
   for (uint64_t b = 0; b < blocks; b++) {
     switch (p.maxbits) {
-      case 16: { uint32_t w[1] = {((const uint16_t*)in)[b]}; gcow::decode_block_1d_fast<1>(blk, p, dtab.data(), w, shift); break; }
-      case 32: { uint32_t w[1] = {((const uint32_t*)in)[b]}; gcow::decode_block_1d_fast<1>(blk, p, dtab.data(), w, shift); break; }
-      case 64: { uint32_t w[2]; memcpy(w, (const uint32_t*)in + 2 * b, 8); gcow::decode_block_1d_fast<2>(blk, p, dtab.data(), w, shift); break; }
-      case 128: { uint32_t w[4]; memcpy(w, (const uint32_t*)in + 4 * b, 16); gcow::decode_block_1d_fast<4>(blk, p, dtab.data(), w, shift); break; }
+      case 16: { uint32_t w[1] = {((const uint16_t*)in)[b]}; gcow::decode_block_1d_rate<16>(blk, dtab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); break; }
+      case 32: { uint32_t w[1] = {((const uint32_t*)in)[b]}; gcow::decode_block_1d_rate<32>(blk, dtab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); break; }
+      case 64: { uint32_t w[2]; memcpy(w, (const uint32_t*)in + 2 * b, 8); gcow::decode_block_1d_rate<64>(blk, dtab.data(), w, shift); gcow::decode_block_1d_fast<2>(alt, p, dtab.data(), w, shift); break; }
+      case 128: { uint32_t w[4]; memcpy(w, (const uint32_t*)in + 4 * b, 16); gcow::decode_block_1d_rate<128>(blk, dtab.data(), w, shift); gcow::decode_block_1d_fast<4>(alt, p, dtab.data(), w, shift); break; }
       default: return -1;
     }
+    if (memcmp(blk, alt, 16)) return -2;   // the two table-driven formulations must agree
     o_scatter(blk, data, n, 0, b);
   }
   return 0;

@@ -603,4 +603,152 @@ GCOW_HD void decode_block_1d_fast(float* f, const ZfpParams& p, const uint16_t* 
   inv_cast<4>(f, q, emax, shift);
 }
 
+// ------------------------------------------- fixed-rate 1-D block codec
+// Specialisation of the table-driven coder for fixed rate with BITS bits per
+// block (16, 32, 64 or 128). In fixed-rate mode minexp is -1074, so every block
+// keeps all 32 planes (kmin = 0) and only the bit budget ends a block. The
+// exponent arithmetic is done on the float's bit pattern, and eight planes of
+// the four coefficients are transposed at once with byte permutes, one bit
+// reversal and four delta swaps.
+GCOW_HD uint32_t byte_perm(uint32_t x, uint32_t y, uint32_t sel) {
+#if defined(__CUDA_ARCH__)
+  return __byte_perm(x, y, sel);
+#else
+  uint64_t v = ((uint64_t)y << 32) | x;
+  uint32_t r = 0;
+  for (int i = 0; i < 4; i++) r |= (uint32_t)((v >> (8 * ((sel >> (4 * i)) & 7))) & 0xff) << (8 * i);
+  return r;
+#endif
+}
+GCOW_HD uint32_t delta_swap(uint32_t x, uint32_t mask, int d) {
+  uint32_t t = ((x >> d) ^ x) & mask;
+  return x ^ t ^ (t << d);
+}
+// Planes k-1 .. k-8 of u[0..3] as eight nibbles in stream order (see plane_group).
+GCOW_HD uint32_t plane_group8(const uint32_t* u, uint32_t k) {
+  const uint32_t s = 32 - k;
+  // top bytes, value 3 in the low byte
+  uint32_t t0 = byte_perm(u[3] << s, u[2] << s, 0x0073);
+  uint32_t t1 = byte_perm(u[1] << s, u[0] << s, 0x0073);
+  uint32_t r = brev32(byte_perm(t0, t1, 0x5410));   // bit 8i+j = plane k-1-j of value i
+  r = delta_swap(r, 0x0000f0f0u, 12);               // 4x8 -> 8x4 bit-matrix transpose
+  r = delta_swap(r, 0x00cc00ccu, 6);
+  r = delta_swap(r, 0x0a0a0a0au, 3);
+  r = delta_swap(r, 0x22222222u, 1);
+  return r;
+}
+GCOW_HD void deposit_group8(uint32_t* u, uint32_t T, uint32_t k) {
+  const uint32_t s = 32 - k;
+  T = delta_swap(T, 0x22222222u, 1);
+  T = delta_swap(T, 0x0a0a0a0au, 3);
+  T = delta_swap(T, 0x00cc00ccu, 6);
+  T = delta_swap(T, 0x0000f0f0u, 12);
+  const uint32_t pk = brev32(T);                    // byte 3-i = top byte of value i
+  u[0] |= (pk & 0xff000000u) >> s;
+  u[1] |= ((pk << 8) & 0xff000000u) >> s;
+  u[2] |= ((pk << 16) & 0xff000000u) >> s;
+  u[3] |= (pk << 24) >> s;
+}
+
+template <int BITS>
+GCOW_HD void encode_block_1d_rate(const float* f, const uint16_t* etab, uint32_t (&w)[(BITS + 31) / 32]) {
+  constexpr int NW = (BITS + 31) / 32;
+#pragma unroll
+  for (int i = 0; i < NW; i++) w[i] = 0;
+  float m = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float a = f[i] < 0 ? -f[i] : f[i];
+    if (m < a) m = a;
+  }
+  const uint32_t mb = f32_bits(m);
+  if (mb == 0) return;                           // all zero: a single 0 bit
+  uint32_t ex = mb >> 23;                        // emax = ex - 126 (subnormals: ex = 0 -> -126)
+  if (ex > 254) ex = 254;
+  w[0] = 2u * ex + 3u;                           // flag bit + biased exponent (emax + 127 = ex + 1)
+  const float scale = bits_f32(ex >= 29 ? (283u - ex) << 23 : 0x7f800000u);   // 2^(30 - emax)
+  int32_t q[4];
+  uint32_t u[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) q[i] = trunc_to_i32(scale * f[i]);
+  fwd_lift(q[0], q[1], q[2], q[3]);
+#pragma unroll
+  for (int i = 0; i < 4; i++) u[i] = int2nb(q[i]);
+  const uint32_t mm = u[0] | u[1] | u[2] | u[3];
+  const uint32_t z = mm ? clz32(mm) : 32u;
+  uint32_t pos = kHeaderBits + z, k = 32 - z, n = 0;
+  while (pos < (uint32_t)BITS && k > 0) {
+    const uint32_t T = plane_group8(u, k);
+    const uint32_t cnt = k < 8 ? k : 8;
+    uint32_t j = 0;
+    while (n < 4 && j < cnt && pos < (uint32_t)BITS) {
+      const uint32_t e = etab[n * 16 + ((T >> (4 * j)) & 15u)];
+      if (NW == 1) w[0] |= (e & 0x7fu) << pos; else reg_put<NW>(w, pos, e & 0x7fu);
+      pos += (e >> 7) & 7u;
+      n = e >> 10;
+      j++;
+    }
+    if (j < cnt && pos < (uint32_t)BITS) {       // all four significant: the rest is verbatim
+      if (NW == 1) w[0] |= (T >> (4 * j)) << pos; else reg_put<NW>(w, pos, T >> (4 * j));
+      pos += 4 * (cnt - j);
+    }
+    k -= cnt;
+  }
+  if (BITS < 32 * NW) w[NW - 1] &= low_mask32(BITS - 32 * (NW - 1));
+}
+
+template <int BITS>
+GCOW_HD void decode_block_1d_rate(float* f, const uint16_t* dtab, const uint32_t (&w)[(BITS + 31) / 32],
+                                  int shift = 0) {
+  constexpr int NW = (BITS + 31) / 32;
+  if (!(w[0] & 1u)) {
+    f[0] = f[1] = f[2] = f[3] = 0;
+    return;
+  }
+  const int emax = (int)((w[0] >> 1) & 0xffu) - kEBias;
+  uint32_t u[4] = {0, 0, 0, 0};
+  uint32_t pos = kHeaderBits, n = 0, k = 32;
+  constexpr uint32_t end = BITS;
+  {
+    const uint32_t avail = end - pos;
+    const uint32_t S = (NW == 1 ? (w[0] >> pos) : reg_peek<NW>(w, pos)) & low_mask32(avail);
+    uint32_t z = S ? (uint32_t)ctz32(S) : 32u;
+    if (z > avail) z = avail;
+    pos += z;
+    k -= z;
+  }
+  while (pos < end && k > 0) {
+    const uint32_t cnt = k < 8 ? k : 8;
+    uint32_t T = 0, j = 0;
+    while (n < 4 && j < cnt && end - pos >= 7) {
+      const uint32_t pk = NW == 1 ? (w[0] >> pos) : reg_peek<NW>(w, pos);
+      const uint32_t e = dtab[n * 128 + (pk & 127u)];
+      T |= (e & 15u) << (4 * j);
+      pos += (e >> 4) & 7u;
+      n = e >> 7;
+      j++;
+    }
+    if (n == 4 && j < cnt && pos < end) {
+      const uint32_t nb = 4 * (cnt - j), avail = end - pos;
+      const uint32_t take = nb < avail ? nb : avail;
+      const uint32_t pk = NW == 1 ? (w[0] >> pos) : reg_peek<NW>(w, pos);
+      T |= (pk & low_mask32(take)) << (4 * j);
+      pos += take;
+      j = cnt;
+    }
+    if (T) deposit_group8(u, T, k);
+    if (j < cnt) {
+      RegSrc<NW> src{w, pos};
+      decode_planes_from<4>(u, end - pos, 0, k - j, n, src);
+      break;
+    }
+    k -= cnt;
+  }
+  int32_t q[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) q[i] = nb2int(u[i]);
+  inv_lift(q[0], q[1], q[2], q[3]);
+  inv_cast<4>(f, q, emax, shift);
+}
+
 }  // namespace gcow

@@ -196,8 +196,6 @@ allreduce_fused_kernel(const ArArgs a) {
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
 
-  ZfpParams p = default_params();
-  p.minbits = p.maxbits = BITS;
   const int P = a.world, r = a.rank, cta = blockIdx.x, tid = threadIdx.x;
   const ArLayout& L = a.L;
   const uint64_t SB = L.shard_blocks, NB = L.blocks;
@@ -216,7 +214,7 @@ allreduce_fused_kernel(const ArArgs a) {
         float f[4];
         load_block(f, a.in, a.n, gb, in_al);
         uint32_t w[NW];
-        encode_block_1d_fast<NW>(f, p, etab, w);
+        encode_block_1d_rate<BITS>(f, etab, w);
         for (int step = 0; step < P; step++) {
           int j = (r + 1 + step) % P;
           C::st(a.arena[j] + a.region_off + (uint64_t)r * L.slot_bytes, gb, w);
@@ -245,7 +243,7 @@ allreduce_fused_kernel(const ArArgs a) {
           uint32_t w[NW];
           C::ld(local + a.region_off + (uint64_t)s * L.slot_bytes, gb, w);
           float d[4];
-          decode_block_1d_fast<NW>(d, p, dtab, w, 0);
+          decode_block_1d_rate<BITS>(d, dtab, w, 0);
           if (s == 0) { acc[0] = d[0]; acc[1] = d[1]; acc[2] = d[2]; acc[3] = d[3]; }
           else { acc[0] += d[0]; acc[1] += d[1]; acc[2] += d[2]; acc[3] += d[3]; }
         }
@@ -270,7 +268,7 @@ allreduce_fused_kernel(const ArArgs a) {
       float f[4];
       load_block(f, a.in, a.n, gb, in_al);
       uint32_t w[NW];
-      encode_block_1d_fast<NW>(f, p, etab, w);
+      encode_block_1d_rate<BITS>(f, etab, w);
       C::st(dst, b, w);
     }
     __syncthreads();
@@ -303,11 +301,11 @@ allreduce_fused_kernel(const ArArgs a) {
           uint32_t c[NW];
           C::ld(local + a.region_off + (uint64_t)s * L.slot_bytes, b, c);
           float d[4];
-          decode_block_1d_fast<NW>(d, p, dtab, c, 0);
+          decode_block_1d_rate<BITS>(d, dtab, c, 0);
           if (s == 0) { acc[0] = d[0]; acc[1] = d[1]; acc[2] = d[2]; acc[3] = d[3]; }
           else { acc[0] += d[0]; acc[1] += d[1]; acc[2] += d[2]; acc[3] += d[3]; }
         }
-        encode_block_1d_fast<NW>(acc, p, etab, w);
+        encode_block_1d_rate<BITS>(acc, etab, w);
       }
       if (a.variant == kTwoShotNvls) {
         if (BITS == 16) {
@@ -356,7 +354,7 @@ allreduce_fused_kernel(const ArArgs a) {
       uint32_t w[NW];
       C::ld(src, b, w);
       float d[4];
-      decode_block_1d_fast<NW>(d, p, dtab, w, a.shift);
+      decode_block_1d_rate<BITS>(d, dtab, w, a.shift);
       if (a.postscale != 1.0f) {
 #pragma unroll
         for (int i = 0; i < 4; i++) d[i] *= a.postscale;

@@ -79,15 +79,14 @@ void store_block(const float* f, float* out, uint64_t n, uint64_t gb) {
 }
 
 // status: [0] code, [1] phase, [2] peer, [3] cta, [4] expected, [5] seen
-template <int NW>
+template <int BITS>
 void run_rank(Model& m, int r, const float* in, float* out, uint32_t epoch, int timeout_ms,
               const Fault& ft, uint32_t* status) {
+  constexpr int NW = (BITS + 31) / 32;
   const int P = m.P, G = m.G, parity = (int)(epoch & 1), bytes = m.bits / 8;
   const ArLayout& L = m.L;
   const uint64_t SB = L.shard_blocks, NB = L.blocks;
   const uint64_t roff = region_offset(parity, m.region_cap);
-  ZfpParams p = default_params();
-  p.minbits = p.maxbits = (uint32_t)m.bits;
   auto fail = [&](int phase, int peer, int cta, uint32_t seen) {
     if (status[0] == 0) { status[0] = kArTimeout; status[1] = phase; status[2] = peer; status[3] = cta; status[4] = epoch; status[5] = seen; }
   };
@@ -107,7 +106,7 @@ void run_rank(Model& m, int r, const float* in, float* out, uint32_t epoch, int 
           if (gb >= NB) break;
           float f[4]; uint32_t w[NW];
           load_block(f, in, m.n, gb);
-          encode_block_1d_fast<NW>(f, p, m.etab.data(), w);
+          encode_block_1d_rate<BITS>(f, m.etab.data(), w);
           for (int j = 0; j < P; j++) put_code<NW>(m.arena[j].data() + roff + (uint64_t)r * L.slot_bytes, gb, w, bytes);
         }
       for (int j = 0; j < P; j++) signal(j, 0, cta);
@@ -119,7 +118,7 @@ void run_rank(Model& m, int r, const float* in, float* out, uint32_t epoch, int 
           if (gb >= NB) break;
           float f[4]; uint32_t w[NW];
           load_block(f, in, m.n, gb);
-          encode_block_1d_fast<NW>(f, p, m.etab.data(), w);
+          encode_block_1d_rate<BITS>(f, m.etab.data(), w);
           put_code<NW>(m.arena[j].data() + roff + (uint64_t)r * L.slot_bytes, b, w, bytes);
         }
         signal(j, 0, cta);
@@ -144,7 +143,7 @@ void run_rank(Model& m, int r, const float* in, float* out, uint32_t epoch, int 
           for (int s = 0; s < P; s++) {
             uint32_t w[NW]; float d[4];
             get_code<NW>(local + roff + (uint64_t)s * L.slot_bytes, gb, w, bytes);
-            decode_block_1d_fast<NW>(d, p, m.dtab.data(), w, 0);
+            decode_block_1d_rate<BITS>(d, m.dtab.data(), w, 0);
             for (int i = 0; i < 4; i++) acc[i] = s == 0 ? d[i] : acc[i] + d[i];
           }
           for (int i = 0; i < 4; i++) acc[i] *= inv;
@@ -159,11 +158,11 @@ void run_rank(Model& m, int r, const float* in, float* out, uint32_t epoch, int 
       for (int s = 0; s < P; s++) {
         uint32_t w[NW]; float d[4];
         get_code<NW>(local + roff + (uint64_t)s * L.slot_bytes, b, w, bytes);
-        decode_block_1d_fast<NW>(d, p, m.dtab.data(), w, 0);
+        decode_block_1d_rate<BITS>(d, m.dtab.data(), w, 0);
         for (int i = 0; i < 4; i++) acc[i] = s == 0 ? d[i] : acc[i] + d[i];
       }
       uint32_t w[NW];
-      encode_block_1d_fast<NW>(acc, p, m.etab.data(), w);
+      encode_block_1d_rate<BITS>(acc, m.etab.data(), w);
       for (int j = 0; j < P; j++)
         put_code<NW>(m.arena[j].data() + roff + L.recv_bytes + (uint64_t)r * shard_bytes, b, w, bytes);
     }
@@ -184,7 +183,7 @@ void run_rank(Model& m, int r, const float* in, float* out, uint32_t epoch, int 
         if (gb >= NB) break;
         uint32_t w[NW]; float d[4];
         get_code<NW>(src, b, w, bytes);
-        decode_block_1d_fast<NW>(d, p, m.dtab.data(), w, m.shift);
+        decode_block_1d_rate<BITS>(d, m.dtab.data(), w, m.shift);
         store_block(d, out, m.n, gb);
       }
     }
@@ -230,10 +229,10 @@ int gcow_protocol_model(const float* xs, float* outs, int P, uint64_t n, int G, 
         float* out = outs + ((uint64_t)c * P + r) * n;
         uint32_t epoch = first_epoch + (uint32_t)c;
         switch (bits) {
-          case 16: run_rank<1>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
-          case 32: run_rank<1>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
-          case 64: run_rank<2>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
-          default: run_rank<4>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+          case 16: run_rank<16>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+          case 32: run_rank<32>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+          case 64: run_rank<64>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+          default: run_rank<128>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
         }
       });
     }

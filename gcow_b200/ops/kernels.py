@@ -79,42 +79,64 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
 
 
 def _gemm_ok(x2d: torch.Tensor, w: torch.Tensor) -> bool:
-    return (x2d.is_cuda and x2d.shape[1] % 8 == 0 and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
-            and x2d.shape[0] >= 64)
+    return x2d.is_cuda and x2d.shape[1] % 8 == 0 and w.shape[1] % 8 == 0 and x2d.shape[0] >= 64
+
+
+def _pad_rows(t: torch.Tensor, rows: int) -> torch.Tensor:
+    if t.shape[0] == rows:
+        return t
+    out = torch.zeros((rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+    out[:t.shape[0]] = t
+    return out
 
 
 class _LinearFn(torch.autograd.Function):
-    """y = x W^T + b with all three GEMMs (forward, dgrad, wgrad) on the tcgen05 kernel."""
+    """y = x W^T + b with all three GEMMs (forward, dgrad, wgrad) on the tcgen05 kernel.
+    An output width that is not a multiple of 8 (e.g. a 30522-word vocabulary) is
+    padded internally: the result is a [.., N] view of a [M, N8] buffer whose pad
+    columns are zero-weighted."""
 
     @staticmethod
     def forward(ctx, x, w, b):
+        N = w.shape[0]
+        N8 = (N + 7) // 8 * 8
         xb = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
-        wb = w.to(torch.bfloat16).contiguous()
-        bias = b.float().contiguous() if b is not None else None
+        wb = _pad_rows(w.to(torch.bfloat16).contiguous(), N8)
+        bias = _pad_rows(b.float().contiguous(), N8) if b is not None else None
         y = gemm_bf16(xb, wb, bias=bias)
         ctx.save_for_backward(xb, wb)
-        ctx.has_bias = b is not None
-        ctx.x_shape = x.shape
-        ctx.w_dtype = w.dtype
-        return y.view(*x.shape[:-1], w.shape[0])
+        ctx.meta = (x.shape, w.dtype, b is not None, N, N8)
+        return y[:, :N].view(*x.shape[:-1], N) if N == N8 else y[:, :N].unflatten(0, x.shape[:-1])
 
     @staticmethod
     def backward(ctx, gy):
         xb, wb = ctx.saved_tensors
-        g = gy.reshape(-1, gy.shape[-1]).to(torch.bfloat16).contiguous()
+        x_shape, w_dtype, has_bias, N, N8 = ctx.meta
+        M = xb.shape[0]
+        g = gy.reshape(M, N) if gy.is_contiguous() or N == N8 else gy.flatten(0, -2)
+        if (g.dtype == torch.bfloat16 and g.stride(1) == 1 and g.stride(0) == N8 and g.storage_offset() == 0
+                and g.untyped_storage().nbytes() >= M * N8 * 2):
+            g = g.as_strided((M, N8), (N8, 1))          # the padded buffer itself (pad columns are zero)
+        else:
+            g = g.to(torch.bfloat16)
+            if N != N8:
+                gp = torch.zeros((M, N8), dtype=torch.bfloat16, device=g.device)
+                gp[:, :N] = g
+                g = gp
+            else:
+                g = g.contiguous()
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
             # dx[M,K] = g[M,N] @ W[N,K]  ->  A = g, B = W^T stored [K,N]
-            gx = gemm_bf16(g, wb.t().contiguous()).view(ctx.x_shape)
+            gx = gemm_bf16(g, wb.t().contiguous()).view(x_shape)
         if ctx.needs_input_grad[1]:
             # dW[N,K] = g^T[N,M] @ x[M,K]  ->  A = g^T stored [N,M], B = x^T stored [K,M]
-            M = g.shape[0]
             if M % 8 == 0:
-                gw = gemm_bf16(g.t().contiguous(), xb.t().contiguous(), out_dtype=torch.float32).to(ctx.w_dtype)
+                gw = gemm_bf16(g.t().contiguous(), xb.t().contiguous(), out_dtype=torch.float32)[:N].to(w_dtype)
             else:
-                gw = (g.float().t() @ xb.float()).to(ctx.w_dtype)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = g.float().sum(0)
+                gw = (g.float().t() @ xb.float())[:N].to(w_dtype)
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(g)[:N]
         return gx, gw, gb
 
 
@@ -129,17 +151,207 @@ def linear(x, w, b):
     return _LinearFn.apply(x, w, b)
 
 
+def _stream(dev):
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _chk(err: int, what: str) -> None:
+    if err:
+        raise RuntimeError(f"{what} refused the call: {err}")
+
+
+def colsum(g: torch.Tensor) -> torch.Tensor:
+    """fp32 column sums of a bf16 [rows, cols] matrix (bias gradient)."""
+    global _launches
+    rows, cols = g.shape
+    lib = _native.cuda()
+    if cols % 2 or g.stride(1) != 1 or g.stride(0) % 2:
+        return g.float().sum(0)
+    parts = lib.gcow_colsum_parts(rows)
+    part = torch.empty(parts * cols, dtype=torch.float32, device=g.device)
+    out = torch.empty(cols, dtype=torch.float32, device=g.device)
+    _chk(lib.gcow_colsum(g.data_ptr(), part.data_ptr(), out.data_ptr(), rows, cols, g.stride(0), _stream(g.device)),
+         "gcow_colsum")
+    _launches += 2
+    return out
+
+
+# ------------------------------------------------------------------ 1x1 conv
+class _Conv1x1Fn(torch.autograd.Function):
+    """1x1 stride-1 convolution on channels-last activations as a GEMM:
+    [N*H*W, Cin] x [Cout, Cin]^T."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        N, C, H, W = x.shape
+        xm = x.permute(0, 2, 3, 1).reshape(-1, C)          # a view for channels-last input
+        if xm.dtype != torch.bfloat16 or not xm.is_contiguous():
+            xm = xm.to(torch.bfloat16).contiguous()
+        wb = w.reshape(w.shape[0], C).to(torch.bfloat16).contiguous()
+        y = gemm_bf16(xm, wb, bias=b.float().contiguous() if b is not None else None)
+        ctx.save_for_backward(xm, wb)
+        ctx.meta = (N, C, H, W, w.shape, w.dtype, b is not None)
+        return y.view(N, H, W, w.shape[0]).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, gy):
+        xm, wb = ctx.saved_tensors
+        N, C, H, W, wshape, wdtype, has_bias = ctx.meta
+        g = gy.permute(0, 2, 3, 1).reshape(-1, wshape[0])
+        if g.dtype != torch.bfloat16 or not g.is_contiguous():
+            g = g.to(torch.bfloat16).contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = gemm_bf16(g, wb.t().contiguous()).view(N, H, W, C).permute(0, 3, 1, 2)
+        if ctx.needs_input_grad[1]:
+            gw = gemm_bf16(g.t().contiguous(), xm.t().contiguous(), out_dtype=torch.float32)
+            gw = gw.view(wshape).to(wdtype).contiguous(memory_format=torch.channels_last)
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(g)
+        return gx, gw, gb
+
+
 def conv1x1_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return False
+    if not (x.is_cuda and x.dim() == 4 and _have("gcow_gemm_bf16")):
+        return False
+    cin, cout = x.shape[1], w.shape[0]
+    rows = x.shape[0] * x.shape[2] * x.shape[3]
+    return cin % 8 == 0 and cout % 8 == 0 and rows % 8 == 0 and rows >= 128 and \
+        x.is_contiguous(memory_format=torch.channels_last)
 
 
-def conv1x1(x, w, b):  # pragma: no cover
-    raise NotImplementedError
+def conv1x1(x, w, b):
+    return _Conv1x1Fn.apply(x, w, b)
+
+
+# ----------------------------------------------------------------- LayerNorm
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        global _launches
+        H = x.shape[-1]
+        xb = x.reshape(-1, H).to(torch.bfloat16).contiguous()
+        rows = xb.shape[0]
+        y = torch.empty_like(xb)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        g32, b32 = gamma.float().contiguous(), beta.float().contiguous()
+        _chk(_native.cuda().gcow_layernorm_fwd(xb.data_ptr(), g32.data_ptr(), b32.data_ptr(), y.data_ptr(),
+                                               mean.data_ptr(), rstd.data_ptr(), rows, H, eps, _stream(x.device)),
+             "gcow_layernorm_fwd")
+        _launches += 1
+        ctx.save_for_backward(xb, g32, mean, rstd)
+        ctx.shape, ctx.pdtype = x.shape, gamma.dtype
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        xb, g32, mean, rstd = ctx.saved_tensors
+        rows, H = xb.shape
+        g = gy.reshape(rows, H).to(torch.bfloat16).contiguous()
+        lib = _native.cuda()
+        dx = torch.empty_like(xb)
+        parts = lib.gcow_layernorm_bwd_parts(rows)
+        part = torch.empty(parts * 2 * H, dtype=torch.float32, device=xb.device)
+        dgb = torch.empty(2 * H, dtype=torch.float32, device=xb.device)
+        _chk(lib.gcow_layernorm_bwd(g.data_ptr(), xb.data_ptr(), g32.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                    dx.data_ptr(), part.data_ptr(), dgb.data_ptr(), rows, H, _stream(xb.device)),
+             "gcow_layernorm_bwd")
+        _launches += 2
+        return dx.view(ctx.shape), dgb[:H].to(ctx.pdtype), dgb[H:].to(ctx.pdtype), None
 
 
 def layernorm_usable(x: torch.Tensor, mod) -> bool:
-    return False
+    H = x.shape[-1]
+    return x.is_cuda and _have("gcow_layernorm_fwd") and H % 8 == 0 and H <= 4096 and \
+        mod.elementwise_affine and mod.bias is not None and len(mod.normalized_shape) == 1
 
 
-def layernorm(x, w, b, eps):  # pragma: no cover
-    raise NotImplementedError
+def layernorm(x, w, b, eps):
+    return _LayerNormFn.apply(x, w, b, eps)
+
+
+# ---------------------------------------------------------------------- GELU
+class _GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        global _launches
+        xb = x.to(torch.bfloat16).contiguous()
+        y = torch.empty_like(xb)
+        _chk(_native.cuda().gcow_gelu_fwd(xb.data_ptr(), y.data_ptr(), xb.numel(), _stream(x.device)), "gcow_gelu_fwd")
+        _launches += 1
+        ctx.save_for_backward(xb)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        (xb,) = ctx.saved_tensors
+        g = gy.to(torch.bfloat16).contiguous()
+        dx = torch.empty_like(xb)
+        _chk(_native.cuda().gcow_gelu_bwd(g.data_ptr(), xb.data_ptr(), dx.data_ptr(), xb.numel(), _stream(xb.device)),
+             "gcow_gelu_bwd")
+        _launches += 1
+        return dx
+
+
+def gelu_usable(x: torch.Tensor) -> bool:
+    return x.is_cuda and _have("gcow_gelu_fwd") and x.numel() % 8 == 0
+
+
+def gelu(x):
+    return _GeluFn.apply(x)
+
+
+# ------------------------------------------------------ softmax cross-entropy
+class _XentFn(torch.autograd.Function):
+    """Mean cross-entropy over non-ignored rows. The forward kernel leaves the
+    gradient (softmax - onehot) / count in the logits buffer, which therefore must
+    not be used again by the caller."""
+
+    @staticmethod
+    def forward(ctx, logits, target, ignore_index, valid_cols):
+        global _launches
+        rows, ld = logits.shape[0], logits.stride(0)
+        count = (target != ignore_index).sum().float().reshape(1)
+        row_loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        _chk(_native.cuda().gcow_softmax_xent(logits.data_ptr(), target.data_ptr(), row_loss.data_ptr(),
+                                              count.data_ptr(), rows, valid_cols, ld, ignore_index,
+                                              _stream(logits.device)), "gcow_softmax_xent")
+        _launches += 1
+        ctx.mark_dirty(logits)
+        ctx.save_for_backward(logits)
+        return row_loss.sum()
+
+    @staticmethod
+    def backward(ctx, g):
+        (grad,) = ctx.saved_tensors
+        return grad * g.to(grad.dtype), None, None, None
+
+
+def xent_usable(logits: torch.Tensor) -> bool:
+    return (logits.is_cuda and _have("gcow_softmax_xent") and logits.dtype == torch.bfloat16 and logits.dim() == 2
+            and logits.stride(1) == 1 and logits.stride(0) % 8 == 0 and logits.requires_grad
+            and not logits.is_leaf)
+
+
+def softmax_xent(logits, target, ignore_index=-100, valid_cols=None):
+    return _XentFn.apply(logits, target, ignore_index, valid_cols or logits.shape[1])
+
+
+# ------------------------------------------------------- image normalisation
+def u8_to_bf16_norm(x_u8: torch.Tensor, mean255, std255) -> torch.Tensor:
+    """uint8 NHWC [N,H,W,3] -> normalised bf16 tensor of logical shape [N,3,H,W] in
+    channels-last memory."""
+    global _launches
+    import ctypes as C_
+    N, H, W, C = x_u8.shape
+    assert C == 3 and x_u8.is_contiguous()
+    y = torch.empty((N, H, W, 3), dtype=torch.bfloat16, device=x_u8.device)
+    m = (C_.c_float * 3)(*mean255)
+    s = (C_.c_float * 3)(*std255)
+    _chk(_native.cuda().gcow_u8_to_bf16_norm(x_u8.data_ptr(), y.data_ptr(), N * H * W, 3, m, s, _stream(x_u8.device)),
+         "gcow_u8_to_bf16_norm")
+    _launches += 1
+    return y.permute(0, 3, 1, 2)

@@ -51,6 +51,8 @@ class Embedding(nn.Embedding):
 
 
 def gelu(x: torch.Tensor) -> torch.Tensor:
+    if backend.get_backend() == "own" and K.gelu_usable(x):
+        return K.gelu(x)
     return F.gelu(x)
 
 
@@ -63,4 +65,8 @@ def attention(qkv: torch.Tensor) -> torch.Tensor:
 
 
 def cross_entropy(logits: torch.Tensor, target: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """Mean cross-entropy. With the own backend a non-leaf bf16 logits buffer is
+    consumed (overwritten with its gradient) by the fused kernel."""
+    if backend.get_backend() == "own" and K.xent_usable(logits):
+        return K.softmax_xent(logits, target, ignore_index)
     return F.cross_entropy(logits.float(), target, ignore_index=ignore_index)

@@ -182,6 +182,9 @@ class Trainer:
 
     def preprocess(self, x_u8: torch.Tensor) -> torch.Tensor:
         """uint8 NHWC -> normalised bf16, logical NCHW in channels-last memory."""
+        if ops_backend.get_backend() == "own":
+            from .ops import kernels
+            return kernels.u8_to_bf16_norm(x_u8, [m * 255.0 for m in IMAGENET_MEAN], [s * 255.0 for s in IMAGENET_STD])
         x = x_u8.permute(0, 3, 1, 2)
         return ((x.to(torch.float32) - self.mean) / self.std).to(torch.bfloat16).contiguous(
             memory_format=torch.channels_last)
