@@ -163,6 +163,13 @@ class CompressedAllReduce:
             return "twoshot"
         return v
 
+    def ctas_for(self, numel: int) -> int:
+        """Grid size for a message: at least 512 blocks per CTA so that small
+        messages do not pay for launching and synchronising the whole grid.
+        Depends only on (numel, world, configuration): identical on every rank."""
+        shard_blocks = -(-((numel + 3) // 4) // self.world)
+        return max(1, min(self.ctas, -(-shard_blocks // 512)))
+
     def enable_tracing(self, on: bool = True) -> None:
         """Per-CTA globaltimer stamps at the four phase boundaries of the last call."""
         self.stamps = torch.zeros(self.ctas * 4, dtype=torch.int64, device=self.device) if on else None
@@ -196,7 +203,7 @@ class CompressedAllReduce:
         if v == 1 and shift:          # one-shot has no final decode to fold the shift into
             post, shift = post * 2.0 ** (-shift), 0
         err = self.lib.gcow_ar_launch(
-            x.data_ptr(), out.data_ptr(), n, self.rank, self.world, v, self.bits, self.ctas, shift,
+            x.data_ptr(), out.data_ptr(), n, self.rank, self.world, v, self.bits, self.ctas_for(n), shift,
             C.c_float(post), self._peer_array, C.c_void_p(self.arena.mc_ptr), self.region_cap, self.epoch,
             int(self.cfg.timeout_ms) * 1_000_000, self.status.data_ptr(), self.status[8:].data_ptr(),
             self.stamps.data_ptr() if self.stamps is not None else None, s.cuda_stream)

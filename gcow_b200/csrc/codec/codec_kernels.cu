@@ -20,11 +20,18 @@ namespace gcow {
 
 constexpr int kThreads = 256;
 
-__device__ __forceinline__ void build_enc_table(uint16_t* etab) {
-  for (int i = threadIdx.x; i < kEncTabSize; i += blockDim.x) etab[i] = make_enc_entry(i >> 4, i & 15);
+// Coder tables live in global memory (filled once per device by the host, see
+// gcow_codec_tables) and are copied into shared memory by every CTA.
+__device__ __align__(16) uint16_t g_enc_table[kEncTabSize];
+__device__ __align__(16) uint16_t g_dec_table[kDecBudgetTabSize];
+
+__device__ __forceinline__ void load_enc_table(uint16_t* etab, const uint16_t* __restrict__ src) {
+  for (int i = threadIdx.x; i < kEncTabSize / 2; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(etab)[i] = reinterpret_cast<const uint32_t*>(src)[i];
 }
-__device__ __forceinline__ void build_dec_table(uint16_t* dtab) {
-  for (int i = threadIdx.x; i < kDecTabSize; i += blockDim.x) dtab[i] = make_dec_entry(i >> 7, i & 127);
+__device__ __forceinline__ void load_dec_table(uint16_t* dtab, const uint16_t* __restrict__ src) {
+  for (int i = threadIdx.x; i < kDecBudgetTabSize / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(dtab)[i] = reinterpret_cast<const uint4*>(src)[i];
 }
 
 // Load block b of a 1-D array of n floats (tail block padded).
@@ -80,9 +87,10 @@ template <> struct CodeIO<128> {
 
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
-encode_1d_fixed_kernel(const float* __restrict__ in, uint64_t n, void* __restrict__ out, int aligned) {
-  __shared__ uint16_t etab[kEncTabSize];
-  build_enc_table(etab);
+encode_1d_fixed_kernel(const float* __restrict__ in, uint64_t n, void* __restrict__ out, int aligned,
+                       const uint16_t* __restrict__ tab) {
+  __shared__ __align__(16) uint16_t etab[kEncTabSize];
+  load_enc_table(etab, tab);
   __syncthreads();
   const uint64_t blocks = num_blocks_1d(n);
   for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
@@ -98,9 +106,9 @@ encode_1d_fixed_kernel(const float* __restrict__ in, uint64_t n, void* __restric
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
 decode_1d_fixed_kernel(const void* __restrict__ in, float* __restrict__ out, uint64_t n, int shift,
-                       int aligned) {
-  __shared__ uint16_t dtab[kDecTabSize];
-  build_dec_table(dtab);
+                       int aligned, const uint16_t* __restrict__ tab) {
+  __shared__ __align__(16) uint16_t dtab[kDecBudgetTabSize];
+  load_dec_table(dtab, tab);
   __syncthreads();
   const uint64_t blocks = num_blocks_1d(n);
   for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
@@ -415,7 +423,36 @@ inline ZfpParams load_params(const int32_t* p) {
 
 using namespace gcow;
 
+#include <mutex>
+
 extern "C" {
+
+// Device pointers of the coder tables on the current device; the tables are
+// built on the host and uploaded on the first call per device (a synchronous
+// copy, so make that first call outside any stream capture).
+int gcow_codec_tables(const void** etab, const void** dtab) {
+  static std::mutex mu;
+  static const void* e_addr[64] = {};
+  static const void* d_addr[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= 64) return err ? (int)err : -1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!e_addr[dev]) {
+    static uint16_t he[kEncTabSize], hd[kDecBudgetTabSize];
+    build_codec_tables(he, hd);
+    if ((err = cudaMemcpyToSymbol(g_enc_table, he, sizeof he)) != cudaSuccess) return (int)err;
+    if ((err = cudaMemcpyToSymbol(g_dec_table, hd, sizeof hd)) != cudaSuccess) return (int)err;
+    void *pe = nullptr, *pd = nullptr;
+    if ((err = cudaGetSymbolAddress(&pe, g_enc_table)) != cudaSuccess) return (int)err;
+    if ((err = cudaGetSymbolAddress(&pd, g_dec_table)) != cudaSuccess) return (int)err;
+    d_addr[dev] = pd;
+    e_addr[dev] = pe;
+  }
+  *etab = e_addr[dev];
+  *dtab = d_addr[dev];
+  return 0;
+}
 
 // Fixed-rate 1-D encode; maxbits in {16, 32, 64, 128}. `out` holds
 // blocks*maxbits/8 bytes (caller rounds the buffer up to 8 bytes).
@@ -425,11 +462,14 @@ int gcow_encode_1d_fixed(const float* in, uint64_t n, int maxbits, void* out, vo
   if (!blocks) return 0;
   int aligned = ((uintptr_t)in & 15) == 0;
   int g = grid_for(blocks);
+  const void *etp, *dtp;
+  if (int rc = gcow_codec_tables(&etp, &dtp)) return rc;
+  const uint16_t* et = (const uint16_t*)etp;
   switch (maxbits) {
-    case 16: encode_1d_fixed_kernel<16><<<g, kThreads, 0, s>>>(in, n, out, aligned); break;
-    case 32: encode_1d_fixed_kernel<32><<<g, kThreads, 0, s>>>(in, n, out, aligned); break;
-    case 64: encode_1d_fixed_kernel<64><<<g, kThreads, 0, s>>>(in, n, out, aligned); break;
-    case 128: encode_1d_fixed_kernel<128><<<g, kThreads, 0, s>>>(in, n, out, aligned); break;
+    case 16: encode_1d_fixed_kernel<16><<<g, kThreads, 0, s>>>(in, n, out, aligned, et); break;
+    case 32: encode_1d_fixed_kernel<32><<<g, kThreads, 0, s>>>(in, n, out, aligned, et); break;
+    case 64: encode_1d_fixed_kernel<64><<<g, kThreads, 0, s>>>(in, n, out, aligned, et); break;
+    case 128: encode_1d_fixed_kernel<128><<<g, kThreads, 0, s>>>(in, n, out, aligned, et); break;
     default: return -1;
   }
   return (int)cudaGetLastError();
@@ -441,11 +481,14 @@ int gcow_decode_1d_fixed(const void* in, float* out, uint64_t n, int maxbits, in
   if (!blocks) return 0;
   int aligned = ((uintptr_t)out & 15) == 0;
   int g = grid_for(blocks);
+  const void *etp, *dtp;
+  if (int rc = gcow_codec_tables(&etp, &dtp)) return rc;
+  const uint16_t* dt = (const uint16_t*)dtp;
   switch (maxbits) {
-    case 16: decode_1d_fixed_kernel<16><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned); break;
-    case 32: decode_1d_fixed_kernel<32><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned); break;
-    case 64: decode_1d_fixed_kernel<64><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned); break;
-    case 128: decode_1d_fixed_kernel<128><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned); break;
+    case 16: decode_1d_fixed_kernel<16><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt); break;
+    case 32: decode_1d_fixed_kernel<32><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt); break;
+    case 64: decode_1d_fixed_kernel<64><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt); break;
+    case 128: decode_1d_fixed_kernel<128><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt); break;
     default: return -1;
   }
   return (int)cudaGetLastError();

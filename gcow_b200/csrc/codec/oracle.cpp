@@ -456,16 +456,17 @@ int gcow_fast1d_compress(const float* data, uint64_t n, const int32_t* params, v
 }
 int gcow_fast1d_decompress(const void* in, float* data, uint64_t n, const int32_t* params, int shift) {
   ZfpParams p = load_params(params);
-  std::vector<uint16_t> dtab(gcow::kDecTabSize);
+  std::vector<uint16_t> dtab(gcow::kDecTabSize), btab(gcow::kDecBudgetTabSize), etab(gcow::kEncTabSize);
   for (uint32_t i = 0; i < (uint32_t)gcow::kDecTabSize; i++) dtab[i] = gcow::make_dec_entry(i / 128, i % 128);
+  gcow::build_codec_tables(etab.data(), btab.data());
   uint64_t blocks = gcow::num_blocks_1d(n);
   float blk[4], alt[4];
   for (uint64_t b = 0; b < blocks; b++) {
     switch (p.maxbits) {
-      case 16: { uint32_t w[1] = {((const uint16_t*)in)[b]}; gcow::decode_block_1d_rate<16>(blk, dtab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); break; }
-      case 32: { uint32_t w[1] = {((const uint32_t*)in)[b]}; gcow::decode_block_1d_rate<32>(blk, dtab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); break; }
-      case 64: { uint32_t w[2]; memcpy(w, (const uint32_t*)in + 2 * b, 8); gcow::decode_block_1d_rate<64>(blk, dtab.data(), w, shift); gcow::decode_block_1d_fast<2>(alt, p, dtab.data(), w, shift); break; }
-      case 128: { uint32_t w[4]; memcpy(w, (const uint32_t*)in + 4 * b, 16); gcow::decode_block_1d_rate<128>(blk, dtab.data(), w, shift); gcow::decode_block_1d_fast<4>(alt, p, dtab.data(), w, shift); break; }
+      case 16: { uint32_t w[1] = {((const uint16_t*)in)[b]}; gcow::decode_block_1d_rate<16>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); break; }
+      case 32: { uint32_t w[1] = {((const uint32_t*)in)[b]}; gcow::decode_block_1d_rate<32>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); break; }
+      case 64: { uint32_t w[2]; memcpy(w, (const uint32_t*)in + 2 * b, 8); gcow::decode_block_1d_rate<64>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<2>(alt, p, dtab.data(), w, shift); break; }
+      case 128: { uint32_t w[4]; memcpy(w, (const uint32_t*)in + 4 * b, 16); gcow::decode_block_1d_rate<128>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<4>(alt, p, dtab.data(), w, shift); break; }
       default: return -1;
     }
     if (memcmp(blk, alt, 16)) return -2;   // the two table-driven formulations must agree

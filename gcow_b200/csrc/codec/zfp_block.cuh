@@ -399,6 +399,33 @@ GCOW_HD uint16_t make_dec_entry(uint32_t n, uint32_t peek) {
   return (uint16_t)(x | (s.used << 4) | (n << 7));
 }
 
+// Decoder entry for a plane when only `a` bits of budget remain (a = 7 stands for
+// "7 or more"): index ((n * 8 + a) * 128 + next bits masked to a). When the
+// budget ends inside a unary run the pending one-bit lands where the run
+// stopped, exactly as in the serial decoder, so one table serves whole planes
+// and the ragged end of a block alike. Entry: plane | used << 4 | n' << 7.
+constexpr int kDecBudgetTabSize = 5 * 8 * 128;
+GCOW_HD uint16_t make_dec_budget_entry(uint32_t n, uint32_t a, uint32_t peek) {
+  TinySrc s{peek, 0};
+  uint32_t bits = a;
+  uint32_t m = n < bits ? n : bits;
+  bits -= m;
+  uint32_t x = (uint32_t)s.get(m);
+  for (; bits && n < 4; n++) {
+    bits--;
+    if (s.get(1)) {
+      for (; bits && n < 3; n++) {
+        bits--;
+        if (s.get(1)) break;
+      }
+      x += 1u << n;
+    } else {
+      break;
+    }
+  }
+  return (uint16_t)(x | ((a - bits) << 4) | (n << 7));
+}
+
 // OR the bits of v (up to 32) in at bit `pos` of a little-endian array of NW
 // 32-bit words; bits past the array fall off.
 template <int NW>
@@ -678,25 +705,26 @@ GCOW_HD void encode_block_1d_rate(const float* f, const uint16_t* etab, uint32_t
   const uint32_t z = mm ? clz32(mm) : 32u;
   uint32_t pos = kHeaderBits + z, k = 32 - z, n = 0;
   while (pos < (uint32_t)BITS && k > 0) {
-    const uint32_t T = plane_group8(u, k);
+    uint32_t T = plane_group8(u, k);
     const uint32_t cnt = k < 8 ? k : 8;
-    uint32_t j = 0;
-    while (n < 4 && j < cnt && pos < (uint32_t)BITS) {
-      const uint32_t e = etab[n * 16 + ((T >> (4 * j)) & 15u)];
+    // one table row per significance count, including n = 4 (four verbatim bits)
+    for (uint32_t j = 0; j < cnt && pos < (uint32_t)BITS; j++, T >>= 4) {
+      if (NW > 1 && n == 4) {                    // long blocks: append the rest of the group at once
+        reg_put<NW>(w, pos, T);
+        pos += 4 * (cnt - j);
+        break;
+      }
+      const uint32_t e = etab[n * 16 + (T & 15u)];
       if (NW == 1) w[0] |= (e & 0x7fu) << pos; else reg_put<NW>(w, pos, e & 0x7fu);
       pos += (e >> 7) & 7u;
       n = e >> 10;
-      j++;
-    }
-    if (j < cnt && pos < (uint32_t)BITS) {       // all four significant: the rest is verbatim
-      if (NW == 1) w[0] |= (T >> (4 * j)) << pos; else reg_put<NW>(w, pos, T >> (4 * j));
-      pos += 4 * (cnt - j);
     }
     k -= cnt;
   }
   if (BITS < 32 * NW) w[NW - 1] &= low_mask32(BITS - 32 * (NW - 1));
 }
 
+// `dtab` is the budget-aware table (kDecBudgetTabSize entries).
 template <int BITS>
 GCOW_HD void decode_block_1d_rate(float* f, const uint16_t* dtab, const uint32_t (&w)[(BITS + 31) / 32],
                                   int shift = 0) {
@@ -719,29 +747,24 @@ GCOW_HD void decode_block_1d_rate(float* f, const uint16_t* dtab, const uint32_t
   }
   while (pos < end && k > 0) {
     const uint32_t cnt = k < 8 ? k : 8;
-    uint32_t T = 0, j = 0;
-    while (n < 4 && j < cnt && end - pos >= 7) {
+    uint32_t T = 0;
+    for (uint32_t j = 0; j < cnt && pos < end; j++) {
+      const uint32_t avail = end - pos;
       const uint32_t pk = NW == 1 ? (w[0] >> pos) : reg_peek<NW>(w, pos);
-      const uint32_t e = dtab[n * 128 + (pk & 127u)];
+      if (NW > 1 && n == 4) {                    // verbatim planes of a long block in one go
+        const uint32_t nb = 4 * (cnt - j);
+        const uint32_t take = nb < avail ? nb : avail;
+        T |= (pk & low_mask32(take)) << (4 * j);
+        pos += take;
+        break;
+      }
+      const uint32_t a = avail < 7 ? avail : 7;
+      const uint32_t e = dtab[((n * 8 + a) << 7) + (pk & low_mask32(a))];
       T |= (e & 15u) << (4 * j);
       pos += (e >> 4) & 7u;
       n = e >> 7;
-      j++;
-    }
-    if (n == 4 && j < cnt && pos < end) {
-      const uint32_t nb = 4 * (cnt - j), avail = end - pos;
-      const uint32_t take = nb < avail ? nb : avail;
-      const uint32_t pk = NW == 1 ? (w[0] >> pos) : reg_peek<NW>(w, pos);
-      T |= (pk & low_mask32(take)) << (4 * j);
-      pos += take;
-      j = cnt;
     }
     if (T) deposit_group8(u, T, k);
-    if (j < cnt) {
-      RegSrc<NW> src{w, pos};
-      decode_planes_from<4>(u, end - pos, 0, k - j, n, src);
-      break;
-    }
     k -= cnt;
   }
   int32_t q[4];
@@ -749,6 +772,15 @@ GCOW_HD void decode_block_1d_rate(float* f, const uint16_t* dtab, const uint32_t
   for (int i = 0; i < 4; i++) q[i] = nb2int(u[i]);
   inv_lift(q[0], q[1], q[2], q[3]);
   inv_cast<4>(f, q, emax, shift);
+}
+
+// Host-side construction of both tables (the kernels copy them from global memory).
+inline void build_codec_tables(uint16_t* etab, uint16_t* dtab_budget) {
+  for (uint32_t i = 0; i < (uint32_t)kEncTabSize; i++) etab[i] = make_enc_entry(i >> 4, i & 15);
+  for (uint32_t i = 0; i < (uint32_t)kDecBudgetTabSize; i++) {
+    const uint32_t n = i >> 10, a = (i >> 7) & 7, pk = i & 127;
+    dtab_budget[i] = make_dec_budget_entry(n, a, pk & low_mask32(a));
+  }
 }
 
 }  // namespace gcow

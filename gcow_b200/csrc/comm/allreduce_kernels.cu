@@ -47,6 +47,8 @@ struct ArArgs {
   uint32_t* status;           // 8 words, see record_failure
   uint32_t* abort_flag;       // local device word
   unsigned long long* stamps; // optional [gridDim.x][4] globaltimer stamps, or nullptr
+  const uint16_t* enc_table;  // coder tables in global memory (see gcow_codec_tables)
+  const uint16_t* dec_table;
   ArLayout L;
 };
 
@@ -188,11 +190,13 @@ __global__ void __launch_bounds__(kArThreads)
 allreduce_fused_kernel(const ArArgs a) {
   using C = Code<BITS>;
   constexpr int NW = C::NW;
-  __shared__ uint16_t etab[kEncTabSize];
-  __shared__ uint16_t dtab[kDecTabSize];
+  __shared__ __align__(16) uint16_t etab[kEncTabSize];
+  __shared__ __align__(16) uint16_t dtab[kDecBudgetTabSize];
   __shared__ int s_ok;
-  for (int i = threadIdx.x; i < kEncTabSize; i += blockDim.x) etab[i] = make_enc_entry(i >> 4, i & 15);
-  for (int i = threadIdx.x; i < kDecTabSize; i += blockDim.x) dtab[i] = make_dec_entry(i >> 7, i & 127);
+  for (int i = threadIdx.x; i < kEncTabSize / 2; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(etab)[i] = reinterpret_cast<const uint32_t*>(a.enc_table)[i];
+  for (int i = threadIdx.x; i < kDecBudgetTabSize / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(dtab)[i] = reinterpret_cast<const uint4*>(a.dec_table)[i];
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
 
@@ -383,6 +387,8 @@ int max_coresident_ctas(int device) {
 
 using namespace gcow;
 
+extern "C" int gcow_codec_tables(const void** etab, const void** dtab);
+
 extern "C" {
 
 uint64_t gcow_ar_arena_bytes(uint64_t region_bytes) { return arena_bytes_for(region_bytes); }
@@ -431,6 +437,10 @@ int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world,
   a.status = status; a.abort_flag = abort_flag; a.stamps = stamps;
   a.L = ar_layout(n, world, ctas, bits, variant);
   if (a.L.region_bytes > region_cap) return -2;
+  const void *etp, *dtp;
+  if (int rc = gcow_codec_tables(&etp, &dtp)) return rc;
+  a.enc_table = (const uint16_t*)etp;
+  a.dec_table = (const uint16_t*)dtp;
   if (n == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   switch (bits) {

@@ -209,9 +209,8 @@ int gcow_protocol_model(const float* xs, float* outs, int P, uint64_t n, int G, 
   m.region_cap = m.L.region_bytes;
   m.arena.assign(P, std::vector<uint8_t>(arena_bytes_for(m.region_cap), 0));
   m.etab.resize(kEncTabSize);
-  m.dtab.resize(kDecTabSize);
-  for (int i = 0; i < kEncTabSize; i++) m.etab[i] = make_enc_entry(i / 16, i % 16);
-  for (int i = 0; i < kDecTabSize; i++) m.dtab[i] = make_dec_entry(i / 128, i % 128);
+  m.dtab.resize(kDecBudgetTabSize);
+  build_codec_tables(m.etab.data(), m.dtab.data());
   if (stale_epoch >= 0)
     for (int r = 0; r < P; r++)
       for (uint64_t o = 0; o < kFlagBytes; o += 4) *reinterpret_cast<uint32_t*>(m.arena[r].data() + o) = (uint32_t)stale_epoch;

@@ -320,13 +320,14 @@ class _XentFn(torch.autograd.Function):
                                               count.data_ptr(), rows, valid_cols, ld, ignore_index,
                                               _stream(logits.device)), "gcow_softmax_xent")
         _launches += 1
-        ctx.mark_dirty(logits)
-        ctx.save_for_backward(logits)
+        # the kernel has turned `logits` into its own gradient; keep that buffer
+        ctx.grad_buf = logits.detach()
         return row_loss.sum()
 
     @staticmethod
     def backward(ctx, g):
-        (grad,) = ctx.saved_tensors
+        grad = ctx.grad_buf
+        ctx.grad_buf = None
         return grad * g.to(grad.dtype), None, None, None
 
 
