@@ -11,9 +11,12 @@
 //   warps 2-5   epilogue: tcgen05.ld their 32-lane quarter of the accumulator,
 //               add bias / residual, optional GELU, convert and store - while the
 //               MMA warp already works on the other accumulator.
-// Both operands are K-major (row-major A[M,K], row-major B[N,K]), which is the
-// layout of activations and of nn.Linear / 1x1-convolution weights. No TMA
-// multicast is used anywhere. Every mbarrier wait is bounded: after a fixed
+// Each operand may be K-major (stored [rows][K], the layout of activations and
+// of nn.Linear / 1x1-convolution weights in the forward product) or MN-major
+// (stored [K][rows]); the backward products dX = dY*W and dW = dY^T*X read the
+// same tensors with the other major-ness, so no transposed copy is ever made.
+// An MN-major tile is fetched as 64-column boxes of 64 K-rows each (8 KB apart).
+// No TMA multicast is used anywhere. Every mbarrier wait is bounded: after a fixed
 // number of polls the CTA raises an error word, all roles leave their loops,
 // outstanding MMAs are drained (bounded), TMEM is freed and the kernel returns.
 //
@@ -121,10 +124,24 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return d;
 }
 
+// MN-major tile: boxes of [64 K-rows][64 elements = 128 bytes], 128-byte swizzle.
+// Groups of 8 K-rows are 1024 bytes apart (stride offset); the next 64 elements
+// along M/N start one box (8192 bytes) later (leading offset).
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+  d |= (uint64_t)(8192u >> 4) << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 __device__ __forceinline__ float gelu_f(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
 }
 
+template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const Params p) {
@@ -165,8 +182,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = 0; kb < kblocks; kb++) {
           if (!(ok = mbar_wait(sm, &sm->empty[s], phase ^ 1, p.error, 1))) break;
           mbar_expect_tx(&sm->full[s], A_BYTES + B_BYTES);
-          tma_load_2d(smem_u32(smA + s * A_BYTES), &tmap_a, smem_u32(&sm->full[s]), kb * BK, m0);
-          tma_load_2d(smem_u32(smB + s * B_BYTES), &tmap_b, smem_u32(&sm->full[s]), kb * BK, n0);
+          const uint32_t bar = smem_u32(&sm->full[s]);
+          if (!A_MN) {
+            tma_load_2d(smem_u32(smA + s * A_BYTES), &tmap_a, bar, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; i++)
+              tma_load_2d(smem_u32(smA + s * A_BYTES + i * 8192), &tmap_a, bar, m0 + 64 * i, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(smem_u32(smB + s * B_BYTES), &tmap_b, bar, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; i++)
+              tma_load_2d(smem_u32(smB + s * B_BYTES + i * 8192), &tmap_b, bar, n0 + 64 * i, kb * BK);
+          }
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
       }
@@ -179,7 +209,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N256 M128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)A_MN << 15) | ((uint32_t)B_MN << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint32_t s = 0, phase = 0, t = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
@@ -190,13 +221,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = 0; kb < kblocks; kb++) {
           if (!(ok = mbar_wait(sm, &sm->full[s], phase, p.error, 3))) break;
           tc_fence_after();
-          const uint64_t da = smem_desc_sw128(smem_u32(smA + s * A_BYTES));
-          const uint64_t db = smem_desc_sw128(smem_u32(smB + s * B_BYTES));
+          const uint32_t sa = smem_u32(smA + s * A_BYTES), sb = smem_u32(smB + s * B_BYTES);
+          const uint64_t da = A_MN ? smem_desc_mn_sw128(sa) : smem_desc_sw128(sa);
+          const uint64_t db = B_MN ? smem_desc_mn_sw128(sb) : smem_desc_sw128(sb);
+          // one K step of 16: 32 bytes along a K-major row, 16 rows (2048 bytes) of an MN-major tile
+          constexpr uint64_t ka = A_MN ? (2048 >> 4) : (32 >> 4), kbs = B_MN ? (2048 >> 4) : (32 >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; k++) {
-            // advance 16 elements = 32 bytes inside the swizzled 128-byte row
-            tc_mma(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
-          }
+          for (int k = 0; k < BK / UMMA_K; k++)
+            tc_mma(d_tmem, da + ka * k, db + kbs * k, idesc, (kb | k) != 0);
           tc_commit(&sm->empty[s]);
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
@@ -320,7 +352,7 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D bf16 row-major [rows, cols] with leading dimension ld (elements); box = 64 x box_rows.
+// 2-D bf16 row-major [rows, cols] with leading dimension ld (elements); box = 64 columns x box_rows.
 static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
@@ -344,29 +376,37 @@ using namespace gcow::gemm;
 
 extern "C" {
 
-// C[M,N] (+)= A[M,K] * B[N,K]^T  (+ bias[N]) (GELU) (+ residual[M,N]).
-// A, B bf16 row-major with leading dimensions lda, ldb (multiples of 8, 16-byte
-// aligned bases); C bf16 or fp32 (flags & 1) with ldc a multiple of 8 (bf16) or
+// C[M,N] (+)= op(A) * op(B)^T  (+ bias[N]) (GELU) (+ residual[M,N]).
+// a_mn == 0: A is stored [M][K] (lda = row length); a_mn == 1: A is stored [K][M].
+// b_mn == 0: B is stored [N][K];                    b_mn == 1: B is stored [K][N].
+// bf16 operands, leading dimensions multiples of 8, 16-byte aligned bases; C bf16 or fp32 (flags & 1) with ldc a multiple of 8 (bf16) or
 // 4 (fp32). `error` is a device word that stays 0 unless a wait gave up.
 // Returns 0, a negative argument error, or a CUDA error code.
 int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                    const float* bias, const void* residual, int flags, uint32_t* error, int max_ctas,
-                   void* stream) {
+                   int a_mn, int b_mn, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (K % 8 || lda % 8 || ldb % 8) return -1;
+  if (lda % 8 || ldb % 8) return -1;
+  if ((!a_mn || !b_mn) && K % 8) return -1;   // a K-major operand has K as its row length
   if ((flags & kOutF32) ? (ldc % 4) : (ldc % 8)) return -1;
   if ((uintptr_t)C & 15) return -1;
   if ((flags & kBias) && !bias) return -1;
   if ((flags & kResidual) && (!residual || ((uintptr_t)residual & 15))) return -1;
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
+  // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
+  int rc = a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
+                : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
   if (rc) return rc;
-  rc = make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
+  rc = b_mn ? make_map(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64)
+            : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
   if (rc) return rc;
   static std::once_flag once;
   static int sms = 148;
   std::call_once(once, [] {
-    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    cudaFuncSetAttribute(gemm_bf16_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    cudaFuncSetAttribute(gemm_bf16_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    cudaFuncSetAttribute(gemm_bf16_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    cudaFuncSetAttribute(gemm_bf16_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -377,7 +417,11 @@ int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < sms ? tiles : sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  gemm_bf16_kernel<<<grid, THREADS, kSmemBytes, (cudaStream_t)stream>>>(ma, mb, p);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!a_mn && !b_mn) gemm_bf16_kernel<false, false><<<grid, THREADS, kSmemBytes, st>>>(ma, mb, p);
+  else if (!a_mn && b_mn) gemm_bf16_kernel<false, true><<<grid, THREADS, kSmemBytes, st>>>(ma, mb, p);
+  else if (a_mn && !b_mn) gemm_bf16_kernel<true, false><<<grid, THREADS, kSmemBytes, st>>>(ma, mb, p);
+  else gemm_bf16_kernel<true, true><<<grid, THREADS, kSmemBytes, st>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }
 

@@ -50,16 +50,19 @@ def check_errors(device: torch.device | None = None) -> None:
 
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, gelu: bool = False, out_dtype=torch.bfloat16,
-              out: torch.Tensor | None = None, accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
-    """C[M,N] = A[M,K] @ B[N,K]^T (+bias) (GELU) (+residual) on the tcgen05 kernel.
+              out: torch.Tensor | None = None, accumulate: bool = False, max_ctas: int = 0,
+              a_t: bool = False, b_t: bool = False) -> torch.Tensor:
+    """C[M,N] = op(A) @ op(B)^T (+bias) (GELU) (+residual) on the tcgen05 kernel.
 
-    a, b: bf16, last dimension contiguous, leading dimension and K multiples of 8.
-    bias: fp32 [N]. residual/out: [M,N] of ``out_dtype`` (bf16 or fp32)."""
+    a: bf16 [M,K] (or [K,M] with ``a_t``: the stored matrix is used transposed without a
+    copy). b: bf16 [N,K] (or [K,N] with ``b_t``). Last dimension contiguous, leading
+    dimensions multiples of 8. bias: fp32 [N]. residual/out: [M,N] of ``out_dtype``."""
     global _launches
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
-    assert a.stride(1) == 1 and b.stride(1) == 1 and a.shape[1] == b.shape[1]
-    M, K = a.shape
-    N = b.shape[0]
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    (K, M) = a.shape if a_t else a.shape[::-1]
+    (Kb, N) = b.shape if b_t else b.shape[::-1]
+    assert K == Kb, (a.shape, b.shape, a_t, b_t)
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     flags = (OUT_F32 if out.dtype == torch.float32 else 0) | (BIAS if bias is not None else 0) | \
@@ -71,7 +74,8 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
     err = _native.cuda().gcow_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
-        flags, _error_word(a.device).data_ptr(), max_ctas, torch.cuda.current_stream(a.device).cuda_stream)
+        flags, _error_word(a.device).data_ptr(), max_ctas, int(a_t), int(b_t),
+        torch.cuda.current_stream(a.device).cuda_stream)
     if err:
         raise RuntimeError(f"gcow_gemm_bf16 refused the call: {err}")
     _launches += 1
@@ -127,14 +131,11 @@ class _LinearFn(torch.autograd.Function):
                 g = g.contiguous()
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
-            # dx[M,K] = g[M,N] @ W[N,K]  ->  A = g, B = W^T stored [K,N]
-            gx = gemm_bf16(g, wb.t().contiguous()).view(x_shape)
+            # dx[M,K] = g[M,N] @ W[N,K]: W is stored [reduction N][K], i.e. the B operand transposed
+            gx = gemm_bf16(g, wb, b_t=True).view(x_shape)
         if ctx.needs_input_grad[1]:
-            # dW[N,K] = g^T[N,M] @ x[M,K]  ->  A = g^T stored [N,M], B = x^T stored [K,M]
-            if M % 8 == 0:
-                gw = gemm_bf16(g.t().contiguous(), xb.t().contiguous(), out_dtype=torch.float32)[:N].to(w_dtype)
-            else:
-                gw = (g.float().t() @ xb.float())[:N].to(w_dtype)
+            # dW[N,K] = g^T @ x: both g [M,N] and x [M,K] are stored [reduction M][rows]
+            gw = gemm_bf16(g, xb, a_t=True, b_t=True, out_dtype=torch.float32)[:N].to(w_dtype)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)[:N]
         return gx, gw, gb
@@ -202,9 +203,9 @@ class _Conv1x1Fn(torch.autograd.Function):
             g = g.to(torch.bfloat16).contiguous()
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
-            gx = gemm_bf16(g, wb.t().contiguous()).view(N, H, W, C).permute(0, 3, 1, 2)
+            gx = gemm_bf16(g, wb, b_t=True).view(N, H, W, C).permute(0, 3, 1, 2)
         if ctx.needs_input_grad[1]:
-            gw = gemm_bf16(g.t().contiguous(), xm.t().contiguous(), out_dtype=torch.float32)
+            gw = gemm_bf16(g, xm, a_t=True, b_t=True, out_dtype=torch.float32)
             gw = gw.view(wshape).to(wdtype).contiguous(memory_format=torch.channels_last)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)

@@ -75,3 +75,22 @@ def test_linear_autograd_matches_torch():
     assert (y.float() - yr).abs().max().item() < 0.05
     for g, r in ((gx, x.grad), (gw, w.grad), (gb, b.grad)):
         assert (g.float() - r).abs().max().item() <= 0.03 * r.abs().max().item() + 1e-6
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 320), (304, 520, 136), (1024, 1024, 4096)])
+def test_transposed_operands_without_copies(M, N, K):
+    """dgrad (B stored [K,N]) and wgrad (both operands stored [K,rows]) layouts."""
+    from gcow_b200.ops import kernels as K_
+    torch.manual_seed(7)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    ref = _ref(a, b)
+    bt = b.t().contiguous()          # stored [K, N]
+    at = a.t().contiguous()          # stored [K, M]
+    y1 = K_.gemm_bf16(a, bt, b_t=True, out_dtype=torch.float32)
+    y2 = K_.gemm_bf16(at, bt, a_t=True, b_t=True, out_dtype=torch.float32)
+    y3 = K_.gemm_bf16(at, b, a_t=True, out_dtype=torch.float32)
+    K_.check_errors()
+    scale = ref.abs().max().item()
+    for y in (y1, y2, y3):
+        assert (y - ref).abs().max().item() < 1e-3 * scale + 1e-3
