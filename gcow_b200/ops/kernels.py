@@ -212,6 +212,15 @@ class _Conv1x1Fn(torch.autograd.Function):
         return gx, gw, gb
 
 
+def conv1x1_enabled() -> bool:
+    """1x1 convolutions go through the tcgen05 GEMM only on request
+    (GCOW_CONV1X1=own): its 128x256 tile wastes most of the tensor-core work on the
+    64/128-channel layers of a ResNet and its weight-gradient product has a single
+    output tile, so cuDNN is faster on those shapes and stays the default."""
+    import os
+    return os.environ.get("GCOW_CONV1X1", "lib") == "own"
+
+
 def conv1x1_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
     if not (x.is_cuda and x.dim() == 4 and _have("gcow_gemm_bf16")):
         return False
