@@ -164,11 +164,11 @@ class CompressedAllReduce:
         return v
 
     def ctas_for(self, numel: int) -> int:
-        """Grid size for a message: at least 512 blocks per CTA so that small
-        messages do not pay for launching and synchronising the whole grid.
+        """Grid size for a message: one CTA per 64 blocks of a shard (each of its
+        warps then handles one destination), capped by the configured grid.
         Depends only on (numel, world, configuration): identical on every rank."""
         shard_blocks = -(-((numel + 3) // 4) // self.world)
-        return max(1, min(self.ctas, -(-shard_blocks // 512)))
+        return max(1, min(self.ctas, -(-shard_blocks // 64)))
 
     def enable_tracing(self, on: bool = True) -> None:
         """Per-CTA globaltimer stamps at the four phase boundaries of the last call."""

@@ -206,13 +206,22 @@ allreduce_fused_kernel(const ArArgs a) {
   const uint64_t s0 = (uint64_t)cta * L.slice_blocks;
   const uint64_t s1 = s0 + L.slice_blocks < SB ? s0 + L.slice_blocks : SB;
   const bool in_al = ((uintptr_t)a.in & 15) == 0, out_al = ((uintptr_t)a.out & 15) == 0;
+  // Loops over (shard, block of the slice) give each warp one shard, so that short
+  // slices still keep P warps busy: warp w works on shard slot w % P and, when the
+  // 8 warps outnumber the shards evenly, on every (8/P)-th group of 32 blocks.
+  const int warp = tid >> 5, lane = tid & 31, nwarps = kArThreads / 32;
+  const int wps = (nwarps % P == 0) ? nwarps / P : 1;        // warps per shard
+  const int slot = warp % P, sub = warp / P;
+  const bool has_slot = warp < P * wps;
+  const uint64_t b_first = s0 + (uint64_t)sub * 32 + lane, b_step = (uint64_t)wps * 32;
   uint8_t* const local = a.arena[r];
   stamp(a, 0);
 
   if (a.variant == kOneShot) {
     // ---- phase 1: encode once, store to every rank's slot for this source
-    for (int k = 0; k < P; k++) {
-      for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+    if (has_slot) {
+      const int k = slot;
+      for (uint64_t b = b_first; b < s1; b += b_step) {
         uint64_t gb = (uint64_t)k * SB + b;
         if (gb >= NB) break;
         float f[4];
@@ -238,8 +247,9 @@ allreduce_fused_kernel(const ArArgs a) {
     __syncthreads();
     if (!s_ok) return;
     stamp(a, 2);
-    for (int k = 0; k < P; k++) {
-      for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+    if (has_slot) {
+      const int k = slot;
+      for (uint64_t b = b_first; b < s1; b += b_step) {
         uint64_t gb = (uint64_t)k * SB + b;
         if (gb >= NB) break;
         float acc[4];
@@ -263,10 +273,10 @@ allreduce_fused_kernel(const ArArgs a) {
   // ------------------------------------------------------------- two-shot
   const uint64_t shard_bytes = SB * C::BYTES;
   // ---- phase 1: encode shard j, store into owner j's slot for source r
-  for (int step = 0; step < P; step++) {
-    const int j = (r + 1 + step) % P;  // peers first, own shard last
+  if (has_slot) {
+    const int j = (r + 1 + slot) % P;
     uint8_t* dst = a.arena[j] + a.region_off + (uint64_t)r * L.slot_bytes;
-    for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+    for (uint64_t b = b_first; b < s1; b += b_step) {
       uint64_t gb = (uint64_t)j * SB + b;
       if (gb >= NB) break;
       float f[4];
@@ -275,11 +285,11 @@ allreduce_fused_kernel(const ArArgs a) {
       encode_block_1d_rate<BITS>(f, etab, w);
       C::st(dst, b, w);
     }
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence_system();
-      st_release_sys(flag_ptr(a.arena[j], a.parity, 0, r, cta), a.epoch);
-    }
+  }
+  __syncthreads();
+  if (tid < P) {
+    __threadfence_system();
+    st_release_sys(flag_ptr(a.arena[tid], a.parity, 0, r, cta), a.epoch);
   }
   stamp(a, 1);
 
@@ -349,10 +359,10 @@ allreduce_fused_kernel(const ArArgs a) {
   }
   __syncthreads();
   if (!s_ok) return;
-  for (int step = 0; step < P; step++) {
-    const int j = (r + step) % P;
+  if (has_slot) {
+    const int j = slot;
     const uint8_t* src = local + a.region_off + L.recv_bytes + (uint64_t)j * shard_bytes;
-    for (uint64_t b = s0 + tid; b < s1; b += blockDim.x) {
+    for (uint64_t b = b_first; b < s1; b += b_step) {
       uint64_t gb = (uint64_t)j * SB + b;
       if (gb >= NB) break;
       uint32_t w[NW];
