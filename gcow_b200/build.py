@@ -40,7 +40,7 @@ CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wextra", "-pthread"]
 
 def _sources(kind: str) -> list[Path]:
     if kind == "cpu":
-        return sorted(CSRC.rglob("*.cpp"))
+        return sorted(p for p in CSRC.rglob("*.cpp") if "tests" not in p.parts)
     return sorted(CSRC.rglob("*.cu"))
 
 
@@ -131,6 +131,25 @@ def build_cuda(force: bool = False, jobs: int | None = None) -> Path | None:
           "-o", str(LIB / f"{name}.so"), "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
     _stamp_path(name).write_text(json.dumps({"digest": digest}))
     return LIB / f"{name}.so"
+
+
+def build_sanitizer_test(kind: str) -> Path:
+    """Executable of csrc/tests/sanitize_main.cpp + the CPU sources under a sanitizer:
+    kind = 'address' (with undefined-behaviour checks) or 'thread'."""
+    LIB.mkdir(exist_ok=True)
+    exe = LIB / f"sanitize_{kind}"
+    srcs = _sources("cpu") + [CSRC / "tests" / "sanitize_main.cpp"]
+    san = "address,undefined" if kind == "address" else "thread"
+    flags = ["-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={san}", "-fno-sanitize-recover=all",
+             "-pthread"]
+    digest = _digest(srcs + _headers(), flags)
+    st = LIB / f"sanitize_{kind}.stamp"
+    if exe.exists() and st.exists() and st.read_text() == digest:
+        return exe
+    inc = [f"-I{CSRC}", f"-I{CSRC / 'codec'}"]
+    _run(["g++", *flags, *inc, "-x", "c++", *map(str, srcs), "-o", str(exe)])
+    st.write_text(digest)
+    return exe
 
 
 def build_all(force: bool = False) -> None:
