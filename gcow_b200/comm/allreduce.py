@@ -215,6 +215,19 @@ class CompressedAllReduce:
         P = self.world
         self.bytes_wire += int(cb * (P - 1) * (1 if v == 1 else 2.0 / P)) if P > 1 else 0
 
+    def commit(self, src: torch.Tensor, dst: torch.Tensor, verdict: torch.Tensor, stream: torch.cuda.Stream) -> None:
+        """Enqueue ``dst <- src`` on ``stream`` unless a call has failed since the last
+        ``check``; ``verdict`` (one int32 on the device) receives 1 = copied, 2 = skipped."""
+        err = self.lib.gcow_ar_commit(self.status.data_ptr(), src.data_ptr(), dst.data_ptr(), src.numel(),
+                                      verdict.data_ptr(), self.ctas, stream.cuda_stream)
+        if err:
+            raise RuntimeError(f"gcow_ar_commit failed: {err}")
+
+    def reset_status(self, stream: torch.cuda.Stream | None = None) -> None:
+        s = stream or torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(s):
+            self.status.zero_()
+
     # ------------------------------------------------------------------ status
     def check(self, stream: torch.cuda.Stream | None = None) -> None:
         """Synchronise with ``stream`` and raise CollectiveTimeout if any call

@@ -30,7 +30,7 @@ class GcowConfig:
     bucket_mb: int = 25             # DDP bucket size
     average: bool = True            # divide by world size (DDP semantics)
     error_feedback: bool = False    # keep the compression residual per bucket
-    fallback_nccl: bool = True      # on a collective time-out, redo the bucket with NCCL fp32
+    fallback_nccl: bool = False     # reduce out of place and, after a collective time-out, redo the bucket with NCCL fp32
     # runtime
     log_path: str = ""              # JSONL metrics file ("" = off)
     trace: bool = False             # NVTX ranges + device phase stamps

@@ -379,6 +379,23 @@ allreduce_fused_kernel(const ArArgs a) {
   stamp(a, 3);
 }
 
+// Copy src -> dst only if no call so far has failed (status word still 0), and
+// record the verdict for the host. With the all-reduce writing to a side buffer,
+// a bucket whose collective gave up keeps its original local gradient.
+__global__ void __launch_bounds__(256)
+commit_kernel(const uint32_t* __restrict__ status, const float* __restrict__ src, float* __restrict__ dst,
+              uint64_t n, uint32_t* __restrict__ verdict) {
+  const bool ok = *status == 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *verdict = ok ? 1u : 2u;
+  if (!ok) return;
+  const bool al = ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0;
+  const uint64_t n4 = al ? n / 4 : 0;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (uint64_t)gridDim.x * blockDim.x)
+    reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
+  for (uint64_t i = n4 * 4 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+    dst[i] = src[i];
+}
+
 // A flag wait on its own: lets the host-visible time-out path be exercised
 // without a peer (the flag is one that nothing sets).
 __global__ void wait_probe_kernel(const ArArgs a, const uint32_t* flag) {
@@ -460,6 +477,18 @@ int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world,
     case 128: allreduce_fused_kernel<128><<<ctas, kArThreads, 0, s>>>(a); break;
     default: return -1;
   }
+  return (int)cudaGetLastError();
+}
+
+// Conditional commit of an out-of-place all-reduce result (see commit_kernel).
+// verdict receives 1 (copied) or 2 (a call had failed; dst left untouched).
+int gcow_ar_commit(const uint32_t* status, const float* src, float* dst, uint64_t n, uint32_t* verdict,
+                   int ctas, void* stream) {
+  if (!n) return 0;
+  uint64_t g = (n / 4 + 255) / 256;
+  if (g < 1) g = 1;
+  if (g > (uint64_t)(ctas > 0 ? ctas : 148)) g = ctas > 0 ? ctas : 148;
+  commit_kernel<<<(unsigned)g, 256, 0, (cudaStream_t)stream>>>(status, src, dst, n, verdict);
   return (int)cudaGetLastError();
 }
 

@@ -35,14 +35,34 @@ class GcowDDPState:
     launches: int = 0
     residual: dict = field(default_factory=dict)   # error-feedback memory per bucket index
     last_buckets: list = field(default_factory=list)
+    side: dict = field(default_factory=dict)       # out-of-place result buffers per bucket index (safe mode)
+    pending: list = field(default_factory=list)    # (bucket buffer, verdict word) of this step (safe mode)
+    timeouts: int = 0
+    fallbacks: int = 0
 
     def begin_step(self) -> None:
         self.last_buckets.clear()
+        self.pending.clear()
 
     def finish_step(self) -> None:
-        """Call after backward, before the optimizer step: waits for the
-        communication stream and raises CollectiveTimeout if a bucket gave up."""
-        self.ar.check(self.ar.stream)
+        """Call after backward, before the optimizer step: waits for the communication
+        stream. If a bucket's collective gave up: with ``cfg.fallback_nccl`` every
+        bucket that was not committed is all-reduced again by NCCL in fp32 (its buffer
+        still holds the local gradient), otherwise CollectiveTimeout is raised."""
+        try:
+            self.ar.check(self.ar.stream)
+        except CollectiveTimeout:
+            self.timeouts += 1
+            if not (self.cfg.fallback_nccl and self.pending):
+                raise
+            world = dist.get_world_size(self.group)
+            for buf, verdict in self.pending:
+                if int(verdict.item()) != 1:
+                    dist.all_reduce(buf, group=self.group)
+                    if self.cfg.average:
+                        buf.div_(world)
+                    self.fallbacks += 1
+            torch.cuda.current_stream().synchronize()
 
     def state_dict(self) -> dict:
         return {"cfg": self.cfg.asdict(), "residual": {k: v.cpu() for k, v in self.residual.items()}}
@@ -66,7 +86,20 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
                 state.residual[idx] = res
             buf.add_(res)                      # re-inject what compression dropped last time
             sent = buf.clone()
-        ar(buf, stream=ar.stream)
+        if state.cfg.fallback_nccl:
+            # safe mode: reduce into a side buffer; copy back on the device only if no
+            # collective has failed, so a failed bucket keeps its local gradient
+            idx = bucket.index()
+            side = state.side.get(idx)
+            if side is None or side[0].numel() != buf.numel():
+                side = (torch.empty_like(buf), torch.zeros(1, dtype=torch.int32, device=buf.device))
+                state.side[idx] = side
+            ar(buf, out=side[0], stream=ar.stream)
+            ar.commit(side[0], buf, side[1], ar.stream)
+            state.pending.append((buf, side[1]))
+            state.launches += 1
+        else:
+            ar(buf, stream=ar.stream)
         if state.cfg.error_feedback:
             # residual = what this rank wanted to send minus what the codec kept of it
             from ..codec import compress, decompress

@@ -1,0 +1,38 @@
+"""Failure detection on the host: gloo ranks on CPU, failures made by a rank that
+leaves or raises between steps. No GPU is involved."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(mode, tmp_path, nproc=3):
+    out = str(tmp_path / "hb")
+    env = dict(os.environ, GCOW_HB_MODE=mode, GCOW_TEST_OUT=out, MASTER_ADDR="127.0.0.1")
+    port = 29700 + os.getpid() % 200 + (7 if mode == "leave" else 0)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_heartbeat_worker.py")]
+    subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=180)
+    return [json.load(open(f"{out}.{r}")) for r in range(nproc) if os.path.exists(f"{out}.{r}")]
+
+
+def test_rank_that_leaves_is_detected_by_heartbeat(tmp_path):
+    res = _run("leave", tmp_path)
+    assert len(res) == 3
+    survivors = [r for r in res if not r.get("left")]
+    assert len(survivors) == 2
+    for r in survivors:
+        assert r["outcome"] == "restart" and "2" in r["why"]
+        assert r["seconds"] < 30 and r["steps"] >= 3          # noticed within seconds, not at step 200
+
+
+def test_local_failure_is_broadcast_as_abort(tmp_path):
+    res = _run("raise", tmp_path)
+    assert len(res) == 3
+    assert all(r["outcome"] == "restart" for r in res)
+    others = [r for r in res if r["rank"] != 1]
+    assert all("abort posted" in r["why"] or "1" in r["why"] for r in others)

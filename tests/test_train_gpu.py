@@ -51,3 +51,27 @@ def test_smoke_entry():
     import __graft_entry__ as ge
     # the trainer fixture already owns the process group; smoke() reuses it
     ge.smoke()
+
+
+def test_safe_mode_commits_and_falls_back_to_nccl():
+    """Out-of-place reduce + conditional commit. The failure is made on the host: the
+    status word is set as a timed-out kernel would leave it, so the commit kernels of
+    the step skip their copy and finish_step redoes the buckets with NCCL."""
+    from gcow_b200.config import GcowConfig
+    from gcow_b200.train import Trainer, SyntheticImages
+    cfg = GcowConfig(rate=16, comm_ctas=16, bucket_mb=1, fallback_nccl=True)
+    tr = Trainer("resnet18", batch_size=4, cfg=cfg, num_classes=10, device=torch.device("cuda", 0))
+    x, y = SyntheticImages(4, 64, 10, pool=1).next()
+    tr.step(x, y)
+    st = tr.hook_state
+    assert st.pending and all(int(v.item()) == 1 for _, v in st.pending) and st.fallbacks == 0
+    w_ok = tr.ddp.module.fc.weight.detach().clone()
+    st.ar.status[0] = 1            # what record_failure() leaves behind
+    st.ar.status[8] = 1
+    tr.step(x, y)                  # commits are skipped; finish_step falls back to NCCL
+    assert st.timeouts == 1 and st.fallbacks == len(st.pending) > 0
+    assert all(int(v.item()) == 2 for _, v in st.pending)
+    assert math.isfinite(tr.last_loss()) and not torch.equal(tr.ddp.module.fc.weight, w_ok)
+    st.ar.status.zero_()
+    tr.step(x, y)                  # healthy again
+    assert all(int(v.item()) == 1 for _, v in st.pending)
