@@ -1,0 +1,272 @@
+// Fused BatchNorm2d (+ residual add) (+ ReLU) for channels-last bf16 activations
+// (sm_100a), forward and backward, training and inference statistics.
+//
+// x is viewed as R = N*H*W rows of C channels. A thread owns 8 consecutive
+// channels (one 16-byte access) of every (256*8/C)-th row, keeps its partial
+// sums in fp32 registers and the CTA folds them per channel; per-CTA partials
+// are summed in a fixed order by a second small kernel, which also derives the
+// per-channel scale/shift and updates the running statistics. The normalise
+// pass then applies y = x*scale + shift (+ residual), optional ReLU, in one
+// read-modify-write sweep, so the add and the activation never touch memory on
+// their own. Backward mirrors it: one sweep for dgamma/dbeta (with the ReLU
+// mask taken from y, and the masked gradient written out when a residual branch
+// needs it), one sweep for dx.
+//
+// The reference's ResNet uses nn.BatchNorm2d + ReLU + add as separate ATen /
+// cuDNN operators (hw/models/resenet.py:12-22,28-40,80-89).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gcow {
+namespace bn {
+
+typedef __nv_bfloat16 bf16;
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(b[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+  uint4 u;
+  __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; i++) b[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// Fold per-thread sums a[8], b[8] over the threads that share a channel group and
+// write them to part[blockIdx.x][0][C] / [1][C].
+__device__ __forceinline__ void cta_fold(const float (&a)[8], const float (&b)[8], int C, float* __restrict__ part) {
+  __shared__ float sm[kThreads * 17];          // 16 values per thread, padded against bank conflicts
+  const int groups = C / 8, tid = threadIdx.x;
+  float* mine = sm + tid * 17;
+#pragma unroll
+  for (int i = 0; i < 8; i++) { mine[i] = a[i]; mine[8 + i] = b[i]; }
+  __syncthreads();
+  const int lanes = kThreads / groups;          // threads per channel group (>= 1)
+  for (int idx = tid; idx < groups * 16; idx += kThreads) {
+    const int g = idx / 16, k = idx % 16;
+    float s = 0;
+    for (int j = 0; j < lanes; j++) s += sm[(j * groups + g) * 17 + k];
+    const int c = g * 8 + (k & 7);
+    part[(size_t)blockIdx.x * 2 * C + (k < 8 ? 0 : C) + c] = s;
+  }
+}
+
+// ---- forward statistics: partial sum(x), sum(x^2)
+__global__ void __launch_bounds__(kThreads)
+stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int64_t R, int C) {
+  const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
+  float s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int64_t r = (int64_t)blockIdx.x * rstep + r0; r < R; r += (int64_t)gridDim.x * rstep) {
+    float v[8];
+    load8(x + r * C + g * 8, v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) { s[i] += v[i]; q[i] += v[i] * v[i]; }
+  }
+  cta_fold(s, q, C, part);
+}
+
+// ---- finalize forward: mean/rstd, scale/shift, running statistics
+__global__ void finalize_fwd_kernel(const float* __restrict__ part, int parts, int C, int64_t R, float eps, float momentum,
+                                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                                    float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ scale,
+                                    float* __restrict__ shift, float* __restrict__ run_mean, float* __restrict__ run_var) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s = 0, q = 0;
+  for (int p = 0; p < parts; p++) { s += part[(size_t)p * 2 * C + c]; q += part[(size_t)p * 2 * C + C + c]; }
+  const double mu = s / (double)R;
+  double var = q / (double)R - mu * mu;
+  if (var < 0) var = 0;
+  const float rs = rsqrtf((float)var + eps);
+  mean[c] = (float)mu; rstd[c] = rs;
+  const float sc = gamma[c] * rs;
+  scale[c] = sc; shift[c] = beta[c] - (float)mu * sc;
+  if (run_mean) {
+    const double unbiased = R > 1 ? var * (double)R / (double)(R - 1) : var;
+    run_mean[c] = (1.0f - momentum) * run_mean[c] + momentum * (float)mu;
+    run_var[c] = (1.0f - momentum) * run_var[c] + momentum * (float)unbiased;
+  }
+}
+
+// scale/shift from given (running) statistics, for inference
+__global__ void affine_from_stats_kernel(const float* __restrict__ gamma, const float* __restrict__ beta,
+                                         const float* __restrict__ mean_in, const float* __restrict__ var_in, float eps,
+                                         int C, float* __restrict__ scale, float* __restrict__ shift) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float sc = gamma[c] * rsqrtf(var_in[c] + eps);
+  scale[c] = sc; shift[c] = beta[c] - mean_in[c] * sc;
+}
+
+// ---- normalise: y = x*scale + shift (+ residual) (ReLU)
+__global__ void __launch_bounds__(kThreads)
+apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, bf16* __restrict__ y,
+             const float* __restrict__ scale, const float* __restrict__ shift, int64_t R, int C, int relu) {
+  const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
+  float sc[8], sh[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) { sc[i] = scale[g * 8 + i]; sh[i] = shift[g * 8 + i]; }
+  for (int64_t r = (int64_t)blockIdx.x * rstep + r0; r < R; r += (int64_t)gridDim.x * rstep) {
+    const int64_t off = r * C + g * 8;
+    float v[8];
+    load8(x + off, v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = v[i] * sc[i] + sh[i];
+    if (residual) {
+      float w[8];
+      load8(residual + off, w);
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] += w[i];
+    }
+    if (relu) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = fmaxf(v[i], 0.0f);
+    }
+    store8(y + off, v);
+  }
+}
+
+// ---- backward sweep 1: partial sum(g), sum(g*xhat); g = dy masked by (y > 0) when relu.
+// When gmask_out is given, the masked gradient is written there (the residual branch's gradient).
+__global__ void __launch_bounds__(kThreads)
+bwd_reduce_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, const bf16* __restrict__ x,
+                  const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ gmask_out,
+                  float* __restrict__ part, int64_t R, int C, int relu) {
+  const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
+  float mu[8], rs[8], s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; i++) { mu[i] = mean[g * 8 + i]; rs[i] = rstd[g * 8 + i]; }
+  for (int64_t r = (int64_t)blockIdx.x * rstep + r0; r < R; r += (int64_t)gridDim.x * rstep) {
+    const int64_t off = r * C + g * 8;
+    float gv[8], xv[8];
+    load8(dy + off, gv);
+    load8(x + off, xv);
+    if (relu) {
+      float yv[8];
+      load8(y + off, yv);
+#pragma unroll
+      for (int i = 0; i < 8; i++) gv[i] = yv[i] > 0.0f ? gv[i] : 0.0f;
+    }
+    if (gmask_out) store8(gmask_out + off, gv);
+#pragma unroll
+    for (int i = 0; i < 8; i++) { s[i] += gv[i]; q[i] += gv[i] * (xv[i] - mu[i]) * rs[i]; }
+  }
+  cta_fold(s, q, C, part);
+}
+
+// ---- finalize backward: dbeta = sum g, dgamma = sum g*xhat (fixed order)
+__global__ void finalize_bwd_kernel(const float* __restrict__ part, int parts, int C, float* __restrict__ dgamma,
+                                    float* __restrict__ dbeta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0, q = 0;
+  for (int p = 0; p < parts; p++) { s += part[(size_t)p * 2 * C + c]; q += part[(size_t)p * 2 * C + C + c]; }
+  dbeta[c] = s; dgamma[c] = q;
+}
+
+// ---- backward sweep 2: dx = gamma*rstd * (g - dbeta/R - xhat*dgamma/R)
+__global__ void __launch_bounds__(kThreads)
+bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, const bf16* __restrict__ x,
+              const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
+              const float* __restrict__ dgamma, const float* __restrict__ dbeta, bf16* __restrict__ dx, int64_t R, int C,
+              int relu) {
+  const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
+  float mu[8], rs[8], k0[8], k1[8], k2[8];
+  const float invR = 1.0f / (float)R;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int c = g * 8 + i;
+    mu[i] = mean[c]; rs[i] = rstd[c];
+    k0[i] = gamma[c] * rs[i];
+    k1[i] = dbeta[c] * invR;
+    k2[i] = dgamma[c] * invR;
+  }
+  for (int64_t r = (int64_t)blockIdx.x * rstep + r0; r < R; r += (int64_t)gridDim.x * rstep) {
+    const int64_t off = r * C + g * 8;
+    float gv[8], xv[8];
+    load8(dy + off, gv);
+    load8(x + off, xv);
+    if (relu) {
+      float yv[8];
+      load8(y + off, yv);
+#pragma unroll
+      for (int i = 0; i < 8; i++) gv[i] = yv[i] > 0.0f ? gv[i] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) gv[i] = k0[i] * (gv[i] - k1[i] - (xv[i] - mu[i]) * rs[i] * k2[i]);
+    store8(dx + off, gv);
+  }
+}
+
+inline int grid_for(int64_t R, int C) {
+  const int rstep = kThreads / (C / 8);
+  int64_t g = (R + rstep - 1) / rstep;
+  if (g > 148 * 4) g = 148 * 4;
+  return (int)(g < 1 ? 1 : g);
+}
+inline bool shape_ok(int C) { return C % 8 == 0 && C >= 8 && C <= 2048 && kThreads % (C / 8) == 0; }
+
+}  // namespace bn
+}  // namespace gcow
+
+using namespace gcow::bn;
+
+extern "C" {
+
+int gcow_bn_supported(int C) { return shape_ok(C) ? 1 : 0; }
+int gcow_bn_parts(int64_t R, int C) { return shape_ok(C) ? grid_for(R, C) : 0; }
+
+// Training forward. part: gcow_bn_parts * 2 * C floats of scratch. stats: 4*C floats out
+// (mean, rstd, scale, shift). run_mean/run_var may be null.
+int gcow_bn_fwd_train(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                      float* run_mean, float* run_var, float* stats, float* part, int64_t R, int C, float eps,
+                      float momentum, int relu, void* stream) {
+  if (!shape_ok(C) || R <= 0) return -1;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int g = grid_for(R, C);
+  float *mean = stats, *rstd = stats + C, *scale = stats + 2 * C, *shift = stats + 3 * C;
+  stats_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, part, R, C);
+  finalize_fwd_kernel<<<(C + 127) / 128, 128, 0, s>>>(part, g, C, R, eps, momentum, gamma, beta, mean, rstd, scale, shift,
+                                                      run_mean, run_var);
+  apply_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, (const bf16*)residual, (bf16*)y, scale, shift, R, C, relu);
+  return (int)cudaGetLastError();
+}
+
+// Inference forward with given statistics; scratch: 2*C floats.
+int gcow_bn_fwd_eval(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                     const float* run_mean, const float* run_var, float* scratch, int64_t R, int C, float eps, int relu,
+                     void* stream) {
+  if (!shape_ok(C) || R <= 0) return -1;
+  cudaStream_t s = (cudaStream_t)stream;
+  affine_from_stats_kernel<<<(C + 127) / 128, 128, 0, s>>>(gamma, beta, run_mean, run_var, eps, C, scratch, scratch + C);
+  apply_kernel<<<grid_for(R, C), kThreads, 0, s>>>((const bf16*)x, (const bf16*)residual, (bf16*)y, scratch, scratch + C, R, C, relu);
+  return (int)cudaGetLastError();
+}
+
+// Backward. stats as written by the forward. dres (nullable) receives the gradient of the
+// residual input (the ReLU-masked dy). dgb: 2*C floats out (dgamma, dbeta).
+int gcow_bn_bwd(const void* dy, const void* y, const void* x, const float* gamma, const float* stats, void* dx,
+                void* dres, float* dgb, float* part, int64_t R, int C, int relu, void* stream) {
+  if (!shape_ok(C) || R <= 0) return -1;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int g = grid_for(R, C);
+  const float *mean = stats, *rstd = stats + C;
+  bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, (bf16*)dres, part, R, C, relu);
+  finalize_bwd_kernel<<<(C + 127) / 128, 128, 0, s>>>(part, g, C, dgb, dgb + C);
+  // the second sweep re-derives the mask from y, or reads the masked gradient if it was written
+  if (dres)
+    bwd_dx_kernel<<<g, kThreads, 0, s>>>((const bf16*)dres, (const bf16*)y, (const bf16*)x, gamma, mean, rstd, dgb, dgb + C,
+                                         (bf16*)dx, R, C, 0);
+  else
+    bwd_dx_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, gamma, mean, rstd, dgb, dgb + C,
+                                         (bf16*)dx, R, C, relu);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

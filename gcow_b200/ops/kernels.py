@@ -366,3 +366,148 @@ def u8_to_bf16_norm(x_u8: torch.Tensor, mean255, std255) -> torch.Tensor:
          "gcow_u8_to_bf16_norm")
     _launches += 1
     return y.permute(0, 3, 1, 2)
+
+
+# ------------------------------------------------- BatchNorm (+add) (+ReLU)
+def _nhwc_rows(x: torch.Tensor):
+    N, C, H, W = x.shape
+    return N * H * W, C
+
+
+class _BatchNormActFn(torch.autograd.Function):
+    """y = relu?(bn(x) (+ residual)) on channels-last bf16 tensors, training statistics."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, run_mean, run_var, residual, relu, momentum, eps):
+        global _launches
+        R, C = _nhwc_rows(x)
+        lib = _native.cuda()
+        y = torch.empty_like(x, memory_format=torch.channels_last)
+        stats = torch.empty(4 * C, dtype=torch.float32, device=x.device)
+        part = torch.empty(lib.gcow_bn_parts(R, C) * 2 * C, dtype=torch.float32, device=x.device)
+        g32, b32 = gamma.float().contiguous(), beta.float().contiguous()
+        _chk(lib.gcow_bn_fwd_train(x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
+                                   g32.data_ptr(), b32.data_ptr(),
+                                   run_mean.data_ptr() if run_mean is not None else None,
+                                   run_var.data_ptr() if run_var is not None else None,
+                                   stats.data_ptr(), part.data_ptr(), R, C, eps, momentum, int(relu), _stream(x.device)),
+             "gcow_bn_fwd_train")
+        _launches += 3
+        ctx.save_for_backward(x, y, g32, stats)
+        ctx.meta = (R, C, bool(relu), residual is not None, gamma.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        x, y, g32, stats = ctx.saved_tensors
+        R, C, relu, has_res, pdtype = ctx.meta
+        lib = _native.cuda()
+        if gy.dtype != torch.bfloat16 or not gy.is_contiguous(memory_format=torch.channels_last):
+            gy = gy.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        dx = torch.empty_like(x, memory_format=torch.channels_last)
+        dres = torch.empty_like(x, memory_format=torch.channels_last) if has_res else None
+        dgb = torch.empty(2 * C, dtype=torch.float32, device=x.device)
+        part = torch.empty(lib.gcow_bn_parts(R, C) * 2 * C, dtype=torch.float32, device=x.device)
+        _chk(lib.gcow_bn_bwd(gy.data_ptr(), y.data_ptr(), x.data_ptr(), g32.data_ptr(), stats.data_ptr(), dx.data_ptr(),
+                             dres.data_ptr() if dres is not None else None, dgb.data_ptr(), part.data_ptr(), R, C,
+                             int(relu), _stream(x.device)), "gcow_bn_bwd")
+        _launches += 3
+        return dx, dgb[:C].to(pdtype), dgb[C:].to(pdtype), None, None, dres, None, None, None
+
+
+def batchnorm_usable(x: torch.Tensor, mod, residual=None) -> bool:
+    if not (x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16 and _have("gcow_bn_fwd_train")):
+        return False
+    if not x.is_contiguous(memory_format=torch.channels_last) or not mod.affine:
+        return False
+    if residual is not None and not (residual.dtype == torch.bfloat16 and residual.shape == x.shape
+                                     and residual.is_contiguous(memory_format=torch.channels_last)):
+        return False
+    return bool(_native.cuda().gcow_bn_supported(x.shape[1]))
+
+
+def batchnorm_act(x, mod, residual=None, relu=False):
+    """Fused BN(+add)(+ReLU) using ``mod``'s parameters and running statistics."""
+    global _launches
+    if mod.training or not mod.track_running_stats:
+        if mod.training and mod.track_running_stats and mod.num_batches_tracked is not None:
+            mod.num_batches_tracked += 1
+        mom = mod.momentum if mod.momentum is not None else 0.1
+        rm = mod.running_mean if (mod.training and mod.track_running_stats) else None
+        rv = mod.running_var if (mod.training and mod.track_running_stats) else None
+        return _BatchNormActFn.apply(x, mod.weight, mod.bias, rm, rv, residual, relu, mom, mod.eps)
+    R, C = _nhwc_rows(x)
+    y = torch.empty_like(x, memory_format=torch.channels_last)
+    scratch = torch.empty(2 * C, dtype=torch.float32, device=x.device)
+    _chk(_native.cuda().gcow_bn_fwd_eval(x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
+                                         mod.weight.float().data_ptr(), mod.bias.float().data_ptr(),
+                                         mod.running_mean.data_ptr(), mod.running_var.data_ptr(), scratch.data_ptr(),
+                                         R, C, mod.eps, int(relu), _stream(x.device)), "gcow_bn_fwd_eval")
+    _launches += 2
+    return y
+
+
+# ------------------------------------------------------------------- pooling
+class _MaxPool3x3s2Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        global _launches
+        N, C, H, W = x.shape
+        OH, OW = (H - 1) // 2 + 1, (W - 1) // 2 + 1
+        y = torch.empty((N, C, OH, OW), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        idx = torch.empty((N, OH, OW, C), dtype=torch.uint8, device=x.device)
+        _chk(_native.cuda().gcow_maxpool3x3s2_fwd(x.data_ptr(), y.data_ptr(), idx.data_ptr(), N, H, W, C, _stream(x.device)),
+             "gcow_maxpool3x3s2_fwd")
+        _launches += 1
+        ctx.save_for_backward(idx)
+        ctx.shape = (N, C, H, W)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        (idx,) = ctx.saved_tensors
+        N, C, H, W = ctx.shape
+        if gy.dtype != torch.bfloat16 or not gy.is_contiguous(memory_format=torch.channels_last):
+            gy = gy.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        dx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=gy.device, memory_format=torch.channels_last)
+        _chk(_native.cuda().gcow_maxpool3x3s2_bwd(gy.data_ptr(), idx.data_ptr(), dx.data_ptr(), N, H, W, C, _stream(gy.device)),
+             "gcow_maxpool3x3s2_bwd")
+        _launches += 1
+        return dx
+
+
+class _GlobalAvgPoolFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        global _launches
+        N, C, H, W = x.shape
+        y = torch.empty((N, C, 1, 1), dtype=x.dtype, device=x.device)
+        _chk(_native.cuda().gcow_avgpool_fwd(x.data_ptr(), y.data_ptr(), N, H * W, C, _stream(x.device)), "gcow_avgpool_fwd")
+        _launches += 1
+        ctx.shape = (N, C, H, W)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        N, C, H, W = ctx.shape
+        g = gy.reshape(N, C).to(torch.bfloat16).contiguous()
+        dx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=gy.device, memory_format=torch.channels_last)
+        _chk(_native.cuda().gcow_avgpool_bwd(g.data_ptr(), dx.data_ptr(), N, H * W, C, _stream(gy.device)), "gcow_avgpool_bwd")
+        _launches += 1
+        return dx
+
+
+def pool_usable(x: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.is_contiguous(memory_format=torch.channels_last) and _have("gcow_maxpool3x3s2_fwd"))
+
+
+def maxpool3x3s2(x):
+    return _MaxPool3x3s2Fn.apply(x)
+
+
+def global_avgpool(x):
+    return _GlobalAvgPoolFn.apply(x)

@@ -37,7 +37,33 @@ class Conv2d(nn.Conv2d):
 
 
 class BatchNorm2d(nn.BatchNorm2d):
-    pass
+    """BatchNorm2d whose forward can also take the residual to add and apply the
+    ReLU that follows: ``bn(x, residual=idt, relu=True)`` is ``relu(bn(x) + idt)`` in
+    one fused kernel on the own backend, and the same three PyTorch ops otherwise."""
+
+    def forward(self, x, residual=None, relu=False):
+        if backend.get_backend() == "own" and K.batchnorm_usable(x, self, residual):
+            return K.batchnorm_act(x, self, residual, relu)
+        y = super().forward(x)
+        if residual is not None:
+            y = y + residual
+        return F.relu(y) if relu else y
+
+
+class MaxPool3x3s2(nn.Module):
+    """3x3 / stride 2 / padding 1 max pooling (the ResNet stem pool)."""
+
+    def forward(self, x):
+        if backend.get_backend() == "own" and K.pool_usable(x):
+            return K.maxpool3x3s2(x)
+        return F.max_pool2d(x, 3, 2, 1)
+
+
+class GlobalAvgPool(nn.Module):
+    def forward(self, x):
+        if backend.get_backend() == "own" and K.pool_usable(x):
+            return K.global_avgpool(x)
+        return F.adaptive_avg_pool2d(x, 1)
 
 
 class LayerNorm(nn.LayerNorm):

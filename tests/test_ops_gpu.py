@@ -132,3 +132,73 @@ def test_bert_tiny_own_vs_torch_ops():
     assert abs(losses["own"] - losses["torch"]) < 0.05
     d = (grads["own"] - grads["torch"]).abs().max().item()
     assert d < 0.1 * grads["torch"].abs().max().item() + 1e-4
+
+
+@pytest.mark.parametrize("C,hw,res,relu", [(64, 56, False, True), (256, 14, True, True), (2048, 7, True, True), (128, 28, False, False)])
+def test_batchnorm_act_fused_matches_torch(C, hw, res, relu):
+    from gcow_b200.ops import nn as gnn, set_backend
+    torch.manual_seed(C)
+    N = 16
+    mk = lambda: (torch.randn(N, C, hw, hw, device="cuda") * 2 + 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    x0, r0, w = mk(), mk(), mk()
+    outs = {}
+    for be in ("torch", "own"):
+        set_backend(be)
+        bn = gnn.BatchNorm2d(C).cuda()
+        with torch.no_grad():
+            bn.weight.uniform_(0.5, 1.5); bn.bias.uniform_(-0.5, 0.5)
+            torch.manual_seed(1); bn.weight.copy_(torch.rand(C) + 0.5); bn.bias.copy_(torch.rand(C) - 0.5)
+        x = x0.clone().requires_grad_(True)
+        r = r0.clone().requires_grad_(True) if res else None
+        y = bn(x, residual=r, relu=relu)
+        (y.float() * w.float()).sum().backward()
+        outs[be] = (y.detach().float(), x.grad.float(), r.grad.float() if res else None, bn.weight.grad.clone(),
+                    bn.bias.grad.clone(), bn.running_mean.clone(), bn.running_var.clone())
+    set_backend("own")
+    a, b = outs["own"], outs["torch"]
+    assert (a[0] - b[0]).abs().max().item() < 0.06
+    assert (a[1] - b[1]).abs().max().item() < 0.03 * b[1].abs().max().item() + 0.02
+    if res:
+        assert (a[2] - b[2]).abs().max().item() < 0.05
+    assert (a[3] - b[3]).abs().max().item() < 0.02 * b[3].abs().max().item() + 0.5
+    assert (a[4] - b[4]).abs().max().item() < 0.02 * b[4].abs().max().item() + 0.5
+    assert (a[5] - b[5]).abs().max().item() < 1e-2 and (a[6] - b[6]).abs().max().item() < 2e-2
+
+
+def test_pools_match_torch():
+    from gcow_b200.ops import kernels as K
+    torch.manual_seed(5)
+    x = torch.relu(torch.randn(8, 64, 57, 57, device="cuda")).bfloat16().contiguous(memory_format=torch.channels_last)
+    xa = x.clone().requires_grad_(True)
+    xb = x.clone().float().requires_grad_(True)
+    ya, yb = K.maxpool3x3s2(xa), F.max_pool2d(xb, 3, 2, 1)
+    assert ya.shape == yb.shape and torch.equal(ya.float(), yb)
+    w = torch.randn_like(yb)
+    (ya.float() * w).sum().backward(); (yb * w).sum().backward()
+    assert (xa.grad.float() - xb.grad).abs().max().item() < 0.02 * xb.grad.abs().max().item() + 1e-3
+    xa2 = x.clone().requires_grad_(True); xb2 = x.clone().float().requires_grad_(True)
+    pa, pb = K.global_avgpool(xa2), F.adaptive_avg_pool2d(xb2, 1)
+    assert (pa.float() - pb).abs().max().item() < 0.01
+    pa.float().sum().backward(); pb.sum().backward()
+    assert (xa2.grad.float() - xb2.grad).abs().max().item() < 1e-5
+
+
+def test_resnet_own_vs_torch_backends_agree():
+    from gcow_b200.models import resnet18
+    from gcow_b200 import ops
+    torch.manual_seed(6)
+    m = resnet18(num_classes=10).cuda().to(memory_format=torch.channels_last)
+    x = torch.randn(8, 3, 64, 64, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 10, (8,), device="cuda")
+    res = {}
+    for be in ("torch", "own"):
+        ops.set_backend(be)
+        m.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = F.cross_entropy(m(x).float(), y)
+        loss.backward()
+        res[be] = (loss.item(), m.conv1.weight.grad.clone())
+    ops.set_backend("own")
+    assert abs(res["own"][0] - res["torch"][0]) < 0.05
+    d = (res["own"][1] - res["torch"][1]).abs().max().item()
+    assert d < 0.15 * res["torch"][1].abs().max().item() + 1e-3
