@@ -25,11 +25,12 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--shape", type=int, nargs=3, default=None, metavar=("M", "N", "K"), help="time one shape only")
     args = ap.parse_args(argv)
     pk = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
     peak, how = (json.loads(pk.read_text()).get("bf16_tflops", 1590.0), "measured") if pk.exists() else (1590.0, "fallback")
     rows = []
-    for M, N, Kd in SHAPES:
+    for M, N, Kd in ([tuple(args.shape)] if args.shape else SHAPES):
         a = torch.randn(M, Kd, device="cuda").bfloat16()
         b = torch.randn(N, Kd, device="cuda").bfloat16()
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
