@@ -128,3 +128,19 @@ _declare_prev_bn = declare
 def declare(lib, proto):  # noqa: F811
     _declare_prev_bn(lib, proto)
     _declare_bn_pool(lib, proto)
+
+
+def _declare_conv(lib, proto):
+    def opt(name, restype, *args):
+        if hasattr(lib, name):
+            proto(lib, name, restype, *args)
+    opt("gcow_im2col", i32, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, ptr)
+    opt("gcow_col2im", i32, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, ptr)
+
+
+_declare_prev_conv = declare
+
+
+def declare(lib, proto):  # noqa: F811
+    _declare_prev_conv(lib, proto)
+    _declare_conv(lib, proto)

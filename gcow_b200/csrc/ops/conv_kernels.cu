@@ -1,0 +1,101 @@
+// Convolution as GEMM for channels-last bf16 activations (sm_100a): im2col gathers
+// the K = KH*KW*Cin patch of every output pixel into a row (tap-major, channels
+// fastest, 16-byte copies), the tcgen05 GEMM does the product, and col2im folds the
+// patch gradients back as a gather over the taps that touch an input pixel (no
+// atomics, deterministic). Covers 3x3, 7x7 and strided 1x1 convolutions with
+// Cin a multiple of 8. Replaces the cuDNN convolutions of the reference's ResNet
+// (hw/models/resenet.py:14,79,113).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gcow {
+namespace conv {
+
+typedef __nv_bfloat16 bf16;
+
+struct Geo {
+  int N, H, W, C, KH, KW, stride, pad, OH, OW;
+};
+
+// col[(n,oh,ow)][(kh,kw,c)] = x[n][oh*s-p+kh][ow*s-p+kw][c] or 0
+__global__ void im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, Geo g) {
+  const int cg = g.C / 8, taps = g.KH * g.KW;
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * taps * cg;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int c8 = (int)(t % cg);
+    int64_t r = t / cg;
+    const int tap = (int)(r % taps);
+    int64_t p = r / taps;
+    const int ow = (int)(p % g.OW); p /= g.OW;
+    const int oh = (int)(p % g.OH);
+    const int n = (int)(p / g.OH);
+    const int ih = oh * g.stride - g.pad + tap / g.KW, iw = ow * g.stride - g.pad + tap % g.KW;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W)
+      v = *reinterpret_cast<const uint4*>(x + (((int64_t)n * g.H + ih) * g.W + iw) * g.C + c8 * 8);
+    *reinterpret_cast<uint4*>(col + t * 8) = v;
+  }
+}
+
+// dx[n][ih][iw][c] = sum over taps (kh,kw) and outputs (oh,ow) with oh*s-p+kh == ih, ow*s-p+kw == iw of dcol
+__global__ void col2im_kernel(const bf16* __restrict__ dcol, bf16* __restrict__ dx, Geo g) {
+  const int cg = g.C / 8, taps = g.KH * g.KW;
+  const int64_t total = (int64_t)g.N * g.H * g.W * cg;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int c8 = (int)(t % cg);
+    int64_t p = t / cg;
+    const int iw = (int)(p % g.W); p /= g.W;
+    const int ih = (int)(p % g.H);
+    const int n = (int)(p / g.H);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int kh = 0; kh < g.KH; kh++) {
+      const int a = ih + g.pad - kh;
+      if (a < 0 || a % g.stride) continue;
+      const int oh = a / g.stride;
+      if (oh >= g.OH) continue;
+      for (int kw = 0; kw < g.KW; kw++) {
+        const int b = iw + g.pad - kw;
+        if (b < 0 || b % g.stride) continue;
+        const int ow = b / g.stride;
+        if (ow >= g.OW) continue;
+        const int64_t row = ((int64_t)n * g.OH + oh) * g.OW + ow;
+        const uint4 u = *reinterpret_cast<const uint4*>(dcol + ((row * taps + kh * g.KW + kw) * cg + c8) * 8);
+        const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(q[i]); acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; i++) ob[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    *reinterpret_cast<uint4*>(dx + t * 8) = o;
+  }
+}
+
+inline int grid1d(int64_t items) { int64_t b = (items + 255) / 256; return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b)); }
+
+}  // namespace conv
+}  // namespace gcow
+
+using namespace gcow::conv;
+
+extern "C" {
+
+int gcow_im2col(const void* x, void* col, int N, int H, int W, int C, int KH, int KW, int stride, int pad, void* stream) {
+  if (C % 8 || stride < 1) return -1;
+  Geo g{N, H, W, C, KH, KW, stride, pad, (H + 2 * pad - KH) / stride + 1, (W + 2 * pad - KW) / stride + 1};
+  const int64_t total = (int64_t)N * g.OH * g.OW * KH * KW * (C / 8);
+  im2col_kernel<<<grid1d(total), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)col, g);
+  return (int)cudaGetLastError();
+}
+
+int gcow_col2im(const void* dcol, void* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, void* stream) {
+  if (C % 8 || stride < 1) return -1;
+  Geo g{N, H, W, C, KH, KW, stride, pad, (H + 2 * pad - KH) / stride + 1, (W + 2 * pad - KW) / stride + 1};
+  col2im_kernel<<<grid1d((int64_t)N * H * W * (C / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)dcol, (bf16*)dx, g);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -511,3 +511,67 @@ def maxpool3x3s2(x):
 
 def global_avgpool(x):
     return _GlobalAvgPoolFn.apply(x)
+
+
+# ------------------------------------------------ convolution as im2col + GEMM
+class _ConvGemmFn(torch.autograd.Function):
+    """KxK convolution (any stride/padding, groups = 1) on channels-last bf16 input:
+    own im2col -> tcgen05 GEMM -> (backward) GEMMs + own col2im."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, stride, pad):
+        global _launches
+        N, C, H, W = x.shape
+        Co, _, KH, KW = w.shape
+        OH, OW = (H + 2 * pad - KH) // stride + 1, (W + 2 * pad - KW) // stride + 1
+        lib = _native.cuda()
+        if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
+            x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        col = torch.empty((N * OH * OW, KH * KW * C), dtype=torch.bfloat16, device=x.device)
+        _chk(lib.gcow_im2col(x.data_ptr(), col.data_ptr(), N, H, W, C, KH, KW, stride, pad, _stream(x.device)), "gcow_im2col")
+        _launches += 1
+        wr = w.permute(0, 2, 3, 1).reshape(Co, KH * KW * C).to(torch.bfloat16).contiguous()      # [Co, (kh,kw,c)]
+        y = gemm_bf16(col, wr, bias=b.float().contiguous() if b is not None else None)
+        ctx.save_for_backward(col, wr)
+        ctx.meta = (N, C, H, W, Co, KH, KW, OH, OW, stride, pad, w.dtype, b is not None)
+        return y.view(N, OH, OW, Co).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        col, wr = ctx.saved_tensors
+        N, C, H, W, Co, KH, KW, OH, OW, stride, pad, wdtype, has_bias = ctx.meta
+        g = gy.permute(0, 2, 3, 1).reshape(-1, Co)
+        if g.dtype != torch.bfloat16 or not g.is_contiguous():
+            g = g.to(torch.bfloat16).contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            dcol = gemm_bf16(g, wr, b_t=True)                                   # [pixels, K]
+            gx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=g.device, memory_format=torch.channels_last)
+            _chk(_native.cuda().gcow_col2im(dcol.data_ptr(), gx.data_ptr(), N, H, W, C, KH, KW, stride, pad,
+                                            _stream(g.device)), "gcow_col2im")
+            _launches += 1
+        if ctx.needs_input_grad[1]:
+            gw = gemm_bf16(g, col, a_t=True, b_t=True, out_dtype=torch.float32)   # [Co, K]
+            gw = gw.view(Co, KH, KW, C).permute(0, 3, 1, 2).to(wdtype).contiguous(memory_format=torch.channels_last)
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(g)
+        return gx, gw, gb, None, None
+
+
+def conv_gemm_enabled() -> bool:
+    """KxK convolutions run as own im2col + tcgen05 GEMM only on request (GCOW_CONV=own);
+    the explicit patch matrix costs KH*KW times the activation traffic, so cuDNN's
+    implicit GEMM stays the default."""
+    import os
+    return os.environ.get("GCOW_CONV", "lib") == "own"
+
+
+def conv_gemm_usable(x: torch.Tensor, w: torch.Tensor, groups: int, dilation) -> bool:
+    if not (x.is_cuda and x.dim() == 4 and _have("gcow_im2col") and groups == 1 and tuple(dilation) == (1, 1)):
+        return False
+    return x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.shape[0] * x.shape[2] * x.shape[3] >= 128
+
+
+def conv_gemm(x, w, b, stride, pad):
+    return _ConvGemmFn.apply(x, w, b, stride, pad)

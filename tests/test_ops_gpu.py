@@ -219,3 +219,25 @@ def test_resnet_own_vs_torch_backends_agree():
     assert abs(res["own"][0] - res["torch"][0]) < 0.05
     d = (res["own"][1] - res["torch"][1]).abs().max().item()
     assert d < 0.15 * res["torch"][1].abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("k,stride,pad", [(3, 1, 1), (3, 2, 1), (1, 2, 0), (7, 2, 3)])
+def test_conv_as_im2col_gemm_matches_torch(k, stride, pad):
+    from gcow_b200.ops import kernels as K
+    torch.manual_seed(k * 10 + stride)
+    x = torch.randn(4, 16, 30, 30, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    w = (torch.randn(24, 16, k, k, device="cuda") * 0.1).requires_grad_(True)
+    b = torch.randn(24, device="cuda", requires_grad=True)
+    y = K.conv_gemm(x, w, b, stride, pad)
+    wgt = torch.randn_like(y.float())
+    (y.float() * wgt).sum().backward()
+    gx, gw, gb = x.grad.float().clone(), w.grad.clone(), b.grad.clone()
+    x.grad = w.grad = b.grad = None
+    xr = x.detach().float().requires_grad_(True)
+    yr = F.conv2d(xr, w, b, stride=stride, padding=pad)
+    (yr * wgt).sum().backward()
+    tol = lambda r: 0.02 * r.abs().max().item() + 1e-2
+    assert y.shape == yr.shape and (y.float() - yr).abs().max().item() < tol(yr)
+    assert (gx - xr.grad).abs().max().item() < tol(xr.grad)
+    assert (gw - w.grad).abs().max().item() < tol(w.grad)
+    assert (gb - b.grad).abs().max().item() < tol(b.grad)
