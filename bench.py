@@ -66,7 +66,7 @@ def main() -> int:
     ap.add_argument("--rate", type=float, default=8.0)
     ap.add_argument("--ops", default="own", choices=["own", "torch"])
     ap.add_argument("--variant", default="auto")
-    ap.add_argument("--comm-ctas", type=int, default=32)
+    ap.add_argument("--comm-ctas", type=int, default=148)
     ap.add_argument("--seq-len", type=int, default=512)
     args = ap.parse_args()
     if args.impl == "reference":

@@ -85,7 +85,7 @@ class ClockSampler:
     """Samples SM clocks and throttle reasons in a background thread while a timed
     region runs; ``stop()`` returns {"sm_mhz": median, "sm_max_mhz": ..., "reasons": [...]}."""
 
-    def __init__(self, gpu: int = 0, period_s: float = 0.2):
+    def __init__(self, gpu: int = 0, period_s: float = 0.1):
         self.gpu, self.period = gpu, period_s
         self.samples: list[dict] = []
         self._stop = threading.Event()
