@@ -3,9 +3,10 @@
 # thin C-ABI shim into baseline/_ref/libgcowref.so. The reference ships no
 # installable Python package, so this is its offline "install".
 #   usage: baseline/build_ref.sh [path-to-reference-checkout]
+# Without an argument: $GCOW_REFERENCE, else a checkout named "reference" beside this repository.
 set -euo pipefail
 here="$(cd "$(dirname "$0")" && pwd)"
-ref="${1:-/root/reference}"
+ref="${1:-${GCOW_REFERENCE:-$here/../../reference}}"
 out="$here/_ref"
 mkdir -p "$out"
 g++ -std=c++11 -O2 -fPIC -shared -w -x c++ \

@@ -64,6 +64,15 @@ class GcowDDPState:
                     self.fallbacks += 1
             torch.cuda.current_stream().synchronize()
 
+    def step_record(self) -> dict:
+        """Metrics of the step that just finished, for the JSONL log."""
+        ar = self.ar
+        return {"buckets": len(self.last_buckets), "bucket_numel": list(self.last_buckets),
+                "variants": [ar.pick_variant(n) for n in self.last_buckets],
+                "fp32_bytes": sum(self.last_buckets) * 4,
+                "wire_bytes_per_rank": sum(((n + 3) // 4) * ar.bits // 8 for n in self.last_buckets),
+                "rate": self.cfg.rate, "world": ar.world, "timeouts": self.timeouts, "fallbacks": self.fallbacks}
+
     def state_dict(self) -> dict:
         return {"cfg": self.cfg.asdict(), "residual": {k: v.cpu() for k, v in self.residual.items()}}
 
@@ -77,6 +86,9 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
     ar = state.ar
     cur = torch.cuda.current_stream(buf.device)
     ar.stream.wait_stream(cur)
+    if state.cfg.trace:
+        torch.cuda.nvtx.range_push(f"gcow_allreduce bucket {bucket.index()} {buf.numel() * 4 >> 20} MB "
+                                   f"{ar.pick_variant(buf.numel())}")
     with torch.cuda.stream(ar.stream):
         if state.cfg.error_feedback:
             idx = bucket.index()
@@ -108,6 +120,8 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
         buf.record_stream(ar.stream)
         fut = torch.futures.Future(devices=[buf.device])
         fut.set_result(buf)
+    if state.cfg.trace:
+        torch.cuda.nvtx.range_pop()
     state.buckets_seen += 1
     state.launches += 1
     state.last_buckets.append(buf.numel())

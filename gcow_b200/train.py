@@ -235,7 +235,8 @@ class Trainer:
             prev = float(self.loss_host[pslot])
             if math.isnan(prev):
                 raise FloatingPointError("loss is NaN: training diverged")   # train_imagenet.py:445-446
-        self.logger.log(step=self.steps, loss=prev)
+        if self.logger.enabled:
+            self.logger.log(step=self.steps, loss=prev, **(self.hook_state.step_record() if self.hook_state else {}))
         return StepResult(prev, self.steps)
 
     def last_loss(self) -> float:

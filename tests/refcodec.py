@@ -10,7 +10,7 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent
 SO = ROOT / "baseline" / "_ref" / "libgcowref.so"
-REF = Path(os.environ.get("GCOW_REFERENCE", "/root/reference"))
+REF = Path(os.environ.get("GCOW_REFERENCE", str(ROOT.parent / "reference")))   # a checkout beside this repository
 
 _lib = None
 
