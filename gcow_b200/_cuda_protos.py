@@ -71,7 +71,7 @@ def _declare_gemm(lib, proto):
     def opt(name, restype, *args):
         if hasattr(lib, name):
             proto(lib, name, restype, *args)
-    opt("gcow_gemm_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, i32, ptr, i32, i32, i32, ptr)
+    opt("gcow_gemm_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, i32, ptr, i32, i32, i32, i32, ptr)
 
 
 _declare_prev_gemm = declare

@@ -35,10 +35,12 @@ def main(argv=None):
         b = torch.randn(N, Kd, device="cuda").bfloat16()
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         ms_own, _ = time_cuda(lambda: K.gemm_bf16(a, b, out=out), args.iters)
+        ms_128, _ = time_cuda(lambda: K.gemm_bf16(a, b, out=out, tile_rows=128), args.iters)
+        ms_256, _ = time_cuda(lambda: K.gemm_bf16(a, b, out=out, tile_rows=256), args.iters)
         K.check_errors()
         ms_lib, _ = time_cuda(lambda: torch.matmul(a, b.t(), out=out), args.iters)
         fl = 2.0 * M * N * Kd
-        row = {"M": M, "N": N, "K": Kd, "own_ms": ms_own, "cublas_ms": ms_lib, "own_tflops": fl / ms_own / 1e9,
+        row = {"M": M, "N": N, "K": Kd, "own_ms": ms_own, "tile128_ms": ms_128, "tile256_ms": ms_256, "cublas_ms": ms_lib, "own_tflops": fl / ms_own / 1e9,
                "cublas_tflops": fl / ms_lib / 1e9, "own_frac_of_peak": fl / ms_own / 1e9 / peak,
                "peak": f"{how} {peak:.0f} TFLOP/s"}
         rows.append(row)

@@ -1,16 +1,21 @@
 // bf16 GEMM on the 5th-generation tensor cores (sm_100a): C[M,N] = A[M,K] * B[N,K]^T
 // with fp32 accumulation in tensor memory and a fused epilogue.
 //
-// Persistent, warp-specialised kernel, one CTA per SM:
-//   warp 0      TMA producer: cp.async.bulk.tensor tiles of A (128x64) and B (256x64),
-//               128-byte swizzle, into a 4-stage shared-memory ring (mbarrier tx counts);
-//   warp 1      allocates 512 TMEM columns (two 128x256 fp32 accumulators) and one
-//               elected thread issues tcgen05.mma (M128 N256 K16, kind::f16) from
-//               shared-memory descriptors; tcgen05.commit releases ring stages and
-//               publishes finished accumulators;
-//   warps 2-5   epilogue: tcgen05.ld their 32-lane quarter of the accumulator,
-//               add bias / residual, optional GELU, convert and store - while the
-//               MMA warp already works on the other accumulator.
+// Persistent, warp-specialised kernel, one CTA per SM, in two tile shapes:
+//   256x256 (default): A 256x64 + B 256x64 per stage (64 KB, 3 stages). Each K step issues
+//            two M128 N256 K16 MMAs that share the B tile, one per 128-row half; the two
+//            fp32 accumulators fill all 512 TMEM columns. Twice the flops per byte fetched
+//            from L2 compared with 128x256 - the kernel is bound by the per-SM L2->shared
+//            bandwidth, not by the tensor pipe. Eight epilogue warps drain half 0 then half
+//            1, releasing each half separately so the next tile's MMAs restart early.
+//   128x256 (small M): A 128x64 + B 256x64 per stage (48 KB, 4 stages), two 128x256
+//            accumulators used alternately so the epilogue fully overlaps the next tile.
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles, 128-byte swizzle, mbarrier tx counts;
+//   warp 1      allocates the 512 TMEM columns; one elected thread issues tcgen05.mma
+//               (kind::f16) from shared-memory descriptors; tcgen05.commit releases ring
+//               stages and publishes finished accumulators;
+//   warps 2+    epilogue: tcgen05.ld their 32-lane quarter of the accumulator, add bias /
+//               residual, optional GELU, convert and store.
 // Each operand may be K-major (stored [rows][K], the layout of activations and
 // of nn.Linear / 1x1-convolution weights in the forward product) or MN-major
 // (stored [K][rows]); the backward products dX = dY*W and dW = dY^T*X read the
@@ -31,11 +36,21 @@
 namespace gcow {
 namespace gemm {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-constexpr int THREADS = 192;
+constexpr int BN = 256, BK = 64, UMMA_K = 16;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int MAX_STAGES = 4;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t kSpinLimit = 1u << 26;   // polls before a wait gives up
+
+template <int BM_> struct Shape {
+  static constexpr int BM = BM_;
+  static constexpr int HALVES = BM_ / 128;                 // 128-row accumulators per tile
+  static constexpr int STAGES = BM_ == 256 ? 3 : 4;
+  static constexpr int A_BYTES = BM_ * BK * 2;
+  static constexpr int EPI_WARPS = 8;                      // two warps per TMEM lane quarter, half the columns each
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+  static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES);
+};
 
 enum Flags : int { kOutF32 = 1, kBias = 2, kGelu = 4, kResidual = 8, kAccumulate = 16 };
 
@@ -48,7 +63,7 @@ struct Params {
 };
 
 struct Smem {
-  uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain;
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], drain;
   uint32_t tmem_base;
   volatile uint32_t abort;
 };
@@ -141,10 +156,12 @@ __device__ __forceinline__ float gelu_f(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
 }
 
-template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int BM_, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(Shape<BM_>::THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const Params p) {
+  using S = Shape<BM_>;
+  constexpr int BM = S::BM, STAGES = S::STAGES, A_BYTES = S::A_BYTES, HALVES = S::HALVES, EPI_WARPS = S::EPI_WARPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* smA = base;
@@ -158,7 +175,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(&sm->tmem_full[a], 1); mbar_init(&sm->tmem_empty[a], 128); }
+    for (int a = 0; a < 2; a++) { mbar_init(&sm->tmem_full[a], 1); mbar_init(&sm->tmem_empty[a], EPI_WARPS * 32); }
     mbar_init(&sm->drain, 1);
     sm->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -208,31 +225,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N256 M128
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, operand major-ness, N256 M128
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)A_MN << 15) | ((uint32_t)B_MN << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       uint32_t s = 0, phase = 0, t = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
-        const uint32_t a = t & 1, aphase = (t >> 1) & 1;
-        if (!(ok = mbar_wait(sm, &sm->tmem_empty[a], aphase ^ 1, p.error, 2))) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + a * BN;
-        for (int kb = 0; kb < kblocks; kb++) {
+        // HALVES == 1: accumulators alternate per tile. HALVES == 2: both are used by every tile.
+        const uint32_t acc0 = HALVES == 1 ? (t & 1) : 0, aphase = HALVES == 1 ? ((t >> 1) & 1) : (t & 1);
+        for (int kb = 0; kb < kblocks && ok; kb++) {
           if (!(ok = mbar_wait(sm, &sm->full[s], phase, p.error, 3))) break;
           tc_fence_after();
           const uint32_t sa = smem_u32(smA + s * A_BYTES), sb = smem_u32(smB + s * B_BYTES);
-          const uint64_t da = A_MN ? smem_desc_mn_sw128(sa) : smem_desc_sw128(sa);
           const uint64_t db = B_MN ? smem_desc_mn_sw128(sb) : smem_desc_sw128(sb);
           // one K step of 16: 32 bytes along a K-major row, 16 rows (2048 bytes) of an MN-major tile
           constexpr uint64_t ka = A_MN ? (2048 >> 4) : (32 >> 4), kbs = B_MN ? (2048 >> 4) : (32 >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; k++)
-            tc_mma(d_tmem, da + ka * k, db + kbs * k, idesc, (kb | k) != 0);
+          for (int h = 0; h < HALVES; h++) {
+            if (kb == 0) {   // first write to this accumulator: its previous contents must have been read out
+              if (!(ok = mbar_wait(sm, &sm->tmem_empty[acc0 + h], aphase ^ 1, p.error, 2))) break;
+              tc_fence_after();
+            }
+            // 128 rows of A are 16 KB in either layout (128 rows x 128 B, or two 64-column boxes)
+            const uint64_t da = A_MN ? smem_desc_mn_sw128(sa + h * 16384) : smem_desc_sw128(sa + h * 16384);
+            const uint32_t d_tmem = tmem_base + (acc0 + h) * BN;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; k++)
+              tc_mma(d_tmem, da + ka * k, db + kbs * k, idesc, (kb | k) != 0);
+          }
+          if (!ok) break;
           tc_commit(&sm->empty[s]);
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
-        if (ok) tc_commit(&sm->tmem_full[a]);
+        if (ok) tc_commit(&sm->tmem_full[acc0]);
       }
       // drain: everything issued by this thread has finished before TMEM is freed
       tc_commit(&sm->drain);
@@ -240,87 +265,111 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // ----------------------------------------------------------------- epilogue
-    const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    const int row_in_tile = q * 32 + lane;
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int ew = warp - 2;                      // 0 .. EPI_WARPS-1
+    constexpr int COLS = BN / (EPI_WARPS / 4);    // columns of each accumulator this warp drains
+    const int col0 = (ew / 4) * COLS;
     uint32_t t = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-      const uint32_t a = t & 1, aphase = (t >> 1) & 1;
-      ok = mbar_wait(sm, &sm->tmem_full[a], aphase, p.error, 4);
+      const uint32_t acc0 = HALVES == 1 ? (t & 1) : 0, aphase = HALVES == 1 ? ((t >> 1) & 1) : (t & 1);
+      ok = mbar_wait(sm, &sm->tmem_full[acc0], aphase, p.error, 4);
       ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below need the whole warp
       if (!ok) break;
       tc_fence_after();
-      const int m = m0 + row_in_tile;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        uint32_t r[32];
-        tc_ld32(taddr + c * 32, r);
-        tc_wait_ld();
-        const int n = n0 + c * 32;
-        if (m < p.M && n < p.N) {
-          float v[32];
+      for (int h = 0; h < HALVES; h++) {
+        const int m = m0 + h * 128 + q * 32 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc0 + h) * BN + col0;
+        // Tensor-memory loads are software pipelined: the load of chunk c+1 is in flight
+        // while chunk c is converted and stored.
+        auto process = [&](const uint32_t (&r)[32], int c) {
+          const int n = n0 + col0 + c * 32;
+          if (m < p.M && n < p.N) {
+            float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-          if (p.flags & kBias) {
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+            if (p.flags & kBias) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) if (n + j < p.N) v[j] += __ldg(p.bias + n + j);
-          }
-          if (p.flags & kGelu) {
-#pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
-          }
-          const size_t off = (size_t)m * p.ldc + n;
-          if (p.flags & kOutF32) {
-            float* C = reinterpret_cast<float*>(p.C) + off;
-            const float* R = reinterpret_cast<const float*>(p.residual) + off;
-            if (n + 32 <= p.N) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                if (p.flags & kResidual) { float4 x = *reinterpret_cast<const float4*>(R + j); o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w; }
-                if (p.flags & kAccumulate) { float4 x = *reinterpret_cast<const float4*>(C + j); o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w; }
-                *reinterpret_cast<float4*>(C + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && n + j < p.N; j++) {
-                float o = v[j];
-                if (p.flags & kResidual) o += R[j];
-                if (p.flags & kAccumulate) o += C[j];
-                C[j] = o;
-              }
+              for (int j = 0; j < 32; j++) if (n + j < p.N) v[j] += __ldg(p.bias + n + j);
             }
-          } else {
-            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
-            const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.residual) + off;
-            if (n + 32 <= p.N) {
+            if (p.flags & kGelu) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                if (p.flags & kResidual) {
-                  uint4 x = *reinterpret_cast<const uint4*>(R + j);
-                  const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+              for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
+            }
+            const size_t off = (size_t)m * p.ldc + n;
+            if (p.flags & kOutF32) {
+              float* C = reinterpret_cast<float*>(p.C) + off;
+              const float* R = reinterpret_cast<const float*>(p.residual) + off;
+              if (n + 32 <= p.N) {
 #pragma unroll
-                  for (int e = 0; e < 4; e++) { float2 f = __bfloat1622float2(xb[e]); v[j + 2 * e] += f.x; v[j + 2 * e + 1] += f.y; }
+                for (int j = 0; j < 32; j += 4) {
+                  float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                  if (p.flags & kResidual) { float4 x = *reinterpret_cast<const float4*>(R + j); o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w; }
+                  if (p.flags & kAccumulate) { float4 x = *reinterpret_cast<const float4*>(C + j); o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w; }
+                  *reinterpret_cast<float4*>(C + j) = o;
                 }
-                uint4 o;
-                __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+              } else {
 #pragma unroll
-                for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
-                *reinterpret_cast<uint4*>(C + j) = o;
+                for (int j = 0; j < 32; j++) {     // unrolled with a predicate: v[] stays in registers
+                  if (n + j < p.N) {
+                    float o = v[j];
+                    if (p.flags & kResidual) o += R[j];
+                    if (p.flags & kAccumulate) o += C[j];
+                    C[j] = o;
+                  }
+                }
               }
             } else {
-              for (int j = 0; j < 32 && n + j < p.N; j++) {
-                float o = v[j];
-                if (p.flags & kResidual) o += __bfloat162float(R[j]);
-                C[j] = __float2bfloat16(o);
+              __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
+              const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.residual) + off;
+              if (n + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  if (p.flags & kResidual) {
+                    uint4 x = *reinterpret_cast<const uint4*>(R + j);
+                    const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) { float2 f = __bfloat1622float2(xb[e]); v[j + 2 * e] += f.x; v[j + 2 * e + 1] += f.y; }
+                  }
+                  uint4 o;
+                  __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                  for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                  *reinterpret_cast<uint4*>(C + j) = o;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                  if (n + j < p.N) {
+                    float o = v[j];
+                    if (p.flags & kResidual) o += __bfloat162float(R[j]);
+                    C[j] = __float2bfloat16(o);
+                  }
+                }
               }
             }
+          }
+        };
+        constexpr int NCH = COLS / 32;
+        uint32_t ra[32], rb[32];
+        tc_ld32(taddr, ra);
+#pragma unroll 1
+        for (int c = 0; c < NCH; c += 2) {
+          tc_wait_ld();
+          if (c + 1 < NCH) tc_ld32(taddr + (c + 1) * 32, rb);
+          process(ra, c);
+          if (c + 1 < NCH) {
+            tc_wait_ld();
+            if (c + 2 < NCH) tc_ld32(taddr + (c + 2) * 32, ra);
+            process(rb, c + 1);
           }
         }
+        // this accumulator has been read out: the MMA warp may overwrite it
+        tc_fence_before();
+        mbar_arrive(&sm->tmem_empty[acc0 + h]);
       }
-      tc_fence_before();
-      mbar_arrive(&sm->tmem_empty[a]);
     }
   }
 
@@ -367,7 +416,7 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t c
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
-constexpr size_t kSmemBytes = STAGES * (A_BYTES + B_BYTES) + sizeof(Smem) + 1024;
+template <int BM_> constexpr size_t smem_bytes() { return Shape<BM_>::SMEM + sizeof(Smem) + 1024; }
 
 }  // namespace gemm
 }  // namespace gcow
@@ -381,10 +430,11 @@ extern "C" {
 // b_mn == 0: B is stored [N][K];                    b_mn == 1: B is stored [K][N].
 // bf16 operands, leading dimensions multiples of 8, 16-byte aligned bases; C bf16 or fp32 (flags & 1) with ldc a multiple of 8 (bf16) or
 // 4 (fp32). `error` is a device word that stays 0 unless a wait gave up.
+// tile_rows: 128 or 256 to force a tile shape, anything else lets the launcher choose.
 // Returns 0, a negative argument error, or a CUDA error code.
 int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                    const float* bias, const void* residual, int flags, uint32_t* error, int max_ctas,
-                   int a_mn, int b_mn, void* stream) {
+                   int a_mn, int b_mn, int tile_rows, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (lda % 8 || ldb % 8) return -1;
   if ((!a_mn || !b_mn) && K % 8) return -1;   // a K-major operand has K as its row length
@@ -393,35 +443,50 @@ int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
   if ((flags & kBias) && !bias) return -1;
   if ((flags & kResidual) && (!residual || ((uintptr_t)residual & 15))) return -1;
   CUtensorMap ma, mb;
-  // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
-  int rc = a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
-                : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
-  if (rc) return rc;
-  rc = b_mn ? make_map(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64)
-            : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
-  if (rc) return rc;
   static std::once_flag once;
   static int sms = 148;
   std::call_once(once, [] {
-    cudaFuncSetAttribute(gemm_bf16_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    cudaFuncSetAttribute(gemm_bf16_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    cudaFuncSetAttribute(gemm_bf16_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    cudaFuncSetAttribute(gemm_bf16_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+#define GCOW_GEMM_ATTR(BM_, A, B) cudaFuncSetAttribute(gemm_bf16_kernel<BM_, A, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<BM_>())
+    GCOW_GEMM_ATTR(128, false, false); GCOW_GEMM_ATTR(128, false, true); GCOW_GEMM_ATTR(128, true, false); GCOW_GEMM_ATTR(128, true, true);
+    GCOW_GEMM_ATTR(256, false, false); GCOW_GEMM_ATTR(256, false, true); GCOW_GEMM_ATTR(256, true, false); GCOW_GEMM_ATTR(256, true, true);
+#undef GCOW_GEMM_ATTR
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   });
+  // 256-row tiles halve the L2 traffic per flop; keep 128-row tiles when they are needed to fill the SMs
+  const int tiles256 = ((M + 255) / 256) * ((N + BN - 1) / BN);
+  // ... and for short reductions, where the epilogue of a 256-row tile (which cannot overlap the next tile's
+  // first MMAs) would dominate
+  const int bm = (tile_rows == 128 || tile_rows == 256) ? tile_rows
+                                                          : ((tiles256 >= (sms * 4) / 5 && K >= 2048) ? 256 : 128);
+  // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
+  int rc = a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
+                : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)bm);
+  if (rc) return rc;
+  rc = b_mn ? make_map(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64)
+            : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
+  if (rc) return rc;
   Params p;
   p.C = C; p.bias = bias; p.residual = residual;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags; p.error = error;
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + bm - 1) / bm) * ((N + BN - 1) / BN);
   int grid = tiles < sms ? tiles : sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   cudaStream_t st = (cudaStream_t)stream;
-  if (!a_mn && !b_mn) gemm_bf16_kernel<false, false><<<grid, THREADS, kSmemBytes, st>>>(ma, mb, p);
-  else if (!a_mn && b_mn) gemm_bf16_kernel<false, true><<<grid, THREADS, kSmemBytes, st>>>(ma, mb, p);
-  else if (a_mn && !b_mn) gemm_bf16_kernel<true, false><<<grid, THREADS, kSmemBytes, st>>>(ma, mb, p);
-  else gemm_bf16_kernel<true, true><<<grid, THREADS, kSmemBytes, st>>>(ma, mb, p);
+#define GCOW_GEMM_LAUNCH(BM_, A, B) gemm_bf16_kernel<BM_, A, B><<<grid, Shape<BM_>::THREADS, smem_bytes<BM_>(), st>>>(ma, mb, p)
+  if (bm == 256) {
+    if (!a_mn && !b_mn) GCOW_GEMM_LAUNCH(256, false, false);
+    else if (!a_mn && b_mn) GCOW_GEMM_LAUNCH(256, false, true);
+    else if (a_mn && !b_mn) GCOW_GEMM_LAUNCH(256, true, false);
+    else GCOW_GEMM_LAUNCH(256, true, true);
+  } else {
+    if (!a_mn && !b_mn) GCOW_GEMM_LAUNCH(128, false, false);
+    else if (!a_mn && b_mn) GCOW_GEMM_LAUNCH(128, false, true);
+    else if (a_mn && !b_mn) GCOW_GEMM_LAUNCH(128, true, false);
+    else GCOW_GEMM_LAUNCH(128, true, true);
+  }
+#undef GCOW_GEMM_LAUNCH
   return (int)cudaGetLastError();
 }
 

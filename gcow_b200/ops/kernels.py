@@ -51,12 +51,13 @@ def check_errors(device: torch.device | None = None) -> None:
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, gelu: bool = False, out_dtype=torch.bfloat16,
               out: torch.Tensor | None = None, accumulate: bool = False, max_ctas: int = 0,
-              a_t: bool = False, b_t: bool = False) -> torch.Tensor:
+              a_t: bool = False, b_t: bool = False, tile_rows: int = 0) -> torch.Tensor:
     """C[M,N] = op(A) @ op(B)^T (+bias) (GELU) (+residual) on the tcgen05 kernel.
 
     a: bf16 [M,K] (or [K,M] with ``a_t``: the stored matrix is used transposed without a
     copy). b: bf16 [N,K] (or [K,N] with ``b_t``). Last dimension contiguous, leading
-    dimensions multiples of 8. bias: fp32 [N]. residual/out: [M,N] of ``out_dtype``."""
+    dimensions multiples of 8. bias: fp32 [N]. residual/out: [M,N] of ``out_dtype``.
+    ``tile_rows`` forces the 128- or 256-row tile (0: chosen from the problem size)."""
     global _launches
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
     assert a.stride(1) == 1 and b.stride(1) == 1
@@ -74,7 +75,7 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
     err = _native.cuda().gcow_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
-        flags, _error_word(a.device).data_ptr(), max_ctas, int(a_t), int(b_t),
+        flags, _error_word(a.device).data_ptr(), max_ctas, int(a_t), int(b_t), int(tile_rows),
         torch.cuda.current_stream(a.device).cuda_stream)
     if err:
         raise RuntimeError(f"gcow_gemm_bf16 refused the call: {err}")

@@ -25,11 +25,12 @@ def test_gemm_matches_fp32_reference(M, N, K):
     b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
     ref = _ref(a, b)
     for dt in (torch.float32, torch.bfloat16):
-        y = K_.gemm_bf16(a, b, out_dtype=dt)
-        K_.check_errors()
-        tol = 2e-2 if dt == torch.bfloat16 else 1e-3
-        err = (y.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
-        assert err < tol, (dt, err)
+        for rows in (128, 256):                      # both tile shapes
+            y = K_.gemm_bf16(a, b, out_dtype=dt, tile_rows=rows)
+            K_.check_errors()
+            tol = 2e-2 if dt == torch.bfloat16 else 1e-3
+            err = (y.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+            assert err < tol, (dt, rows, err)
 
 
 def test_gemm_epilogues():
@@ -40,10 +41,11 @@ def test_gemm_epilogues():
     b = (torch.randn(N, K, device="cuda") * 0.3).bfloat16()
     bias = torch.randn(N, device="cuda")
     res = torch.randn(M, N, device="cuda").bfloat16()
-    y = K_.gemm_bf16(a, b, bias=bias, gelu=True, residual=res)
-    K_.check_errors()
     ref = _ref(a, b, bias, res, True)
-    assert (y.float() - ref).abs().max().item() < 0.06
+    for rows in (128, 256):
+        y = K_.gemm_bf16(a, b, bias=bias, gelu=True, residual=res, tile_rows=rows)
+        K_.check_errors()
+        assert (y.float() - ref).abs().max().item() < 0.06
     acc = torch.ones(M, N, device="cuda")
     K_.gemm_bf16(a, b, out=acc, accumulate=True)
     assert (acc - (_ref(a, b) + 1)).abs().max().item() < 2e-2
@@ -54,7 +56,10 @@ def test_strided_operands_and_small_grid():
     big = (torch.randn(640, 512, device="cuda") * 0.5).bfloat16()
     a = big[:, :256]                      # leading dimension 512, K 256
     b = (torch.randn(1024, 256, device="cuda") * 0.5).bfloat16()
-    y = K_.gemm_bf16(a, b, out_dtype=torch.float32, max_ctas=3)   # several tiles per CTA
+    y = K_.gemm_bf16(a, b, out_dtype=torch.float32, max_ctas=3, tile_rows=256)   # several tiles per CTA
+    K_.check_errors()
+    assert (y - _ref(a, b)).abs().max().item() < 2e-2
+    y = K_.gemm_bf16(a, b, out_dtype=torch.float32, max_ctas=3, tile_rows=128)
     K_.check_errors()
     assert (y - _ref(a, b)).abs().max().item() < 2e-2
 
@@ -87,10 +92,11 @@ def test_transposed_operands_without_copies(M, N, K):
     ref = _ref(a, b)
     bt = b.t().contiguous()          # stored [K, N]
     at = a.t().contiguous()          # stored [K, M]
-    y1 = K_.gemm_bf16(a, bt, b_t=True, out_dtype=torch.float32)
-    y2 = K_.gemm_bf16(at, bt, a_t=True, b_t=True, out_dtype=torch.float32)
-    y3 = K_.gemm_bf16(at, b, a_t=True, out_dtype=torch.float32)
-    K_.check_errors()
     scale = ref.abs().max().item()
-    for y in (y1, y2, y3):
-        assert (y - ref).abs().max().item() < 1e-3 * scale + 1e-3
+    for rows in (128, 256):
+        y1 = K_.gemm_bf16(a, bt, b_t=True, out_dtype=torch.float32, tile_rows=rows)
+        y2 = K_.gemm_bf16(at, bt, a_t=True, b_t=True, out_dtype=torch.float32, tile_rows=rows)
+        y3 = K_.gemm_bf16(at, b, a_t=True, out_dtype=torch.float32, tile_rows=rows)
+        K_.check_errors()
+        for y in (y1, y2, y3):
+            assert (y - ref).abs().max().item() < 1e-3 * scale + 1e-3
