@@ -137,6 +137,21 @@ def nccl_fp32_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch
     return fut.then(lambda f: f.value()[0].div_(world))
 
 
+def codec_roundtrip_nccl_hook(state: dict, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """Variable-rate modes (fixed accuracy / fixed precision): round-trip the local bucket
+    through the codec on the GPU, then all-reduce it with NCCL in fp32. ``state`` holds
+    ``params`` (ZfpParams) and the byte counters ``bytes_in`` / ``bytes_out``."""
+    from ..codec import compress, decompress
+    buf = bucket.buffer()
+    c = compress(buf, params=state["params"], dim=1, return_index=True)
+    decompress(c, out=buf)
+    state["bytes_in"] += buf.numel() * 4
+    state["bytes_out"] += c.nbytes
+    world = dist.get_world_size()
+    fut = dist.all_reduce(buf, async_op=True).get_future()
+    return fut.then(lambda f: f.value()[0].div_(world))
+
+
 def wrap_ddp(model: torch.nn.Module, cfg: Optional[GcowConfig] = None, device: Optional[torch.device] = None,
              group=None, max_bucket_numel: Optional[int] = None):
     """Returns (ddp_model, state). ``cfg.variant == 'nccl'`` gives the uncompressed baseline."""

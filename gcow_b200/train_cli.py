@@ -28,8 +28,8 @@ import time
 import torch
 import torch.distributed as dist
 
-from .codec import compress, decompress
 from .config import GcowConfig
+from .parallel.ddp import codec_roundtrip_nccl_hook
 from .train import Trainer, make_loader
 from .utils.checkpoint import load_checkpoint, save_checkpoint
 from .utils.logging import AverageMeter, ProgressMeter, accuracy, append_csv
@@ -96,18 +96,6 @@ class DummyLoader:
             yield self.src.next()
 
 
-def roundtrip_then_nccl_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
-    """accuracy / precision modes: codec round trip of the local bucket on the GPU, then NCCL fp32."""
-    buf = bucket.buffer()
-    c = compress(buf, params=state["params"], dim=1, return_index=True)
-    decompress(c, out=buf)
-    state["bytes_in"] += buf.numel() * 4
-    state["bytes_out"] += c.nbytes
-    world = dist.get_world_size()
-    fut = dist.all_reduce(buf, async_op=True).get_future()
-    return fut.then(lambda f: f.value()[0].div_(world))
-
-
 def validate(tr: Trainer, loader, print_freq: int):
     top1, top5, losses = AverageMeter("Acc@1", ":6.2f"), AverageMeter("Acc@5", ":6.2f"), AverageMeter("Loss", ":.4e")
     tr.ddp.eval()
@@ -143,7 +131,7 @@ def run_one(args, mode: str, variable) -> dict:
         from .codec import ZfpParams
         p = ZfpParams.from_accuracy(float(variable)) if mode == "accuracy" else ZfpParams.from_precision(int(variable))
         hook_state = {"params": p, "bytes_in": 0, "bytes_out": 0}
-        tr.ddp.register_comm_hook(hook_state, roundtrip_then_nccl_hook)
+        tr.ddp.register_comm_hook(hook_state, codec_roundtrip_nccl_hook)
     if args.cifar:
         sched = torch.optim.lr_scheduler.ReduceLROnPlateau(tr.opt, factor=0.1, patience=5)   # train_resnet_cifar10.py:159
     else:
