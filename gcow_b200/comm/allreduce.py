@@ -112,9 +112,14 @@ class CompressedAllReduce:
         if self.cfg.dim != 1 or self.cfg.mode != "rate":
             raise ValueError("the fused all-reduce uses the 1-D fixed-rate codec")
         self.params = ZfpParams.from_rate(self.cfg.rate, 1)
-        if self.params.maxbits not in _FUSED_BITS:
-            raise ValueError(f"fused all-reduce supports 4, 8, 16 or 32 bits/value, not rate {self.cfg.rate}")
-        self.bits = self.params.maxbits
+        # A 1-D block can never be shorter than its 9-bit header, so rates below 2.25 are floored
+        # to 9 bits/block: the header alone, no bit plane. Every such block decodes to zeros, hence
+        # the "all-reduce" at that rate is the zero vector on every rank and needs no traffic at all.
+        self.header_only = self.params.maxbits == 9
+        if self.params.maxbits not in _FUSED_BITS and not self.header_only:
+            raise ValueError(f"fused all-reduce supports 4, 8, 16 or 32 bits/value (or the 9-bit floor), "
+                             f"not rate {self.cfg.rate}")
+        self.bits = 32 if self.header_only else self.params.maxbits
         self.group = group
         self.distributed = dist.is_available() and dist.is_initialized()
         self.world = dist.get_world_size(group) if self.distributed else 1
@@ -192,6 +197,12 @@ class CompressedAllReduce:
     def _launch(self, x: torch.Tensor, out: torch.Tensor, s: torch.cuda.Stream, variant: str | None) -> None:
         n = x.numel()
         if n == 0:
+            return
+        if self.header_only:
+            with torch.cuda.stream(s):
+                out.zero_()
+            self.calls += 1
+            self.bytes_in += n * 4
             return
         vname = variant or self.pick_variant(n)
         v = VARIANTS[vname]

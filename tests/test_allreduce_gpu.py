@@ -37,6 +37,20 @@ def test_single_rank_equals_oracle(rate):
 
 
 @pytest.mark.gpu
+def test_rate_2_is_the_header_only_floor():
+    """9 bits per block keep no bit plane: D(E(x)) = 0, and so is the reduced result (as in the host model)."""
+    p = ZfpParams.from_rate(2, 1)
+    assert p.maxbits == 9
+    x = gen(3, 4099)
+    ref = allreduce_oracle(x[None], p, "twoshot", 0)
+    assert not ref.any()
+    ar = CompressedAllReduce(1 << 16, GcowConfig(rate=2))
+    y = ar(torch.from_numpy(x).cuda())
+    ar.check()
+    assert not y.cpu().numpy().any()
+
+
+@pytest.mark.gpu
 def test_out_of_place_and_stamps():
     ar = CompressedAllReduce(1 << 18, GcowConfig(rate=8, comm_ctas=16))
     ar.enable_tracing()
