@@ -18,6 +18,8 @@ def declare(lib, proto):
     opt("gcow_decode_generic", i32, ptr, ptr, u64, u64, ptr, ptr, i32, ptr)
     opt("gcow_dbg_stage", i32, i32, i32, u64, ptr, ptr, ptr, i32, ptr)
     opt("gcow_dbg_planes", i32, i32, u64, ptr, u32, u32, i32, u32, ptr, ptr, ptr)
+    opt("gcow_dbg_gather", i32, i32, ptr, u64, u64, u64, ptr, ptr)
+    opt("gcow_dbg_encode_block", i32, i32, ptr, u64, ptr, u32, ptr, ptr, ptr)
 
 
 def _declare_comm(lib, proto):

@@ -406,6 +406,34 @@ __global__ void dbg_planes_kernel(const uint32_t* __restrict__ u, uint64_t nb, u
   sink.finish();
 }
 
+// Block formation alone (the FPGA design's gather / chunk stage): block b of the
+// array, padded at the edges, to blocks[b * 4^DIM ...].
+template <int DIM>
+__global__ void dbg_gather_kernel(const float* __restrict__ data, uint64_t nx, uint64_t ny, uint64_t nb,
+                                  float* __restrict__ blocks) {
+  constexpr int N = 1 << (2 * DIM);
+  uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nb) return;
+  float f[N];
+  gather_block<DIM>(f, data, nx, ny, b);
+#pragma unroll
+  for (int i = 0; i < N; i++) blocks[b * N + i] = f[i];
+}
+// One whole block (header + planes + padding) per thread into its own words.
+template <int DIM>
+__global__ void dbg_encode_block_kernel(const float* __restrict__ blocks, uint64_t nb, ZfpParams p,
+                                        uint32_t words_per_block, uint64_t* __restrict__ out, uint32_t* __restrict__ bits) {
+  constexpr int N = 1 << (2 * DIM);
+  uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nb) return;
+  float f[N];
+#pragma unroll
+  for (int i = 0; i < N; i++) f[i] = blocks[b * N + i];
+  WordSink sink(out + b * words_per_block);
+  bits[b] = encode_block<DIM>(f, p, sink);
+  sink.finish();
+}
+
 inline int grid_for(uint64_t items, int per_cta = kThreads, int cap = 148 * 16) {
   uint64_t g = (items + per_cta - 1) / per_cta;
   if (g < 1) g = 1;
@@ -567,6 +595,23 @@ int gcow_dbg_stage(int which, int dim, uint64_t nb, const void* a, void* b, cons
     case 5: GCOW_DISPATCH(dbg_inv_cast_kernel, (const int32_t*)a, nb, emax, shift, (float*)b); break;
     default: return -1;
   }
+  return (int)cudaGetLastError();
+}
+int gcow_dbg_gather(int dim, const float* data, uint64_t nx, uint64_t ny, uint64_t nb, float* blocks, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  int g = (int)((nb + 127) / 128);
+  if (!nb) return 0;
+  GCOW_DISPATCH(dbg_gather_kernel, data, nx, ny, nb, blocks);
+  return (int)cudaGetLastError();
+}
+// out must be zero-initialised by the caller (words_per_block u64 per block).
+int gcow_dbg_encode_block(int dim, const float* blocks, uint64_t nb, const int32_t* params, uint32_t words_per_block,
+                          uint64_t* out, uint32_t* bits, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  int g = (int)((nb + 127) / 128);
+  if (!nb) return 0;
+  ZfpParams p = load_params(params);
+  GCOW_DISPATCH(dbg_encode_block_kernel, blocks, nb, p, words_per_block, out, bits);
   return (int)cudaGetLastError();
 }
 int gcow_dbg_planes(int dim, uint64_t nb, const uint32_t* u, uint32_t budget, uint32_t prec, int header,

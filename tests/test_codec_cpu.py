@@ -131,11 +131,25 @@ def test_encode_all_bitplanes_golden(which):
     assert list(back) == list(u & mask)
 
 
-def test_encode_iblock_golden():
-    # iblock ramp, emax 9, tolerance 1e-3: precision 25, 95 payload bits
+IBLOCK = [6588397, 8685549, 10782701, 12879853, 216303600, 218400752, 220497904, 222595056,
+          426018784, 428115936, 430213088, 432310240, 635734016, 637831168, 639928320, 642025472]
+
+
+@pytest.mark.parametrize("which", [0, 1])
+def test_encode_iblock_golden(which):
+    # integer block, header value 2*9+1, tolerance 1e-3: precision 25, 95 payload bits, two words
     # (sw/tests/test_stages.cpp:742-789, hw/tests/test_encblock.cpp:166-183)
     p = ZfpParams.from_accuracy(1e-3)
-    assert p.block_precision(9, 2) == 25
+    prec = p.block_precision(9, 2)
+    assert prec == 25
+    q = np.array(IBLOCK, dtype=np.int32)
+    lib.gcow_stage_xform(q.ctypes.data, 2, 0, which)
+    u = np.zeros(16, dtype=np.uint32)
+    lib.gcow_stage_reorder(q.ctypes.data, u.ctypes.data, 2, which)
+    out = np.zeros(4, dtype=np.uint64)
+    bits = lib.gcow_stage_encode_planes(u.ctypes.data, 16, p.maxbits - 9, prec, 19, 1, out.ctypes.data, which)
+    assert bits == 9 + 95
+    assert list(out[:2]) == [72375632423897107, 1114129]
 
 
 def test_whole_3x3_golden_words():

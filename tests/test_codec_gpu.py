@@ -149,3 +149,27 @@ def test_stage_kernels_golden():
     qn = np.array(CAST_3, dtype=np.int32)
     cpu.gcow_stage_inv_cast(qn.ctypes.data, ref.ctypes.data, 16, 1, 2, 0)
     assert np.array_equal(fo.view(nb, 16)[3].cpu().numpy(), ref)
+
+
+def test_gather_and_whole_block_stage_kernels():
+    """Block formation with edge padding (5 x 7 ramp of the reference's gather test) and the
+    whole-block encoder (3 x 3 field of its integration test) as stand-alone stage kernels."""
+    lib = _native.cuda()
+    s = torch.cuda.current_stream().cuda_stream
+    ramp = torch.arange(1, 36, dtype=torch.float32, device="cuda").reshape(7, 5).contiguous()
+    blocks = torch.zeros(4 * 16, dtype=torch.float32, device="cuda")
+    assert lib.gcow_dbg_gather(2, ramp.data_ptr(), 5, 7, 4, blocks.data_ptr(), s) == 0
+    b = blocks.view(4, 16).cpu()
+    assert b[1].tolist() == [5, 5, 5, 5, 10, 10, 10, 10, 15, 15, 15, 15, 20, 20, 20, 20]
+    assert b[3].tolist() == [25, 25, 25, 25, 30, 30, 30, 30, 35, 35, 35, 35, 25, 25, 25, 25]
+    assert b[2][:4].tolist() == [21, 22, 23, 24] and b[2][12:].tolist() == [21, 22, 23, 24]
+    f3 = dev(field(3))
+    blk = torch.zeros(16, dtype=torch.float32, device="cuda")
+    assert lib.gcow_dbg_gather(2, f3.data_ptr(), 3, 3, 1, blk.data_ptr(), s) == 0
+    p = ZfpParams.from_accuracy(1e-3)
+    out = torch.zeros(9, dtype=torch.int64, device="cuda")
+    bits = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.gcow_dbg_encode_block(2, blk.data_ptr(), 1, p.as_c(), 9, out.data_ptr(), bits.data_ptr(), s) == 0
+    w = list(np.frombuffer(out.cpu().numpy().tobytes(), dtype=np.uint64)[:4])
+    assert w == [7846959668108800257, 9092781915241025288, 1168152206201298680, 33031166]
+    assert 192 < int(bits[0]) <= 256
