@@ -59,6 +59,8 @@ struct Params {
   const float* bias;       // [N] fp32 or nullptr
   const void* residual;    // same type/ld as C or nullptr
   int M, N, K, ldc, flags;
+  int batch;               // number of independent products (operands are 3-D tensor maps when > 1)
+  long long stride_c;      // elements between consecutive C (and residual) matrices
   uint32_t* error;         // device word, set non-zero when a wait gave up
 };
 
@@ -102,6 +104,16 @@ __device__ __forceinline__ bool mbar_wait(Smem* sm, uint64_t* bar, uint32_t pari
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// x = innermost coordinate, y = row coordinate, z = batch index (used only by batched launches)
+__device__ __forceinline__ void tma_load(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z, bool batched) {
+  if (batched) tma_load_3d(dst, map, bar, x, y, z);
+  else tma_load_2d(dst, map, bar, x, y);
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -170,7 +182,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int tiles_mn = tiles_m * tiles_n;
+  const int num_tiles = tiles_mn * p.batch;
+  const bool batched = p.batch > 1;
   const int kblocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -195,24 +209,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t s = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int bz = tile / tiles_mn, tmn = tile - bz * tiles_mn;
+        const int m0 = (tmn % tiles_m) * BM, n0 = (tmn / tiles_m) * BN;
         for (int kb = 0; kb < kblocks; kb++) {
           if (!(ok = mbar_wait(sm, &sm->empty[s], phase ^ 1, p.error, 1))) break;
           mbar_expect_tx(&sm->full[s], A_BYTES + B_BYTES);
           const uint32_t bar = smem_u32(&sm->full[s]);
           if (!A_MN) {
-            tma_load_2d(smem_u32(smA + s * A_BYTES), &tmap_a, bar, kb * BK, m0);
+            tma_load(smem_u32(smA + s * A_BYTES), &tmap_a, bar, kb * BK, m0, bz, batched);
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; i++)
-              tma_load_2d(smem_u32(smA + s * A_BYTES + i * 8192), &tmap_a, bar, m0 + 64 * i, kb * BK);
+              tma_load(smem_u32(smA + s * A_BYTES + i * 8192), &tmap_a, bar, m0 + 64 * i, kb * BK, bz, batched);
           }
           if (!B_MN) {
-            tma_load_2d(smem_u32(smB + s * B_BYTES), &tmap_b, bar, kb * BK, n0);
+            tma_load(smem_u32(smB + s * B_BYTES), &tmap_b, bar, kb * BK, n0, bz, batched);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; i++)
-              tma_load_2d(smem_u32(smB + s * B_BYTES + i * 8192), &tmap_b, bar, n0 + 64 * i, kb * BK);
+              tma_load(smem_u32(smB + s * B_BYTES + i * 8192), &tmap_b, bar, n0 + 64 * i, kb * BK, bz, batched);
           }
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
@@ -272,7 +287,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t t = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int bz = tile / tiles_mn, tmn = tile - bz * tiles_mn;
+      const int m0 = (tmn % tiles_m) * BM, n0 = (tmn / tiles_m) * BN;
       const uint32_t acc0 = HALVES == 1 ? (t & 1) : 0, aphase = HALVES == 1 ? ((t >> 1) & 1) : (t & 1);
       ok = mbar_wait(sm, &sm->tmem_full[acc0], aphase, p.error, 4);
       ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below need the whole warp
@@ -298,7 +314,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
               for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
             }
-            const size_t off = (size_t)m * p.ldc + n;
+            const size_t off = (size_t)bz * (size_t)p.stride_c + (size_t)m * p.ldc + n;
             if (p.flags & kOutF32) {
               float* C = reinterpret_cast<float*>(p.C) + off;
               const float* R = reinterpret_cast<const float*>(p.residual) + off;
@@ -416,6 +432,22 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t c
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
+// 3-D variant: `batch` matrices, `bstride` elements apart; box = 64 columns x box_rows x 1.
+static int make_map3(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint64_t batch,
+                     uint64_t bstride, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  if (((uintptr_t)ptr & 15) || (ld * 2) % 16 || (bstride * 2) % 16) return -11;
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {ld * 2, bstride * 2};
+  cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
 template <int BM_> constexpr size_t smem_bytes() { return Shape<BM_>::SMEM + sizeof(Smem) + 1024; }
 
 }  // namespace gemm
@@ -432,10 +464,12 @@ extern "C" {
 // 4 (fp32). `error` is a device word that stays 0 unless a wait gave up.
 // tile_rows: 128 or 256 to force a tile shape, anything else lets the launcher choose.
 // Returns 0, a negative argument error, or a CUDA error code.
-int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                   const float* bias, const void* residual, int flags, uint32_t* error, int max_ctas,
-                   int a_mn, int b_mn, int tile_rows, void* stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
+static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                       const float* bias, const void* residual, int flags, uint32_t* error, int max_ctas,
+                       int a_mn, int b_mn, int tile_rows, int batch, long long stride_a, long long stride_b,
+                       long long stride_c, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if (batch > 1 && (stride_a % 8 || stride_b % 8 || stride_c % 8)) return -1;
   if (lda % 8 || ldb % 8) return -1;
   if ((!a_mn || !b_mn) && K % 8) return -1;   // a K-major operand has K as its row length
   if ((flags & kOutF32) ? (ldc % 4) : (ldc % 8)) return -1;
@@ -455,22 +489,32 @@ int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   });
   // 256-row tiles halve the L2 traffic per flop; keep 128-row tiles when they are needed to fill the SMs
-  const int tiles256 = ((M + 255) / 256) * ((N + BN - 1) / BN);
+  const int tiles256 = ((M + 255) / 256) * ((N + BN - 1) / BN) * batch;
   // ... and for short reductions, where the epilogue of a 256-row tile (which cannot overlap the next tile's
   // first MMAs) would dominate
   const int bm = (tile_rows == 128 || tile_rows == 256) ? tile_rows
                                                           : ((tiles256 >= (sms * 4) / 5 && K >= 2048) ? 256 : 128);
   // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
-  int rc = a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
-                : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)bm);
-  if (rc) return rc;
-  rc = b_mn ? make_map(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64)
-            : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
+  int rc;
+  if (batch == 1) {
+    rc = a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
+              : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)bm);
+    if (rc) return rc;
+    rc = b_mn ? make_map(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64)
+              : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
+  } else {
+    rc = a_mn ? make_map3(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, 64)
+              : make_map3(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)bm);
+    if (rc) return rc;
+    rc = b_mn ? make_map3(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, 64)
+              : make_map3(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, BN);
+  }
   if (rc) return rc;
   Params p;
   p.C = C; p.bias = bias; p.residual = residual;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags; p.error = error;
-  const int tiles = ((M + bm - 1) / bm) * ((N + BN - 1) / BN);
+  p.batch = batch; p.stride_c = batch > 1 ? stride_c : 0;
+  const int tiles = ((M + bm - 1) / bm) * ((N + BN - 1) / BN) * batch;
   int grid = tiles < sms ? tiles : sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   cudaStream_t st = (cudaStream_t)stream;
@@ -488,6 +532,23 @@ int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
   }
 #undef GCOW_GEMM_LAUNCH
   return (int)cudaGetLastError();
+}
+
+int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                   const float* bias, const void* residual, int flags, uint32_t* error, int max_ctas,
+                   int a_mn, int b_mn, int tile_rows, void* stream) {
+  return gemm_launch(A, B, C, M, N, K, lda, ldb, ldc, bias, residual, flags, error, max_ctas, a_mn, b_mn, tile_rows,
+                     1, 0, 0, 0, stream);
+}
+
+// `batch` independent products; matrix i of A/B/C (and residual) starts stride_a/b/c elements
+// (multiples of 8) after matrix i-1. Everything else as gcow_gemm_bf16.
+int gcow_gemm_bf16_batched(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                           int batch, long long stride_a, long long stride_b, long long stride_c, const float* bias,
+                           const void* residual, int flags, uint32_t* error, int a_mn, int b_mn, int tile_rows,
+                           void* stream) {
+  return gemm_launch(A, B, C, M, N, K, lda, ldb, ldc, bias, residual, flags, error, 0, a_mn, b_mn, tile_rows, batch,
+                     stride_a, stride_b, stride_c, stream);
 }
 
 }  // extern "C"

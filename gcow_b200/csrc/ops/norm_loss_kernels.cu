@@ -211,6 +211,56 @@ softmax_xent_kernel(bf16* __restrict__ logits, const int64_t* __restrict__ targe
                    : __float2bfloat16(0.0f);
 }
 
+// -------------------------------------------------------------------- softmax
+// Row softmax of scale * x (one warp per row, the row is re-read from L1), and its
+// backward ds = scale * p * (dp - sum(dp * p)). Used by the unfused attention path.
+__global__ void __launch_bounds__(128)
+softmax_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int64_t rows, int S, float scale) {
+  const int lane = threadIdx.x & 31;
+  for (int64_t r = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5); r < rows; r += (int64_t)gridDim.x * 4) {
+    const bf16* xr = x + r * S;
+    float mx = -INFINITY;
+    for (int c = lane * 8; c < S; c += 256) { float v[8]; load8(xr + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; i++) mx = fmaxf(mx, v[i]); }
+    mx = warp_max(mx) * scale;
+    float sum = 0;
+    for (int c = lane * 8; c < S; c += 256) { float v[8]; load8(xr + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; i++) sum += __expf(v[i] * scale - mx); }
+    const float inv = 1.0f / warp_sum(sum);
+    bf16* yr = y + r * S;
+    for (int c = lane * 8; c < S; c += 256) {
+      float v[8];
+      load8(xr + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = __expf(v[i] * scale - mx) * inv;
+      store8(yr + c, v);
+    }
+  }
+}
+__global__ void __launch_bounds__(128)
+softmax_bwd_kernel(const bf16* __restrict__ dp, const bf16* __restrict__ p, bf16* __restrict__ ds, int64_t rows, int S,
+                   float scale) {
+  const int lane = threadIdx.x & 31;
+  for (int64_t r = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5); r < rows; r += (int64_t)gridDim.x * 4) {
+    const bf16 *gr = dp + r * S, *pr = p + r * S;
+    float dot = 0;
+    for (int c = lane * 8; c < S; c += 256) { float g[8], q[8]; load8(gr + c, g); load8(pr + c, q);
+#pragma unroll
+      for (int i = 0; i < 8; i++) dot += g[i] * q[i]; }
+    dot = warp_sum(dot);
+    bf16* dr = ds + r * S;
+    for (int c = lane * 8; c < S; c += 256) {
+      float g[8], q[8];
+      load8(gr + c, g); load8(pr + c, q);
+#pragma unroll
+      for (int i = 0; i < 8; i++) g[i] = scale * q[i] * (g[i] - dot);
+      store8(dr + c, g);
+    }
+  }
+}
+
 // -------------------------------------------------------------- column sums
 // part[blockIdx.y][c] = sum over this CTA's row range of g[r][c]  (bf16 in, fp32 out)
 __global__ void __launch_bounds__(256)
@@ -293,6 +343,19 @@ int gcow_softmax_xent(void* logits, const int64_t* target, float* row_loss, cons
                       int V, int ld, int ignore_index, void* stream) {
   if (ld % 8 || V > ld || rows <= 0) return -1;
   softmax_xent_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((bf16*)logits, target, row_loss, valid_count, V, ld, ignore_index);
+  return (int)cudaGetLastError();
+}
+
+int gcow_softmax_fwd(const void* x, void* y, int64_t rows, int S, float scale, void* stream) {
+  if (S % 8 || rows <= 0) return -1;
+  int64_t g = (rows + 3) / 4; if (g > 148 * 16) g = 148 * 16;
+  softmax_fwd_kernel<<<(int)g, 128, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, rows, S, scale);
+  return (int)cudaGetLastError();
+}
+int gcow_softmax_bwd(const void* dp, const void* p, void* ds, int64_t rows, int S, float scale, void* stream) {
+  if (S % 8 || rows <= 0) return -1;
+  int64_t g = (rows + 3) / 4; if (g > 148 * 16) g = 148 * 16;
+  softmax_bwd_kernel<<<(int)g, 128, 0, (cudaStream_t)stream>>>((const bf16*)dp, (const bf16*)p, (bf16*)ds, rows, S, scale);
   return (int)cudaGetLastError();
 }
 

@@ -576,3 +576,81 @@ def conv_gemm_usable(x: torch.Tensor, w: torch.Tensor, groups: int, dilation) ->
 
 def conv_gemm(x, w, b, stride, pad):
     return _ConvGemmFn.apply(x, w, b, stride, pad)
+
+
+# ------------------------------------------------ batched GEMM and attention
+def bmm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
+             out_dtype=torch.bfloat16) -> torch.Tensor:
+    """Batched C[i] = op(A[i]) @ op(B[i])^T on the tcgen05 kernel. a, b: bf16 [batch, rows, cols]
+    with contiguous matrices (row length and batch stride multiples of 8)."""
+    global _launches
+    assert a.dim() == 3 and b.dim() == 3 and a.shape[0] == b.shape[0]
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(2) == 1 and b.stride(2) == 1
+    batch = a.shape[0]
+    (K, M) = (a.shape[1], a.shape[2]) if a_t else (a.shape[2], a.shape[1])
+    (Kb, N) = (b.shape[1], b.shape[2]) if b_t else (b.shape[2], b.shape[1])
+    assert K == Kb
+    out = torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
+    flags = OUT_F32 if out_dtype == torch.float32 else 0
+    err = _native.cuda().gcow_gemm_bf16_batched(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(1), b.stride(1), out.stride(1), batch,
+        a.stride(0), b.stride(0), out.stride(0), None, None, flags, _error_word(a.device).data_ptr(),
+        int(a_t), int(b_t), 128, _stream(a.device))
+    _chk(err, "gcow_gemm_bf16_batched")
+    _launches += 1
+    return out
+
+
+class _AttentionFn(torch.autograd.Function):
+    """Unfused multi-head self-attention on own kernels: batched QK^T GEMM, row softmax,
+    batched PV GEMM; the backward is five batched GEMMs and the softmax backward.
+    q, k, v: bf16 [batch*heads, S, D] contiguous."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        global _launches
+        lib = _native.cuda()
+        s = bmm_bf16(q, k)                                   # [BH, S, S] = Q K^T
+        p = torch.empty_like(s)
+        _chk(lib.gcow_softmax_fwd(s.data_ptr(), p.data_ptr(), s.shape[0] * s.shape[1], s.shape[2], scale,
+                                  _stream(q.device)), "gcow_softmax_fwd")
+        _launches += 1
+        o = bmm_bf16(p, v, b_t=True)                         # [BH, S, D] = P V   (V stored [S(red), D])
+        ctx.save_for_backward(q, k, v, p)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, go):
+        global _launches
+        q, k, v, p = ctx.saved_tensors
+        go = go.to(torch.bfloat16).contiguous()
+        dv = bmm_bf16(p, go, a_t=True, b_t=True)             # P^T dO
+        dp = bmm_bf16(go, v)                                 # dO V^T
+        ds = torch.empty_like(p)
+        _chk(_native.cuda().gcow_softmax_bwd(dp.data_ptr(), p.data_ptr(), ds.data_ptr(), p.shape[0] * p.shape[1],
+                                             p.shape[2], ctx.scale, _stream(q.device)), "gcow_softmax_bwd")
+        _launches += 1
+        dq = bmm_bf16(ds, k, b_t=True)                       # dS K
+        dk = bmm_bf16(ds, q, a_t=True, b_t=True)             # dS^T Q
+        return dq, dk, dv, None
+
+
+def attention_enabled() -> bool:
+    """The unfused own attention is opt-in (GCOW_ATTENTION=own): it materialises the S x S
+    score matrices, so the fused library kernel behind scaled_dot_product_attention is faster."""
+    import os
+    return os.environ.get("GCOW_ATTENTION", "lib") == "own"
+
+
+def attention_usable(qkv: torch.Tensor) -> bool:
+    B, S, _, H, D = qkv.shape
+    return qkv.is_cuda and _have("gcow_gemm_bf16_batched") and S % 8 == 0 and D % 8 == 0 and S <= 4096
+
+
+def attention(qkv: torch.Tensor) -> torch.Tensor:
+    """qkv: [B, S, 3, H, D] -> context [B, S, H*D]."""
+    B, S, _, H, D = qkv.shape
+    t = qkv.to(torch.bfloat16).permute(2, 0, 3, 1, 4).contiguous().view(3, B * H, S, D)
+    o = _AttentionFn.apply(t[0], t[1], t[2], 1.0 / (D ** 0.5))
+    return o.view(B, H, S, D).permute(0, 2, 1, 3).reshape(B, S, H * D)

@@ -90,6 +90,8 @@ def gelu(x: torch.Tensor) -> torch.Tensor:
 def attention(qkv: torch.Tensor) -> torch.Tensor:
     """qkv: [B, S, 3, heads, head_dim] -> context [B, S, heads*head_dim] (no mask, no dropout)."""
     B, S, _, H, D = qkv.shape
+    if backend.get_backend() == "own" and K.attention_enabled() and K.attention_usable(qkv):
+        return K.attention(qkv)
     q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))     # [B, H, S, D]
     ctx = F.scaled_dot_product_attention(q, k, v)
     return ctx.transpose(1, 2).reshape(B, S, H * D)

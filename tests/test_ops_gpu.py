@@ -241,3 +241,29 @@ def test_conv_as_im2col_gemm_matches_torch(k, stride, pad):
     assert (gx - xr.grad).abs().max().item() < tol(xr.grad)
     assert (gw - w.grad).abs().max().item() < tol(w.grad)
     assert (gb - b.grad).abs().max().item() < tol(b.grad)
+
+
+def test_batched_gemm_and_own_attention():
+    from gcow_b200.ops import kernels as K
+    torch.manual_seed(8)
+    a = (torch.randn(6, 200, 72, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(6, 136, 72, device="cuda") * 0.5).bfloat16()
+    ref = torch.einsum("bmk,bnk->bmn", a.float(), b.float())
+    y = K.bmm_bf16(a, b, out_dtype=torch.float32)
+    y2 = K.bmm_bf16(a.transpose(1, 2).contiguous(), b.transpose(1, 2).contiguous(), a_t=True, b_t=True, out_dtype=torch.float32)
+    K.check_errors()
+    assert (y - ref).abs().max().item() < 2e-2 and (y2 - ref).abs().max().item() < 2e-2
+    # attention against scaled_dot_product_attention in fp32
+    B, S, H, D = 2, 128, 4, 64
+    qkv = (torch.randn(B, S, 3, H, D, device="cuda") * 0.7).bfloat16().requires_grad_(True)
+    w = torch.randn(B, S, H * D, device="cuda")
+    o = K.attention(qkv)
+    (o.float() * w).sum().backward()
+    K.check_errors()
+    g = qkv.grad.float().clone()
+    x = qkv.detach().float().requires_grad_(True)
+    q, k, v = (x[:, :, i].transpose(1, 2) for i in range(3))
+    oref = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, S, H * D)
+    (oref * w).sum().backward()
+    assert (o.float() - oref).abs().max().item() < 0.03
+    assert (g - x.grad).abs().max().item() < 0.05 * x.grad.abs().max().item() + 0.02
