@@ -120,7 +120,7 @@ def _declare_bn_pool(lib, proto):
     f32, i64 = C.c_float, C.c_int64
     opt("gcow_bn_supported", i32, i32)
     opt("gcow_bn_parts", i32, i64, i32)
-    opt("gcow_bn_fwd_train", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, f32, f32, i32, ptr)
+    opt("gcow_bn_fwd_train", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, f32, f32, i32, ptr)
     opt("gcow_bn_fwd_eval", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, f32, i32, ptr)
     opt("gcow_bn_bwd", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, i32, ptr)
     opt("gcow_maxpool3x3s2_fwd", i32, ptr, ptr, ptr, i32, i32, i32, i32, ptr)

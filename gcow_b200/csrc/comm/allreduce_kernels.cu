@@ -186,7 +186,7 @@ __device__ __forceinline__ void stamp(const ArArgs& a, int slot) {
 }
 
 template <int BITS>
-__global__ void __launch_bounds__(kArThreads)
+__global__ void __launch_bounds__(kArThreads, 8)
 allreduce_fused_kernel(const ArArgs a) {
   using C = Code<BITS>;
   constexpr int NW = C::NW;

@@ -32,7 +32,7 @@
 namespace gcow {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxCtas = 1024;
+constexpr int kMaxCtas = 2048;
 constexpr uint64_t kFlagBytes = 2ull * 2 * kMaxRanks * kMaxCtas * 4;
 
 enum ArVariant : int { kTwoShot = 0, kOneShot = 1, kTwoShotNvls = 2 };

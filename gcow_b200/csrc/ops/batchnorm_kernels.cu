@@ -8,9 +8,10 @@
 // per-channel scale/shift and updates the running statistics. The normalise
 // pass then applies y = x*scale + shift (+ residual), optional ReLU, in one
 // read-modify-write sweep, so the add and the activation never touch memory on
-// their own. Backward mirrors it: one sweep for dgamma/dbeta (with the ReLU
-// mask taken from y, and the masked gradient written out when a residual branch
-// needs it), one sweep for dx.
+// their own, and records the ReLU outcome as one bit per element (one byte per
+// thread and row). Backward mirrors it: one sweep for dgamma/dbeta (reading that
+// bit mask instead of the activations, and writing the masked gradient out when a
+// residual branch needs it), one sweep for dx.
 //
 // The reference's ResNet uses nn.BatchNorm2d + ReLU + add as separate ATen /
 // cuDNN operators (hw/models/resenet.py:12-22,28-40,80-89).
@@ -71,15 +72,35 @@ stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int64_t R, in
   cta_fold(s, q, C, part);
 }
 
+// Sum the per-CTA partials of 32 channels with a 32 x 8 thread block: thread (cx, py)
+// adds partials py, py+8, ... of channel c (coalesced across cx), then the 8 rows are
+// added in a fixed order, so the result does not depend on scheduling.
+constexpr int kFinX = 32, kFinY = 8;
+__device__ __forceinline__ void fold_partials(const float* __restrict__ part, int parts, int C, int c, double& s_out,
+                                              double& q_out) {
+  __shared__ double sm_s[kFinY][kFinX + 1], sm_q[kFinY][kFinX + 1];
+  const int cx = threadIdx.x, py = threadIdx.y;
+  double s = 0, q = 0;   // the variance is a difference of two large sums: fold in double
+  if (c < C)
+    for (int p = py; p < parts; p += kFinY) { s += part[(size_t)p * 2 * C + c]; q += part[(size_t)p * 2 * C + C + c]; }
+  sm_s[py][cx] = s; sm_q[py][cx] = q;
+  __syncthreads();
+  s = 0; q = 0;
+#pragma unroll
+  for (int j = 0; j < kFinY; j++) { s += sm_s[j][cx]; q += sm_q[j][cx]; }
+  s_out = s; q_out = q;
+}
+
 // ---- finalize forward: mean/rstd, scale/shift, running statistics
-__global__ void finalize_fwd_kernel(const float* __restrict__ part, int parts, int C, int64_t R, float eps, float momentum,
-                                    const float* __restrict__ gamma, const float* __restrict__ beta,
-                                    float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ scale,
-                                    float* __restrict__ shift, float* __restrict__ run_mean, float* __restrict__ run_var) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s = 0, q = 0;
-  for (int p = 0; p < parts; p++) { s += part[(size_t)p * 2 * C + c]; q += part[(size_t)p * 2 * C + C + c]; }
+__global__ void __launch_bounds__(kFinX * kFinY)
+finalize_fwd_kernel(const float* __restrict__ part, int parts, int C, int64_t R, float eps, float momentum,
+                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                    float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ scale,
+                    float* __restrict__ shift, float* __restrict__ run_mean, float* __restrict__ run_var) {
+  const int c = blockIdx.x * kFinX + threadIdx.x;
+  double s, q;
+  fold_partials(part, parts, C, c, s, q);
+  if (c >= C || threadIdx.y != 0) return;
   const double mu = s / (double)R;
   double var = q / (double)R - mu * mu;
   if (var < 0) var = 0;
@@ -107,7 +128,8 @@ __global__ void affine_from_stats_kernel(const float* __restrict__ gamma, const 
 // ---- normalise: y = x*scale + shift (+ residual) (ReLU)
 __global__ void __launch_bounds__(kThreads)
 apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, bf16* __restrict__ y,
-             const float* __restrict__ scale, const float* __restrict__ shift, int64_t R, int C, int relu) {
+             uint8_t* __restrict__ mask, const float* __restrict__ scale, const float* __restrict__ shift, int64_t R,
+             int C, int relu) {
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float sc[8], sh[8];
 #pragma unroll
@@ -125,8 +147,10 @@ apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, bf16
       for (int i = 0; i < 8; i++) v[i] += w[i];
     }
     if (relu) {
+      uint32_t bits = 0;
 #pragma unroll
-      for (int i = 0; i < 8; i++) v[i] = fmaxf(v[i], 0.0f);
+      for (int i = 0; i < 8; i++) { bits |= (v[i] > 0.0f ? 1u : 0u) << i; v[i] = fmaxf(v[i], 0.0f); }
+      if (mask) mask[r * groups + g] = (uint8_t)bits;      // bit i: channel g*8+i passed the ReLU
     }
     store8(y + off, v);
   }
@@ -135,7 +159,7 @@ apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, bf16
 // ---- backward sweep 1: partial sum(g), sum(g*xhat); g = dy masked by (y > 0) when relu.
 // When gmask_out is given, the masked gradient is written there (the residual branch's gradient).
 __global__ void __launch_bounds__(kThreads)
-bwd_reduce_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, const bf16* __restrict__ x,
+bwd_reduce_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask, const bf16* __restrict__ x,
                   const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ gmask_out,
                   float* __restrict__ part, int64_t R, int C, int relu) {
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
@@ -148,10 +172,9 @@ bwd_reduce_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, const
     load8(dy + off, gv);
     load8(x + off, xv);
     if (relu) {
-      float yv[8];
-      load8(y + off, yv);
+      const uint32_t bits = mask[r * groups + g];
 #pragma unroll
-      for (int i = 0; i < 8; i++) gv[i] = yv[i] > 0.0f ? gv[i] : 0.0f;
+      for (int i = 0; i < 8; i++) gv[i] = (bits >> i) & 1u ? gv[i] : 0.0f;
     }
     if (gmask_out) store8(gmask_out + off, gv);
 #pragma unroll
@@ -161,18 +184,19 @@ bwd_reduce_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, const
 }
 
 // ---- finalize backward: dbeta = sum g, dgamma = sum g*xhat (fixed order)
-__global__ void finalize_bwd_kernel(const float* __restrict__ part, int parts, int C, float* __restrict__ dgamma,
-                                    float* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float s = 0, q = 0;
-  for (int p = 0; p < parts; p++) { s += part[(size_t)p * 2 * C + c]; q += part[(size_t)p * 2 * C + C + c]; }
-  dbeta[c] = s; dgamma[c] = q;
+__global__ void __launch_bounds__(kFinX * kFinY)
+finalize_bwd_kernel(const float* __restrict__ part, int parts, int C, float* __restrict__ dgamma,
+                    float* __restrict__ dbeta) {
+  const int c = blockIdx.x * kFinX + threadIdx.x;
+  double s, q;
+  fold_partials(part, parts, C, c, s, q);
+  if (c >= C || threadIdx.y != 0) return;
+  dbeta[c] = (float)s; dgamma[c] = (float)q;
 }
 
 // ---- backward sweep 2: dx = gamma*rstd * (g - dbeta/R - xhat*dgamma/R)
 __global__ void __launch_bounds__(kThreads)
-bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, const bf16* __restrict__ x,
+bwd_dx_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask, const bf16* __restrict__ x,
               const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
               const float* __restrict__ dgamma, const float* __restrict__ dbeta, bf16* __restrict__ dx, int64_t R, int C,
               int relu) {
@@ -193,10 +217,9 @@ bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, const bf1
     load8(dy + off, gv);
     load8(x + off, xv);
     if (relu) {
-      float yv[8];
-      load8(y + off, yv);
+      const uint32_t bits = mask[r * groups + g];
 #pragma unroll
-      for (int i = 0; i < 8; i++) gv[i] = yv[i] > 0.0f ? gv[i] : 0.0f;
+      for (int i = 0; i < 8; i++) gv[i] = (bits >> i) & 1u ? gv[i] : 0.0f;
     }
 #pragma unroll
     for (int i = 0; i < 8; i++) gv[i] = k0[i] * (gv[i] - k1[i] - (xv[i] - mu[i]) * rs[i] * k2[i]);
@@ -207,7 +230,7 @@ bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, const bf1
 inline int grid_for(int64_t R, int C) {
   const int rstep = kThreads / (C / 8);
   int64_t g = (R + rstep - 1) / rstep;
-  if (g > 148 * 4) g = 148 * 4;
+  if (g > 148 * 3) g = 148 * 3;
   return (int)(g < 1 ? 1 : g);
 }
 inline bool shape_ok(int C) { return C % 8 == 0 && C >= 8 && C <= 2048 && kThreads % (C / 8) == 0; }
@@ -223,8 +246,9 @@ int gcow_bn_supported(int C) { return shape_ok(C) ? 1 : 0; }
 int gcow_bn_parts(int64_t R, int C) { return shape_ok(C) ? grid_for(R, C) : 0; }
 
 // Training forward. part: gcow_bn_parts * 2 * C floats of scratch. stats: 4*C floats out
-// (mean, rstd, scale, shift). run_mean/run_var may be null.
-int gcow_bn_fwd_train(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+// (mean, rstd, scale, shift). run_mean/run_var may be null. mask: R*C/8 bytes out (ReLU
+// outcome, one bit per element), required when relu != 0 and a backward pass will follow.
+int gcow_bn_fwd_train(const void* x, const void* residual, void* y, void* mask, const float* gamma, const float* beta,
                       float* run_mean, float* run_var, float* stats, float* part, int64_t R, int C, float eps,
                       float momentum, int relu, void* stream) {
   if (!shape_ok(C) || R <= 0) return -1;
@@ -232,9 +256,9 @@ int gcow_bn_fwd_train(const void* x, const void* residual, void* y, const float*
   const int g = grid_for(R, C);
   float *mean = stats, *rstd = stats + C, *scale = stats + 2 * C, *shift = stats + 3 * C;
   stats_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, part, R, C);
-  finalize_fwd_kernel<<<(C + 127) / 128, 128, 0, s>>>(part, g, C, R, eps, momentum, gamma, beta, mean, rstd, scale, shift,
-                                                      run_mean, run_var);
-  apply_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, (const bf16*)residual, (bf16*)y, scale, shift, R, C, relu);
+  finalize_fwd_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, s>>>(part, g, C, R, eps, momentum, gamma, beta, mean,
+                                                                             rstd, scale, shift, run_mean, run_var);
+  apply_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, (const bf16*)residual, (bf16*)y, (uint8_t*)mask, scale, shift, R, C, relu);
   return (int)cudaGetLastError();
 }
 
@@ -245,26 +269,26 @@ int gcow_bn_fwd_eval(const void* x, const void* residual, void* y, const float* 
   if (!shape_ok(C) || R <= 0) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   affine_from_stats_kernel<<<(C + 127) / 128, 128, 0, s>>>(gamma, beta, run_mean, run_var, eps, C, scratch, scratch + C);
-  apply_kernel<<<grid_for(R, C), kThreads, 0, s>>>((const bf16*)x, (const bf16*)residual, (bf16*)y, scratch, scratch + C, R, C, relu);
+  apply_kernel<<<grid_for(R, C), kThreads, 0, s>>>((const bf16*)x, (const bf16*)residual, (bf16*)y, nullptr, scratch, scratch + C, R, C, relu);
   return (int)cudaGetLastError();
 }
 
-// Backward. stats as written by the forward. dres (nullable) receives the gradient of the
-// residual input (the ReLU-masked dy). dgb: 2*C floats out (dgamma, dbeta).
-int gcow_bn_bwd(const void* dy, const void* y, const void* x, const float* gamma, const float* stats, void* dx,
+// Backward. stats and mask as written by the forward. dres (nullable) receives the gradient
+// of the residual input (the ReLU-masked dy). dgb: 2*C floats out (dgamma, dbeta).
+int gcow_bn_bwd(const void* dy, const void* mask, const void* x, const float* gamma, const float* stats, void* dx,
                 void* dres, float* dgb, float* part, int64_t R, int C, int relu, void* stream) {
   if (!shape_ok(C) || R <= 0) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   const int g = grid_for(R, C);
   const float *mean = stats, *rstd = stats + C;
-  bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, (bf16*)dres, part, R, C, relu);
-  finalize_bwd_kernel<<<(C + 127) / 128, 128, 0, s>>>(part, g, C, dgb, dgb + C);
-  // the second sweep re-derives the mask from y, or reads the masked gradient if it was written
+  bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const uint8_t*)mask, (const bf16*)x, mean, rstd, (bf16*)dres, part, R, C, relu);
+  finalize_bwd_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, s>>>(part, g, C, dgb, dgb + C);
+  // the second sweep applies the mask again, or reads the masked gradient if it was written
   if (dres)
-    bwd_dx_kernel<<<g, kThreads, 0, s>>>((const bf16*)dres, (const bf16*)y, (const bf16*)x, gamma, mean, rstd, dgb, dgb + C,
+    bwd_dx_kernel<<<g, kThreads, 0, s>>>((const bf16*)dres, (const uint8_t*)mask, (const bf16*)x, gamma, mean, rstd, dgb, dgb + C,
                                          (bf16*)dx, R, C, 0);
   else
-    bwd_dx_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, gamma, mean, rstd, dgb, dgb + C,
+    bwd_dx_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const uint8_t*)mask, (const bf16*)x, gamma, mean, rstd, dgb, dgb + C,
                                          (bf16*)dx, R, C, relu);
   return (int)cudaGetLastError();
 }

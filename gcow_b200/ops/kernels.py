@@ -387,21 +387,22 @@ class _BatchNormActFn(torch.autograd.Function):
         stats = torch.empty(4 * C, dtype=torch.float32, device=x.device)
         part = torch.empty(lib.gcow_bn_parts(R, C) * 2 * C, dtype=torch.float32, device=x.device)
         g32, b32 = gamma.float().contiguous(), beta.float().contiguous()
+        mask = torch.empty(R * C // 8, dtype=torch.uint8, device=x.device) if relu else None
         _chk(lib.gcow_bn_fwd_train(x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
-                                   g32.data_ptr(), b32.data_ptr(),
+                                   mask.data_ptr() if mask is not None else None, g32.data_ptr(), b32.data_ptr(),
                                    run_mean.data_ptr() if run_mean is not None else None,
                                    run_var.data_ptr() if run_var is not None else None,
                                    stats.data_ptr(), part.data_ptr(), R, C, eps, momentum, int(relu), _stream(x.device)),
              "gcow_bn_fwd_train")
         _launches += 3
-        ctx.save_for_backward(x, y, g32, stats)
+        ctx.save_for_backward(x, mask, g32, stats)      # the ReLU bit mask stands in for y in the backward
         ctx.meta = (R, C, bool(relu), residual is not None, gamma.dtype)
         return y
 
     @staticmethod
     def backward(ctx, gy):
         global _launches
-        x, y, g32, stats = ctx.saved_tensors
+        x, mask, g32, stats = ctx.saved_tensors
         R, C, relu, has_res, pdtype = ctx.meta
         lib = _native.cuda()
         if gy.dtype != torch.bfloat16 or not gy.is_contiguous(memory_format=torch.channels_last):
@@ -410,7 +411,8 @@ class _BatchNormActFn(torch.autograd.Function):
         dres = torch.empty_like(x, memory_format=torch.channels_last) if has_res else None
         dgb = torch.empty(2 * C, dtype=torch.float32, device=x.device)
         part = torch.empty(lib.gcow_bn_parts(R, C) * 2 * C, dtype=torch.float32, device=x.device)
-        _chk(lib.gcow_bn_bwd(gy.data_ptr(), y.data_ptr(), x.data_ptr(), g32.data_ptr(), stats.data_ptr(), dx.data_ptr(),
+        _chk(lib.gcow_bn_bwd(gy.data_ptr(), mask.data_ptr() if mask is not None else None, x.data_ptr(), g32.data_ptr(),
+                             stats.data_ptr(), dx.data_ptr(),
                              dres.data_ptr() if dres is not None else None, dgb.data_ptr(), part.data_ptr(), R, C,
                              int(relu), _stream(x.device)), "gcow_bn_bwd")
         _launches += 3

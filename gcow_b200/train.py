@@ -206,7 +206,9 @@ class Trainer:
         if self.hook_state is not None:
             self.hook_state.begin_step()
         loss = self.compute_loss(dev)
-        self.opt.zero_grad(set_to_none=False) if self.steps else None
+        # gradients are dropped rather than zeroed: autograd then assigns instead of accumulating, and DDP points
+        # .grad back at its bucket views during backward
+        self.opt.zero_grad(set_to_none=True)
         loss.backward()
         if self.hook_state is not None:
             self.hook_state.finish_step()
