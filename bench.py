@@ -109,10 +109,12 @@ def main() -> int:
         tr.step_device(pool[it["i"] % len(pool)])
         it["i"] += 1
 
+    nxt = {"b": loader.next()}
+
     def e2e_step():
-        inp, tgt = loader.next()
-        tr.stage(inp, tgt)
-        tr.step(inp, tgt)
+        # this step's batch was staged by the previous call; the next one is copied while this step computes
+        cur, nxt["b"] = nxt["b"], loader.next()
+        tr.step(cur[0], cur[1], prefetch=nxt["b"])
 
     for _ in range(args.warmup):
         dev_step()

@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(kThreads)
 stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int64_t R, int C) {
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 4
   for (int64_t r = (int64_t)blockIdx.x * rstep + r0; r < R; r += (int64_t)gridDim.x * rstep) {
     float v[8];
     load8(x + r * C + g * 8, v);
@@ -134,6 +135,7 @@ apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, bf16
   float sc[8], sh[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) { sc[i] = scale[g * 8 + i]; sh[i] = shift[g * 8 + i]; }
+#pragma unroll 4
   for (int64_t r = (int64_t)blockIdx.x * rstep + r0; r < R; r += (int64_t)gridDim.x * rstep) {
     const int64_t off = r * C + g * 8;
     float v[8];
@@ -166,6 +168,7 @@ bwd_reduce_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask,
   float mu[8], rs[8], s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
   for (int i = 0; i < 8; i++) { mu[i] = mean[g * 8 + i]; rs[i] = rstd[g * 8 + i]; }
+#pragma unroll 4
   for (int64_t r = (int64_t)blockIdx.x * rstep + r0; r < R; r += (int64_t)gridDim.x * rstep) {
     const int64_t off = r * C + g * 8;
     float gv[8], xv[8];
@@ -211,6 +214,7 @@ bwd_dx_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask, con
     k1[i] = dbeta[c] * invR;
     k2[i] = dgamma[c] * invR;
   }
+#pragma unroll 4
   for (int64_t r = (int64_t)blockIdx.x * rstep + r0; r < R; r += (int64_t)gridDim.x * rstep) {
     const int64_t off = r * C + g * 8;
     float gv[8], xv[8];

@@ -216,13 +216,16 @@ class Trainer:
         self.steps += 1
         return loss.detach()
 
-    def step(self, inputs, targets=None) -> StepResult:
+    def step(self, inputs, targets=None, prefetch=None) -> StepResult:
         """One end-to-end step from pinned host tensors. The returned loss is the
         previous step's (its device->host copy has completed by now), so the host
-        never stalls the device."""
+        never stalls the device. ``prefetch=(inputs, targets)`` of the NEXT step starts
+        that batch's host->device copy on the prefetch stream while this step computes."""
         if self._staged is None:
             self.stage(inputs, targets)
         dev = self._take_staged()
+        if prefetch is not None:
+            self.stage(*prefetch)
         loss = self.step_device(dev)
         slot = self.steps & 1
         self.loss_host[slot:slot + 1].copy_(loss.view(1), non_blocking=True)
