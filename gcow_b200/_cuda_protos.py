@@ -15,6 +15,7 @@ def declare(lib, proto):
     opt("gcow_decode_1d_fixed", i32, ptr, ptr, u64, i32, i32, ptr)
     opt("gcow_encode_generic_scratch_bytes", u64, ptr, u64, i32)
     opt("gcow_encode_generic", i32, ptr, u64, u64, ptr, ptr, u64, ptr, ptr, ptr)
+    opt("gcow_encode_fixed_direct", i32, ptr, u64, u64, ptr, ptr, ptr)
     opt("gcow_decode_generic", i32, ptr, ptr, u64, u64, ptr, ptr, i32, ptr)
     opt("gcow_dbg_stage", i32, i32, i32, u64, ptr, ptr, ptr, i32, ptr)
     opt("gcow_dbg_planes", i32, i32, u64, ptr, u32, u32, i32, u32, ptr, ptr, ptr)

@@ -70,6 +70,21 @@ def main(argv=None):
                    "roofline": f"of {how} {hbm:.0f} GB/s copy"}
             res["gpu"].append(row)
             print(json.dumps(row), flush=True)
+    if torch.cuda.is_available():
+        # 2-D (the reference codec's own case): 8192 x 8192 smooth field, fixed rate 8 and tolerance 1e-3
+        n2 = 8192
+        i = torch.arange(n2, device="cuda", dtype=torch.float32) * (2.0 / n2)
+        field = torch.exp(-(i[None, :] ** 2 + i[:, None] ** 2)).contiguous()
+        res["gpu_2d"] = []
+        for name, kw in (("rate8", dict(rate=8)), ("tol1e-3", dict(tolerance=1e-3))):
+            c = g.compress(field, dim=2, return_index=True, **kw)
+            out2 = torch.empty_like(field)
+            med_e, _ = time_cuda(lambda: g.compress(field, dim=2, **kw), args.iters)
+            med_d, _ = time_cuda(lambda: g.decompress(c, out=out2), args.iters)
+            row = {"case": "2d " + name, "n": n2, "enc_ms": med_e, "dec_ms": med_d, "enc_gbs": field.numel() * 4 / med_e / 1e6,
+                   "dec_gbs": field.numel() * 4 / med_d / 1e6, "bits_per_value": 8.0 * c.nbytes / field.numel()}
+            res["gpu_2d"].append(row)
+            print(json.dumps(row), flush=True)
     if args.no_cpu:
         return res
     # CPU side: reference sw codec (1 thread) and this library's oracle
@@ -97,6 +112,19 @@ def main(argv=None):
         row["oracle_mt_dec_gbs"] = n * 4 / (t2 - t1) / 1e9
         res["cpu"].append(row)
         print(json.dumps(row), flush=True)
+    if have_ref:
+        # the reference's own entry point: 2-D zfp_compress, tolerance 1e-3 and fixed rate 8
+        import math
+        n2 = 2048
+        ii = np.arange(n2, dtype=np.float64) * 2.0 / n2
+        f2 = np.exp(-(ii[None, :] ** 2 + ii[:, None] ** 2)).astype(np.float32)
+        for name, p in (("tol1e-3", ZfpParams.from_accuracy(1e-3)), ("rate8", ZfpParams.from_rate(8, 2))):
+            tup = (p.minbits, p.maxbits, p.maxprec, p.minexp)
+            t0 = time.perf_counter(); s2 = refcodec.compress(f2, tup, 2); t1 = time.perf_counter()
+            row = {"case": "2d " + name + " reference zfp_compress", "n": n2, "ref_enc_gbs": f2.size * 4 / (t1 - t0) / 1e9,
+                   "bytes": len(s2)}
+            res["cpu"].append(row)
+            print(json.dumps(row), flush=True)
     if args.json:
         Path(args.json).parent.mkdir(parents=True, exist_ok=True)
         Path(args.json).write_text(json.dumps(res, indent=1))

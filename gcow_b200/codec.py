@@ -181,6 +181,14 @@ def compress(x: torch.Tensor, *, rate: float | None = None, tolerance: float | N
             _check(lib.gcow_encode_1d_fixed(x.data_ptr(), nx, p.maxbits, out.data_ptr(), _stream_ptr()),
                    "gcow_encode_1d_fixed")
             return Compressed(out, p, shape, None)
+        if p.fixed_rate and p.maxbits % 64 == 0:
+            # whole words per block: one pass, no scratch
+            nbytes = compressed_nbytes(shape, p)
+            out = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+            _check(lib.gcow_encode_fixed_direct(x.data_ptr(), nx, ny, p.as_c(), out.data_ptr(), _stream_ptr()),
+                   "gcow_encode_fixed_direct")
+            idx = (torch.arange(blocks + 1, dtype=torch.int64, device=x.device) * p.maxbits) if return_index else None
+            return Compressed(out, p, shape, idx)
         scratch_bytes = lib.gcow_encode_generic_scratch_bytes(p.as_c(), blocks, dim)
         scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=x.device)
         out = torch.empty(cap, dtype=torch.uint8, device=x.device)

@@ -202,6 +202,24 @@ encode_slots_kernel(const float* __restrict__ in, uint64_t nx, uint64_t ny, ZfpP
   }
 }
 
+// Fixed rate with a whole number of 64-bit words per block (any DIM): block b owns
+// words [b*W, (b+1)*W) of the stream, so every thread packs straight into them and
+// no scratch, offset table or second pass is needed.
+template <int DIM>
+__global__ void __launch_bounds__(kThreads)
+encode_fixed_direct_kernel(const float* __restrict__ in, uint64_t nx, uint64_t ny, ZfpParams p, uint64_t blocks,
+                           uint64_t* __restrict__ out) {
+  const uint32_t W = p.maxbits / 64;
+  for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
+       b += (uint64_t)gridDim.x * blockDim.x) {
+    float f[1 << (2 * DIM)];
+    gather_block<DIM>(f, in, nx, ny, b);
+    WordSink sink(out + b * W);
+    encode_block<DIM>(f, p, sink);     // pads to minbits = maxbits, i.e. exactly W words
+    sink.finish();
+  }
+}
+
 // Exclusive prefix sum of block lengths -> bit offsets (blocks + 1 entries).
 // Three steps: per-tile sums, scan of the tile sums by one CTA, per-tile scan.
 constexpr int kScanTile = 2048;  // elements per CTA (256 threads x 8)
@@ -560,6 +578,21 @@ int gcow_encode_generic(const float* in, uint64_t nx, uint64_t ny, const int32_t
     scan_apply_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums, block_bits);
   }
   scatter_slots_kernel<<<g, kThreads, 0, s>>>(slots, lens, block_bits, blocks, (unsigned long long*)out);
+  return (int)cudaGetLastError();
+}
+
+// Fixed-rate encode without scratch; maxbits must be a multiple of 64 (e.g. 2-D at
+// 4, 8, 16 bits/value; 1-D at 16 bits/value and up). `out` holds blocks*maxbits/8 bytes.
+int gcow_encode_fixed_direct(const float* in, uint64_t nx, uint64_t ny, const int32_t* params, uint64_t* out,
+                             void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  ZfpParams p = load_params(params);
+  if (!is_fixed_rate(p) || p.maxbits % 64) return -1;
+  uint64_t blocks = ny ? num_blocks_2d(nx, ny) : num_blocks_1d(nx);
+  if (!blocks) return 0;
+  int g = grid_for(blocks);
+  if (ny) encode_fixed_direct_kernel<2><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, out);
+  else encode_fixed_direct_kernel<1><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, out);
   return (int)cudaGetLastError();
 }
 
