@@ -77,6 +77,7 @@ def _declare_gemm(lib, proto):
     i64 = C.c_int64
     opt("gcow_gemm_bf16_batched", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i64, i64, i64, ptr, ptr, i32,
         ptr, i32, i32, i32, ptr)
+    opt("gcow_reduce_partials", i32, ptr, ptr, i32, i64, ptr)
     opt("gcow_softmax_fwd", i32, ptr, ptr, i64, i32, C.c_float, ptr)
     opt("gcow_softmax_bwd", i32, ptr, ptr, ptr, i64, i32, C.c_float, ptr)
     opt("gcow_gemm_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, i32, ptr, i32, i32, i32, i32, ptr)

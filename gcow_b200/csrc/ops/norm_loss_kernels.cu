@@ -76,6 +76,11 @@ layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ gamma
 }
 
 // dx per row; per-CTA partial sums of dgamma/dbeta go to part[blockIdx.x][2][H].
+// A lane always works on the same columns (lane*8 + 256*k), so its dgamma/dbeta
+// contributions stay in registers across all rows of the warp (CH = H/256 chunks of
+// 8 columns, CH <= 4) and touch shared memory once at the end; wider rows (CH == 0)
+// accumulate in shared memory.
+template <int CH>
 __global__ void __launch_bounds__(128)
 layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ gamma,
                      const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ dx,
@@ -84,13 +89,57 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* dg = sm + (size_t)warp * 2 * H;
   float* db = dg + H;
-  for (int c = lane; c < H; c += 32) { dg[c] = 0; db[c] = 0; }
-  __syncwarp();
+  constexpr int NR = CH > 0 ? CH : 1;
+  float rg[NR][8], rb[NR][8], gam[NR][8];
+  if (CH > 0) {
+#pragma unroll
+    for (int k = 0; k < NR; k++)
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int c = lane * 8 + 256 * k + i;
+        rg[k][i] = 0; rb[k][i] = 0; gam[k][i] = c < H ? gamma[c] : 0.0f;
+      }
+  } else {
+    for (int c = lane; c < H; c += 32) { dg[c] = 0; db[c] = 0; }
+    __syncwarp();
+  }
   for (int r = blockIdx.x * 4 + warp; r < rows; r += gridDim.x * 4) {
     const bf16* xr = x + (size_t)r * H;
     const bf16* gr = dy + (size_t)r * H;
     const float mu = mean[r], rs = rstd[r];
     float s1 = 0, s2 = 0;
+    if (CH > 0) {
+      float xh[NR][8], gg[NR][8];
+#pragma unroll
+      for (int k = 0; k < NR; k++) {
+        const int c = lane * 8 + 256 * k;
+        if (c < H) {
+          float xv[8], gv[8];
+          load8(xr + c, xv); load8(gr + c, gv);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            xh[k][i] = (xv[i] - mu) * rs;
+            gg[k][i] = gv[i] * gam[k][i];
+            s1 += gg[k][i]; s2 += gg[k][i] * xh[k][i];
+            rg[k][i] += gv[i] * xh[k][i];
+            rb[k][i] += gv[i];
+          }
+        }
+      }
+      s1 = warp_sum(s1) / H; s2 = warp_sum(s2) / H;
+      bf16* dr = dx + (size_t)r * H;
+#pragma unroll
+      for (int k = 0; k < NR; k++) {
+        const int c = lane * 8 + 256 * k;
+        if (c < H) {
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; i++) o[i] = rs * (gg[k][i] - s1 - xh[k][i] * s2);
+          store8(dr + c, o);
+        }
+      }
+      continue;
+    }
     for (int c = lane * 8; c < H; c += 256) {
       float xv[8], gv[8];
       load8(xr + c, xv); load8(gr + c, gv);
@@ -114,6 +163,15 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
       }
       store8(dr + c, o);
     }
+  }
+  if (CH > 0) {
+#pragma unroll
+    for (int k = 0; k < NR; k++)
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int c = lane * 8 + 256 * k + i;
+        if (c < H) { dg[c] = rg[k][i]; db[c] = rb[k][i]; }
+      }
   }
   __syncthreads();
   float* out = part + (size_t)blockIdx.x * 2 * H;
@@ -317,9 +375,17 @@ int gcow_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
   const int parts = gcow_layernorm_bwd_parts(rows);
   const size_t smem = (size_t)8 * H * sizeof(float);
   static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4096 * 4); attr = true; }
-  layernorm_bwd_kernel<<<parts, 128, smem, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd,
-                                                                    (bf16*)dx, part, rows, H);
+  if (!attr) { cudaFuncSetAttribute(layernorm_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4096 * 4); attr = true; }
+  const int ch = (H + 255) / 256;
+#define GCOW_LN_BWD(CH) layernorm_bwd_kernel<CH><<<parts, 128, smem, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (bf16*)dx, part, rows, H)
+  switch (ch) {
+    case 1: GCOW_LN_BWD(1); break;
+    case 2: GCOW_LN_BWD(2); break;
+    case 3: GCOW_LN_BWD(3); break;
+    case 4: GCOW_LN_BWD(4); break;
+    default: GCOW_LN_BWD(0); break;
+  }
+#undef GCOW_LN_BWD
   reduce_partials_kernel<<<(2 * H + 255) / 256, 256, 0, (cudaStream_t)stream>>>(part, dgamma_dbeta, parts, 2 * H);
   return (int)cudaGetLastError();
 }
@@ -343,6 +409,13 @@ int gcow_softmax_xent(void* logits, const int64_t* target, float* row_loss, cons
                       int V, int ld, int ignore_index, void* stream) {
   if (ld % 8 || V > ld || rows <= 0) return -1;
   softmax_xent_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((bf16*)logits, target, row_loss, valid_count, V, ld, ignore_index);
+  return (int)cudaGetLastError();
+}
+
+// out[i] = sum_p part[p * n + i] in a fixed order (split-K partial products, bias partials).
+int gcow_reduce_partials(const float* part, float* out, int parts, int64_t n, void* stream) {
+  if (n <= 0 || parts <= 0 || n > 0x7fffffff) return -1;
+  reduce_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(part, out, parts, (int)n);
   return (int)cudaGetLastError();
 }
 

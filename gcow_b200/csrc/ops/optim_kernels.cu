@@ -77,15 +77,25 @@ adamw_kernel(const OptChunk* __restrict__ chunks, uint32_t nchunks, float lr, fl
   const float step = lr / bc1;
   for (uint32_t ci = blockIdx.x; ci < nchunks; ci += gridDim.x) {
     const OptChunk c = chunks[ci];
+    auto upd = [&](float& p, float g, float& m, float& v) {
+      g *= grad_scale;
+      p *= 1.0f - lr * wd;
+      m = b1 * m + (1.0f - b1) * g;
+      v = b2 * v + (1.0f - b2) * g * g;
+      const float denom = sqrtf(v) / bc2_sqrt + eps;
+      p -= step * (m / denom);
+    };
     for_each4(c, [&](uint32_t i, int w) {
-      for (int k = 0; k < w; k++) {
-        float p = c.p[i + k], g = c.g[i + k] * grad_scale, m = c.s0[i + k], v = c.s1[i + k];
-        p *= 1.0f - lr * wd;
-        m = b1 * m + (1.0f - b1) * g;
-        v = b2 * v + (1.0f - b2) * g * g;
-        float denom = sqrtf(v) / bc2_sqrt + eps;
-        p -= step * (m / denom);
-        c.p[i + k] = p; c.s0[i + k] = m; c.s1[i + k] = v;
+      if (w == 4) {
+        float4 p = *reinterpret_cast<float4*>(c.p + i), m = *reinterpret_cast<float4*>(c.s0 + i),
+               v = *reinterpret_cast<float4*>(c.s1 + i);
+        const float4 g = *reinterpret_cast<const float4*>(c.g + i);
+        upd(p.x, g.x, m.x, v.x); upd(p.y, g.y, m.y, v.y); upd(p.z, g.z, m.z, v.z); upd(p.w, g.w, m.w, v.w);
+        *reinterpret_cast<float4*>(c.p + i) = p;
+        *reinterpret_cast<float4*>(c.s0 + i) = m;
+        *reinterpret_cast<float4*>(c.s1 + i) = v;
+      } else {
+        upd(c.p[i], c.g[i], c.s0[i], c.s1[i]);
       }
     });
   }

@@ -83,6 +83,31 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
     return out
 
 
+def wgrad_gemm(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """dW[N, K] = g^T x for g [M, N], x [M, K] (both stored with the reduction dimension M outermost), fp32.
+    The output has few tiles while M is long, so the reduction is split across CTAs: the rows are cut into
+    ``s`` slabs that run as one batched launch, and the ``s`` partial products are added in a fixed order."""
+    global _launches
+    M, N = g.shape
+    K = x.shape[1]
+    tiles = -(-N // 128) * -(-K // 256)
+    s = 1
+    while s < 8 and tiles * s < 120 and M % (2 * s) == 0 and (M // (2 * s)) % 64 == 0 and M // (2 * s) >= 512:
+        s *= 2
+    if s == 1 or g.stride(0) != N or x.stride(0) != K:
+        return gemm_bf16(g, x, a_t=True, b_t=True, out_dtype=torch.float32)
+    lib = _native.cuda()
+    part = torch.empty((s, N, K), dtype=torch.float32, device=g.device)
+    err = lib.gcow_gemm_bf16_batched(
+        g.data_ptr(), x.data_ptr(), part.data_ptr(), N, K, M // s, N, K, K, s, (M // s) * N, (M // s) * K, N * K,
+        None, None, OUT_F32, _error_word(g.device).data_ptr(), 1, 1, 0, _stream(g.device))
+    _chk(err, "gcow_gemm_bf16_batched")
+    out = torch.empty((N, K), dtype=torch.float32, device=g.device)
+    _chk(lib.gcow_reduce_partials(part.data_ptr(), out.data_ptr(), s, N * K, _stream(g.device)), "gcow_reduce_partials")
+    _launches += 2
+    return out
+
+
 def _gemm_ok(x2d: torch.Tensor, w: torch.Tensor) -> bool:
     return x2d.is_cuda and x2d.shape[1] % 8 == 0 and w.shape[1] % 8 == 0 and x2d.shape[0] >= 64
 
@@ -136,7 +161,7 @@ class _LinearFn(torch.autograd.Function):
             gx = gemm_bf16(g, wb, b_t=True).view(x_shape)
         if ctx.needs_input_grad[1]:
             # dW[N,K] = g^T @ x: both g [M,N] and x [M,K] are stored [reduction M][rows]
-            gw = gemm_bf16(g, xb, a_t=True, b_t=True, out_dtype=torch.float32)[:N].to(w_dtype)
+            gw = wgrad_gemm(g, xb)[:N].to(w_dtype)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)[:N]
         return gx, gw, gb
@@ -206,7 +231,7 @@ class _Conv1x1Fn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             gx = gemm_bf16(g, wb, b_t=True).view(N, H, W, C).permute(0, 3, 1, 2)
         if ctx.needs_input_grad[1]:
-            gw = gemm_bf16(g, xm, a_t=True, b_t=True, out_dtype=torch.float32)
+            gw = wgrad_gemm(g, xm)
             gw = gw.view(wshape).to(wdtype).contiguous(memory_format=torch.channels_last)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)
@@ -555,7 +580,7 @@ class _ConvGemmFn(torch.autograd.Function):
                                             _stream(g.device)), "gcow_col2im")
             _launches += 1
         if ctx.needs_input_grad[1]:
-            gw = gemm_bf16(g, col, a_t=True, b_t=True, out_dtype=torch.float32)   # [Co, K]
+            gw = wgrad_gemm(g, col)                                               # [Co, K]
             gw = gw.view(Co, KH, KW, C).permute(0, 3, 1, 2).to(wdtype).contiguous(memory_format=torch.channels_last)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)

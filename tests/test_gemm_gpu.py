@@ -100,3 +100,15 @@ def test_transposed_operands_without_copies(M, N, K):
         K_.check_errors()
         for y in (y1, y2, y3):
             assert (y - ref).abs().max().item() < 1e-3 * scale + 1e-3
+
+
+def test_wgrad_split_k_matches_reference():
+    from gcow_b200.ops import kernels as K_
+    torch.manual_seed(9)
+    for M, N, K in ((8192, 256, 512), (16384, 1024, 1024), (4096, 64, 2304), (1000, 256, 256)):
+        g = (torch.randn(M, N, device="cuda") * 0.3).bfloat16()
+        x = (torch.randn(M, K, device="cuda") * 0.3).bfloat16()
+        ref = g.float().t() @ x.float()
+        y = K_.wgrad_gemm(g, x)
+        K_.check_errors()
+        assert y.shape == (N, K) and (y - ref).abs().max().item() < 2e-3 * ref.abs().max().item() + 1e-2
