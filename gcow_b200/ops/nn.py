@@ -87,11 +87,37 @@ def gelu(x: torch.Tensor) -> torch.Tensor:
     return F.gelu(x)
 
 
+class _PackedSdpaFn(torch.autograd.Function):
+    """scaled_dot_product_attention on a packed [B, S, 3, H, D] tensor. Autograd through
+    three slices of one tensor costs three zero-filled buffers, three copies and two adds per
+    layer; here the three gradients are written into one packed tensor with a single copy."""
+
+    @staticmethod
+    def forward(ctx, qkv):
+        B, S, _, H, D = qkv.shape
+        with torch.enable_grad():
+            q, k, v = (qkv[:, :, i].transpose(1, 2).detach().requires_grad_(True) for i in range(3))
+            o = F.scaled_dot_product_attention(q, k, v)                # [B, H, S, D]
+        ctx.inner = (q, k, v, o)
+        ctx.shape = (B, S, H, D)
+        return o.detach().transpose(1, 2).reshape(B, S, H * D)
+
+    @staticmethod
+    def backward(ctx, go):
+        q, k, v, o = ctx.inner
+        ctx.inner = None
+        B, S, H, D = ctx.shape
+        dq, dk, dv = torch.autograd.grad(o, (q, k, v), go.reshape(B, S, H, D).transpose(1, 2))
+        return torch.stack((dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)), dim=2)
+
+
 def attention(qkv: torch.Tensor) -> torch.Tensor:
     """qkv: [B, S, 3, heads, head_dim] -> context [B, S, heads*head_dim] (no mask, no dropout)."""
     B, S, _, H, D = qkv.shape
     if backend.get_backend() == "own" and K.attention_enabled() and K.attention_usable(qkv):
         return K.attention(qkv)
+    if qkv.is_cuda and qkv.requires_grad and backend.get_backend() == "own":
+        return _PackedSdpaFn.apply(qkv)
     q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))     # [B, H, S, D]
     ctx = F.scaled_dot_product_attention(q, k, v)
     return ctx.transpose(1, 2).reshape(B, S, H * D)

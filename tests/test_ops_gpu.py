@@ -267,3 +267,21 @@ def test_batched_gemm_and_own_attention():
     (oref * w).sum().backward()
     assert (o.float() - oref).abs().max().item() < 0.03
     assert (g - x.grad).abs().max().item() < 0.05 * x.grad.abs().max().item() + 0.02
+
+
+def test_packed_sdpa_matches_plain_autograd():
+    from gcow_b200.ops import nn as gnn, set_backend
+    torch.manual_seed(10)
+    B, S, H, D = 2, 64, 4, 64
+    base = (torch.randn(B, S, 3, H, D, device="cuda") * 0.5).bfloat16()
+    w = torch.randn(B, S, H * D, device="cuda").bfloat16()
+    outs = {}
+    for be in ("torch", "own"):
+        set_backend(be)
+        qkv = base.clone().requires_grad_(True)
+        o = gnn.attention(qkv * 1.0)
+        (o * w).sum().backward()
+        outs[be] = (o.detach().float(), qkv.grad.float())
+    set_backend("own")
+    assert (outs["own"][0] - outs["torch"][0]).abs().max().item() < 1e-2
+    assert (outs["own"][1] - outs["torch"][1]).abs().max().item() < 2e-2 * outs["torch"][1].abs().max().item() + 1e-3
