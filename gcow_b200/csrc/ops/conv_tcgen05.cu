@@ -1,0 +1,511 @@
+// Implicit-GEMM convolution on the 5th-generation tensor cores (sm_100a), NHWC bf16,
+// stride 1, any odd or even filter size with zero padding. No im2col matrix is ever
+// written: the TMA unit gathers the shifted input window of every filter tap
+// straight from the activation tensor, and its out-of-bounds zero fill IS the padding.
+//
+//   forward   Y[n,h,w,co] = sum_{r,s,ci} X[n, h+r-ph, w+s-pw, ci] * Wt[co,r,s,ci]
+//             GEMM view: M = output pixels, N = Co, K = (r,s,ci).
+//             An M tile is a box of bw x bh x bn output pixels (<= 128 rows) of a 4-D tensor
+//             map {C, W, H, N}; for tap (r,s) the same box is fetched at (w0+s-pw, h0+r-ph).
+//             Rows of the box land in shared memory as 128-byte channel rows with the
+//             128-byte swizzle, exactly the K-major operand layout of tcgen05.mma.
+//   dgrad     the same kernel on dY with the filter flipped and its channel roles swapped
+//             (flip_weights_kernel), padding k-1-p.
+//   wgrad     dW[co, (r,s,ci)] = sum_pixels dY[pixel, co] * X[pixel + (r,s) - p, ci]
+//             GEMM view: M = Co, N = taps*Ci, K = pixels. Both operands are MN-major:
+//             64-pixel boxes of dY (A) and of the shifted X (B, one 64-channel box per
+//             (tap, channel chunk) column group, each with its own shift). The pixel
+//             range is split over CTAs; fp32 partial results are summed by a second
+//             kernel in a fixed order.
+//
+// Same structure as the GEMM kernel: persistent CTAs, warp 0 issues TMA loads into an
+// mbarrier ring, one thread of warp 1 issues tcgen05.mma into two alternating TMEM
+// accumulators, eight epilogue warps read them back with tcgen05.ld. No multicast;
+// every wait is bounded and gives up by raising an error word.
+//
+// Replaces the cuDNN 3x3 convolutions behind nn.Conv2d in the reference's models
+// (hw/models/resenet.py:14,48-50).
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace gcow {
+namespace conv {
+
+using namespace gcow::tc;
+
+constexpr int BK = 64, UMMA_K = 16, MAX_STAGES = 8;
+constexpr int A_BYTES = 128 * BK * 2;          // 128 rows (or two 64-column boxes) of 128 bytes
+constexpr int EPI_WARPS = 8, THREADS = 64 + 32 * EPI_WARPS;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int kSmemBudget = 200 * 1024;
+
+enum Flags : int { kBias = 2 };
+
+struct Params {
+  void* out;            // forward: bf16 [N, H, W, Co]; wgrad: fp32 partials [split][Co][taps * Ci]
+  const float* bias;    // forward only, [Co] or nullptr
+  int N, H, W;          // extents of the output pixels (forward) / of dY (wgrad)
+  int Ci, Co;           // forward: reduction channels and output channels; wgrad: channels of X and of dY
+  int kh, kw, pad_h, pad_w;
+  int bw, bh, bn;       // pixel box of one TMA load
+  int tiles_w, tiles_h, tiles_n;   // number of pixel boxes along W, H, N
+  int bn_cols;          // GEMM N of one tile: 64, 128 or 256
+  int stages;
+  int split, chunks_per_split;     // wgrad: CTAs-groups over the pixel range
+  int flags;
+  uint32_t* error;
+};
+
+struct Smem {
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], drain;
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+};
+
+template <bool WGRAD>
+__global__ void __launch_bounds__(THREADS, 1)
+conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int b_bytes = p.bn_cols * BK * 2;
+  const int stage_bytes = A_BYTES + b_bytes;
+  const int STAGES = p.stages;
+  Smem* sm = reinterpret_cast<Smem*>(base + STAGES * stage_bytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int taps = p.kh * p.kw;
+  const int cchunks = p.Ci / BK;
+  const int pix_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
+  // forward: tiles over (pixel box, Co tile), reduction over (tap, channel chunk)
+  // wgrad:   tiles over (split, Co tile, column tile of taps*Ci), reduction over pixel boxes
+  const int tiles_c = WGRAD ? (p.Co + 127) / 128 : (p.Co + p.bn_cols - 1) / p.bn_cols;
+  const int col_groups = taps * cchunks;                          // wgrad: 64-column groups of N
+  const int tiles_col = (col_groups * BK + p.bn_cols - 1) / p.bn_cols;
+  const int num_tiles = WGRAD ? p.split * tiles_c * tiles_col : pix_tiles * tiles_c;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&sm->tmem_full[a], 1); mbar_init(&sm->tmem_empty[a], EPI_WARPS * 32); }
+    mbar_init(&sm->drain, 1);
+    sm->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  // reduction length of a tile (wgrad: the pixel boxes of its split)
+  auto tile_kblocks = [&](int tile) -> int {
+    if (!WGRAD) return taps * cchunks;
+    const int sp = tile / (tiles_c * tiles_col);
+    const int first = sp * p.chunks_per_split;
+    int last = first + p.chunks_per_split;
+    if (last > pix_tiles) last = pix_tiles;
+    return last - first;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t s = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!WGRAD) {
+          const int tcn = tile % tiles_c, pt = tile / tiles_c;
+          const int w0 = (pt % p.tiles_w) * p.bw, h0 = ((pt / p.tiles_w) % p.tiles_h) * p.bh;
+          const int n0 = (pt / (p.tiles_w * p.tiles_h)) * p.bn;
+          const int co0 = tcn * p.bn_cols;
+          const uint32_t a_tx = (uint32_t)(p.bw * p.bh * p.bn) * 128u;
+          for (int tap = 0; tap < taps && ok; tap++) {
+            const int r = tap / p.kw, sx = tap - r * p.kw;
+            for (int cc = 0; cc < cchunks; cc++) {
+              if (!(ok = mbar_wait_abortable(&sm->abort, &sm->empty[s], phase ^ 1, p.error, 1))) break;
+              mbar_expect_tx(&sm->full[s], a_tx + (uint32_t)b_bytes);
+              const uint32_t bar = smem_u32(&sm->full[s]);
+              uint8_t* st = base + s * stage_bytes;
+              tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0);
+              tma_load_2d(smem_u32(st + A_BYTES), &map_b, bar, tap * p.Ci + cc * BK, co0);
+              if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
+            }
+          }
+        } else {
+          const int tcol = tile % tiles_col;
+          int rest = tile / tiles_col;
+          const int tco = rest % tiles_c, sp = rest / tiles_c;
+          const int co0 = tco * 128;
+          const int g0 = tcol * (p.bn_cols / BK);                 // first 64-column group of this tile
+          const int first = sp * p.chunks_per_split, nk = tile_kblocks(tile);
+          for (int kb = 0; kb < nk; kb++) {
+            const int chunk = first + kb;
+            const int w0 = (chunk % p.tiles_w) * p.bw, h0 = ((chunk / p.tiles_w) % p.tiles_h) * p.bh;
+            const int n0 = (chunk / (p.tiles_w * p.tiles_h)) * p.bn;
+            if (!(ok = mbar_wait_abortable(&sm->abort, &sm->empty[s], phase ^ 1, p.error, 1))) break;
+            mbar_expect_tx(&sm->full[s], (uint32_t)(A_BYTES + b_bytes));
+            const uint32_t bar = smem_u32(&sm->full[s]);
+            uint8_t* st = base + s * stage_bytes;
+            // channel coordinates past the tensor read zeros
+            tma_load_4d(smem_u32(st), &map_a, bar, co0, w0, h0, n0);
+            tma_load_4d(smem_u32(st + 8192), &map_a, bar, co0 + 64, w0, h0, n0);
+            for (int i = 0; i < p.bn_cols / BK; i++) {
+              const int g = g0 + i;
+              int tap = g / cchunks, c0 = (g - tap * cchunks) * BK;
+              if (g >= col_groups) { tap = 0; c0 = p.Ci; }
+              const int r = tap / p.kw, sx = tap - r * p.kw;
+              tma_load_4d(smem_u32(st + A_BYTES + i * 8192), &map_b, bar, c0, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0);
+            }
+            if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
+          }
+        }
+      }
+      if (!ok) {
+        // giving up: let copies already in flight land before the CTA's shared memory is released
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, operand major-ness, N = bn_cols, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)WGRAD << 15) | ((uint32_t)WGRAD << 16) |
+                             ((uint32_t)(p.bn_cols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      constexpr uint64_t kstep = WGRAD ? (2048 >> 4) : (32 >> 4);
+      uint32_t s = 0, phase = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+        const uint32_t acc = t & 1, aphase = (t >> 1) & 1;
+        const int nk = tile_kblocks(tile);
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->tmem_empty[acc], aphase ^ 1, p.error, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int kb = 0; kb < nk; kb++) {
+          if (!(ok = mbar_wait_abortable(&sm->abort, &sm->full[s], phase, p.error, 3))) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(base + s * stage_bytes), sb = sa + A_BYTES;
+          const uint64_t da = WGRAD ? smem_desc_mn_sw128(sa) : smem_desc_sw128(sa);
+          const uint64_t db = WGRAD ? smem_desc_mn_sw128(sb) : smem_desc_sw128(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++)
+            tc_mma(d_tmem, da + kstep * k, db + kstep * k, idesc, (kb | k) != 0);
+          tc_commit(&sm->empty[s]);
+          if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&sm->tmem_full[acc]);
+      }
+      // drain: everything issued by this thread has finished before TMEM is freed
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < kSpinLimit; it++) if (mbar_try_wait(&sm->drain, 0)) break;
+    }
+  } else {
+    // ----------------------------------------------------------------- epilogue
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int ew = warp - 2;
+    const int cols = p.bn_cols / 2;               // columns of the accumulator this warp drains
+    const int col0 = (ew / 4) * cols;
+    const int nch = cols / 32;                    // 1, 2 or 4 chunks of 32 columns
+    const int row = q * 32 + lane;                // accumulator row of this thread
+    uint32_t t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+      const uint32_t acc = t & 1, aphase = (t >> 1) & 1;
+      // where this thread's row goes
+      bool row_ok;
+      size_t row_off;        // element offset of the row's first column of this tile
+      int n_first, n_limit;  // first column index of this tile, and the column bound
+      if (!WGRAD) {
+        const int tcn = tile % tiles_c, pt = tile / tiles_c;
+        const int iw = row % p.bw, ih = (row / p.bw) % p.bh, in = row / (p.bw * p.bh);
+        const int w = (pt % p.tiles_w) * p.bw + iw, h = ((pt / p.tiles_w) % p.tiles_h) * p.bh + ih;
+        const int n = (pt / (p.tiles_w * p.tiles_h)) * p.bn + in;
+        row_ok = in < p.bn && w < p.W && h < p.H && n < p.N;
+        n_first = tcn * p.bn_cols;
+        n_limit = p.Co;
+        row_off = (((size_t)n * p.H + h) * p.W + w) * (size_t)p.Co;
+      } else {
+        const int tcol = tile % tiles_col;
+        int rest = tile / tiles_col;
+        const int tco = rest % tiles_c, sp = rest / tiles_c;
+        const int co = tco * 128 + row;
+        const int ncols = col_groups * BK;
+        row_ok = co < p.Co;
+        n_first = tcol * p.bn_cols;
+        n_limit = ncols;
+        row_off = ((size_t)sp * p.Co + co) * (size_t)ncols;
+      }
+      ok = mbar_wait_abortable(&sm->abort, &sm->tmem_full[acc], aphase, p.error, 4);
+      ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below need the whole warp
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256 + col0;
+      auto process = [&](const uint32_t (&r)[32], int c) {
+        const int n = n_first + col0 + c * 32;
+        if (row_ok && n < n_limit) {
+          if (WGRAD) {
+            float* C = reinterpret_cast<float*>(p.out) + row_off + n;
+            if (n + 32 <= n_limit) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(C + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j++) if (n + j < n_limit) C[j] = __uint_as_float(r[j]);
+            }
+          } else {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+            if (p.flags & kBias) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) if (n + j < n_limit) v[j] += __ldg(p.bias + n + j);
+            }
+            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.out) + row_off + n;
+            if (n + 32 <= n_limit) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                *reinterpret_cast<uint4*>(C + j) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j++) if (n + j < n_limit) C[j] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+      };
+      uint32_t ra[32], rb[32];
+      tc_ld32(taddr, ra);
+#pragma unroll 1
+      for (int c = 0; c < nch; c += 2) {
+        tc_wait_ld();
+        if (c + 1 < nch) tc_ld32(taddr + (c + 1) * 32, rb);
+        process(ra, c);
+        if (c + 1 < nch) {
+          tc_wait_ld();
+          if (c + 2 < nch) tc_ld32(taddr + (c + 2) * 32, ra);
+          process(rb, c + 1);
+        }
+      }
+      // this accumulator has been read out: the MMA warp may overwrite it
+      tc_fence_before();
+      mbar_arrive(&sm->tmem_empty[acc]);
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// wt[ci][kh-1-r][kw-1-s][co] = w[co][r][s][ci]: the filter of the data-gradient convolution
+__global__ void flip_weights_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int kh,
+                                    int kw, int Ci) {
+  const size_t total = (size_t)Co * kh * kw * Ci;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    // i indexes the destination, so that writes are coalesced
+    const int co = (int)(i % Co);
+    size_t rest = i / Co;
+    const int s = (int)(rest % kw); rest /= kw;
+    const int r = (int)(rest % kh);
+    const int ci = (int)(rest / kh);
+    wt[i] = w[(((size_t)co * kh + (kh - 1 - r)) * kw + (kw - 1 - s)) * Ci + ci];
+  }
+}
+
+// ------------------------------------------------------------------- host side
+// 4-D bf16 NHWC tensor as {C, W, H, N}; box = 64 channels x bw x bh x bn pixels.
+static int make_map_nhwc(CUtensorMap* map, const void* ptr, uint64_t N, uint64_t H, uint64_t W, uint64_t C, uint32_t bw,
+                         uint32_t bh, uint32_t bn) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -10;
+  if (((uintptr_t)ptr & 15) || (C * 2) % 16) return -11;
+  if (bw > 256 || bh > 256 || bn > 256) return -11;
+  cuuint64_t dims[4] = {C, W, H, N};
+  cuuint64_t strides[3] = {C * 2, W * C * 2, H * W * C * 2};
+  cuuint32_t box[4] = {(cuuint32_t)BK, bw, bh, bn};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+// 2-D bf16 [rows][cols] row-major, box = 64 columns x box_rows
+static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -10;
+  if (((uintptr_t)ptr & 15) || (cols * 2) % 16) return -11;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+// Pixel box bw x bh x bn covering a W x H x N grid with the fewest wasted rows.
+// `exact` != 0: the box must hold exactly `rows` pixels (wgrad: 64); else at most `rows`.
+// Ties go to the longer contiguous run (larger bw, then bh).
+static void pick_box(int W, int H, int N, int rows, int exact, int* obw, int* obh, int* obn) {
+  double best = -1.0;
+  *obw = 1; *obh = 1; *obn = rows;
+  for (int bw = 1; bw <= rows; bw++) {
+    if (bw > W + 7) break;
+    for (int bh = 1; bw * bh <= rows; bh++) {
+      if (bh > H + 7) break;
+      int bn = rows / (bw * bh);
+      if (bn > N) bn = N;
+      if (bn > 256) bn = 256;
+      if (bn < 1) continue;
+      if (exact && bw * bh * bn != rows) continue;
+      const double covered = (double)((W + bw - 1) / bw) * bw * ((H + bh - 1) / bh) * bh * ((N + bn - 1) / bn) * bn;
+      const double eff = ((double)W * H * N / covered) * ((double)(bw * bh * bn) / rows);
+      const double score = eff + 1e-4 * bw + 1e-6 * bh;
+      if (score > best) { best = score; *obw = bw; *obh = bh; *obn = bn; }
+    }
+  }
+}
+
+static int device_sms() {
+  static std::once_flag once;
+  static int sms = 148;
+  std::call_once(once, [] {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(conv_igemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048);
+    cudaFuncSetAttribute(conv_igemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048);
+  });
+  return sms;
+}
+
+static int stages_for(int bn_cols) {
+  int st = kSmemBudget / (A_BYTES + bn_cols * BK * 2);
+  return st > MAX_STAGES ? MAX_STAGES : st;
+}
+
+struct WgradPlan { int bw, bh, bn, tiles_w, tiles_h, tiles_n, split, per; };
+
+static WgradPlan wgrad_plan(int N, int Ho, int Wo, int Ci, int Co, int taps, int sms) {
+  WgradPlan q;
+  pick_box(Wo, Ho, N, 64, 1, &q.bw, &q.bh, &q.bn);
+  q.tiles_w = (Wo + q.bw - 1) / q.bw; q.tiles_h = (Ho + q.bh - 1) / q.bh; q.tiles_n = (N + q.bn - 1) / q.bn;
+  const int chunks = q.tiles_w * q.tiles_h * q.tiles_n;
+  const int base = ((Co + 127) / 128) * ((taps * Ci + 255) / 256);
+  int split = (sms + base - 1) / base;
+  if (split > (chunks + 7) / 8) split = (chunks + 7) / 8;      // at least 8 pixel boxes per CTA
+  if (split < 1) split = 1;
+  q.per = (chunks + split - 1) / split;
+  q.split = (chunks + q.per - 1) / q.per;                       // no empty split
+  return q;
+}
+
+}  // namespace conv
+}  // namespace gcow
+
+using namespace gcow::conv;
+
+extern "C" {
+
+// y[N,Ho,Wo,Co] = conv(x[N,Hin,Win,Ci], w[Co,kh,kw,Ci]) (+ bias), stride 1, zero padding (pad_h, pad_w);
+// Ho = Hin + 2*pad_h - kh + 1. bf16, NHWC; Ci a multiple of 64, Co a multiple of 8.
+// `error` is a device word that stays 0 unless a wait gave up. Returns 0, a negative argument error or a CUDA error.
+int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int N, int Hin, int Win, int Ci, int Co,
+                  int kh, int kw, int pad_h, int pad_w, uint32_t* error, void* stream) {
+  const int Ho = Hin + 2 * pad_h - kh + 1, Wo = Win + 2 * pad_w - kw + 1;
+  if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
+  if (Ci % 64 || Co % 8 || kh < 1 || kw < 1 || pad_h < 0 || pad_w < 0) return -1;
+  if ((uintptr_t)y & 15) return -1;
+  const int sms = device_sms();
+  Params p{};
+  pick_box(Wo, Ho, N, 128, 0, &p.bw, &p.bh, &p.bn);
+  p.tiles_w = (Wo + p.bw - 1) / p.bw; p.tiles_h = (Ho + p.bh - 1) / p.bh; p.tiles_n = (N + p.bn - 1) / p.bn;
+  p.bn_cols = Co <= 64 ? 64 : (Co <= 128 ? 128 : 256);
+  p.stages = stages_for(p.bn_cols);
+  p.out = y; p.bias = bias; p.N = N; p.H = Ho; p.W = Wo; p.Ci = Ci; p.Co = Co;
+  p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w;
+  p.split = 1; p.chunks_per_split = 0;
+  p.flags = bias ? kBias : 0;
+  p.error = error;
+  CUtensorMap ma, mb;
+  int rc = make_map_nhwc(&ma, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, p.bw, p.bh, p.bn);
+  if (rc) return rc;
+  rc = make_map_2d(&mb, w, (uint64_t)Co, (uint64_t)kh * kw * Ci, (uint32_t)p.bn_cols);
+  if (rc) return rc;
+  const long long tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n * ((Co + p.bn_cols - 1) / p.bn_cols);
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  const size_t smem = (size_t)p.stages * (A_BYTES + p.bn_cols * BK * 2) + sizeof(Smem) + 1024;
+  conv_igemm_kernel<false><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+// Number of fp32 partial results gcow_conv_wgrad writes for these extents (the first dimension of `part`).
+int gcow_conv_wgrad_split(int N, int Hin, int Win, int Ci, int Co, int kh, int kw, int pad_h, int pad_w) {
+  const int Ho = Hin + 2 * pad_h - kh + 1, Wo = Win + 2 * pad_w - kw + 1;
+  if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
+  return wgrad_plan(N, Ho, Wo, Ci, Co, kh * kw, device_sms()).split;
+}
+
+// part[split][Co][kh*kw*Ci] (fp32) = partial sums over pixel ranges of dy[N,Ho,Wo,Co]^T * shifted x[N,Hin,Win,Ci];
+// the caller adds the `split` slices (gcow_reduce_partials). Ci a multiple of 64, Co a multiple of 8.
+int gcow_conv_wgrad(const void* dy, const void* x, float* part, int N, int Hin, int Win, int Ci, int Co, int kh, int kw,
+                    int pad_h, int pad_w, uint32_t* error, void* stream) {
+  const int Ho = Hin + 2 * pad_h - kh + 1, Wo = Win + 2 * pad_w - kw + 1;
+  if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
+  if (Ci % 64 || Co % 8 || kh < 1 || kw < 1 || pad_h < 0 || pad_w < 0) return -1;
+  if ((uintptr_t)part & 15) return -1;
+  const int sms = device_sms();
+  const WgradPlan q = wgrad_plan(N, Ho, Wo, Ci, Co, kh * kw, sms);
+  Params p{};
+  p.bw = q.bw; p.bh = q.bh; p.bn = q.bn; p.tiles_w = q.tiles_w; p.tiles_h = q.tiles_h; p.tiles_n = q.tiles_n;
+  p.bn_cols = 256;
+  p.stages = stages_for(p.bn_cols);
+  p.out = part; p.bias = nullptr; p.N = N; p.H = Ho; p.W = Wo; p.Ci = Ci; p.Co = Co;
+  p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w;
+  p.split = q.split; p.chunks_per_split = q.per;
+  p.flags = 0;
+  p.error = error;
+  CUtensorMap ma, mb;
+  int rc = make_map_nhwc(&ma, dy, (uint64_t)N, (uint64_t)Ho, (uint64_t)Wo, (uint64_t)Co, q.bw, q.bh, q.bn);
+  if (rc) return rc;
+  rc = make_map_nhwc(&mb, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, q.bw, q.bh, q.bn);
+  if (rc) return rc;
+  const long long tiles = (long long)q.split * ((Co + 127) / 128) * ((kh * kw * Ci + 255) / 256);
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  const size_t smem = (size_t)p.stages * (A_BYTES + p.bn_cols * BK * 2) + sizeof(Smem) + 1024;
+  conv_igemm_kernel<true><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+// wt[Ci][kh][kw][Co] = w[Co][kh][kw][Ci] rotated by 180 degrees: with it, the gradient with respect to the input of a
+// stride-1 convolution is gcow_conv_fwd(dy, wt, ..., Ci = Co, Co = Ci, pad = k - 1 - pad).
+int gcow_conv_flip_weights(const void* w, void* wt, int Co, int kh, int kw, int Ci, void* stream) {
+  const size_t total = (size_t)Co * kh * kw * Ci;
+  if (!total) return 0;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 1184) blocks = 1184;
+  flip_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wt, Co, kh, kw, Ci);
+  return (int)cudaGetLastError();
+}
+
+// The pixel box chosen for given extents: out = {bw, bh, bn}. For tests of the tiling rule.
+void gcow_conv_pick_box(int W, int H, int N, int rows, int exact, int* out) {
+  pick_box(W, H, N, rows, exact, &out[0], &out[1], &out[2]);
+}
+
+}  // extern "C"

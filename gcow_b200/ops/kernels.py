@@ -592,7 +592,7 @@ def conv_gemm_enabled() -> bool:
     the explicit patch matrix costs KH*KW times the activation traffic, so cuDNN's
     implicit GEMM stays the default."""
     import os
-    return os.environ.get("GCOW_CONV", "lib") == "own"
+    return os.environ.get("GCOW_CONV", "lib") in ("own", "igemm")
 
 
 def conv_gemm_usable(x: torch.Tensor, w: torch.Tensor, groups: int, dilation) -> bool:
@@ -603,6 +603,92 @@ def conv_gemm_usable(x: torch.Tensor, w: torch.Tensor, groups: int, dilation) ->
 
 def conv_gemm(x, w, b, stride, pad):
     return _ConvGemmFn.apply(x, w, b, stride, pad)
+
+
+# ------------------------------------------------ implicit-GEMM convolution (stride 1)
+class _ConvIgemmFn(torch.autograd.Function):
+    """Stride-1 KxK convolution, channels-last bf16, as an implicit GEMM on the tcgen05 kernel
+    (csrc/ops/conv_tcgen05.cu): forward, data gradient (the same kernel on dY with the flipped
+    filter) and weight gradient (split over pixel ranges + ordered sum). No patch matrix."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, pad_h, pad_w):
+        global _launches
+        N, C, H, W = x.shape
+        Co, _, KH, KW = w.shape
+        lib = _native.cuda()
+        if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
+            x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        wr = w.detach().permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()                        # [Co, kh, kw, Ci]
+        OH, OW = H + 2 * pad_h - KH + 1, W + 2 * pad_w - KW + 1
+        y = torch.empty((N, Co, OH, OW), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
+        bias = b.detach().float().contiguous() if b is not None else None
+        _chk(lib.gcow_conv_fwd(x.data_ptr(), wr.data_ptr(), y.data_ptr(), bias.data_ptr() if bias is not None else None,
+                               N, H, W, C, Co, KH, KW, pad_h, pad_w, _error_word(x.device).data_ptr(), _stream(x.device)),
+             "gcow_conv_fwd")
+        _launches += 1
+        ctx.save_for_backward(x, wr)
+        ctx.meta = (N, C, H, W, Co, KH, KW, OH, OW, pad_h, pad_w, b is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        x, wr = ctx.saved_tensors
+        N, C, H, W, Co, KH, KW, OH, OW, pad_h, pad_w, has_bias = ctx.meta
+        lib = _native.cuda()
+        if gy.dtype != torch.bfloat16 or not gy.is_contiguous(memory_format=torch.channels_last):
+            gy = gy.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        dev, st, err = gy.device, _stream(gy.device), _error_word(gy.device).data_ptr()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            wt = torch.empty((C, KH, KW, Co), dtype=torch.bfloat16, device=dev)
+            _chk(lib.gcow_conv_flip_weights(wr.data_ptr(), wt.data_ptr(), Co, KH, KW, C, st), "gcow_conv_flip_weights")
+            gx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=dev, memory_format=torch.channels_last)
+            _chk(lib.gcow_conv_fwd(gy.data_ptr(), wt.data_ptr(), gx.data_ptr(), None, N, OH, OW, Co, C, KH, KW,
+                                   KH - 1 - pad_h, KW - 1 - pad_w, err, st), "gcow_conv_fwd (dgrad)")
+            _launches += 2
+        if ctx.needs_input_grad[1]:
+            split = lib.gcow_conv_wgrad_split(N, H, W, C, Co, KH, KW, pad_h, pad_w)
+            part = torch.empty((split, Co, KH * KW * C), dtype=torch.float32, device=dev)
+            _chk(lib.gcow_conv_wgrad(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, KH, KW, pad_h, pad_w,
+                                     err, st), "gcow_conv_wgrad")
+            _launches += 1
+            if split > 1:
+                out = torch.empty((Co, KH * KW * C), dtype=torch.float32, device=dev)
+                _chk(lib.gcow_reduce_partials(part.data_ptr(), out.data_ptr(), split, out.numel(), st), "gcow_reduce_partials")
+                _launches += 1
+            else:
+                out = part[0]
+            gw = out.view(Co, KH, KW, C).permute(0, 3, 1, 2)          # logical [Co, Ci, kh, kw], channels-last memory
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(gy.permute(0, 2, 3, 1).reshape(-1, Co))
+        return gx, gw, gb, None, None
+
+
+def conv_igemm_mode() -> str:
+    """GCOW_CONV selects the KxK convolution path of the own backend: ``igemm`` (implicit GEMM on the
+    tcgen05 kernel, stride 1 only), ``own`` (im2col + GEMM, any stride) or ``lib`` (cuDNN)."""
+    import os
+    return os.environ.get("GCOW_CONV", "lib")
+
+
+def conv_igemm_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups: int, dilation) -> bool:
+    """Stride 1, dense, input channels a multiple of 64 (whole 128-byte channel rows per filter tap),
+    output channels a multiple of 8, padding below the filter size."""
+    if not (x.is_cuda and x.dim() == 4 and _have("gcow_conv_fwd") and groups == 1 and tuple(dilation) == (1, 1)):
+        return False
+    if tuple(stride) != (1, 1) or not all(isinstance(p, int) for p in padding):
+        return False
+    KH, KW = w.shape[2], w.shape[3]
+    if KH * KW == 1 or padding[0] >= KH or padding[1] >= KW:
+        return False
+    # the data gradient swaps the channel roles, so both counts must be whole 64-channel rows
+    return x.shape[1] % 64 == 0 and w.shape[0] % 64 == 0
+
+
+def conv_igemm(x, w, b, padding):
+    return _ConvIgemmFn.apply(x, w, b, int(padding[0]), int(padding[1]))
 
 
 # ------------------------------------------------ batched GEMM and attention

@@ -1,0 +1,92 @@
+"""Implicit-GEMM convolution (forward, data gradient, weight gradient) against an fp32
+PyTorch convolution of the same bf16-rounded operands."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+# (N, Ci, H, W, Co, kh, kw, pad_h, pad_w): whole boxes, ragged edges, narrow and wide channel counts,
+# a filter without padding, an even filter and an asymmetric one
+CASES = [
+    (4, 64, 16, 16, 64, 3, 3, 1, 1),
+    (3, 64, 9, 7, 128, 3, 3, 1, 1),
+    (2, 128, 14, 14, 256, 3, 3, 1, 1),
+    (5, 64, 7, 7, 320, 3, 3, 1, 1),
+    (2, 64, 12, 10, 64, 3, 3, 0, 0),
+    (2, 64, 11, 13, 64, 5, 5, 2, 2),
+    (2, 64, 10, 10, 64, 2, 2, 1, 1),
+    (2, 192, 8, 9, 64, 1, 3, 0, 1),
+]
+
+
+def _mk(N, Ci, H, W, Co, kh, kw):
+    x = (torch.randn(N, Ci, H, W, device="cuda") * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(Co, Ci, kh, kw, device="cuda") * 0.1).bfloat16().float().contiguous(memory_format=torch.channels_last)
+    b = torch.randn(Co, device="cuda") * 0.1
+    return x, w, b
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_conv_igemm_forward_and_gradients(case):
+    from gcow_b200.ops import kernels as K
+    N, Ci, H, W, Co, kh, kw, ph, pw = case
+    torch.manual_seed(sum(case))
+    x, w, b = _mk(N, Ci, H, W, Co, kh, kw)
+    xr = x.float().requires_grad_(True)
+    wr = w.clone().requires_grad_(True)
+    br = b.clone().requires_grad_(True)
+    ref = F.conv2d(xr, wr, br, stride=1, padding=(ph, pw))
+    gy = (torch.randn_like(ref) * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    ref.backward(gy.float())
+
+    xo = x.clone().requires_grad_(True)
+    wo = w.clone().requires_grad_(True)
+    bo = b.clone().requires_grad_(True)
+    assert K.conv_igemm_usable(xo, wo, (1, 1), (ph, pw), 1, (1, 1))
+    y = K.conv_igemm(xo, wo, bo, (ph, pw))
+    K.check_errors()
+    assert y.shape == ref.shape and y.dtype == torch.bfloat16
+    assert _rel(y, ref) < 2e-2
+    y.backward(gy)
+    K.check_errors()
+    assert _rel(xo.grad, xr.grad) < 2e-2
+    assert wo.grad.dtype == torch.float32 and wo.grad.shape == wr.grad.shape
+    assert _rel(wo.grad, wr.grad) < 5e-3
+    assert _rel(bo.grad, br.grad) < 5e-3
+
+
+def test_conv_igemm_resnet_layer_shape():
+    """One ResNet-50 3x3 layer at a batch that needs several waves of tiles and every split of the weight gradient."""
+    from gcow_b200.ops import kernels as K
+    torch.manual_seed(5)
+    N, C, HW = 32, 128, 28
+    x, w, _ = _mk(N, C, HW, HW, C, 3, 3)
+    xr, wr = x.float().requires_grad_(True), w.clone().requires_grad_(True)
+    ref = F.conv2d(xr, wr, None, padding=1)
+    gy = (torch.randn_like(ref) * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    ref.backward(gy.float())
+    xo, wo = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    y = K.conv_igemm(xo, wo, None, (1, 1))
+    y.backward(gy)
+    K.check_errors()
+    assert _rel(y, ref) < 2e-2 and _rel(xo.grad, xr.grad) < 2e-2 and _rel(wo.grad, wr.grad) < 5e-3
+
+
+def test_conv2d_module_uses_igemm_when_selected(monkeypatch):
+    from gcow_b200.ops import kernels as K, nn as gnn, set_backend
+    monkeypatch.setenv("GCOW_CONV", "igemm")
+    set_backend("own")
+    torch.manual_seed(6)
+    conv = gnn.Conv2d(64, 64, 3, padding=1, bias=False).cuda().to(memory_format=torch.channels_last)
+    x = torch.randn(4, 64, 14, 14, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    before = K.launch_count()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = conv(x)
+    assert K.launch_count() == before + 1
+    ref = F.conv2d(x.float(), conv.weight.bfloat16().float(), padding=1)
+    assert _rel(y, ref) < 2e-2
