@@ -25,6 +25,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--layouts", action="store_true", help="also time the MN-major operand layouts of the backward products")
     ap.add_argument("--shape", type=int, nargs=3, default=None, metavar=("M", "N", "K"), help="time one shape only")
     args = ap.parse_args(argv)
     pk = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
@@ -43,6 +44,12 @@ def main(argv=None):
         row = {"M": M, "N": N, "K": Kd, "own_ms": ms_own, "tile128_ms": ms_128, "tile256_ms": ms_256, "cublas_ms": ms_lib, "own_tflops": fl / ms_own / 1e9,
                "cublas_tflops": fl / ms_lib / 1e9, "own_frac_of_peak": fl / ms_own / 1e9 / peak,
                "peak": f"{how} {peak:.0f} TFLOP/s"}
+        if args.layouts:
+            at, bt = a.t().contiguous(), b.t().contiguous()          # [K, M], [K, N]
+            for name, (x, y, kw) in {"b_mn": (a, bt, dict(b_t=True)), "a_mn_b_mn": (at, bt, dict(a_t=True, b_t=True))}.items():
+                ms, _ = time_cuda(lambda: K.gemm_bf16(x, y, out=out, **kw), args.iters)
+                row[f"{name}_ms"], row[f"{name}_tflops"] = ms, fl / ms / 1e9
+            K.check_errors()
         rows.append(row)
         print(json.dumps(row), flush=True)
     if args.json:

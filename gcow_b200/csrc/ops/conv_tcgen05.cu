@@ -25,6 +25,9 @@
 //
 // Replaces the cuDNN 3x3 convolutions behind nn.Conv2d in the reference's models
 // (hw/models/resenet.py:14,48-50).
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -40,7 +43,7 @@ constexpr int EPI_WARPS = 8, THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int kSmemBudget = 200 * 1024;
 
-enum Flags : int { kBias = 2 };
+enum Flags : int { kBias = 2, kDbgNoShift = 256, kDbgNoStore = 512 };
 
 struct Params {
   void* out;            // forward: bf16 [N, H, W, Co]; wgrad: fp32 partials [split][Co][taps * Ci]
@@ -129,7 +132,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               mbar_expect_tx(&sm->full[s], a_tx + (uint32_t)b_bytes);
               const uint32_t bar = smem_u32(&sm->full[s]);
               uint8_t* st = base + s * stage_bytes;
-              tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0);
+              if (p.flags & kDbgNoShift) tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0, h0, n0);
+              else tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0);
               tma_load_2d(smem_u32(st + A_BYTES), &map_b, bar, tap * p.Ci + cc * BK, co0);
               if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
             }
@@ -244,7 +248,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256 + col0;
       auto process = [&](const uint32_t (&r)[32], int c) {
         const int n = n_first + col0 + c * 32;
-        if (row_ok && n < n_limit) {
+        if (row_ok && n < n_limit && !(p.flags & kDbgNoStore)) {
           if (WGRAD) {
             float* C = reinterpret_cast<float*>(p.out) + row_off + n;
             if (n + 32 <= n_limit) {
@@ -394,9 +398,27 @@ static int device_sms() {
   return sms;
 }
 
+struct Tune { int bw = 0, bh = 0, bn = 0, stages = 0, flags = 0; };
+static const Tune& tune() {
+  static Tune t;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* e = getenv("GCOW_CONV_TUNE");
+    if (!e) return;
+    const char* q;
+    if ((q = strstr(e, "box="))) sscanf(q, "box=%dx%dx%d", &t.bw, &t.bh, &t.bn);
+    if ((q = strstr(e, "stages="))) sscanf(q, "stages=%d", &t.stages);
+    if (strstr(e, "noshift")) t.flags |= kDbgNoShift;
+    if (strstr(e, "nostore")) t.flags |= kDbgNoStore;
+  });
+  return t;
+}
+
 static int stages_for(int bn_cols) {
   int st = kSmemBudget / (A_BYTES + bn_cols * BK * 2);
-  return st > MAX_STAGES ? MAX_STAGES : st;
+  st = st > MAX_STAGES ? MAX_STAGES : st;
+  if (tune().stages > 0 && tune().stages < st) st = tune().stages;
+  return st;
 }
 
 struct WgradPlan { int bw, bh, bn, tiles_w, tiles_h, tiles_n, split, per; };
@@ -407,7 +429,7 @@ static WgradPlan wgrad_plan(int N, int Ho, int Wo, int Ci, int Co, int taps, int
   q.tiles_w = (Wo + q.bw - 1) / q.bw; q.tiles_h = (Ho + q.bh - 1) / q.bh; q.tiles_n = (N + q.bn - 1) / q.bn;
   const int chunks = q.tiles_w * q.tiles_h * q.tiles_n;
   const int base = ((Co + 127) / 128) * ((taps * Ci + 255) / 256);
-  int split = (sms + base - 1) / base;
+  int split = sms / base;                                       // one wave: never more tiles than SMs
   if (split > (chunks + 7) / 8) split = (chunks + 7) / 8;      // at least 8 pixel boxes per CTA
   if (split < 1) split = 1;
   q.per = (chunks + split - 1) / split;
@@ -434,13 +456,14 @@ int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int 
   const int sms = device_sms();
   Params p{};
   pick_box(Wo, Ho, N, 128, 0, &p.bw, &p.bh, &p.bn);
+  if (tune().bw > 0 && tune().bw * tune().bh * tune().bn <= 128) { p.bw = tune().bw; p.bh = tune().bh; p.bn = tune().bn; }
   p.tiles_w = (Wo + p.bw - 1) / p.bw; p.tiles_h = (Ho + p.bh - 1) / p.bh; p.tiles_n = (N + p.bn - 1) / p.bn;
   p.bn_cols = Co <= 64 ? 64 : (Co <= 128 ? 128 : 256);
   p.stages = stages_for(p.bn_cols);
   p.out = y; p.bias = bias; p.N = N; p.H = Ho; p.W = Wo; p.Ci = Ci; p.Co = Co;
   p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w;
   p.split = 1; p.chunks_per_split = 0;
-  p.flags = bias ? kBias : 0;
+  p.flags = (bias ? kBias : 0) | tune().flags;
   p.error = error;
   CUtensorMap ma, mb;
   int rc = make_map_nhwc(&ma, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, p.bw, p.bh, p.bn);

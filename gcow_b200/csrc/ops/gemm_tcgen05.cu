@@ -27,6 +27,7 @@
 //
 // Replaces the cuBLAS GEMMs behind nn.Linear / 1x1 convolutions in the
 // reference's models (hw/models/resenet.py:11,17,90).
+#include <stdlib.h>
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -57,6 +58,7 @@ struct Params {
   const void* residual;    // same type/ld as C or nullptr
   int M, N, K, ldc, flags;
   int batch;               // number of independent products (operands are 3-D tensor maps when > 1)
+  int a_merged, b_merged;  // MN-major operand fetched as ONE box per stage (its row length is a multiple of 64)
   long long stride_c;      // elements between consecutive C (and residual) matrices
   uint32_t* error;         // device word, set non-zero when a wait gave up
 };
@@ -68,6 +70,14 @@ struct Smem {
 };
 
 using namespace gcow::tc;
+
+// Merged MN-major fetch: the matrix [K][rows] is described as {64 elements, K, rows / 64 (, batch)}, so one
+// box {64, 64, tile rows / 64} brings every 64-column group of the tile, 8 KB apart, in a single copy.
+__device__ __forceinline__ void tma_load_mn(uint32_t dst, const CUtensorMap* map, uint32_t bar, int k, int chunk, int z,
+                                            bool batched) {
+  if (batched) tma_load_4d(dst, map, bar, 0, k, chunk, z);
+  else tma_load_3d(dst, map, bar, 0, k, chunk);
+}
 
 __device__ __forceinline__ bool mbar_wait(Smem* sm, uint64_t* bar, uint32_t parity, uint32_t* error, uint32_t code) {
   return mbar_wait_abortable(&sm->abort, bar, parity, error, code);
@@ -122,6 +132,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t bar = smem_u32(&sm->full[s]);
           if (!A_MN) {
             tma_load(smem_u32(smA + s * A_BYTES), &tmap_a, bar, kb * BK, m0, bz, batched);
+          } else if (p.a_merged) {
+            tma_load_mn(smem_u32(smA + s * A_BYTES), &tmap_a, bar, kb * BK, m0 / 64, bz, batched);
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; i++)
@@ -129,6 +141,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (!B_MN) {
             tma_load(smem_u32(smB + s * B_BYTES), &tmap_b, bar, kb * BK, n0, bz, batched);
+          } else if (p.b_merged) {
+            tma_load_mn(smem_u32(smB + s * B_BYTES), &tmap_b, bar, kb * BK, n0 / 64, bz, batched);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; i++)
@@ -338,6 +352,23 @@ static int make_map3(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
+// MN-major matrix [K][cols] (cols a multiple of 64) as {64, K, cols / 64 (, batch)}; box = 64 x 64 x chunks.
+static int make_map_mn(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t cols, uint64_t ld, uint64_t batch,
+                       uint64_t bstride, uint32_t chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  if (((uintptr_t)ptr & 15) || (ld * 2) % 16 || (bstride * 2) % 16 || cols % 64) return -11;
+  const cuuint32_t rank = batch > 1 ? 4 : 3;
+  cuuint64_t dims[4] = {64, K, cols / 64, batch};
+  cuuint64_t strides[3] = {ld * 2, 128, bstride * 2};
+  cuuint32_t box[4] = {64, 64, chunks, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
 template <int BM_> constexpr size_t smem_bytes() { return Shape<BM_>::SMEM + sizeof(Smem) + 1024; }
 
 }  // namespace gemm
@@ -401,7 +432,22 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
                                                           : ((tiles256 >= (sms * 4) / 5 && K >= 2048) ? 256 : 128);
   // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
   int rc;
-  if (batch == 1) {
+  // an MN-major operand whose row length is a multiple of 64 is fetched with one copy per stage
+  static const bool no_merge = getenv("GCOW_GEMM_NO_MERGE") != nullptr;
+  const int a_merged = a_mn && M % 64 == 0 && !no_merge, b_merged = b_mn && N % 64 == 0 && !no_merge;
+  if (a_merged || b_merged) {
+    rc = a_merged ? make_map_mn(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)bm / 64)
+         : batch == 1 ? (a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
+                              : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)bm))
+                      : (a_mn ? make_map3(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, 64)
+                              : make_map3(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)bm));
+    if (rc) return rc;
+    rc = b_merged ? make_map_mn(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, BN / 64)
+         : batch == 1 ? (b_mn ? make_map(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64)
+                              : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN))
+                      : (b_mn ? make_map3(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, 64)
+                              : make_map3(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, BN));
+  } else if (batch == 1) {
     rc = a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
               : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)bm);
     if (rc) return rc;
@@ -419,6 +465,7 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   p.C = C; p.bias = bias; p.residual = residual;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags; p.error = error;
   p.batch = batch; p.stride_c = batch > 1 ? stride_c : 0;
+  p.a_merged = a_merged; p.b_merged = b_merged;
   const int tiles = ((M + bm - 1) / bm) * ((N + BN - 1) / BN) * batch;
   int grid = tiles < sms ? tiles : sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
