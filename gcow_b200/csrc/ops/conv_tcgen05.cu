@@ -19,9 +19,16 @@
 //             kernel in a fixed order.
 //
 // Same structure as the GEMM kernel: persistent CTAs, warp 0 issues TMA loads into an
-// mbarrier ring, one thread of warp 1 issues tcgen05.mma into two alternating TMEM
-// accumulators, eight epilogue warps read them back with tcgen05.ld. No multicast;
-// every wait is bounded and gives up by raising an error word.
+// mbarrier ring, one thread of warp 1 issues tcgen05.mma into TMEM accumulators, eight
+// epilogue warps read them back with tcgen05.ld. No multicast; every wait is bounded and
+// gives up by raising an error word.
+//
+// What sets the speed (measured): a TMA copy costs a few hundred cycles per instruction
+// on top of its bytes, and an M128 x N x K16 MMA takes about as long for N = 64 as for
+// N = 256. So a stage is fetched with as few, as large boxes as possible - the forward
+// tile is one box of up to 256 pixels (two 128-row accumulators that share the filter
+// tile), the weight gradient folds its 64-channel groups into a fifth box dimension -
+// and the launcher picks the tile from a small cost model of those two effects.
 //
 // Replaces the cuDNN 3x3 convolutions behind nn.Conv2d in the reference's models
 // (hw/models/resenet.py:14,48-50).
@@ -38,12 +45,12 @@ namespace conv {
 using namespace gcow::tc;
 
 constexpr int BK = 64, UMMA_K = 16, MAX_STAGES = 8;
-constexpr int A_BYTES = 128 * BK * 2;          // 128 rows (or two 64-column boxes) of 128 bytes
+constexpr int HALF_BYTES = 128 * BK * 2;       // one 128-row operand tile: 128 rows (or two 64-column boxes) of 128 bytes
 constexpr int EPI_WARPS = 8, THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int kSmemBudget = 200 * 1024;
 
-enum Flags : int { kBias = 2, kDbgNoShift = 256, kDbgNoStore = 512 };
+enum Flags : int { kBias = 2 };
 
 struct Params {
   void* out;            // forward: bf16 [N, H, W, Co]; wgrad: fp32 partials [split][Co][taps * Ci]
@@ -55,22 +62,25 @@ struct Params {
   int tiles_w, tiles_h, tiles_n;   // number of pixel boxes along W, H, N
   int bn_cols;          // GEMM N of one tile: 64, 128 or 256
   int stages;
-  int split, chunks_per_split;     // wgrad: CTAs-groups over the pixel range
+  int split, chunks_per_split;     // wgrad: CTA groups over the pixel range
+  int b_chunks;         // wgrad: 64-channel groups of X fetched by one copy (1, 2 or 4)
   int flags;
   uint32_t* error;
 };
 
 struct Smem {
-  uint64_t full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], drain;
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[4], drain;
   uint32_t tmem_base;
   volatile uint32_t abort;
 };
 
-template <bool WGRAD>
+// HALVES: 128-row accumulators per tile
+template <bool WGRAD, int HALVES>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = HALVES * HALF_BYTES;
   const int b_bytes = p.bn_cols * BK * 2;
   const int stage_bytes = A_BYTES + b_bytes;
   const int STAGES = p.stages;
@@ -82,14 +92,19 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int pix_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
   // forward: tiles over (pixel box, Co tile), reduction over (tap, channel chunk)
   // wgrad:   tiles over (split, Co tile, column tile of taps*Ci), reduction over pixel boxes
-  const int tiles_c = WGRAD ? (p.Co + 127) / 128 : (p.Co + p.bn_cols - 1) / p.bn_cols;
+  const int tiles_c = WGRAD ? (p.Co + 128 * HALVES - 1) / (128 * HALVES) : (p.Co + p.bn_cols - 1) / p.bn_cols;
   const int col_groups = taps * cchunks;                          // wgrad: 64-column groups of N
   const int tiles_col = (col_groups * BK + p.bn_cols - 1) / p.bn_cols;
   const int num_tiles = WGRAD ? p.split * tiles_c * tiles_col : pix_tiles * tiles_c;
+  // Accumulators: tile t uses buffer b = t & 1 when two tiles fit in the 512 columns, else always buffer 0;
+  // half h of buffer b sits at column b * 256 + h * (columns per half).
+  const bool dbuf = HALVES * p.bn_cols <= 256;
+  const uint32_t half_cols = dbuf ? (uint32_t)p.bn_cols : 256u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(&sm->tmem_full[a], 1); mbar_init(&sm->tmem_empty[a], EPI_WARPS * 32); }
+    for (int a = 0; a < 2; a++) mbar_init(&sm->tmem_full[a], 1);
+    for (int a = 0; a < 4; a++) mbar_init(&sm->tmem_empty[a], EPI_WARPS * 32);
     mbar_init(&sm->drain, 1);
     sm->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -132,8 +147,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               mbar_expect_tx(&sm->full[s], a_tx + (uint32_t)b_bytes);
               const uint32_t bar = smem_u32(&sm->full[s]);
               uint8_t* st = base + s * stage_bytes;
-              if (p.flags & kDbgNoShift) tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0, h0, n0);
-              else tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0);
+              tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0);
               tma_load_2d(smem_u32(st + A_BYTES), &map_b, bar, tap * p.Ci + cc * BK, co0);
               if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
             }
@@ -142,7 +156,6 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const int tcol = tile % tiles_col;
           int rest = tile / tiles_col;
           const int tco = rest % tiles_c, sp = rest / tiles_c;
-          const int co0 = tco * 128;
           const int g0 = tcol * (p.bn_cols / BK);                 // first 64-column group of this tile
           const int first = sp * p.chunks_per_split, nk = tile_kblocks(tile);
           for (int kb = 0; kb < nk; kb++) {
@@ -153,15 +166,15 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             mbar_expect_tx(&sm->full[s], (uint32_t)(A_BYTES + b_bytes));
             const uint32_t bar = smem_u32(&sm->full[s]);
             uint8_t* st = base + s * stage_bytes;
-            // channel coordinates past the tensor read zeros
-            tma_load_4d(smem_u32(st), &map_a, bar, co0, w0, h0, n0);
-            tma_load_4d(smem_u32(st + 8192), &map_a, bar, co0 + 64, w0, h0, n0);
-            for (int i = 0; i < p.bn_cols / BK; i++) {
+            // dY: every 64-channel group of the tile's rows in one copy (groups past Co read zeros)
+            tma_load_5d(smem_u32(st), &map_a, bar, 0, w0, h0, n0, tco * 2 * HALVES);
+            // X: runs of b_chunks channel groups share a filter tap, hence a shift, hence a copy
+            for (int i = 0; i < p.bn_cols / BK; i += p.b_chunks) {
               const int g = g0 + i;
-              int tap = g / cchunks, c0 = (g - tap * cchunks) * BK;
-              if (g >= col_groups) { tap = 0; c0 = p.Ci; }
+              int tap = g / cchunks, ch = g - tap * cchunks;
+              if (g >= col_groups) { tap = 0; ch = cchunks; }     // past the last column group: zeros
               const int r = tap / p.kw, sx = tap - r * p.kw;
-              tma_load_4d(smem_u32(st + A_BYTES + i * 8192), &map_b, bar, c0, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0);
+              tma_load_5d(smem_u32(st + A_BYTES + i * 8192), &map_b, bar, 0, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0, ch);
             }
             if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
           }
@@ -182,24 +195,30 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t s = 0, phase = 0, t = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
-        const uint32_t acc = t & 1, aphase = (t >> 1) & 1;
+        const uint32_t buf = dbuf ? (t & 1) : 0, use = dbuf ? (t >> 1) : t;
         const int nk = tile_kblocks(tile);
-        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->tmem_empty[acc], aphase ^ 1, p.error, 2))) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * 256;
-        for (int kb = 0; kb < nk; kb++) {
+        for (int kb = 0; kb < nk && ok; kb++) {
           if (!(ok = mbar_wait_abortable(&sm->abort, &sm->full[s], phase, p.error, 3))) break;
           tc_fence_after();
           const uint32_t sa = smem_u32(base + s * stage_bytes), sb = sa + A_BYTES;
-          const uint64_t da = WGRAD ? smem_desc_mn_sw128(sa) : smem_desc_sw128(sa);
           const uint64_t db = WGRAD ? smem_desc_mn_sw128(sb) : smem_desc_sw128(sb);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; k++)
-            tc_mma(d_tmem, da + kstep * k, db + kstep * k, idesc, (kb | k) != 0);
+          for (int h = 0; h < HALVES; h++) {
+            if (kb == 0) {   // first write to this accumulator: its previous contents must have been read out
+              if (!(ok = mbar_wait_abortable(&sm->abort, &sm->tmem_empty[buf * 2 + h], (use & 1) ^ 1, p.error, 2))) break;
+              tc_fence_after();
+            }
+            const uint64_t da = WGRAD ? smem_desc_mn_sw128(sa + h * HALF_BYTES) : smem_desc_sw128(sa + h * HALF_BYTES);
+            const uint32_t d_tmem = tmem_base + buf * 256 + h * half_cols;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; k++)
+              tc_mma(d_tmem, da + kstep * k, db + kstep * k, idesc, (kb | k) != 0);
+          }
+          if (!ok) break;
           tc_commit(&sm->empty[s]);
           if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
         }
-        if (ok) tc_commit(&sm->tmem_full[acc]);
+        if (ok) tc_commit(&sm->tmem_full[buf]);
       }
       // drain: everything issued by this thread has finished before TMEM is freed
       tc_commit(&sm->drain);
@@ -209,98 +228,101 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // ----------------------------------------------------------------- epilogue
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
     const int ew = warp - 2;
-    const int cols = p.bn_cols / 2;               // columns of the accumulator this warp drains
+    const int cols = p.bn_cols / 2;               // columns of each accumulator this warp drains
     const int col0 = (ew / 4) * cols;
     const int nch = cols / 32;                    // 1, 2 or 4 chunks of 32 columns
-    const int row = q * 32 + lane;                // accumulator row of this thread
     uint32_t t = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
-      const uint32_t acc = t & 1, aphase = (t >> 1) & 1;
-      // where this thread's row goes
-      bool row_ok;
-      size_t row_off;        // element offset of the row's first column of this tile
-      int n_first, n_limit;  // first column index of this tile, and the column bound
-      if (!WGRAD) {
-        const int tcn = tile % tiles_c, pt = tile / tiles_c;
-        const int iw = row % p.bw, ih = (row / p.bw) % p.bh, in = row / (p.bw * p.bh);
-        const int w = (pt % p.tiles_w) * p.bw + iw, h = ((pt / p.tiles_w) % p.tiles_h) * p.bh + ih;
-        const int n = (pt / (p.tiles_w * p.tiles_h)) * p.bn + in;
-        row_ok = in < p.bn && w < p.W && h < p.H && n < p.N;
-        n_first = tcn * p.bn_cols;
-        n_limit = p.Co;
-        row_off = (((size_t)n * p.H + h) * p.W + w) * (size_t)p.Co;
-      } else {
-        const int tcol = tile % tiles_col;
-        int rest = tile / tiles_col;
-        const int tco = rest % tiles_c, sp = rest / tiles_c;
-        const int co = tco * 128 + row;
-        const int ncols = col_groups * BK;
-        row_ok = co < p.Co;
-        n_first = tcol * p.bn_cols;
-        n_limit = ncols;
-        row_off = ((size_t)sp * p.Co + co) * (size_t)ncols;
-      }
-      ok = mbar_wait_abortable(&sm->abort, &sm->tmem_full[acc], aphase, p.error, 4);
+      const uint32_t buf = dbuf ? (t & 1) : 0, use = dbuf ? (t >> 1) : t;
+      ok = mbar_wait_abortable(&sm->abort, &sm->tmem_full[buf], use & 1, p.error, 4);
       ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below need the whole warp
       if (!ok) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256 + col0;
-      auto process = [&](const uint32_t (&r)[32], int c) {
-        const int n = n_first + col0 + c * 32;
-        if (row_ok && n < n_limit && !(p.flags & kDbgNoStore)) {
-          if (WGRAD) {
-            float* C = reinterpret_cast<float*>(p.out) + row_off + n;
-            if (n + 32 <= n_limit) {
+#pragma unroll 1
+      for (int h = 0; h < HALVES; h++) {
+        const int row = h * 128 + q * 32 + lane;    // tile row of this thread
+        // where this thread's row goes
+        bool row_ok;
+        size_t row_off;        // element offset of the row's first column of this tile
+        int n_first, n_limit;  // first column index of this tile, and the column bound
+        if (!WGRAD) {
+          const int tcn = tile % tiles_c, pt = tile / tiles_c;
+          const int iw = row % p.bw, ih = (row / p.bw) % p.bh, in = row / (p.bw * p.bh);
+          const int w = (pt % p.tiles_w) * p.bw + iw, hh = ((pt / p.tiles_w) % p.tiles_h) * p.bh + ih;
+          const int n = (pt / (p.tiles_w * p.tiles_h)) * p.bn + in;
+          row_ok = in < p.bn && w < p.W && hh < p.H && n < p.N;
+          n_first = tcn * p.bn_cols;
+          n_limit = p.Co;
+          row_off = (((size_t)n * p.H + hh) * p.W + w) * (size_t)p.Co;
+        } else {
+          const int tcol = tile % tiles_col;
+          int rest = tile / tiles_col;
+          const int tco = rest % tiles_c, sp = rest / tiles_c;
+          const int co = tco * 128 * HALVES + row;
+          const int ncols = col_groups * BK;
+          row_ok = co < p.Co;
+          n_first = tcol * p.bn_cols;
+          n_limit = ncols;
+          row_off = ((size_t)sp * p.Co + co) * (size_t)ncols;
+        }
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + h * half_cols + col0;
+        auto process = [&](const uint32_t (&r)[32], int c) {
+          const int n = n_first + col0 + c * 32;
+          if (row_ok && n < n_limit) {
+            if (WGRAD) {
+              float* C = reinterpret_cast<float*>(p.out) + row_off + n;
+              if (n + 32 <= n_limit) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(C + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            } else {
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(C + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              } else {
 #pragma unroll
-              for (int j = 0; j < 32; j++) if (n + j < n_limit) C[j] = __uint_as_float(r[j]);
-            }
-          } else {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-            if (p.flags & kBias) {
-#pragma unroll
-              for (int j = 0; j < 32; j++) if (n + j < n_limit) v[j] += __ldg(p.bias + n + j);
-            }
-            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.out) + row_off + n;
-            if (n + 32 <= n_limit) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 o;
-                __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
-                *reinterpret_cast<uint4*>(C + j) = o;
+                for (int j = 0; j < 32; j++) if (n + j < n_limit) C[j] = __uint_as_float(r[j]);
               }
             } else {
+              float v[32];
 #pragma unroll
-              for (int j = 0; j < 32; j++) if (n + j < n_limit) C[j] = __float2bfloat16(v[j]);
+              for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+              if (p.flags & kBias) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) if (n + j < n_limit) v[j] += __ldg(p.bias + n + j);
+              }
+              __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.out) + row_off + n;
+              if (n + 32 <= n_limit) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 o;
+                  __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                  for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                  *reinterpret_cast<uint4*>(C + j) = o;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) if (n + j < n_limit) C[j] = __float2bfloat16(v[j]);
+              }
             }
           }
-        }
-      };
-      uint32_t ra[32], rb[32];
-      tc_ld32(taddr, ra);
+        };
+        uint32_t ra[32], rb[32];
+        tc_ld32(taddr, ra);
 #pragma unroll 1
-      for (int c = 0; c < nch; c += 2) {
-        tc_wait_ld();
-        if (c + 1 < nch) tc_ld32(taddr + (c + 1) * 32, rb);
-        process(ra, c);
-        if (c + 1 < nch) {
+        for (int c = 0; c < nch; c += 2) {
           tc_wait_ld();
-          if (c + 2 < nch) tc_ld32(taddr + (c + 2) * 32, ra);
-          process(rb, c + 1);
+          if (c + 1 < nch) tc_ld32(taddr + (c + 1) * 32, rb);
+          process(ra, c);
+          if (c + 1 < nch) {
+            tc_wait_ld();
+            if (c + 2 < nch) tc_ld32(taddr + (c + 2) * 32, ra);
+            process(rb, c + 1);
+          }
         }
+        // this accumulator has been read out: the MMA warp may overwrite it
+        tc_fence_before();
+        mbar_arrive(&sm->tmem_empty[buf * 2 + h]);
       }
-      // this accumulator has been read out: the MMA warp may overwrite it
-      tc_fence_before();
-      mbar_arrive(&sm->tmem_empty[acc]);
     }
   }
 
@@ -330,18 +352,20 @@ __global__ void flip_weights_kernel(const __nv_bfloat16* __restrict__ w, __nv_bf
 }
 
 // ------------------------------------------------------------------- host side
-// 4-D bf16 NHWC tensor as {C, W, H, N}; box = 64 channels x bw x bh x bn pixels.
+// bf16 NHWC tensor as {C, W, H, N}; box = 64 channels x bw x bh x bn pixels.
+// chunks > 0: five dimensions {64, W, H, N, C / 64}, the box also spans `chunks` 64-channel groups,
+// which land 64 * bw * bh * bn * 2 bytes apart in shared memory (C must be a multiple of 64).
 static int make_map_nhwc(CUtensorMap* map, const void* ptr, uint64_t N, uint64_t H, uint64_t W, uint64_t C, uint32_t bw,
-                         uint32_t bh, uint32_t bn) {
+                         uint32_t bh, uint32_t bn, uint32_t chunks) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return -10;
   if (((uintptr_t)ptr & 15) || (C * 2) % 16) return -11;
-  if (bw > 256 || bh > 256 || bn > 256) return -11;
-  cuuint64_t dims[4] = {C, W, H, N};
-  cuuint64_t strides[3] = {C * 2, W * C * 2, H * W * C * 2};
-  cuuint32_t box[4] = {(cuuint32_t)BK, bw, bh, bn};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+  if (bw > 256 || bh > 256 || bn > 256 || (chunks && C % 64)) return -11;
+  cuuint64_t dims[5] = {chunks ? 64 : C, W, H, N, C / 64};
+  cuuint64_t strides[4] = {C * 2, W * C * 2, H * W * C * 2, 128};
+  cuuint32_t box[5] = {(cuuint32_t)BK, bw, bh, bn, chunks};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, chunks ? 5 : 4, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -12;
@@ -364,13 +388,13 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_
 
 // Pixel box bw x bh x bn covering a W x H x N grid with the fewest wasted rows.
 // `exact` != 0: the box must hold exactly `rows` pixels (wgrad: 64); else at most `rows`.
-// Ties go to the longer contiguous run (larger bw, then bh).
-static void pick_box(int W, int H, int N, int rows, int exact, int* obw, int* obh, int* obn) {
-  double best = -1.0;
-  *obw = 1; *obh = 1; *obn = rows;
-  for (int bw = 1; bw <= rows; bw++) {
+// Ties go to the longer contiguous run (larger bw, then bh). Returns the fraction of fetched rows that are pixels.
+static double pick_box(int W, int H, int N, int rows, int exact, int* obw, int* obh, int* obn) {
+  double best = -1.0, best_eff = 0.0;
+  *obw = 1; *obh = 1; *obn = rows > 256 ? 256 : rows;
+  for (int bw = 1; bw <= rows && bw <= 256; bw++) {
     if (bw > W + 7) break;
-    for (int bh = 1; bw * bh <= rows; bh++) {
+    for (int bh = 1; bw * bh <= rows && bh <= 256; bh++) {
       if (bh > H + 7) break;
       int bn = rows / (bw * bh);
       if (bn > N) bn = N;
@@ -380,25 +404,14 @@ static void pick_box(int W, int H, int N, int rows, int exact, int* obw, int* ob
       const double covered = (double)((W + bw - 1) / bw) * bw * ((H + bh - 1) / bh) * bh * ((N + bn - 1) / bn) * bn;
       const double eff = ((double)W * H * N / covered) * ((double)(bw * bh * bn) / rows);
       const double score = eff + 1e-4 * bw + 1e-6 * bh;
-      if (score > best) { best = score; *obw = bw; *obh = bh; *obn = bn; }
+      if (score > best) { best = score; best_eff = eff; *obw = bw; *obh = bh; *obn = bn; }
     }
   }
+  return best_eff;
 }
 
-static int device_sms() {
-  static std::once_flag once;
-  static int sms = 148;
-  std::call_once(once, [] {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(conv_igemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048);
-    cudaFuncSetAttribute(conv_igemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048);
-  });
-  return sms;
-}
-
-struct Tune { int bw = 0, bh = 0, bn = 0, stages = 0, flags = 0; };
+// Tuning overrides for experiments: GCOW_CONV_TUNE="box=8x8x2,stages=3,rows=128"
+struct Tune { int bw = 0, bh = 0, bn = 0, stages = 0, rows = 0; };
 static const Tune& tune() {
   static Tune t;
   static std::once_flag once;
@@ -408,32 +421,61 @@ static const Tune& tune() {
     const char* q;
     if ((q = strstr(e, "box="))) sscanf(q, "box=%dx%dx%d", &t.bw, &t.bh, &t.bn);
     if ((q = strstr(e, "stages="))) sscanf(q, "stages=%d", &t.stages);
-    if (strstr(e, "noshift")) t.flags |= kDbgNoShift;
-    if (strstr(e, "nostore")) t.flags |= kDbgNoStore;
+    if ((q = strstr(e, "rows="))) sscanf(q, "rows=%d", &t.rows);
   });
   return t;
 }
 
-static int stages_for(int bn_cols) {
-  int st = kSmemBudget / (A_BYTES + bn_cols * BK * 2);
+static size_t smem_for(int halves, int bn_cols, int stages) {
+  return (size_t)stages * (halves * HALF_BYTES + bn_cols * BK * 2) + sizeof(Smem) + 1024;
+}
+
+static int device_sms() {
+  static std::once_flag once;
+  static int sms = 148;
+  std::call_once(once, [] {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int cap = kSmemBudget + 2048;
+    cudaFuncSetAttribute(conv_igemm_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    cudaFuncSetAttribute(conv_igemm_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    cudaFuncSetAttribute(conv_igemm_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    cudaFuncSetAttribute(conv_igemm_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+  });
+  return sms;
+}
+
+static int stages_for(int halves, int bn_cols) {
+  int st = kSmemBudget / (halves * HALF_BYTES + bn_cols * BK * 2);
   st = st > MAX_STAGES ? MAX_STAGES : st;
   if (tune().stages > 0 && tune().stages < st) st = tune().stages;
   return st;
 }
 
-struct WgradPlan { int bw, bh, bn, tiles_w, tiles_h, tiles_n, split, per; };
+// Cycles of one reduction step as measured on B200: every TMA copy costs about 220 cycles plus its bytes at
+// about 100 bytes per cycle, every M128 x N x K16 MMA about 128 cycles whatever N; the slower side wins.
+static double step_cycles(int copies, double bytes, int mmas) {
+  const double tma = 220.0 * copies + bytes / 100.0, mma = 128.0 * mmas;
+  return tma > mma ? tma : mma;
+}
+
+struct WgradPlan { int bw, bh, bn, tiles_w, tiles_h, tiles_n, split, per, b_chunks, halves; };
 
 static WgradPlan wgrad_plan(int N, int Ho, int Wo, int Ci, int Co, int taps, int sms) {
   WgradPlan q;
   pick_box(Wo, Ho, N, 64, 1, &q.bw, &q.bh, &q.bn);
   q.tiles_w = (Wo + q.bw - 1) / q.bw; q.tiles_h = (Ho + q.bh - 1) / q.bh; q.tiles_n = (N + q.bn - 1) / q.bn;
   const int chunks = q.tiles_w * q.tiles_h * q.tiles_n;
-  const int base = ((Co + 127) / 128) * ((taps * Ci + 255) / 256);
+  q.halves = Co >= 256 ? 2 : 1;                                 // 256 output rows per tile share each X box
+  const int base = ((Co + 128 * q.halves - 1) / (128 * q.halves)) * ((taps * Ci + 255) / 256);
   int split = sms / base;                                       // one wave: never more tiles than SMs
   if (split > (chunks + 7) / 8) split = (chunks + 7) / 8;      // at least 8 pixel boxes per CTA
   if (split < 1) split = 1;
   q.per = (chunks + split - 1) / split;
   q.split = (chunks + q.per - 1) / q.per;                       // no empty split
+  const int cchunks = Ci / 64;
+  q.b_chunks = cchunks % 4 == 0 ? 4 : (cchunks % 2 == 0 ? 2 : 1);
   return q;
 }
 
@@ -455,25 +497,46 @@ int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int 
   if ((uintptr_t)y & 15) return -1;
   const int sms = device_sms();
   Params p{};
-  pick_box(Wo, Ho, N, 128, 0, &p.bw, &p.bh, &p.bn);
-  if (tune().bw > 0 && tune().bw * tune().bh * tune().bn <= 128) { p.bw = tune().bw; p.bh = tune().bh; p.bn = tune().bn; }
-  p.tiles_w = (Wo + p.bw - 1) / p.bw; p.tiles_h = (Ho + p.bh - 1) / p.bh; p.tiles_n = (N + p.bn - 1) / p.bn;
   p.bn_cols = Co <= 64 ? 64 : (Co <= 128 ? 128 : 256);
-  p.stages = stages_for(p.bn_cols);
+  const int tiles_c = (Co + p.bn_cols - 1) / p.bn_cols;
+  const int ksteps = kh * kw * (Ci / 64);
+  // one or two 128-row accumulators per tile: fewer, larger copies against fewer tiles to spread over the SMs
+  int halves = 1;
+  {
+    double cost[3] = {0, 0, 0};
+    for (int hv = 1; hv <= 2; hv++) {
+      int bw, bh, bn;
+      pick_box(Wo, Ho, N, 128 * hv, 0, &bw, &bh, &bn);
+      const long long tiles = (long long)((Wo + bw - 1) / bw) * ((Ho + bh - 1) / bh) * ((N + bn - 1) / bn) * tiles_c;
+      const long long waves = (tiles + sms - 1) / sms;
+      cost[hv] = (double)waves * ksteps * step_cycles(2, hv * HALF_BYTES + p.bn_cols * 128.0, 4 * hv);
+    }
+    // two 256-column accumulators fill the tensor memory: the epilogue no longer overlaps the next tile, and the
+    // 64 KB stages leave a ring of three (measured: 1.45 x the modelled step)
+    if (p.bn_cols == 256) cost[2] *= 1.45;
+    halves = cost[2] < cost[1] ? 2 : 1;
+    if (tune().rows == 128) halves = 1;
+    if (tune().rows == 256) halves = 2;
+  }
+  pick_box(Wo, Ho, N, 128 * halves, 0, &p.bw, &p.bh, &p.bn);
+  if (tune().bw > 0 && tune().bw * tune().bh * tune().bn <= 128 * halves) { p.bw = tune().bw; p.bh = tune().bh; p.bn = tune().bn; }
+  p.tiles_w = (Wo + p.bw - 1) / p.bw; p.tiles_h = (Ho + p.bh - 1) / p.bh; p.tiles_n = (N + p.bn - 1) / p.bn;
+  p.stages = stages_for(halves, p.bn_cols);
   p.out = y; p.bias = bias; p.N = N; p.H = Ho; p.W = Wo; p.Ci = Ci; p.Co = Co;
   p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w;
-  p.split = 1; p.chunks_per_split = 0;
-  p.flags = (bias ? kBias : 0) | tune().flags;
+  p.split = 1; p.chunks_per_split = 0; p.b_chunks = 1;
+  p.flags = bias ? kBias : 0;
   p.error = error;
   CUtensorMap ma, mb;
-  int rc = make_map_nhwc(&ma, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, p.bw, p.bh, p.bn);
+  int rc = make_map_nhwc(&ma, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, p.bw, p.bh, p.bn, 0);
   if (rc) return rc;
   rc = make_map_2d(&mb, w, (uint64_t)Co, (uint64_t)kh * kw * Ci, (uint32_t)p.bn_cols);
   if (rc) return rc;
-  const long long tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n * ((Co + p.bn_cols - 1) / p.bn_cols);
+  const long long tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n * tiles_c;
   const int grid = (int)(tiles < sms ? tiles : sms);
-  const size_t smem = (size_t)p.stages * (A_BYTES + p.bn_cols * BK * 2) + sizeof(Smem) + 1024;
-  conv_igemm_kernel<false><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
+  const size_t smem = smem_for(halves, p.bn_cols, p.stages);
+  if (halves == 2) conv_igemm_kernel<false, 2><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
+  else conv_igemm_kernel<false, 1><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }
 
@@ -485,33 +548,34 @@ int gcow_conv_wgrad_split(int N, int Hin, int Win, int Ci, int Co, int kh, int k
 }
 
 // part[split][Co][kh*kw*Ci] (fp32) = partial sums over pixel ranges of dy[N,Ho,Wo,Co]^T * shifted x[N,Hin,Win,Ci];
-// the caller adds the `split` slices (gcow_reduce_partials). Ci a multiple of 64, Co a multiple of 8.
+// the caller adds the `split` slices (gcow_reduce_partials). Ci and Co multiples of 64.
 int gcow_conv_wgrad(const void* dy, const void* x, float* part, int N, int Hin, int Win, int Ci, int Co, int kh, int kw,
                     int pad_h, int pad_w, uint32_t* error, void* stream) {
   const int Ho = Hin + 2 * pad_h - kh + 1, Wo = Win + 2 * pad_w - kw + 1;
   if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
-  if (Ci % 64 || Co % 8 || kh < 1 || kw < 1 || pad_h < 0 || pad_w < 0) return -1;
+  if (Ci % 64 || Co % 64 || kh < 1 || kw < 1 || pad_h < 0 || pad_w < 0) return -1;
   if ((uintptr_t)part & 15) return -1;
   const int sms = device_sms();
   const WgradPlan q = wgrad_plan(N, Ho, Wo, Ci, Co, kh * kw, sms);
   Params p{};
   p.bw = q.bw; p.bh = q.bh; p.bn = q.bn; p.tiles_w = q.tiles_w; p.tiles_h = q.tiles_h; p.tiles_n = q.tiles_n;
   p.bn_cols = 256;
-  p.stages = stages_for(p.bn_cols);
+  p.stages = stages_for(q.halves, p.bn_cols);
   p.out = part; p.bias = nullptr; p.N = N; p.H = Ho; p.W = Wo; p.Ci = Ci; p.Co = Co;
   p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w;
-  p.split = q.split; p.chunks_per_split = q.per;
+  p.split = q.split; p.chunks_per_split = q.per; p.b_chunks = q.b_chunks;
   p.flags = 0;
   p.error = error;
   CUtensorMap ma, mb;
-  int rc = make_map_nhwc(&ma, dy, (uint64_t)N, (uint64_t)Ho, (uint64_t)Wo, (uint64_t)Co, q.bw, q.bh, q.bn);
+  int rc = make_map_nhwc(&ma, dy, (uint64_t)N, (uint64_t)Ho, (uint64_t)Wo, (uint64_t)Co, q.bw, q.bh, q.bn, 2u * q.halves);
   if (rc) return rc;
-  rc = make_map_nhwc(&mb, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, q.bw, q.bh, q.bn);
+  rc = make_map_nhwc(&mb, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, q.bw, q.bh, q.bn, (uint32_t)q.b_chunks);
   if (rc) return rc;
-  const long long tiles = (long long)q.split * ((Co + 127) / 128) * ((kh * kw * Ci + 255) / 256);
+  const long long tiles = (long long)q.split * ((Co + 128 * q.halves - 1) / (128 * q.halves)) * ((kh * kw * Ci + 255) / 256);
   const int grid = (int)(tiles < sms ? tiles : sms);
-  const size_t smem = (size_t)p.stages * (A_BYTES + p.bn_cols * BK * 2) + sizeof(Smem) + 1024;
-  conv_igemm_kernel<true><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
+  const size_t smem = smem_for(q.halves, p.bn_cols, p.stages);
+  if (q.halves == 2) conv_igemm_kernel<true, 2><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
+  else conv_igemm_kernel<true, 1><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }
 
