@@ -50,12 +50,15 @@ template <int BM_> struct Shape {
   static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES);
 };
 
-enum Flags : int { kOutF32 = 1, kBias = 2, kGelu = 4, kResidual = 8, kAccumulate = 16 };
+enum Flags : int { kOutF32 = 1, kBias = 2, kGelu = 4, kResidual = 8, kAccumulate = 16,
+                   kAuxOut = 32,     // bf16 output only: also store the value before GELU to aux (what the GELU gradient needs)
+                   kGeluGrad = 64 }; // bf16 output only: multiply by GELU'(aux) - the gradient through a fused GELU
 
 struct Params {
   void* C;                 // bf16 or fp32 [M, ldc]
   const float* bias;       // [N] fp32 or nullptr
   const void* residual;    // same type/ld as C or nullptr
+  void* aux;               // bf16, same shape/ld as C: written (kAuxOut) or read (kGeluGrad)
   int M, N, K, ldc, flags;
   int batch;               // number of independent products (operands are 3-D tensor maps when > 1)
   int a_merged, b_merged;  // MN-major operand fetched as ONE box per stage (its row length is a multiple of 64)
@@ -94,6 +97,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t* smA = base;
   uint8_t* smB = base + STAGES * A_BYTES;
   Smem* sm = reinterpret_cast<Smem*>(base + STAGES * (A_BYTES + B_BYTES));
+  // per-warp staging buffers of the epilogue, 16-byte aligned behind the barriers
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>(((uintptr_t)(sm + 1) + 15) & ~(uintptr_t)15);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
@@ -221,6 +226,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // while chunk c is converted and stored.
         auto process = [&](const uint32_t (&r)[32], int c) {
           const int n = n0 + col0 + c * 32;
+          if (!(p.flags & kOutF32) && n + 32 <= p.N && m0 + h * 128 + q * 32 < p.M) {
+            // bf16 output, whole 32-column chunk (warp-uniform): every global access goes through the
+            // warp's staging buffer so that it is coalesced
+            uint8_t* stg = stage_base + ew * kStageWarpBytes;
+            const bool row_ok = m < p.M;
+            const size_t off = (size_t)bz * (size_t)p.stride_c + (size_t)m * p.ldc + n;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+            if (p.flags & kBias) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] += __ldg(p.bias + n + j);
+            }
+            if (p.flags & kAuxOut) warp_store_rows_bf16(stg, lane, v, reinterpret_cast<__nv_bfloat16*>(p.aux), off, row_ok);
+            if (p.flags & kGeluGrad) {
+              float x[32];
+              warp_load_rows_bf16<false>(stg, lane, reinterpret_cast<const __nv_bfloat16*>(p.aux), off, row_ok, x);
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] *= gelu_grad_f(x[j]);
+            }
+            if (p.flags & kGelu) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
+            }
+            if (p.flags & kResidual)
+              warp_load_rows_bf16<true>(stg, lane, reinterpret_cast<const __nv_bfloat16*>(p.residual), off, row_ok, v);
+            warp_store_rows_bf16(stg, lane, v, reinterpret_cast<__nv_bfloat16*>(p.C), off, row_ok);
+            return;
+          }
           if (m < p.M && n < p.N) {
             float v[32];
 #pragma unroll
@@ -229,11 +263,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
               for (int j = 0; j < 32; j++) if (n + j < p.N) v[j] += __ldg(p.bias + n + j);
             }
+            const size_t off = (size_t)bz * (size_t)p.stride_c + (size_t)m * p.ldc + n;
             if (p.flags & kGelu) {
 #pragma unroll
               for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
             }
-            const size_t off = (size_t)bz * (size_t)p.stride_c + (size_t)m * p.ldc + n;
             if (p.flags & kOutF32) {
               float* C = reinterpret_cast<float*>(p.C) + off;
               const float* R = reinterpret_cast<const float*>(p.residual) + off;
@@ -369,7 +403,9 @@ static int make_map_mn(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t c
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
-template <int BM_> constexpr size_t smem_bytes() { return Shape<BM_>::SMEM + sizeof(Smem) + 1024; }
+template <int BM_> constexpr size_t smem_bytes() {
+  return Shape<BM_>::SMEM + sizeof(Smem) + 16 + (size_t)Shape<BM_>::EPI_WARPS * kStageWarpBytes + 1024;
+}
 
 }  // namespace gemm
 
@@ -401,7 +437,7 @@ extern "C" {
 // tile_rows: 128 or 256 to force a tile shape, anything else lets the launcher choose.
 // Returns 0, a negative argument error, or a CUDA error code.
 static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                       const float* bias, const void* residual, int flags, uint32_t* error, int max_ctas,
+                       const float* bias, const void* residual, void* aux, int flags, uint32_t* error, int max_ctas,
                        int a_mn, int b_mn, int tile_rows, int batch, long long stride_a, long long stride_b,
                        long long stride_c, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
@@ -412,6 +448,8 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   if ((uintptr_t)C & 15) return -1;
   if ((flags & kBias) && !bias) return -1;
   if ((flags & kResidual) && (!residual || ((uintptr_t)residual & 15))) return -1;
+  if ((flags & (kAuxOut | kGeluGrad)) && (!aux || ((uintptr_t)aux & 15) || N % 32 || (flags & kOutF32))) return -1;
+  if ((flags & kAuxOut) && (flags & kGeluGrad)) return -1;
   CUtensorMap ma, mb;
   static std::once_flag once;
   static int sms = 148;
@@ -462,7 +500,7 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   }
   if (rc) return rc;
   Params p;
-  p.C = C; p.bias = bias; p.residual = residual;
+  p.C = C; p.bias = bias; p.residual = residual; p.aux = aux;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags; p.error = error;
   p.batch = batch; p.stride_c = batch > 1 ? stride_c : 0;
   p.a_merged = a_merged; p.b_merged = b_merged;
@@ -489,7 +527,17 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
 int gcow_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                    const float* bias, const void* residual, int flags, uint32_t* error, int max_ctas,
                    int a_mn, int b_mn, int tile_rows, void* stream) {
-  return gemm_launch(A, B, C, M, N, K, lda, ldb, ldc, bias, residual, flags, error, max_ctas, a_mn, b_mn, tile_rows,
+  return gemm_launch(A, B, C, M, N, K, lda, ldb, ldc, bias, residual, nullptr, flags, error, max_ctas, a_mn, b_mn, tile_rows,
+                     1, 0, 0, 0, stream);
+}
+
+// As gcow_gemm_bf16 with a bf16 side tensor `aux` of C's shape and leading dimension (N a multiple of 32, bf16 C):
+// flags & 32: aux receives the value before GELU (acc + bias) while C gets GELU of it;
+// flags & 64: the result is multiplied by GELU'(aux) before the residual is added - the backward of that GELU.
+int gcow_gemm_bf16_aux(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                       const float* bias, const void* residual, void* aux, int flags, uint32_t* error, int a_mn, int b_mn,
+                       int tile_rows, void* stream) {
+  return gemm_launch(A, B, C, M, N, K, lda, ldb, ldc, bias, residual, aux, flags, error, 0, a_mn, b_mn, tile_rows,
                      1, 0, 0, 0, stream);
 }
 
@@ -499,7 +547,7 @@ int gcow_gemm_bf16_batched(const void* A, const void* B, void* C, int M, int N, 
                            int batch, long long stride_a, long long stride_b, long long stride_c, const float* bias,
                            const void* residual, int flags, uint32_t* error, int a_mn, int b_mn, int tile_rows,
                            void* stream) {
-  return gemm_launch(A, B, C, M, N, K, lda, ldb, ldc, bias, residual, flags, error, 0, a_mn, b_mn, tile_rows, batch,
+  return gemm_launch(A, B, C, M, N, K, lda, ldb, ldc, bias, residual, nullptr, flags, error, 0, a_mn, b_mn, tile_rows, batch,
                      stride_a, stride_b, stride_c, stream);
 }
 

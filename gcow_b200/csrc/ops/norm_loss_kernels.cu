@@ -336,6 +336,38 @@ colsum_partial_kernel(const bf16* __restrict__ g, float* __restrict__ part, int 
   if (c + 1 < cols) part[(size_t)blockIdx.y * cols + c + 1] = s1;
 }
 
+// Wide variant: 16-byte loads (8 columns per thread), 8 row lanes per CTA with independent accumulators,
+// folded through shared memory. One CTA covers 256 columns x rows_per rows.
+__global__ void __launch_bounds__(256)
+colsum_partial8_kernel(const bf16* __restrict__ g, float* __restrict__ part, int rows, int cols, int ld, int rows_per) {
+  __shared__ float red[8][256 + 8];
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;       // column group (8 columns), row lane
+  const int c = blockIdx.x * 256 + cg * 8;
+  const int r0 = blockIdx.y * rows_per, r1 = min(rows, r0 + rows_per);
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) acc[j] = 0.0f;
+  if (c < cols) {
+#pragma unroll 4
+    for (int r = r0 + rl; r < r1; r += 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(g + (size_t)r * ld + c);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(b[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++) red[rl][cg * 8 + j] = acc[j];
+  __syncthreads();
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col < cols) {
+    float s = 0.0f;
+#pragma unroll
+    for (int l = 0; l < 8; l++) s += red[l][threadIdx.x];     // fixed order
+    part[(size_t)blockIdx.y * cols + col] = s;
+  }
+}
+
 // ------------------------------------------------------- image normalisation
 // uint8 NHWC [n, 3] pixels -> bf16 NHWC padded to `cpad` channels (extra channels 0):
 // y = (x - mean_c) / std_c with mean/std given in 0..255 units.
@@ -434,13 +466,18 @@ int gcow_softmax_bwd(const void* dp, const void* p, void* ds, int64_t rows, int 
 
 // Column sums of a bf16 [rows, cols] matrix (ld even, cols even) into fp32 out[cols];
 // `part` must hold gcow_colsum_parts(rows) * cols floats.
-int gcow_colsum_parts(int rows) { int p = (rows + 255) / 256; return p < 64 ? (p < 1 ? 1 : p) : 64; }
+int gcow_colsum_parts(int rows) { int p = (rows + 127) / 128; return p < 128 ? (p < 1 ? 1 : p) : 128; }
 int gcow_colsum(const void* g, float* part, float* out, int rows, int cols, int ld, void* stream) {
   if (cols % 2 || ld % 2 || rows <= 0) return -1;
   const int parts = gcow_colsum_parts(rows);
   const int rows_per = (rows + parts - 1) / parts;
-  dim3 grid((cols / 2 + 255) / 256, parts);
-  colsum_partial_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)g, part, rows, cols, ld, rows_per);
+  if (cols % 8 == 0 && ld % 8 == 0 && ((uintptr_t)g & 15) == 0) {
+    dim3 grid((cols + 255) / 256, parts);
+    colsum_partial8_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)g, part, rows, cols, ld, rows_per);
+  } else {
+    dim3 grid((cols / 2 + 255) / 256, parts);
+    colsum_partial_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)g, part, rows, cols, ld, rows_per);
+  }
   reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, (cudaStream_t)stream>>>(part, out, parts, cols);
   return (int)cudaGetLastError();
 }

@@ -117,8 +117,89 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr) {
   return d;
 }
 
+// GELU pieces for GEMM epilogues, where eight warps do the elementwise math of a whole tile and libm's erff
+// (a long dependent chain) would take longer than the tile's main loop. Phi(x) = 0.5 (1 + erf(x / sqrt 2)) from
+// the rational approximation erf(z) = 1 - (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z) (Abramowitz &
+// Stegun 7.1.26, absolute error below 1.5e-7); exp(-z^2) = exp(-x^2 / 2) is also what the derivative needs.
+__device__ __forceinline__ void gelu_parts(float x, float& cdf, float& gauss) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
+  gauss = __expf(-0.5f * x * x);
+  float q = fmaf(1.061405429f, t, -1.453152027f);
+  q = fmaf(q, t, 1.421413741f);
+  q = fmaf(q, t, -0.284496736f);
+  q = fmaf(q, t, 0.254829592f);
+  q = 0.5f * q * t * gauss;
+  cdf = x >= 0.0f ? 1.0f - q : q;
+}
 __device__ __forceinline__ float gelu_f(float x) {
-  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+  float cdf, g;
+  gelu_parts(x, cdf, g);
+  return x * cdf;
+}
+// d/dx of x Phi(x) = Phi(x) + x phi(x)
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  float cdf, g;
+  gelu_parts(x, cdf, g);
+  return fmaf(x * 0.3989422804014327f, g, cdf);
+}
+
+// Coalesced bf16 rows for epilogues. After tcgen05.ld a lane owns one row of the tile (32 consecutive columns),
+// so a direct 16-byte store per lane touches 32 different rows per instruction: 32 memory transactions of 16
+// useful bytes. These helpers pass the warp's 32 x 32 block through a private shared-memory buffer of 32 rows
+// x 80 bytes (64 data + 16 pad: conflict-free for both access patterns) so that four lanes cover the 64 bytes
+// of one row and an instruction touches 8 rows: a quarter of the transactions, all of them whole sectors.
+// row_off: element offset of the lane's own row start (column 0 of the block), row_ok: whether that row exists.
+constexpr int kStageRowBytes = 80, kStageWarpBytes = 32 * kStageRowBytes;
+
+__device__ __forceinline__ void warp_store_rows_bf16(uint8_t* stg, int lane, const float (&v)[32], __nv_bfloat16* base,
+                                                     size_t row_off, bool row_ok) {
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    uint4 o;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[8 * k + 2 * e], v[8 * k + 2 * e + 1]);
+    *reinterpret_cast<uint4*>(stg + lane * kStageRowBytes + k * 16) = o;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 4; it++) {
+    const int row = it * 8 + (lane >> 2), ch = lane & 3;
+    const unsigned long long off = __shfl_sync(0xffffffffu, (unsigned long long)row_off, row);
+    const int ok = __shfl_sync(0xffffffffu, (int)row_ok, row);
+    const uint4 x = *reinterpret_cast<const uint4*>(stg + row * kStageRowBytes + ch * 16);
+    if (ok) *reinterpret_cast<uint4*>(base + off + ch * 8) = x;
+  }
+  __syncwarp();
+}
+
+// out[j] (+)= the lane's own row of a bf16 tensor, fetched with the same coalesced pattern
+template <bool ADD>
+__device__ __forceinline__ void warp_load_rows_bf16(uint8_t* stg, int lane, const __nv_bfloat16* base, size_t row_off,
+                                                    bool row_ok, float (&out)[32]) {
+#pragma unroll
+  for (int it = 0; it < 4; it++) {
+    const int row = it * 8 + (lane >> 2), ch = lane & 3;
+    const unsigned long long off = __shfl_sync(0xffffffffu, (unsigned long long)row_off, row);
+    const int ok = __shfl_sync(0xffffffffu, (int)row_ok, row);
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (ok) x = *reinterpret_cast<const uint4*>(base + off + ch * 8);
+    *reinterpret_cast<uint4*>(stg + row * kStageRowBytes + ch * 16) = x;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const uint4 x = *reinterpret_cast<const uint4*>(stg + lane * kStageRowBytes + k * 16);
+    const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const float2 f = __bfloat1622float2(xb[e]);
+      if (ADD) { out[8 * k + 2 * e] += f.x; out[8 * k + 2 * e + 1] += f.y; }
+      else { out[8 * k + 2 * e] = f.x; out[8 * k + 2 * e + 1] = f.y; }
+    }
+  }
+  __syncwarp();
 }
 
 // Host side: the driver's tensor-map encoder, looked up once through the runtime.

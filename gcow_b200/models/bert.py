@@ -43,9 +43,8 @@ class BertLayer(nn.Module):
         B, S, H = x.shape
         qkv = self.qkv(x).view(B, S, 3, self.heads, H // self.heads)
         ctx = gnn.attention(qkv)               # [B, S, H]
-        x = self.ln1(x + self.proj(ctx))
-        h = gnn.gelu(self.fc1(x))
-        return self.ln2(x + self.fc2(h))
+        x = self.ln1(gnn.linear_residual(ctx, self.proj, x))
+        return self.ln2(gnn.ffn_residual(x, self.fc1, self.fc2))
 
 
 class BertForPreTraining(nn.Module):

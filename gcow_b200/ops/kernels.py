@@ -12,7 +12,7 @@ from .. import _native
 _launches = 0
 _err_words: dict = {}
 
-OUT_F32, BIAS, GELU, RESIDUAL, ACCUMULATE = 1, 2, 4, 8, 16
+OUT_F32, BIAS, GELU, RESIDUAL, ACCUMULATE, AUX_OUT, GELU_GRAD = 1, 2, 4, 8, 16, 32, 64
 
 
 def launch_count() -> int:
@@ -51,8 +51,13 @@ def check_errors(device: torch.device | None = None) -> None:
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, gelu: bool = False, out_dtype=torch.bfloat16,
               out: torch.Tensor | None = None, accumulate: bool = False, max_ctas: int = 0,
-              a_t: bool = False, b_t: bool = False, tile_rows: int = 0) -> torch.Tensor:
+              a_t: bool = False, b_t: bool = False, tile_rows: int = 0,
+              pre_gelu_out: torch.Tensor | None = None, gelu_grad_of: torch.Tensor | None = None) -> torch.Tensor:
     """C[M,N] = op(A) @ op(B)^T (+bias) (GELU) (+residual) on the tcgen05 kernel.
+
+    ``pre_gelu_out`` (bf16 [M,N], with ``gelu``): also receives the value before the GELU, which its
+    gradient needs. ``gelu_grad_of`` (bf16 [M,N]): the product is multiplied by GELU'(that tensor) before
+    the residual is added, i.e. the backward of a GELU fused into the GEMM that produces its input gradient.
 
     a: bf16 [M,K] (or [K,M] with ``a_t``: the stored matrix is used transposed without a
     copy). b: bf16 [N,K] (or [K,N] with ``b_t``). Last dimension contiguous, leading
@@ -72,11 +77,23 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
         assert bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == N
     if residual is not None:
         assert residual.dtype == out.dtype and residual.stride() == out.stride()
-    err = _native.cuda().gcow_gemm_bf16(
-        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
-        bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
-        flags, _error_word(a.device).data_ptr(), max_ctas, int(a_t), int(b_t), int(tile_rows),
-        torch.cuda.current_stream(a.device).cuda_stream)
+    aux = pre_gelu_out if pre_gelu_out is not None else gelu_grad_of
+    if aux is not None:
+        assert pre_gelu_out is None or gelu_grad_of is None
+        assert aux.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and aux.shape == out.shape
+        assert aux.stride() == out.stride() and N % 32 == 0 and max_ctas == 0
+        flags |= AUX_OUT if pre_gelu_out is not None else GELU_GRAD
+        err = _native.cuda().gcow_gemm_bf16_aux(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
+            aux.data_ptr(), flags, _error_word(a.device).data_ptr(), int(a_t), int(b_t), int(tile_rows),
+            torch.cuda.current_stream(a.device).cuda_stream)
+    else:
+        err = _native.cuda().gcow_gemm_bf16(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
+            flags, _error_word(a.device).data_ptr(), max_ctas, int(a_t), int(b_t), int(tile_rows),
+            torch.cuda.current_stream(a.device).cuda_stream)
     if err:
         raise RuntimeError(f"gcow_gemm_bf16 refused the call: {err}")
     _launches += 1
@@ -165,6 +182,79 @@ class _LinearFn(torch.autograd.Function):
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)[:N]
         return gx, gw, gb
+
+
+class _LinearResidualFn(torch.autograd.Function):
+    """y = r + x W^T + b with the residual added in the GEMM epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, r):
+        xb = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+        wb = w.to(torch.bfloat16).contiguous()
+        rb = r.reshape(-1, r.shape[-1]).to(torch.bfloat16).contiguous()
+        y = gemm_bf16(xb, wb, bias=b.float().contiguous() if b is not None else None, residual=rb)
+        ctx.save_for_backward(xb, wb)
+        ctx.meta = (x.shape, r.shape, b is not None)
+        return y.view(r.shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        xb, wb = ctx.saved_tensors
+        x_shape, r_shape, has_bias = ctx.meta
+        g = gy.reshape(-1, gy.shape[-1]).to(torch.bfloat16).contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = gemm_bf16(g, wb, b_t=True).view(x_shape)
+        if ctx.needs_input_grad[1]:
+            gw = wgrad_gemm(g, xb)
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(g)
+        return gx, gw, gb, (gy if ctx.needs_input_grad[3] else None)
+
+
+class _FfnResidualFn(torch.autograd.Function):
+    """y = x + GELU(x W1^T + b1) W2^T + b2 as two GEMMs forward and four backward, with every elementwise
+    step in a GEMM epilogue: bias + GELU (keeping the pre-activation), bias + residual, GELU' on the way
+    back, and the sum of the two gradient paths into x."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2):
+        xb = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+        w1b, w2b = w1.to(torch.bfloat16).contiguous(), w2.to(torch.bfloat16).contiguous()
+        M, F = xb.shape[0], w1b.shape[0]
+        pre = torch.empty((M, F), dtype=torch.bfloat16, device=xb.device)
+        act = gemm_bf16(xb, w1b, bias=b1.float().contiguous(), gelu=True, pre_gelu_out=pre)
+        y = gemm_bf16(act, w2b, bias=b2.float().contiguous(), residual=xb)
+        ctx.save_for_backward(xb, w1b, w2b, pre, act)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        xb, w1b, w2b, pre, act = ctx.saved_tensors
+        g = gy.reshape(-1, gy.shape[-1]).to(torch.bfloat16).contiguous()
+        dpre = gemm_bf16(g, w2b, b_t=True, gelu_grad_of=pre)                 # (g W2) * GELU'(pre)
+        gw2 = wgrad_gemm(g, act) if ctx.needs_input_grad[3] else None
+        gb2 = colsum(g) if ctx.needs_input_grad[4] else None
+        gx = gemm_bf16(dpre, w1b, b_t=True, residual=g).view(ctx.shape) if ctx.needs_input_grad[0] else None
+        gw1 = wgrad_gemm(dpre, xb) if ctx.needs_input_grad[1] else None
+        gb1 = colsum(dpre) if ctx.needs_input_grad[2] else None
+        return gx, gw1, gb1, gw2, gb2
+
+
+def fused_mlp_usable(x: torch.Tensor, *weights: torch.Tensor) -> bool:
+    """Inputs on the GPU, the aux-epilogue entry built, every width a multiple of 32."""
+    if not (x.is_cuda and _have("gcow_gemm_bf16_aux") and x.shape[-1] % 32 == 0):
+        return False
+    return all(w.shape[0] % 32 == 0 and w.shape[1] % 32 == 0 for w in weights) and x.numel() // x.shape[-1] >= 64
+
+
+def linear_residual(x, w, b, r):
+    return _LinearResidualFn.apply(x, w, b, r)
+
+
+def ffn_residual(x, w1, b1, w2, b2):
+    return _FfnResidualFn.apply(x, w1, b1, w2, b2)
 
 
 def gemm_usable(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -22,6 +22,23 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return F.linear(x, weight, bias)
 
 
+def linear_residual(x: torch.Tensor, lin: nn.Linear, residual: torch.Tensor) -> torch.Tensor:
+    """``residual + lin(x)``; on the own backend the addition happens in the GEMM epilogue."""
+    if (backend.get_backend() == "own" and lin.bias is not None and residual.shape[-1] == lin.out_features
+            and K.fused_mlp_usable(x, lin.weight)):
+        return K.linear_residual(x, lin.weight, lin.bias, residual)
+    return residual + linear(x, lin.weight, lin.bias)
+
+
+def ffn_residual(x: torch.Tensor, fc1: nn.Linear, fc2: nn.Linear) -> torch.Tensor:
+    """``x + fc2(gelu(fc1(x)))`` - the transformer feed-forward block. On the own backend bias, GELU, its
+    gradient and both residual additions run inside the epilogues of the four GEMMs involved."""
+    if (backend.get_backend() == "own" and fc1.bias is not None and fc2.bias is not None
+            and K.fused_mlp_usable(x, fc1.weight, fc2.weight)):
+        return K.ffn_residual(x, fc1.weight, fc1.bias, fc2.weight, fc2.bias)
+    return x + linear(gelu(linear(x, fc1.weight, fc1.bias)), fc2.weight, fc2.bias)
+
+
 class Linear(nn.Linear):
     def forward(self, x):
         return linear(x, self.weight, self.bias)
