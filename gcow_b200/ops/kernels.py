@@ -682,7 +682,7 @@ def conv_gemm_enabled() -> bool:
     the explicit patch matrix costs KH*KW times the activation traffic, so cuDNN's
     implicit GEMM stays the default."""
     import os
-    return os.environ.get("GCOW_CONV", "lib") in ("own", "igemm")
+    return os.environ.get("GCOW_CONV", "lib") == "own"
 
 
 def conv_gemm_usable(x: torch.Tensor, w: torch.Tensor, groups: int, dilation) -> bool:
@@ -757,10 +757,17 @@ class _ConvIgemmFn(torch.autograd.Function):
 
 
 def conv_igemm_mode() -> str:
-    """GCOW_CONV selects the KxK convolution path of the own backend: ``igemm`` (implicit GEMM on the
-    tcgen05 kernel, stride 1 only), ``own`` (im2col + GEMM, any stride) or ``lib`` (cuDNN)."""
+    """GCOW_CONV selects the KxK convolution path of the own backend: ``auto`` (default: implicit GEMM on the
+    tcgen05 kernel for stride-1 layers with at least 128 channels, where it is on par with cuDNN, and cuDNN for
+    the rest), ``igemm`` (implicit GEMM wherever it applies), ``own`` (im2col + GEMM, any stride) or ``lib``
+    (cuDNN everywhere)."""
     import os
-    return os.environ.get("GCOW_CONV", "lib")
+    return os.environ.get("GCOW_CONV", "auto")
+
+
+def conv_igemm_wanted(w: torch.Tensor) -> bool:
+    mode = conv_igemm_mode()
+    return mode == "igemm" or (mode == "auto" and min(w.shape[0], w.shape[1]) >= 128)
 
 
 def conv_igemm_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups: int, dilation) -> bool:

@@ -50,7 +50,7 @@ class Conv2d(nn.Conv2d):
                 and self.padding == (0, 0) and self.groups == 1 and K.conv1x1_enabled()
                 and K.conv1x1_usable(x, self.weight)):
             return K.conv1x1(x, self.weight, self.bias)
-        if (backend.get_backend() == "own" and K.conv_igemm_mode() == "igemm"
+        if (backend.get_backend() == "own" and K.conv_igemm_wanted(self.weight)
                 and K.conv_igemm_usable(x, self.weight, self.stride, self.padding, self.groups, self.dilation)):
             return K.conv_igemm(x, self.weight, self.bias, self.padding)
         if (backend.get_backend() == "own" and K.conv_gemm_enabled() and self.stride[0] == self.stride[1]
