@@ -81,6 +81,8 @@ def _declare_gemm(lib, proto):
     opt("gcow_softmax_fwd", i32, ptr, ptr, i64, i32, C.c_float, ptr)
     opt("gcow_softmax_bwd", i32, ptr, ptr, ptr, i64, i32, C.c_float, ptr)
     opt("gcow_gemm_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, i32, ptr, i32, i32, i32, i32, ptr)
+    opt("gcow_gemm2_max_pairs", i32)
+    opt("gcow_gemm2_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, ptr, i32, ptr, ptr)
     opt("gcow_gemm_bf16_aux", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, ptr, i32, ptr, i32, i32, i32, ptr)
 
 

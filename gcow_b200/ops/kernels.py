@@ -80,9 +80,24 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
     aux = pre_gelu_out if pre_gelu_out is not None else gelu_grad_of
     if aux is not None:
         assert pre_gelu_out is None or gelu_grad_of is None
+        flags |= AUX_OUT if pre_gelu_out is not None else GELU_GRAD
+    if (_pair_gemm_enabled() and not a_t and not b_t and out.dtype == torch.bfloat16 and not accumulate and max_ctas == 0
+            and tile_rows == 0 and K % 64 == 0 and N % 32 == 0 and M >= 1024 and N >= 256
+            and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0 and out.stride(0) % 8 == 0):
+        # large K-major product: the CTA-pair kernel (two SMs per 256 x 256 tile)
+        err = _native.cuda().gcow_gemm2_bf16(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
+            aux.data_ptr() if aux is not None else None, flags, _error_word(a.device).data_ptr(),
+            torch.cuda.current_stream(a.device).cuda_stream)
+        if err == 0:
+            _launches += 1
+            return out
+        if err != -2:
+            raise RuntimeError(f"gcow_gemm2_bf16 refused the call: {err}")
+    if aux is not None:
         assert aux.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and aux.shape == out.shape
         assert aux.stride() == out.stride() and N % 32 == 0 and max_ctas == 0
-        flags |= AUX_OUT if pre_gelu_out is not None else GELU_GRAD
         err = _native.cuda().gcow_gemm_bf16_aux(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
             bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
@@ -98,6 +113,20 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
         raise RuntimeError(f"gcow_gemm_bf16 refused the call: {err}")
     _launches += 1
     return out
+
+
+_pair_gemm = None
+
+
+def _pair_gemm_enabled() -> bool:
+    """The CTA-pair GEMM (cta_group::2) serves large K-major products when GCOW_GEMM2=1 and the device can
+    co-schedule clusters of two CTAs with its shared-memory footprint."""
+    global _pair_gemm
+    if _pair_gemm is None:
+        import os
+        _pair_gemm = (os.environ.get("GCOW_GEMM2", "0") == "1" and _have("gcow_gemm2_bf16")
+                      and _native.cuda().gcow_gemm2_max_pairs() > 0)
+    return _pair_gemm
 
 
 def wgrad_gemm(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:

@@ -112,3 +112,39 @@ def test_wgrad_split_k_matches_reference():
         y = K_.wgrad_gemm(g, x)
         K_.check_errors()
         assert y.shape == (N, K) and (y - ref).abs().max().item() < 2e-3 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 512, 256), (2048, 1024, 1024), (1100, 288, 192), (4096, 4096, 64)])
+def test_pair_gemm_matches_fp32_reference(M, N, K, monkeypatch):
+    """The CTA-pair kernel (cta_group::2) incl. ragged edges, a K that is not a whole stage, and every epilogue."""
+    from gcow_b200 import _native
+    from gcow_b200.ops import kernels as K_
+    if not hasattr(_native.cuda(), "gcow_gemm2_bf16") or _native.cuda().gcow_gemm2_max_pairs() <= 0:
+        pytest.skip("clusters of two CTAs cannot be scheduled here")
+    monkeypatch.setattr(K_, "_pair_gemm", True)
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    before = K_.launch_count()
+    y = K_.gemm_bf16(a, b)
+    K_.check_errors()
+    ref = _ref(a, b)
+    assert (y.float() - ref).abs().max().item() / ref.abs().max().item() < 2e-2
+    y = K_.gemm_bf16(a, b, bias=bias, residual=res)
+    ref2 = _ref(a, b, bias=bias, residual=res)
+    assert (y.float() - ref2).abs().max().item() / ref2.abs().max().item() < 2e-2
+    pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    act = K_.gemm_bf16(a, b, bias=bias, gelu=True, pre_gelu_out=pre)
+    K_.check_errors()
+    ref_pre = _ref(a, b, bias=bias)
+    assert (pre.float() - ref_pre).abs().max().item() / ref_pre.abs().max().item() < 2e-2
+    ref_act = torch.nn.functional.gelu(ref_pre)
+    assert (act.float() - ref_act).abs().max().item() / ref_act.abs().max().item() < 2e-2
+    g = K_.gemm_bf16(a, b, gelu_grad_of=pre)
+    x = pre.float()
+    ref_g = ref * (0.5 * (1 + torch.erf(x / 2 ** 0.5)) + x * torch.exp(-0.5 * x * x) / (2 * 3.141592653589793) ** 0.5)
+    assert (g.float() - ref_g).abs().max().item() / ref_g.abs().max().item() < 2e-2
+    K_.check_errors()
+    assert K_.launch_count() == before + 4
