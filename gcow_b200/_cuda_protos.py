@@ -82,7 +82,7 @@ def _declare_gemm(lib, proto):
     opt("gcow_softmax_bwd", i32, ptr, ptr, ptr, i64, i32, C.c_float, ptr)
     opt("gcow_gemm_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, i32, ptr, i32, i32, i32, i32, ptr)
     opt("gcow_gemm2_max_pairs", i32)
-    opt("gcow_gemm2_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, ptr, i32, ptr, ptr)
+    opt("gcow_gemm2_bf16", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, ptr, i32, ptr, i32, ptr)
     opt("gcow_gemm_bf16_aux", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr, ptr, ptr, i32, ptr, i32, i32, i32, ptr)
 
 
@@ -153,6 +153,9 @@ def _declare_conv(lib, proto):
     opt("gcow_conv_wgrad", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, i32, ptr, ptr)
     opt("gcow_conv_flip_weights", i32, ptr, ptr, i32, i32, i32, i32, ptr)
     opt("gcow_conv_pick_box", None, i32, i32, i32, i32, i32, ptr)
+    opt("gcow_embed3_fwd", i32, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, i32, ptr)
+    opt("gcow_embed_type_parts", i32, i32)
+    opt("gcow_embed3_bwd", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, i32, i32, ptr)
 
 
 _declare_prev_conv = declare

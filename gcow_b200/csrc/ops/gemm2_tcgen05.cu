@@ -85,6 +85,20 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+// MN-major operand tile fetched as ONE box {64 columns, 128 K-rows, 2 column groups}: each 64-column group is
+// 128 K-rows x 128 bytes = 16 KB, so groups are 16 KB apart (leading offset) and 8-row groups 1 KB (stride offset).
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128_16k(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+  d |= (uint64_t)(16384u >> 4) << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// B_MN: B is stored [K][N] (the data-gradient product dX = dY * W reads the weight matrix in place)
+template <bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -129,7 +143,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t bar = map_to_cta(smem_u32(&sm->full[s]), 0);
           uint8_t* st = base + s * STAGE_BYTES;
           tma_load_3d_pair(smem_u32(st), &tmap_a, bar, 0, m0, kb * 2);
-          tma_load_3d_pair(smem_u32(st + OPER_BYTES), &tmap_b, bar, 0, n0, kb * 2);
+          if (B_MN) tma_load_3d_pair(smem_u32(st + OPER_BYTES), &tmap_b, bar, 0, kb * BK, n0 / 64);
+          else tma_load_3d_pair(smem_u32(st + OPER_BYTES), &tmap_b, bar, 0, n0, kb * 2);
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
       }
@@ -142,7 +157,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // -------------------------------------------------------------- MMA issuer (CTA 0 only)
     if (lane == 0 && rank == 0) {
       // instruction descriptor: fp32 accumulate, bf16 x bf16, K-major operands, N 256, M 256 (128 rows per CTA)
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
       uint32_t s = 0, phase = 0, t = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += pairs, t++) {
@@ -157,7 +173,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; k++) {
             const uint32_t off = (k >> 2) * CHUNK_BYTES + (k & 3) * 32;     // 64-wide chunk, then 32 bytes per K step
-            tc_mma_pair(d_tmem, smem_desc_sw128(sa + off), smem_desc_sw128(sb + off), idesc, (kb | k) != 0);
+            // MN-major B: 16 K-rows of 128 bytes per step, 128 rows contiguous within a column group
+            const uint64_t db = B_MN ? smem_desc_mn_sw128_16k(sb + k * 2048) : smem_desc_sw128(sb + off);
+            tc_mma_pair(d_tmem, smem_desc_sw128(sa + off), db, idesc, (kb | k) != 0);
           }
           const uint32_t eb = smem_u32(&sm->empty[s]);
           tc_commit_pair(map_to_cta(eb, 0));
@@ -263,6 +281,21 @@ static int make_map_kfold(CUtensorMap* map, const void* ptr, uint64_t rows, uint
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
+// MN-major matrix [K][cols] (cols a multiple of 64) as {64, K, cols / 64}; box = 64 x 128 K-rows x 2 column groups (32 KB).
+static int make_map_mnfold(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t cols, uint64_t ld) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -10;
+  if (((uintptr_t)ptr & 15) || (ld * 2) % 16 || cols % 64) return -11;
+  cuuint64_t dims[3] = {64, K, cols / 64};
+  cuuint64_t strides[2] = {ld * 2, 128};
+  cuuint32_t box[3] = {64, 128, 2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
 constexpr size_t kSmemBytes = (size_t)STAGES * STAGE_BYTES + sizeof(Smem) + 16 + (size_t)EPI_WARPS * kStageWarpBytes + 1024;
 
 }  // namespace gemm2
@@ -277,7 +310,8 @@ int gcow_gemm2_max_pairs() {
   static std::once_flag once;
   static int pairs = 0;
   std::call_once(once, [] {
-    if (cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm2_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm2_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return;
     }
@@ -290,20 +324,21 @@ int gcow_gemm2_max_pairs() {
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr; cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_kernel, &cfg) == cudaSuccess) pairs = n;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_kernel<false>, &cfg) == cudaSuccess) pairs = n;
     else cudaGetLastError();
   });
   return pairs;
 }
 
-// C[M,N] = A[M,K] * B[N,K]^T (+ bias) (GELU) (+ residual), bf16 in and out, K-major operands, on CTA pairs.
+// C[M,N] = A[M,K] * op(B) (+ bias) (GELU) (+ residual), bf16 in and out, on CTA pairs. A is K-major [M][K]; B is
+// [N][K] (b_mn == 0) or [K][N] (b_mn == 1, N a multiple of 64).
 // K a multiple of 64, N a multiple of 32, lda/ldb/ldc multiples of 8, 16-byte aligned bases.
 // flags as gcow_gemm_bf16 (2 bias, 4 GELU, 8 residual, 32 aux receives the pre-GELU value, 64 multiply by GELU'(aux)).
 // Returns 0, a negative argument error (-2: not supported here, use the one-CTA kernel) or a CUDA error code.
 int gcow_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                    const float* bias, const void* residual, void* aux, int flags, uint32_t* error, void* stream) {
+                    const float* bias, const void* residual, void* aux, int flags, uint32_t* error, int b_mn, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (K % 64 || N % 32 || lda % 8 || ldb % 8 || ldc % 8 || ((uintptr_t)C & 15)) return -2;
+  if (K % 64 || N % 32 || lda % 8 || ldb % 8 || ldc % 8 || ((uintptr_t)C & 15) || (b_mn && N % 64)) return -2;
   if (flags & ~(kBias | kGelu | kResidual | kAuxOut | kGeluGrad)) return -2;
   if ((flags & kBias) && !bias) return -1;
   if ((flags & kResidual) && (!residual || ((uintptr_t)residual & 15))) return -1;
@@ -313,7 +348,8 @@ int gcow_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   CUtensorMap ma, mb;
   int rc = make_map_kfold(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda);
   if (rc) return rc;
-  rc = make_map_kfold(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb);
+  rc = b_mn ? make_map_mnfold(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb)
+            : make_map_kfold(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb);
   if (rc) return rc;
   Params p;
   p.C = (__nv_bfloat16*)C; p.bias = bias; p.residual = (const __nv_bfloat16*)residual; p.aux = (__nv_bfloat16*)aux;
@@ -329,7 +365,8 @@ int gcow_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
   cfg.attrs = &attr; cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel, ma, mb, p);
+  if (b_mn) return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel<true>, ma, mb, p);
+  return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel<false>, ma, mb, p);
 }
 
 }  // extern "C"

@@ -72,11 +72,9 @@ class BertForPreTraining(nn.Module):
 
     def forward(self, ids, type_ids=None, mlm_labels=None, nsp_labels=None):
         B, S = ids.shape
-        pos = torch.arange(S, device=ids.device).unsqueeze(0)
         if type_ids is None:                      # single-segment input: every token is type 0
             type_ids = torch.zeros_like(ids)
-        x = self.tok(ids) + self.pos(pos) + self.typ(type_ids)
-        x = self.ln(x)
+        x = self.ln(gnn.embed_sum3(ids, type_ids, self.tok, self.pos, self.typ))
         for layer in self.layers:
             x = layer(x)
         h = self.mlm_ln(gnn.gelu(self.mlm_dense(x)))

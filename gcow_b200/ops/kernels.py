@@ -81,14 +81,16 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
     if aux is not None:
         assert pre_gelu_out is None or gelu_grad_of is None
         flags |= AUX_OUT if pre_gelu_out is not None else GELU_GRAD
-    if (_pair_gemm_enabled() and not a_t and not b_t and out.dtype == torch.bfloat16 and not accumulate and max_ctas == 0
-            and tile_rows == 0 and K % 64 == 0 and N % 32 == 0 and M >= 1024 and N >= 256
-            and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0 and out.stride(0) % 8 == 0):
-        # large K-major product: the CTA-pair kernel (two SMs per 256 x 256 tile)
+    if (_pair_gemm_enabled() and not a_t and out.dtype == torch.bfloat16 and not accumulate and max_ctas == 0
+            and tile_rows == 0 and K % 64 == 0 and N % (64 if b_t else 32) == 0 and M >= 1024 and N >= 256
+            and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+            and not (K >= 2048 and -(-M // 256) * -(-N // 256) >= 118)):
+        # large product with a short reduction: the CTA-pair kernel (two SMs per 256 x 256 tile) has the one-CTA
+        # 256 x 256 tile's traffic per flop AND an overlapped epilogue; long reductions stay on the one-CTA tile
         err = _native.cuda().gcow_gemm2_bf16(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
             bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
-            aux.data_ptr() if aux is not None else None, flags, _error_word(a.device).data_ptr(),
+            aux.data_ptr() if aux is not None else None, flags, _error_word(a.device).data_ptr(), int(b_t),
             torch.cuda.current_stream(a.device).cuda_stream)
         if err == 0:
             _launches += 1
@@ -119,12 +121,12 @@ _pair_gemm = None
 
 
 def _pair_gemm_enabled() -> bool:
-    """The CTA-pair GEMM (cta_group::2) serves large K-major products when GCOW_GEMM2=1 and the device can
-    co-schedule clusters of two CTAs with its shared-memory footprint."""
+    """The CTA-pair GEMM (cta_group::2) serves large products with a short reduction unless GCOW_GEMM2=0, provided
+    the device can co-schedule clusters of two CTAs with its shared-memory footprint."""
     global _pair_gemm
     if _pair_gemm is None:
         import os
-        _pair_gemm = (os.environ.get("GCOW_GEMM2", "0") == "1" and _have("gcow_gemm2_bf16")
+        _pair_gemm = (os.environ.get("GCOW_GEMM2", "1") != "0" and _have("gcow_gemm2_bf16")
                       and _native.cuda().gcow_gemm2_max_pairs() > 0)
     return _pair_gemm
 
@@ -722,6 +724,56 @@ def conv_gemm_usable(x: torch.Tensor, w: torch.Tensor, groups: int, dilation) ->
 
 def conv_gemm(x, w, b, stride, pad):
     return _ConvGemmFn.apply(x, w, b, stride, pad)
+
+
+# ------------------------------------------------ fused input embeddings
+class _Embed3Fn(torch.autograd.Function):
+    """tok[ids] + pos[position] + typ[type_ids] -> bf16 [B, S, H] in one kernel; deterministic backward
+    (ordered sums for the position and type tables, a sorted segmented sum for the token table)."""
+
+    @staticmethod
+    def forward(ctx, ids, type_ids, tok, pos, typ):
+        global _launches
+        B, S = ids.shape
+        H = tok.shape[1]
+        ids_c, ty_c = ids.contiguous(), type_ids.contiguous()
+        y = torch.empty((B, S, H), dtype=torch.bfloat16, device=tok.device)
+        _chk(_native.cuda().gcow_embed3_fwd(ids_c.data_ptr(), ty_c.data_ptr(), tok.data_ptr(), pos.data_ptr(), typ.data_ptr(),
+                                            y.data_ptr(), B * S, S, H, _stream(tok.device)), "gcow_embed3_fwd")
+        _launches += 1
+        ctx.save_for_backward(ids_c, ty_c)
+        ctx.meta = (B, S, H, tok.shape[0], pos.shape[0], typ.shape[0])
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        ids, ty = ctx.saved_tensors
+        B, S, H, V, P, NT = ctx.meta
+        lib, dev = _native.cuda(), gy.device
+        g = gy.to(torch.bfloat16).contiguous()
+        order = torch.argsort(ids.view(-1), stable=True)
+        dtok = torch.zeros((V, H), dtype=torch.float32, device=dev)
+        dpos = torch.zeros((P, H), dtype=torch.float32, device=dev)
+        parts = lib.gcow_embed_type_parts(B * S)
+        tpart = torch.empty((parts, NT * H), dtype=torch.float32, device=dev)
+        dtyp = torch.empty((NT, H), dtype=torch.float32, device=dev)
+        _chk(lib.gcow_embed3_bwd(g.data_ptr(), ids.data_ptr(), ty.data_ptr(), order.data_ptr(), dtok.data_ptr(), dpos.data_ptr(),
+                                 tpart.data_ptr(), B, S, H, NT, _stream(dev)), "gcow_embed3_bwd")
+        _chk(lib.gcow_reduce_partials(tpart.data_ptr(), dtyp.data_ptr(), parts, NT * H, _stream(dev)), "gcow_reduce_partials")
+        _launches += 4
+        return None, None, dtok, dpos, dtyp
+
+
+def embed3_usable(ids: torch.Tensor, tok: torch.Tensor, pos: torch.Tensor, typ: torch.Tensor) -> bool:
+    return (ids.is_cuda and ids.dim() == 2 and ids.dtype == torch.int64 and _have("gcow_embed3_fwd")
+            and tok.dtype == torch.float32 and pos.dtype == torch.float32 and typ.dtype == torch.float32
+            and tok.is_contiguous() and pos.is_contiguous() and typ.is_contiguous()
+            and tok.shape[1] % 4 == 0 and typ.shape[0] <= 4 and ids.shape[1] <= pos.shape[0])
+
+
+def embed3(ids, type_ids, tok, pos, typ):
+    return _Embed3Fn.apply(ids, type_ids, tok, pos, typ)
 
 
 # ------------------------------------------------ implicit-GEMM convolution (stride 1)

@@ -101,6 +101,15 @@ class Embedding(nn.Embedding):
     pass
 
 
+def embed_sum3(ids: torch.Tensor, type_ids: torch.Tensor, tok: nn.Embedding, pos: nn.Embedding, typ: nn.Embedding):
+    """``tok(ids) + pos(arange(S)) + typ(type_ids)`` for ids [B, S]: the BERT input embedding. One gather kernel and
+    a deterministic backward on the own backend."""
+    if backend.get_backend() == "own" and K.embed3_usable(ids, tok.weight, pos.weight, typ.weight):
+        return K.embed3(ids, type_ids, tok.weight, pos.weight, typ.weight)
+    position = torch.arange(ids.shape[1], device=ids.device).unsqueeze(0)
+    return tok(ids) + pos(position) + typ(type_ids)
+
+
 def gelu(x: torch.Tensor) -> torch.Tensor:
     if backend.get_backend() == "own" and K.gelu_usable(x):
         return K.gelu(x)

@@ -148,3 +148,8 @@ def test_pair_gemm_matches_fp32_reference(M, N, K, monkeypatch):
     assert (g.float() - ref_g).abs().max().item() / ref_g.abs().max().item() < 2e-2
     K_.check_errors()
     assert K_.launch_count() == before + 4
+    if N % 64 == 0:        # B stored [K][N]: the data-gradient layout
+        y = K_.gemm_bf16(a, b.t().contiguous(), b_t=True, residual=res)
+        K_.check_errors()
+        ref3 = _ref(a, b, residual=res)
+        assert (y.float() - ref3).abs().max().item() / ref3.abs().max().item() < 2e-2

@@ -325,3 +325,27 @@ def test_fused_ffn_and_linear_residual_match_unfused():
     for i, (a, b) in enumerate(zip(got, ref)):
         err = (a - b).abs().max().item() / (b.abs().max().item() + 1e-6)
         assert err < 3e-2, (i, err)
+
+
+def test_fused_embeddings_match_pytorch():
+    import torch.nn as nn
+    from gcow_b200.ops import nn as gnn, set_backend
+    torch.manual_seed(12)
+    B, S, H, V = 4, 48, 256, 500
+    tok, pos, typ = gnn.Embedding(V, H).cuda(), gnn.Embedding(64, H).cuda(), gnn.Embedding(2, H).cuda()
+    ids = torch.randint(0, V, (B, S), device="cuda")
+    ids[0, :10] = 7                                      # a long run of one id
+    ty = torch.randint(0, 2, (B, S), device="cuda")
+    gy = torch.randn(B, S, H, device="cuda").bfloat16()
+    res = {}
+    for be in ("torch", "own"):
+        set_backend(be)
+        for m in (tok, pos, typ):
+            m.zero_grad(set_to_none=True)
+        y = gnn.embed_sum3(ids, ty, tok, pos, typ)
+        y.backward(gy.to(y.dtype))
+        res[be] = [y.detach().float()] + [m.weight.grad.clone() for m in (tok, pos, typ)]
+    set_backend("own")
+    assert res["own"][0].dtype == torch.float32 and (res["own"][0] - res["torch"][0]).abs().max().item() < 2e-2
+    for a, b in zip(res["own"][1:], res["torch"][1:]):
+        assert (a - b).abs().max().item() < 1e-3 * max(1.0, b.abs().max().item())
