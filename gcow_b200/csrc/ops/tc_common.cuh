@@ -147,10 +147,13 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
 // Coalesced bf16 rows for epilogues. After tcgen05.ld a lane owns one row of the tile (32 consecutive columns),
 // so a direct 16-byte store per lane touches 32 different rows per instruction: 32 memory transactions of 16
 // useful bytes. These helpers pass the warp's 32 x 32 block through a private shared-memory buffer of 32 rows
-// x 80 bytes (64 data + 16 pad: conflict-free for both access patterns) so that four lanes cover the 64 bytes
-// of one row and an instruction touches 8 rows: a quarter of the transactions, all of them whole sectors.
+// x 64 bytes so that four lanes cover the 64 bytes of one row and an instruction touches 8 rows: a quarter of the
+// transactions, all of them whole sectors. The 16-byte chunk k of row r sits at chunk k ^ ((r >> 1) & 3), which keeps
+// both access patterns free of bank conflicts without padding (the 2 KB per warp matter: with eight of them a GEMM
+// CTA still leaves room on its SM for one CTA of the all-reduce kernel).
 // row_off: element offset of the lane's own row start (column 0 of the block), row_ok: whether that row exists.
-constexpr int kStageRowBytes = 80, kStageWarpBytes = 32 * kStageRowBytes;
+constexpr int kStageRowBytes = 64, kStageWarpBytes = 32 * kStageRowBytes;
+__device__ __forceinline__ int stage_offset(int row, int chunk) { return row * kStageRowBytes + ((chunk ^ ((row >> 1) & 3)) << 4); }
 
 __device__ __forceinline__ void warp_store_rows_bf16(uint8_t* stg, int lane, const float (&v)[32], __nv_bfloat16* base,
                                                      size_t row_off, bool row_ok) {
@@ -160,7 +163,7 @@ __device__ __forceinline__ void warp_store_rows_bf16(uint8_t* stg, int lane, con
     __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
     for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[8 * k + 2 * e], v[8 * k + 2 * e + 1]);
-    *reinterpret_cast<uint4*>(stg + lane * kStageRowBytes + k * 16) = o;
+    *reinterpret_cast<uint4*>(stg + stage_offset(lane, k)) = o;
   }
   __syncwarp();
 #pragma unroll
@@ -168,7 +171,7 @@ __device__ __forceinline__ void warp_store_rows_bf16(uint8_t* stg, int lane, con
     const int row = it * 8 + (lane >> 2), ch = lane & 3;
     const unsigned long long off = __shfl_sync(0xffffffffu, (unsigned long long)row_off, row);
     const int ok = __shfl_sync(0xffffffffu, (int)row_ok, row);
-    const uint4 x = *reinterpret_cast<const uint4*>(stg + row * kStageRowBytes + ch * 16);
+    const uint4 x = *reinterpret_cast<const uint4*>(stg + stage_offset(row, ch));
     if (ok) *reinterpret_cast<uint4*>(base + off + ch * 8) = x;
   }
   __syncwarp();
@@ -185,12 +188,12 @@ __device__ __forceinline__ void warp_load_rows_bf16(uint8_t* stg, int lane, cons
     const int ok = __shfl_sync(0xffffffffu, (int)row_ok, row);
     uint4 x = make_uint4(0, 0, 0, 0);
     if (ok) x = *reinterpret_cast<const uint4*>(base + off + ch * 8);
-    *reinterpret_cast<uint4*>(stg + row * kStageRowBytes + ch * 16) = x;
+    *reinterpret_cast<uint4*>(stg + stage_offset(row, ch)) = x;
   }
   __syncwarp();
 #pragma unroll
   for (int k = 0; k < 4; k++) {
-    const uint4 x = *reinterpret_cast<const uint4*>(stg + lane * kStageRowBytes + k * 16);
+    const uint4 x = *reinterpret_cast<const uint4*>(stg + stage_offset(lane, k));
     const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
 #pragma unroll
     for (int e = 0; e < 4; e++) {
