@@ -81,7 +81,7 @@ layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ gamma
 // 8 columns, CH <= 4) and touch shared memory once at the end; wider rows (CH == 0)
 // accumulate in shared memory.
 template <int CH>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, CH > 0 ? 3 : 1)
 layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ gamma,
                      const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ dx,
                      float* __restrict__ part, int rows, int H) {
@@ -90,15 +90,15 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
   float* dg = sm + (size_t)warp * 2 * H;
   float* db = dg + H;
   constexpr int NR = CH > 0 ? CH : 1;
-  float rg[NR][8], rb[NR][8], gam[NR][8];
+  float rg[NR][8], rb[NR][8];
   if (CH > 0) {
+    // gamma lives in shared memory (one copy per CTA): 32 registers less per thread buy a third CTA per SM
+    for (int c = threadIdx.x; c < 256 * NR; c += blockDim.x) sm[c] = c < H ? gamma[c] : 0.0f;
+    __syncthreads();
 #pragma unroll
     for (int k = 0; k < NR; k++)
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const int c = lane * 8 + 256 * k + i;
-        rg[k][i] = 0; rb[k][i] = 0; gam[k][i] = c < H ? gamma[c] : 0.0f;
-      }
+      for (int i = 0; i < 8; i++) { rg[k][i] = 0; rb[k][i] = 0; }
   } else {
     for (int c = lane; c < H; c += 32) { dg[c] = 0; db[c] = 0; }
     __syncwarp();
@@ -114,12 +114,14 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
       for (int k = 0; k < NR; k++) {
         const int c = lane * 8 + 256 * k;
         if (c < H) {
-          float xv[8], gv[8];
+          float xv[8], gv[8], gam[8];
           load8(xr + c, xv); load8(gr + c, gv);
+          *reinterpret_cast<float4*>(gam) = *reinterpret_cast<const float4*>(sm + c);
+          *reinterpret_cast<float4*>(gam + 4) = *reinterpret_cast<const float4*>(sm + c + 4);
 #pragma unroll
           for (int i = 0; i < 8; i++) {
             xh[k][i] = (xv[i] - mu) * rs;
-            gg[k][i] = gv[i] * gam[k][i];
+            gg[k][i] = gv[i] * gam[i];
             s1 += gg[k][i]; s2 += gg[k][i] * xh[k][i];
             rg[k][i] += gv[i] * xh[k][i];
             rb[k][i] += gv[i];
@@ -165,6 +167,7 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
     }
   }
   if (CH > 0) {
+    __syncthreads();      // every warp is done with the gamma copy that these sums overwrite
 #pragma unroll
     for (int k = 0; k < NR; k++)
 #pragma unroll

@@ -139,8 +139,8 @@ def wgrad_gemm(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     M, N = g.shape
     K = x.shape[1]
     tiles = -(-N // 128) * -(-K // 256)
-    s = 1
-    while s < 8 and tiles * s < 120 and M % (2 * s) == 0 and (M // (2 * s)) % 64 == 0 and M // (2 * s) >= 512:
+    s = 1        # doubled while the tiles still fit one wave of 148 CTAs and a slab keeps at least 512 rows
+    while s < 64 and tiles * s * 2 <= 148 and M % (2 * s) == 0 and (M // (2 * s)) % 64 == 0 and M // (2 * s) >= 512:
         s *= 2
     if s == 1 or g.stride(0) != N or x.stride(0) != K:
         return gemm_bf16(g, x, a_t=True, b_t=True, out_dtype=torch.float32)
