@@ -402,7 +402,7 @@ int gcow_layernorm_fwd(const void* x, const float* gamma, const float* beta, voi
 }
 
 // Number of partial rows the backward writes; `part` must hold parts * 2 * H floats.
-int gcow_layernorm_bwd_parts(int rows) { int g = (rows + 3) / 4; return g < 148 * 2 ? g : 148 * 2; }
+int gcow_layernorm_bwd_parts(int rows) { int g = (rows + 3) / 4; return g < 148 * 3 ? g : 148 * 3; }   // three CTAs per SM are resident
 
 int gcow_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
                        void* dx, float* part, float* dgamma_dbeta, int rows, int H, void* stream) {
