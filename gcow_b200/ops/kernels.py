@@ -360,10 +360,10 @@ class _Conv1x1Fn(torch.autograd.Function):
 
 
 def conv1x1_enabled() -> bool:
-    """1x1 convolutions go through the tcgen05 GEMM only on request
-    (GCOW_CONV1X1=own): its 128x256 tile wastes most of the tensor-core work on the
-    64/128-channel layers of a ResNet and its weight-gradient product has a single
-    output tile, so cuDNN is faster on those shapes and stays the default."""
+    """1x1 convolutions go through the tcgen05 GEMM only on request (GCOW_CONV1X1=own). They are products with a
+    short reduction and a large output, i.e. bound by memory; measured on ResNet-50 the own path costs 35.7 ms per
+    step against 29.2 ms with cuDNN (forward product 200704 x 256 x 64: 58 us against 38 us), so cuDNN stays the
+    default."""
     import os
     return os.environ.get("GCOW_CONV1X1", "lib") == "own"
 
