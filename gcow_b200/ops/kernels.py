@@ -485,7 +485,16 @@ class _XentFn(torch.autograd.Function):
     def backward(ctx, g):
         grad = ctx.grad_buf
         ctx.grad_buf = None
-        return grad * g.to(grad.dtype), None, None, None
+        # Scale in place (the buffer is this function's own since the forward overwrote it), and over the whole
+        # padded rows when they are one block of memory: the result is then still a view of that buffer, which the
+        # linear layer below can hand to its GEMMs without re-padding a [rows, vocabulary] tensor.
+        rows, ld = grad.shape[0], grad.stride(0)
+        scale = g.to(grad.dtype)
+        if grad.storage_offset() == 0 and grad.untyped_storage().nbytes() >= rows * ld * grad.element_size():
+            grad.as_strided((rows, ld), (ld, 1)).mul_(scale)
+        else:
+            grad.mul_(scale)
+        return grad, None, None, None
 
 
 def xent_usable(logits: torch.Tensor) -> bool:
