@@ -5,7 +5,7 @@
 //
 //   forward   Y[n,h,w,co] = sum_{r,s,ci} X[n, h+r-ph, w+s-pw, ci] * Wt[co,r,s,ci]
 //             GEMM view: M = output pixels, N = Co, K = (r,s,ci).
-//             An M tile is a box of bw x bh x bn output pixels (<= 128 rows) of a 4-D tensor
+//             An M tile is a box of bw x bh x bn output pixels (<= 256 rows) of a 4-D tensor
 //             map {C, W, H, N}; for tap (r,s) the same box is fetched at (w0+s-pw, h0+r-ph).
 //             Rows of the box land in shared memory as 128-byte channel rows with the
 //             128-byte swizzle, exactly the K-major operand layout of tcgen05.mma.
