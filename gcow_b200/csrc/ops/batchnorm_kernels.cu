@@ -17,10 +17,19 @@
 // cuDNN operators (hw/models/resenet.py:12-22,28-40,80-89).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
 #include <stdint.h>
 
 namespace gcow {
 namespace bn {
+
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may be scheduled while
+// its predecessor in the stream is still running (once every CTA of the predecessor has called pdl_trigger or
+// exited); it must call pdl_wait before touching anything the predecessor writes. This hides the launch gap
+// between the short kernels of one batch-norm call. Both instructions do nothing in a kernel launched normally.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 
 typedef __nv_bfloat16 bf16;
 constexpr int kThreads = 256;
@@ -61,6 +70,7 @@ __device__ __forceinline__ void cta_fold(const float (&a)[8], const float (&b)[8
 // ---- forward statistics: partial sum(x), sum(x^2)
 __global__ void __launch_bounds__(kThreads)
 stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int64_t R, int C) {
+  pdl_trigger();
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll 4
@@ -98,6 +108,8 @@ finalize_fwd_kernel(const float* __restrict__ part, int parts, int C, int64_t R,
                     const float* __restrict__ gamma, const float* __restrict__ beta,
                     float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ scale,
                     float* __restrict__ shift, float* __restrict__ run_mean, float* __restrict__ run_var) {
+  pdl_wait();
+  pdl_trigger();
   const int c = blockIdx.x * kFinX + threadIdx.x;
   double s, q;
   fold_partials(part, parts, C, c, s, q);
@@ -131,6 +143,7 @@ __global__ void __launch_bounds__(kThreads)
 apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, bf16* __restrict__ y,
              uint8_t* __restrict__ mask, const float* __restrict__ scale, const float* __restrict__ shift, int64_t R,
              int C, int relu) {
+  pdl_wait();
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float sc[8], sh[8];
 #pragma unroll
@@ -164,6 +177,7 @@ __global__ void __launch_bounds__(kThreads)
 bwd_reduce_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask, const bf16* __restrict__ x,
                   const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ gmask_out,
                   float* __restrict__ part, int64_t R, int C, int relu) {
+  pdl_trigger();
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float mu[8], rs[8], s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
@@ -190,6 +204,8 @@ bwd_reduce_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask,
 __global__ void __launch_bounds__(kFinX * kFinY)
 finalize_bwd_kernel(const float* __restrict__ part, int parts, int C, float* __restrict__ dgamma,
                     float* __restrict__ dbeta) {
+  pdl_wait();
+  pdl_trigger();
   const int c = blockIdx.x * kFinX + threadIdx.x;
   double s, q;
   fold_partials(part, parts, C, c, s, q);
@@ -203,6 +219,7 @@ bwd_dx_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask, con
               const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
               const float* __restrict__ dgamma, const float* __restrict__ dbeta, bf16* __restrict__ dx, int64_t R, int C,
               int relu) {
+  pdl_wait();
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float mu[8], rs[8], k0[8], k1[8], k2[8];
   const float invR = 1.0f / (float)R;
@@ -237,6 +254,20 @@ inline int grid_for(int64_t R, int C) {
   if (g > 148 * 3) g = 148 * 3;
   return (int)(g < 1 ? 1 : g);
 }
+// Launch `kernel` so that it may overlap the tail of its predecessor in the stream (see pdl_wait). GCOW_PDL=0
+// falls back to ordinary launches.
+template <typename... KArgs, typename... Args>
+static void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+  static const bool enabled = [] { const char* e = getenv("GCOW_PDL"); return !(e && e[0] == '0'); }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr; cfg.numAttrs = enabled ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool shape_ok(int C) { return C % 8 == 0 && C >= 8 && C <= 2048 && kThreads % (C / 8) == 0; }
 
 }  // namespace bn
@@ -260,9 +291,10 @@ int gcow_bn_fwd_train(const void* x, const void* residual, void* y, void* mask, 
   const int g = grid_for(R, C);
   float *mean = stats, *rstd = stats + C, *scale = stats + 2 * C, *shift = stats + 3 * C;
   stats_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, part, R, C);
-  finalize_fwd_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, s>>>(part, g, C, R, eps, momentum, gamma, beta, mean,
-                                                                             rstd, scale, shift, run_mean, run_var);
-  apply_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, (const bf16*)residual, (bf16*)y, (uint8_t*)mask, scale, shift, R, C, relu);
+  launch_dependent(finalize_fwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), s, part, g, C, R, eps, momentum, gamma,
+                   beta, mean, rstd, scale, shift, run_mean, run_var);
+  launch_dependent(apply_kernel, dim3(g), dim3(kThreads), s, (const bf16*)x, (const bf16*)residual, (bf16*)y, (uint8_t*)mask,
+                   (const float*)scale, (const float*)shift, R, C, relu);
   return (int)cudaGetLastError();
 }
 
@@ -286,14 +318,10 @@ int gcow_bn_bwd(const void* dy, const void* mask, const void* x, const float* ga
   const int g = grid_for(R, C);
   const float *mean = stats, *rstd = stats + C;
   bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const uint8_t*)mask, (const bf16*)x, mean, rstd, (bf16*)dres, part, R, C, relu);
-  finalize_bwd_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, s>>>(part, g, C, dgb, dgb + C);
+  launch_dependent(finalize_bwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), s, (const float*)part, g, C, dgb, dgb + C);
   // the second sweep applies the mask again, or reads the masked gradient if it was written
-  if (dres)
-    bwd_dx_kernel<<<g, kThreads, 0, s>>>((const bf16*)dres, (const uint8_t*)mask, (const bf16*)x, gamma, mean, rstd, dgb, dgb + C,
-                                         (bf16*)dx, R, C, 0);
-  else
-    bwd_dx_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const uint8_t*)mask, (const bf16*)x, gamma, mean, rstd, dgb, dgb + C,
-                                         (bf16*)dx, R, C, relu);
+  launch_dependent(bwd_dx_kernel, dim3(g), dim3(kThreads), s, (const bf16*)(dres ? dres : dy), (const uint8_t*)mask, (const bf16*)x,
+                   gamma, mean, rstd, (const float*)dgb, (const float*)(dgb + C), (bf16*)dx, R, C, dres ? 0 : relu);
   return (int)cudaGetLastError();
 }
 
