@@ -17,18 +17,14 @@
 // cuDNN operators (hw/models/resenet.py:12-22,28-40,80-89).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include "pdl.cuh"
 #include <stdlib.h>
 #include <stdint.h>
 
 namespace gcow {
 namespace bn {
 
-// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may be scheduled while
-// its predecessor in the stream is still running (once every CTA of the predecessor has called pdl_trigger or
-// exited); it must call pdl_wait before touching anything the predecessor writes. This hides the launch gap
-// between the short kernels of one batch-norm call. Both instructions do nothing in a kernel launched normally.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 
 typedef __nv_bfloat16 bf16;
@@ -254,20 +250,6 @@ inline int grid_for(int64_t R, int C) {
   if (g > 148 * 3) g = 148 * 3;
   return (int)(g < 1 ? 1 : g);
 }
-// Launch `kernel` so that it may overlap the tail of its predecessor in the stream (see pdl_wait). GCOW_PDL=0
-// falls back to ordinary launches.
-template <typename... KArgs, typename... Args>
-static void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
-  static const bool enabled = [] { const char* e = getenv("GCOW_PDL"); return !(e && e[0] == '0'); }();
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = s;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr; cfg.numAttrs = enabled ? 1 : 0;
-  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
-
 inline bool shape_ok(int C) { return C % 8 == 0 && C >= 8 && C <= 2048 && kThreads % (C / 8) == 0; }
 
 }  // namespace bn
@@ -291,9 +273,9 @@ int gcow_bn_fwd_train(const void* x, const void* residual, void* y, void* mask, 
   const int g = grid_for(R, C);
   float *mean = stats, *rstd = stats + C, *scale = stats + 2 * C, *shift = stats + 3 * C;
   stats_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, part, R, C);
-  launch_dependent(finalize_fwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), s, part, g, C, R, eps, momentum, gamma,
+  gcow::launch_dependent(finalize_fwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), 0, s, part, g, C, R, eps, momentum, gamma,
                    beta, mean, rstd, scale, shift, run_mean, run_var);
-  launch_dependent(apply_kernel, dim3(g), dim3(kThreads), s, (const bf16*)x, (const bf16*)residual, (bf16*)y, (uint8_t*)mask,
+  gcow::launch_dependent(apply_kernel, dim3(g), dim3(kThreads), 0, s, (const bf16*)x, (const bf16*)residual, (bf16*)y, (uint8_t*)mask,
                    (const float*)scale, (const float*)shift, R, C, relu);
   return (int)cudaGetLastError();
 }
@@ -318,9 +300,9 @@ int gcow_bn_bwd(const void* dy, const void* mask, const void* x, const float* ga
   const int g = grid_for(R, C);
   const float *mean = stats, *rstd = stats + C;
   bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const uint8_t*)mask, (const bf16*)x, mean, rstd, (bf16*)dres, part, R, C, relu);
-  launch_dependent(finalize_bwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), s, (const float*)part, g, C, dgb, dgb + C);
+  gcow::launch_dependent(finalize_bwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), 0, s, (const float*)part, g, C, dgb, dgb + C);
   // the second sweep applies the mask again, or reads the masked gradient if it was written
-  launch_dependent(bwd_dx_kernel, dim3(g), dim3(kThreads), s, (const bf16*)(dres ? dres : dy), (const uint8_t*)mask, (const bf16*)x,
+  gcow::launch_dependent(bwd_dx_kernel, dim3(g), dim3(kThreads), 0, s, (const bf16*)(dres ? dres : dy), (const uint8_t*)mask, (const bf16*)x,
                    gamma, mean, rstd, (const float*)dgb, (const float*)(dgb + C), (bf16*)dx, R, C, dres ? 0 : relu);
   return (int)cudaGetLastError();
 }

@@ -122,6 +122,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm->tmem_base;
+  // a kernel launched as a programmatic dependent (the ordered sum of split partial results) may be scheduled
+  // from here on; it waits for this grid to complete before it reads anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer

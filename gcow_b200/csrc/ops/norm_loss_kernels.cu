@@ -9,6 +9,8 @@
 // (hw/models/resenet.py:12-22,80-89; cross-entropy at hw/models/train_imagenet.py:249).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include "pdl.cuh"
 #include <stdint.h>
 
 namespace gcow {
@@ -85,6 +87,7 @@ __global__ void __launch_bounds__(128, CH > 0 ? 3 : 1)
 layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ gamma,
                      const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ dx,
                      float* __restrict__ part, int rows, int H) {
+  pdl_trigger();
   extern __shared__ float sm[];          // [4 warps][2][H]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* dg = sm + (size_t)warp * 2 * H;
@@ -184,6 +187,7 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
 
 // out[c] = sum_p part[p][c]  (fixed order)
 __global__ void reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int n) {
+  pdl_wait();       // launched as a dependent of the kernel that writes `part`
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= n) return;
   float s = 0;
@@ -326,6 +330,7 @@ softmax_bwd_kernel(const bf16* __restrict__ dp, const bf16* __restrict__ p, bf16
 // part[blockIdx.y][c] = sum over this CTA's row range of g[r][c]  (bf16 in, fp32 out)
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const bf16* __restrict__ g, float* __restrict__ part, int rows, int cols, int ld, int rows_per) {
+  pdl_trigger();
   const int c = (blockIdx.x * 256 + threadIdx.x) * 2;
   if (c >= cols) return;
   const int r0 = blockIdx.y * rows_per, r1 = min(rows, r0 + rows_per);
@@ -343,6 +348,7 @@ colsum_partial_kernel(const bf16* __restrict__ g, float* __restrict__ part, int 
 // folded through shared memory. One CTA covers 256 columns x rows_per rows.
 __global__ void __launch_bounds__(256)
 colsum_partial8_kernel(const bf16* __restrict__ g, float* __restrict__ part, int rows, int cols, int ld, int rows_per) {
+  pdl_trigger();
   __shared__ float red[8][256 + 8];
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;       // column group (8 columns), row lane
   const int c = blockIdx.x * 256 + cg * 8;
@@ -421,7 +427,8 @@ int gcow_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
     default: GCOW_LN_BWD(0); break;
   }
 #undef GCOW_LN_BWD
-  reduce_partials_kernel<<<(2 * H + 255) / 256, 256, 0, (cudaStream_t)stream>>>(part, dgamma_dbeta, parts, 2 * H);
+  gcow::launch_dependent(reduce_partials_kernel, dim3((2 * H + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (const float*)part,
+                   dgamma_dbeta, parts, 2 * H);
   return (int)cudaGetLastError();
 }
 
@@ -450,7 +457,8 @@ int gcow_softmax_xent(void* logits, const int64_t* target, float* row_loss, cons
 // out[i] = sum_p part[p * n + i] in a fixed order (split-K partial products, bias partials).
 int gcow_reduce_partials(const float* part, float* out, int parts, int64_t n, void* stream) {
   if (n <= 0 || parts <= 0 || n > 0x7fffffff) return -1;
-  reduce_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(part, out, parts, (int)n);
+  gcow::launch_dependent(reduce_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, part, out, parts,
+                   (int)n);
   return (int)cudaGetLastError();
 }
 
@@ -481,7 +489,8 @@ int gcow_colsum(const void* g, float* part, float* out, int rows, int cols, int 
     dim3 grid((cols / 2 + 255) / 256, parts);
     colsum_partial_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)g, part, rows, cols, ld, rows_per);
   }
-  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, (cudaStream_t)stream>>>(part, out, parts, cols);
+  gcow::launch_dependent(reduce_partials_kernel, dim3((cols + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (const float*)part, out,
+                   parts, cols);
   return (int)cudaGetLastError();
 }
 
