@@ -167,10 +167,13 @@ apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, bf16
   }
 }
 
-// ---- backward sweep 1: partial sum(g), sum(g*xhat); g = dy masked by (y > 0) when relu.
+// ---- backward sweep 1: partial sum(g), sum(g*xhat); g = dy (+ dy2) masked by (y > 0) when relu.
+// dy2 (nullable) is a second gradient of the same output (the output feeds two consumers): adding it here saves
+// the separate addition kernel and its three passes over the tensor.
 // When gmask_out is given, the masked gradient is written there (the residual branch's gradient).
 __global__ void __launch_bounds__(kThreads)
-bwd_reduce_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask, const bf16* __restrict__ x,
+bwd_reduce_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ dy2, const uint8_t* __restrict__ mask,
+                  const bf16* __restrict__ x,
                   const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ gmask_out,
                   float* __restrict__ part, int64_t R, int C, int relu) {
   pdl_trigger();
@@ -184,6 +187,12 @@ bwd_reduce_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask,
     float gv[8], xv[8];
     load8(dy + off, gv);
     load8(x + off, xv);
+    if (dy2) {
+      float w[8];
+      load8(dy2 + off, w);
+#pragma unroll
+      for (int i = 0; i < 8; i++) gv[i] += w[i];
+    }
     if (relu) {
       const uint32_t bits = mask[r * groups + g];
 #pragma unroll
@@ -293,18 +302,26 @@ int gcow_bn_fwd_eval(const void* x, const void* residual, void* y, const float* 
 
 // Backward. stats and mask as written by the forward. dres (nullable) receives the gradient
 // of the residual input (the ReLU-masked dy). dgb: 2*C floats out (dgamma, dbeta).
-int gcow_bn_bwd(const void* dy, const void* mask, const void* x, const float* gamma, const float* stats, void* dx,
-                void* dres, float* dgb, float* part, int64_t R, int C, int relu, void* stream) {
-  if (!shape_ok(C) || R <= 0) return -1;
+// dy2 (nullable): a second gradient of the same output, added to dy on the fly; it needs dres (any buffer of the
+// tensor's size) to carry the masked sum to the second sweep.
+int gcow_bn_bwd2(const void* dy, const void* dy2, const void* mask, const void* x, const float* gamma, const float* stats,
+                 void* dx, void* dres, float* dgb, float* part, int64_t R, int C, int relu, void* stream) {
+  if (!shape_ok(C) || R <= 0 || (dy2 && !dres)) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   const int g = grid_for(R, C);
   const float *mean = stats, *rstd = stats + C;
-  bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const uint8_t*)mask, (const bf16*)x, mean, rstd, (bf16*)dres, part, R, C, relu);
+  bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const bf16*)dy2, (const uint8_t*)mask, (const bf16*)x, mean, rstd,
+                                           (bf16*)dres, part, R, C, relu);
   gcow::launch_dependent(finalize_bwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), 0, s, (const float*)part, g, C, dgb, dgb + C);
   // the second sweep applies the mask again, or reads the masked gradient if it was written
   gcow::launch_dependent(bwd_dx_kernel, dim3(g), dim3(kThreads), 0, s, (const bf16*)(dres ? dres : dy), (const uint8_t*)mask, (const bf16*)x,
                    gamma, mean, rstd, (const float*)dgb, (const float*)(dgb + C), (bf16*)dx, R, C, dres ? 0 : relu);
   return (int)cudaGetLastError();
+}
+
+int gcow_bn_bwd(const void* dy, const void* mask, const void* x, const float* gamma, const float* stats, void* dx,
+                void* dres, float* dgb, float* part, int64_t R, int C, int relu, void* stream) {
+  return gcow_bn_bwd2(dy, nullptr, mask, x, gamma, stats, dx, dres, dgb, part, R, C, relu, stream);
 }
 
 }  // extern "C"

@@ -29,12 +29,15 @@ class Bottleneck(nn.Module):
         self.bn3 = gnn.BatchNorm2d(planes * 4)
         self.relu = nn.ReLU(inplace=True)
         self.downsample = downsample
+        self.fork = False        # set by ResNet: the output feeds the next block's two branches
 
     def forward(self, x):
-        idt = x if self.downsample is None else self.downsample(x)
-        out = self.bn1(self.conv1(x), relu=True)
+        # a forked input is a pair of tensors on the same memory, one per branch (see gnn.BatchNorm2d)
+        xa, xb = x if isinstance(x, tuple) else (x, x)
+        idt = xb if self.downsample is None else self.downsample(xb)
+        out = self.bn1(self.conv1(xa), relu=True)
         out = self.bn2(self.conv2(out), relu=True)
-        return self.bn3(self.conv3(out), residual=idt, relu=True)
+        return self.bn3(self.conv3(out), residual=idt, relu=True, fork=self.fork)
 
 
 class BasicBlock(nn.Module):
@@ -48,11 +51,13 @@ class BasicBlock(nn.Module):
         self.bn2 = gnn.BatchNorm2d(planes)
         self.relu = nn.ReLU(inplace=True)
         self.downsample = downsample
+        self.fork = False
 
     def forward(self, x):
-        idt = x if self.downsample is None else self.downsample(x)
-        out = self.bn1(self.conv1(x), relu=True)
-        return self.bn2(self.conv2(out), residual=idt, relu=True)
+        xa, xb = x if isinstance(x, tuple) else (x, x)
+        idt = xb if self.downsample is None else self.downsample(xb)
+        out = self.bn1(self.conv1(xa), relu=True)
+        return self.bn2(self.conv2(out), residual=idt, relu=True, fork=self.fork)
 
 
 class ResNet(nn.Module):
@@ -76,6 +81,9 @@ class ResNet(nn.Module):
         for m in self.modules():
             if isinstance(m, nn.Conv2d):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
+        blocks = [b for layer in (self.layer1, self.layer2, self.layer3, self.layer4) for b in layer]
+        for b in blocks[:-1]:              # every block output but the last feeds two branches of the next block
+            b.fork = True
         for m in self.modules():           # zero-init the last BN of every residual branch
             if isinstance(m, Bottleneck):
                 nn.init.zeros_(m.bn3.weight)

@@ -531,10 +531,15 @@ def _nhwc_rows(x: torch.Tensor):
 
 
 class _BatchNormActFn(torch.autograd.Function):
-    """y = relu?(bn(x) (+ residual)) on channels-last bf16 tensors, training statistics."""
+    """y = relu?(bn(x) (+ residual)) on channels-last bf16 tensors, training statistics.
+
+    With ``fork`` the result is returned twice, as two tensors on the same memory: a layer output that feeds two
+    consumers (the next block's first convolution and its identity branch) then gets its two gradients delivered
+    separately, and the first backward sweep adds them while it reads them - instead of autograd's addition kernel
+    (two reads and a write of the whole tensor) followed by a third read here."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, run_mean, run_var, residual, relu, momentum, eps):
+    def forward(ctx, x, gamma, beta, run_mean, run_var, residual, relu, momentum, eps, fork=False):
         global _launches
         R, C = _nhwc_rows(x)
         lib = _native.cuda()
@@ -552,26 +557,39 @@ class _BatchNormActFn(torch.autograd.Function):
         _launches += 3
         ctx.save_for_backward(x, mask, g32, stats)      # the ReLU bit mask stands in for y in the backward
         ctx.meta = (R, C, bool(relu), residual is not None, gamma.dtype)
-        return y
+        if not fork:
+            return y
+        # a second tensor on the same storage (not an autograd view of the first)
+        y2 = torch.empty(0, dtype=y.dtype, device=y.device).set_(y.untyped_storage(), y.storage_offset(), y.size(), y.stride())
+        return y, y2
 
     @staticmethod
-    def backward(ctx, gy):
+    def backward(ctx, gy, gy2=None):
         global _launches
         x, mask, g32, stats = ctx.saved_tensors
         R, C, relu, has_res, pdtype = ctx.meta
         lib = _native.cuda()
-        if gy.dtype != torch.bfloat16 or not gy.is_contiguous(memory_format=torch.channels_last):
-            gy = gy.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        if gy is None:
+            gy, gy2 = gy2, None
+
+        def _cl(t):
+            if t.dtype != torch.bfloat16 or not t.is_contiguous(memory_format=torch.channels_last):
+                t = t.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+            return t
+        gy = _cl(gy)
+        gy2 = _cl(gy2) if gy2 is not None else None
         dx = torch.empty_like(x, memory_format=torch.channels_last)
-        dres = torch.empty_like(x, memory_format=torch.channels_last) if has_res else None
+        # the masked (summed) gradient: the residual input's gradient, and what the second sweep reads
+        dres = torch.empty_like(x, memory_format=torch.channels_last) if (has_res or gy2 is not None) else None
         dgb = torch.empty(2 * C, dtype=torch.float32, device=x.device)
         part = torch.empty(lib.gcow_bn_parts(R, C) * 2 * C, dtype=torch.float32, device=x.device)
-        _chk(lib.gcow_bn_bwd(gy.data_ptr(), mask.data_ptr() if mask is not None else None, x.data_ptr(), g32.data_ptr(),
-                             stats.data_ptr(), dx.data_ptr(),
-                             dres.data_ptr() if dres is not None else None, dgb.data_ptr(), part.data_ptr(), R, C,
-                             int(relu), _stream(x.device)), "gcow_bn_bwd")
+        _chk(lib.gcow_bn_bwd2(gy.data_ptr(), gy2.data_ptr() if gy2 is not None else None,
+                              mask.data_ptr() if mask is not None else None, x.data_ptr(), g32.data_ptr(),
+                              stats.data_ptr(), dx.data_ptr(),
+                              dres.data_ptr() if dres is not None else None, dgb.data_ptr(), part.data_ptr(), R, C,
+                              int(relu), _stream(x.device)), "gcow_bn_bwd2")
         _launches += 3
-        return dx, dgb[:C].to(pdtype), dgb[C:].to(pdtype), None, None, dres, None, None, None
+        return dx, dgb[:C].to(pdtype), dgb[C:].to(pdtype), None, None, (dres if has_res else None), None, None, None, None
 
 
 def batchnorm_usable(x: torch.Tensor, mod, residual=None) -> bool:
@@ -585,8 +603,9 @@ def batchnorm_usable(x: torch.Tensor, mod, residual=None) -> bool:
     return bool(_native.cuda().gcow_bn_supported(x.shape[1]))
 
 
-def batchnorm_act(x, mod, residual=None, relu=False):
-    """Fused BN(+add)(+ReLU) using ``mod``'s parameters and running statistics."""
+def batchnorm_act(x, mod, residual=None, relu=False, fork=False):
+    """Fused BN(+add)(+ReLU) using ``mod``'s parameters and running statistics. ``fork``: return the result as two
+    tensors on the same memory (see _BatchNormActFn)."""
     global _launches
     if mod.training or not mod.track_running_stats:
         if mod.training and mod.track_running_stats and mod.num_batches_tracked is not None:
@@ -594,7 +613,7 @@ def batchnorm_act(x, mod, residual=None, relu=False):
         mom = mod.momentum if mod.momentum is not None else 0.1
         rm = mod.running_mean if (mod.training and mod.track_running_stats) else None
         rv = mod.running_var if (mod.training and mod.track_running_stats) else None
-        return _BatchNormActFn.apply(x, mod.weight, mod.bias, rm, rv, residual, relu, mom, mod.eps)
+        return _BatchNormActFn.apply(x, mod.weight, mod.bias, rm, rv, residual, relu, mom, mod.eps, fork)
     R, C = _nhwc_rows(x)
     y = torch.empty_like(x, memory_format=torch.channels_last)
     scratch = torch.empty(2 * C, dtype=torch.float32, device=x.device)
@@ -603,7 +622,7 @@ def batchnorm_act(x, mod, residual=None, relu=False):
                                          mod.running_mean.data_ptr(), mod.running_var.data_ptr(), scratch.data_ptr(),
                                          R, C, mod.eps, int(relu), _stream(x.device)), "gcow_bn_fwd_eval")
     _launches += 2
-    return y
+    return (y, y) if fork else y
 
 
 # ------------------------------------------------------------------- pooling

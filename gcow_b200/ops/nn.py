@@ -63,15 +63,19 @@ class Conv2d(nn.Conv2d):
 class BatchNorm2d(nn.BatchNorm2d):
     """BatchNorm2d whose forward can also take the residual to add and apply the
     ReLU that follows: ``bn(x, residual=idt, relu=True)`` is ``relu(bn(x) + idt)`` in
-    one fused kernel on the own backend, and the same three PyTorch ops otherwise."""
+    one fused kernel on the own backend, and the same three PyTorch ops otherwise.
+    With ``fork=True`` the result comes back as a pair of tensors on the same memory, one per consumer, so that the
+    backward kernel receives the two gradients separately and adds them while reading (otherwise the pair is just
+    the same tensor twice)."""
 
-    def forward(self, x, residual=None, relu=False):
+    def forward(self, x, residual=None, relu=False, fork=False):
         if backend.get_backend() == "own" and K.batchnorm_usable(x, self, residual):
-            return K.batchnorm_act(x, self, residual, relu)
+            return K.batchnorm_act(x, self, residual, relu, fork)
         y = super().forward(x)
         if residual is not None:
             y = y + residual
-        return F.relu(y) if relu else y
+        y = F.relu(y) if relu else y
+        return (y, y) if fork else y
 
 
 class MaxPool3x3s2(nn.Module):

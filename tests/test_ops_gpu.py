@@ -349,3 +349,42 @@ def test_fused_embeddings_match_pytorch():
     assert res["own"][0].dtype == torch.float32 and (res["own"][0] - res["torch"][0]).abs().max().item() < 2e-2
     for a, b in zip(res["own"][1:], res["torch"][1:]):
         assert (a - b).abs().max().item() < 1e-3 * max(1.0, b.abs().max().item())
+
+
+def test_batchnorm_fork_adds_the_two_gradients_in_the_kernel():
+    """bn(x, residual, relu, fork=True) returns two tensors on one memory; their gradients arrive separately and are
+    added inside the backward kernel. Compared with fp32 PyTorch ops on the same values."""
+    import torch.nn.functional as F
+    from gcow_b200.ops import nn as gnn, set_backend
+    set_backend("own")
+    torch.manual_seed(13)
+    N, C, H, W = 8, 64, 12, 12
+    bn = gnn.BatchNorm2d(C).cuda()
+    with torch.no_grad():
+        bn.weight.uniform_(0.5, 1.5); bn.bias.uniform_(-0.3, 0.3)
+    x0 = torch.randn(N, C, H, W, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    r0 = torch.randn(N, C, H, W, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    w1 = torch.randn(N, C, H, W, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    w2 = torch.randn(N, C, H, W, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    x, r = x0.clone().requires_grad_(True), r0.clone().requires_grad_(True)
+    y1, y2 = bn(x, residual=r, relu=True, fork=True)
+    assert y1.data_ptr() == y2.data_ptr() and y1 is not y2
+    ((y1 * w1).sum() + (y2 * w2).sum()).backward()
+    got = [y1.detach().float(), x.grad.float(), r.grad.float(), bn.weight.grad.clone(), bn.bias.grad.clone()]
+
+    xf, rf = x0.float().requires_grad_(True), r0.float().requires_grad_(True)
+    g, b = bn.weight.detach().clone().requires_grad_(True), bn.bias.detach().clone().requires_grad_(True)
+    yr = F.relu(F.batch_norm(xf, None, None, g, b, True, 0.1, bn.eps) + rf)
+    (yr * (w1.float() + w2.float())).sum().backward()
+    ref = [yr.detach(), xf.grad, rf.grad, g.grad, b.grad]
+    for i, (a, e) in enumerate(zip(got, ref)):
+        err = (a - e).abs().max().item() / (e.abs().max().item() + 1e-6)
+        assert err < 3e-2, (i, err)
+    # only one of the two outputs used: the other gradient is absent
+    bn.zero_grad(set_to_none=True)
+    x = x0.clone().requires_grad_(True)
+    y1, y2 = bn(x, relu=True, fork=True)
+    (y2 * w2).sum().backward()
+    xf = x0.float().requires_grad_(True)
+    (F.relu(F.batch_norm(xf, None, None, bn.weight.detach(), bn.bias.detach(), True, 0.1, bn.eps)) * w2.float()).sum().backward()
+    assert (x.grad.float() - xf.grad).abs().max().item() / xf.grad.abs().max().item() < 3e-2
