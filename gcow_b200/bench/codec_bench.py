@@ -114,7 +114,6 @@ def main(argv=None):
         print(json.dumps(row), flush=True)
     if have_ref:
         # the reference's own entry point: 2-D zfp_compress, tolerance 1e-3 and fixed rate 8
-        import math
         n2 = 2048
         ii = np.arange(n2, dtype=np.float64) * 2.0 / n2
         f2 = np.exp(-(ii[None, :] ** 2 + ii[:, None] ** 2)).astype(np.float32)

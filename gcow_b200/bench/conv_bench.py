@@ -15,7 +15,6 @@ import torch
 import torch.nn.functional as F
 
 from gcow_b200 import _native
-from gcow_b200.ops import kernels as K
 from gcow_b200.bench.codec_bench import time_cuda
 
 LAYERS = [(64, 56), (128, 28), (256, 14), (512, 7)]     # (channels, spatial extent)

@@ -21,7 +21,6 @@ from __future__ import annotations
 import math
 import os
 import tempfile
-import time
 from dataclasses import dataclass
 from typing import Optional
 

@@ -20,7 +20,6 @@ Codec modes (hw/models/train_imagenet.py:449-475):
 from __future__ import annotations
 
 import argparse
-import math
 import os
 import sys
 import time
