@@ -43,6 +43,9 @@ def main(argv=None) -> int:
     ap.add_argument("--roundtrip", action="store_true", help="decompress and report the error")
     ap.add_argument("--pad64", action="store_true", help="pad the stream to 64-byte words like the FPGA build (hw/include/types.hpp:80)")
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--print", type=int, default=0, metavar="K", dest="show",
+                    help="print the top-left K x K corner of the field and the first K stream words "
+                         "(the reference's print_2d debugging aid, sw/include/common.hpp:1-21)")
     args = ap.parse_args(argv)
     if not (args.rate or args.tolerance or args.precision):
         args.tolerance = 1e-3                      # the reference kernel's hard-wired setting (hw/src/gcow.cpp:44-45)
@@ -82,6 +85,13 @@ def main(argv=None) -> int:
     if args.out:
         with open(args.out, "wb") as f:
             f.write(stream)
+    if args.show > 0:
+        k = args.show
+        corner = arr[:k, :k] if arr.ndim == 2 else arr[:k * k].reshape(-1, k)
+        for row in corner:
+            print(" ".join(f"{v: .6e}" for v in row))
+        words = np.frombuffer(stream[:8 * k], dtype="<u8")
+        print(" ".join(f"{int(w):016x}" for w in words))
     rc = 0
     if args.golden:
         gold = open(args.golden, "rb").read()
