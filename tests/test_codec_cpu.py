@@ -314,3 +314,25 @@ def test_reference_golden_files(n):
         pytest.skip("reference checkout not present")
     c = g.compress(torch.from_numpy(field(n)), tolerance=1e-3, dim=2)
     assert c.stream.numpy().tobytes() == path.read_bytes()
+
+
+def test_cli_matches_golden_and_prints(tmp_path, capsys):
+    """The command-line counterpart of the reference host program: generate the field, compress at tolerance 1e-3,
+    write the stream, compare with the golden file, print a corner of the field and the first stream words."""
+    from gcow_b200 import cli
+    path = refcodec.REF / "sw" / "tests" / "data" / "compressed_2d_100.zfp"
+    if not path.exists():
+        pytest.skip("reference checkout not present")
+    out = tmp_path / "c.gcow"
+    rc = cli.main(["100", "--device", "cpu", "--golden", str(path), "--out", str(out), "--print", "2", "--iters", "1",
+                   "--roundtrip"])
+    assert rc == 0 and out.read_bytes() == path.read_bytes()
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert len(lines) == 4 and lines[0].split()[0].startswith("1.0")          # field(0, 0) = exp(0)
+    assert len(lines[2].split()) == 2 and all(len(w) == 16 for w in lines[2].split())
+    import json
+    rep = json.loads(lines[3])
+    assert rep["golden_match"] and rep["max_abs_error"] < 1e-3
+    padded = tmp_path / "p.gcow"
+    assert cli.main(["100", "--device", "cpu", "--out", str(padded), "--pad64", "--iters", "1"]) == 0
+    assert len(padded.read_bytes()) % 64 == 0
