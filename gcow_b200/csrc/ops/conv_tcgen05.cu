@@ -479,6 +479,25 @@ static double step_cycles(int copies, double bytes, int mmas) {
   return tma > mma ? tma : mma;
 }
 
+// One or two 128-row accumulators per forward tile: fewer, larger copies against fewer tiles to spread over the SMs.
+static int fwd_halves(int Wo, int Ho, int N, int tiles_c, int ksteps, int bn_cols, int sms) {
+  double cost[3] = {0, 0, 0};
+  for (int hv = 1; hv <= 2; hv++) {
+    int bw, bh, bn;
+    pick_box(Wo, Ho, N, 128 * hv, 0, &bw, &bh, &bn);
+    const long long tiles = (long long)((Wo + bw - 1) / bw) * ((Ho + bh - 1) / bh) * ((N + bn - 1) / bn) * tiles_c;
+    const long long waves = (tiles + sms - 1) / sms;
+    cost[hv] = (double)waves * ksteps * step_cycles(2, hv * HALF_BYTES + bn_cols * 128.0, 4 * hv);
+  }
+  // two 256-column accumulators fill the tensor memory: the epilogue no longer overlaps the next tile, and the
+  // 64 KB stages leave a ring of three (measured: 1.45 x the modelled step)
+  if (bn_cols == 256) cost[2] *= 1.45;
+  int halves = cost[2] < cost[1] ? 2 : 1;
+  if (tune().rows == 128) halves = 1;
+  if (tune().rows == 256) halves = 2;
+  return halves;
+}
+
 struct WgradPlan { int bw, bh, bn, tiles_w, tiles_h, tiles_n, split, per, b_chunks, halves; };
 
 static WgradPlan wgrad_plan(int N, int Ho, int Wo, int Ci, int Co, int taps, int sms) {
@@ -519,24 +538,7 @@ int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int 
   p.bn_cols = Co <= 64 ? 64 : (Co <= 128 ? 128 : 256);
   const int tiles_c = (Co + p.bn_cols - 1) / p.bn_cols;
   const int ksteps = kh * kw * (Ci / 64);
-  // one or two 128-row accumulators per tile: fewer, larger copies against fewer tiles to spread over the SMs
-  int halves = 1;
-  {
-    double cost[3] = {0, 0, 0};
-    for (int hv = 1; hv <= 2; hv++) {
-      int bw, bh, bn;
-      pick_box(Wo, Ho, N, 128 * hv, 0, &bw, &bh, &bn);
-      const long long tiles = (long long)((Wo + bw - 1) / bw) * ((Ho + bh - 1) / bh) * ((N + bn - 1) / bn) * tiles_c;
-      const long long waves = (tiles + sms - 1) / sms;
-      cost[hv] = (double)waves * ksteps * step_cycles(2, hv * HALF_BYTES + p.bn_cols * 128.0, 4 * hv);
-    }
-    // two 256-column accumulators fill the tensor memory: the epilogue no longer overlaps the next tile, and the
-    // 64 KB stages leave a ring of three (measured: 1.45 x the modelled step)
-    if (p.bn_cols == 256) cost[2] *= 1.45;
-    halves = cost[2] < cost[1] ? 2 : 1;
-    if (tune().rows == 128) halves = 1;
-    if (tune().rows == 256) halves = 2;
-  }
+  const int halves = fwd_halves(Wo, Ho, N, tiles_c, ksteps, p.bn_cols, sms);
   pick_box(Wo, Ho, N, 128 * halves, 0, &p.bw, &p.bh, &p.bn);
   if (tune().bw > 0 && tune().bw * tune().bh * tune().bn <= 128 * halves) { p.bw = tune().bw; p.bh = tune().bh; p.bn = tune().bn; }
   p.tiles_w = (Wo + p.bw - 1) / p.bw; p.tiles_h = (Ho + p.bh - 1) / p.bh; p.tiles_n = (N + p.bn - 1) / p.bn;
@@ -607,6 +609,17 @@ int gcow_conv_flip_weights(const void* w, void* wt, int Co, int kh, int kw, int 
   if (blocks > 1184) blocks = 1184;
   flip_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wt, Co, kh, kw, Ci);
   return (int)cudaGetLastError();
+}
+
+// The forward tiling the launcher would choose on a device with `sms` SMs: out = {accumulators per tile (1 or 2),
+// columns per tile, bw, bh, bn, pipeline stages}. For tests and tuning; needs no GPU.
+void gcow_conv_fwd_plan(int N, int Hin, int Win, int Ci, int Co, int kh, int kw, int pad_h, int pad_w, int sms, int* out) {
+  const int Ho = Hin + 2 * pad_h - kh + 1, Wo = Win + 2 * pad_w - kw + 1;
+  const int bn_cols = Co <= 64 ? 64 : (Co <= 128 ? 128 : 256);
+  const int halves = fwd_halves(Wo, Ho, N, (Co + bn_cols - 1) / bn_cols, kh * kw * (Ci / 64), bn_cols, sms);
+  out[0] = halves; out[1] = bn_cols;
+  pick_box(Wo, Ho, N, 128 * halves, 0, &out[2], &out[3], &out[4]);
+  out[5] = stages_for(halves, bn_cols);
 }
 
 // The pixel box chosen for given extents: out = {bw, bh, bn}. For tests of the tiling rule.

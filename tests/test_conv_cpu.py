@@ -39,3 +39,19 @@ def test_pixel_box_wastes_nothing_on_resnet_extents():
         bw, bh, bn = _box(lib, W, W, 256, 128, 0)
         covered = -(-W // bw) * bw * -(-W // bh) * bh * -(-256 // bn) * bn
         assert covered == W * W * 256 and bw * bh * bn == 128, (W, bw, bh, bn)
+
+
+def test_forward_tile_choice_on_resnet_layers():
+    """The launcher's cost model picks 256-pixel tiles where they were measured faster (64, 128 and 512 channels at
+    batch 256 on 148 SMs) and 128-pixel tiles at 256 channels, where two 256-column accumulators would fill the
+    tensor memory and a second wave would be mostly empty."""
+    lib = _lib()
+    if not hasattr(lib, "gcow_conv_fwd_plan"):
+        pytest.skip("library built without the plan export")
+    want = {64: (2, 64), 128: (2, 128), 256: (1, 256), 512: (2, 256)}
+    for (ch, hw) in ((64, 56), (128, 28), (256, 14), (512, 7)):
+        out = (C.c_int * 6)()
+        lib.gcow_conv_fwd_plan(256, hw, hw, ch, ch, 3, 3, 1, 1, 148, out)
+        halves, cols, bw, bh, bn, stages = list(out)
+        assert (halves, cols) == want[ch], (ch, list(out))
+        assert bw * bh * bn <= 128 * halves and 2 <= stages <= 8
