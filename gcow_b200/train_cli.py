@@ -59,6 +59,16 @@ def parse(argv=None) -> argparse.Namespace:
     ap.add_argument("--patience", type=int, default=5, help="epochs without top-1 improvement before stopping")
     ap.add_argument("--out-dir", default="results")
     ap.add_argument("--ops", default="own", choices=["own", "torch"])
+    # launch flags of the reference script (hw/models/train_imagenet.py:60-94); torchrun's environment wins when present
+    ap.add_argument("-j", "--workers", type=int, default=4, help="accepted for compatibility: batches are assembled in-process")
+    ap.add_argument("--pretrained", action="store_true", help="refused: no pretrained weights are available offline")
+    ap.add_argument("--world-size", type=int, default=-1, help="number of nodes (with --multiprocessing-distributed) or of processes")
+    ap.add_argument("--rank", type=int, default=-1, help="node rank (with --multiprocessing-distributed) or process rank")
+    ap.add_argument("--dist-url", default="tcp://127.0.0.1:23456", help="rendezvous tcp://host:port when not started by torchrun")
+    ap.add_argument("--dist-backend", default="nccl", help="accepted for compatibility: GPUs always use NCCL for the control plane")
+    ap.add_argument("--gpu", type=int, default=None, help="GPU of this process when not started by torchrun")
+    ap.add_argument("--multiprocessing-distributed", action="store_true",
+                    help="start one process per visible GPU from this one (what torchrun does otherwise)")
     GcowConfig.add_cli(ap)
     return ap.parse_args(argv)
 
@@ -200,8 +210,44 @@ def run_one(args, mode: str, variable) -> dict:
     return result
 
 
+def launch_env(args, ngpus: int, local: int = 0) -> dict:
+    """RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* for a process that torchrun did not start, from the reference's
+    launch flags: with --multiprocessing-distributed, --world-size counts nodes and every node runs one process per
+    GPU (hw/models/train_imagenet.py:139-147); otherwise it counts processes and --rank is this process's rank."""
+    host, _, port = args.dist_url.replace("tcp://", "").partition(":")
+    nodes_or_procs = max(1, args.world_size)
+    node_or_rank = max(0, args.rank)
+    if args.multiprocessing_distributed:
+        world, rank = nodes_or_procs * ngpus, node_or_rank * ngpus + local
+    else:
+        world, rank = nodes_or_procs, node_or_rank
+        local = args.gpu if args.gpu is not None else 0
+    return {"RANK": str(rank), "LOCAL_RANK": str(local), "WORLD_SIZE": str(world),
+            "MASTER_ADDR": host or "127.0.0.1", "MASTER_PORT": port or "23456"}
+
+
+def _spawned(local: int, ngpus: int, argv) -> None:
+    args = parse(argv)
+    os.environ.update(launch_env(args, ngpus, local))
+    _run(args)
+
+
 def main(argv=None) -> int:
     args = parse(argv)
+    if args.pretrained:
+        raise SystemExit("--pretrained: no pretrained weights can be downloaded here; load a checkpoint with --resume")
+    if "RANK" not in os.environ:                  # not under torchrun: honour the reference's launch flags
+        ngpus = max(1, torch.cuda.device_count())
+        if args.multiprocessing_distributed and ngpus > 1:
+            import torch.multiprocessing as mp
+            mp.spawn(_spawned, nprocs=ngpus, args=(ngpus, list(argv) if argv is not None else sys.argv[1:]))
+            return 0
+        if args.world_size > 1 or args.gpu is not None:
+            os.environ.update(launch_env(args, ngpus))
+    return _run(args)
+
+
+def _run(args) -> int:
     modes = ["precision", "accuracy", "rate", "lossless"] if not args.zfp_mode else [args.zfp_mode]
     for mode in modes:
         variables = {"rate": args.rates, "accuracy": args.tolerances, "precision": args.precisions, "lossless": [0]}[mode]

@@ -18,7 +18,9 @@ def main():
     out = os.environ["GCOW_TEST_OUT"] + f".{rank}"
     dist.init_process_group("gloo")
     store = dist.distributed_c10d._get_default_store()
-    hb = Heartbeat(store, rank, world, interval_s=0.1, timeout_s=1.0).start()
+    # a generous time-out: on a loaded test machine a healthy rank's beat can be late by a second
+    hb = Heartbeat(store, rank, world, interval_s=0.1, timeout_s=3.0).start()
+    dist.barrier()                                        # every rank is up and beating before the steps begin
     res = {"rank": rank, "steps": 0}
 
     def step(i):
