@@ -15,6 +15,8 @@ sw/Makefile:4-5); this is the equivalent single entry point.
 """
 from __future__ import annotations
 
+import contextlib
+import fcntl
 import hashlib
 import json
 import os
@@ -80,6 +82,27 @@ def _run(cmd: list[str], log: Path | None = None) -> None:
         raise RuntimeError(f"native build failed: {cmd[0]} exited {proc.returncode}")
 
 
+@contextlib.contextmanager
+def _build_lock():
+    """Exclusive lock for builds: with one process per GPU every rank may find a stale tree at the same time, and
+    they all write the same object files and libraries. The first rank in builds; the others wait here, then find
+    the stamp up to date. Outputs are written under a temporary name and renamed, so a reader never maps a
+    half-written library."""
+    LIB.mkdir(exist_ok=True)
+    with open(LIB / ".lock", "w") as f:
+        fcntl.flock(f, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(f, fcntl.LOCK_UN)
+
+
+def _replace_text(path: Path, text: str) -> None:
+    tmp = path.with_name(path.name + f".tmp{os.getpid()}")
+    tmp.write_text(text)
+    os.replace(tmp, path)
+
+
 def build_cpu(force: bool = False, sanitize: str | None = None) -> Path:
     """Build libgcow_cpu.so; ``sanitize`` in {None, 'address', 'thread'} builds a
     separately named instrumented copy for the host-side race/memory checks."""
@@ -92,9 +115,14 @@ def build_cpu(force: bool = False, sanitize: str | None = None) -> Path:
     digest = _digest(srcs + _headers(), flags)
     if not force and _up_to_date(name, digest):
         return LIB / f"{name}.so"
-    inc = [f"-I{CSRC}", f"-I{CSRC / 'codec'}"]
-    _run(["g++", *flags, *inc, "-shared", "-x", "c++", *map(str, srcs), "-o", str(LIB / f"{name}.so")])
-    _stamp_path(name).write_text(json.dumps({"digest": digest}))
+    with _build_lock():
+        if not force and _up_to_date(name, digest):      # another process built it while this one waited
+            return LIB / f"{name}.so"
+        inc = [f"-I{CSRC}", f"-I{CSRC / 'codec'}"]
+        tmp = LIB / f"{name}.so.tmp{os.getpid()}"
+        _run(["g++", *flags, *inc, "-shared", "-x", "c++", *map(str, srcs), "-o", str(tmp)])
+        os.replace(tmp, LIB / f"{name}.so")
+        _replace_text(_stamp_path(name), json.dumps({"digest": digest}))
     return LIB / f"{name}.so"
 
 
@@ -111,6 +139,13 @@ def build_cuda(force: bool = False, jobs: int | None = None) -> Path | None:
     if not Path(nvcc).exists():
         so = LIB / f"{name}.so"
         return so if so.exists() else None
+    with _build_lock():
+        if not force and _up_to_date(name, digest):
+            return LIB / f"{name}.so"
+        return _build_cuda_locked(force, jobs, name, srcs, digest, nvcc)
+
+
+def _build_cuda_locked(force, jobs, name, srcs, digest, nvcc) -> Path:
     obj = LIB / "obj"
     obj.mkdir(exist_ok=True)
     inc = [f"-I{CSRC}", f"-I{CSRC / 'codec'}"]
@@ -121,15 +156,19 @@ def build_cuda(force: bool = False, jobs: int | None = None) -> Path | None:
         st = obj / (src.stem + ".stamp")
         if not force and o.exists() and st.exists() and st.read_text() == d:
             return o
-        _run([nvcc, *NVCC_FLAGS, *inc, "-c", str(src), "-o", str(o)], log=obj / (src.stem + ".ptxas.log"))
-        st.write_text(d)
+        tmp = obj / (src.stem + f".o.tmp{os.getpid()}")
+        _run([nvcc, *NVCC_FLAGS, *inc, "-c", str(src), "-o", str(tmp)], log=obj / (src.stem + ".ptxas.log"))
+        os.replace(tmp, o)
+        _replace_text(st, d)
         return o
 
     with ThreadPoolExecutor(max_workers=jobs or min(8, os.cpu_count() or 1)) as ex:
         objs = list(ex.map(one, srcs))
+    tmp = LIB / f"{name}.so.tmp{os.getpid()}"
     _run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *map(str, objs),
-          "-o", str(LIB / f"{name}.so"), "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
-    _stamp_path(name).write_text(json.dumps({"digest": digest}))
+          "-o", str(tmp), "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
+    os.replace(tmp, LIB / f"{name}.so")
+    _replace_text(_stamp_path(name), json.dumps({"digest": digest}))
     return LIB / f"{name}.so"
 
 

@@ -133,7 +133,9 @@ class CompressedAllReduce:
         self.ctas = max(1, min(self.cfg.comm_ctas, self.max_ctas))
         self.max_numel = int(max_numel)
         two = self.lib.gcow_ar_region_bytes(self.max_numel, self.world, self.ctas, self.bits, 0)
-        one_n = min(self.max_numel, max(1, self.cfg.oneshot_max_bytes // 4))
+        # A single rank always takes the one-shot path: y = D(E(x)), ONE lossy round trip, which is what the
+        # reference does to the local gradient on one GPU (hw/models/train_imagenet.py:449-475).
+        one_n = self.max_numel if self.world == 1 else min(self.max_numel, max(1, self.cfg.oneshot_max_bytes // 4))
         one = self.lib.gcow_ar_region_bytes(one_n, self.world, self.ctas, self.bits, 1)
         self.region_cap = int(max(two, one))
         self.oneshot_numel = one_n
@@ -159,7 +161,9 @@ class CompressedAllReduce:
         """Deterministic in (numel, config, world) so that all ranks agree."""
         v = self.cfg.variant
         if v == "auto":
-            if self.world > 1 and numel <= self.oneshot_numel:
+            if self.world == 1:
+                return "oneshot"
+            if numel <= self.oneshot_numel:
                 return "oneshot"
             return "nvls" if (self.arena.mc_ptr and self.world > 1) else "twoshot"
         if v == "nvls" and not self.arena.mc_ptr:

@@ -26,7 +26,8 @@ class GcowConfig:
     variant: str = "auto"           # auto | oneshot | twoshot | nvls | nccl
     oneshot_max_bytes: int = 1 << 20  # buckets up to this many fp32 bytes use one-shot
     comm_ctas: int = 32             # CTAs of the persistent fused kernel
-    timeout_ms: int = 2000          # bound of every device-side wait
+    timeout_ms: int = 30000         # bound of every device-side wait (as generous as a collective watchdog: a peer may be
+                                    # late because of a checkpoint write or a data stall; tests pass short bounds)
     bucket_mb: int = 25             # DDP bucket size
     average: bool = True            # divide by world size (DDP semantics)
     error_feedback: bool = False    # keep the compression residual per bucket

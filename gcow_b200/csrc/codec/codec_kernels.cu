@@ -540,6 +540,32 @@ int gcow_decode_1d_fixed(const void* in, float* out, uint64_t n, int maxbits, in
   return (int)cudaGetLastError();
 }
 
+// Launch sequence of the generic encoder, shared by the entry point that takes the caller's scratch and the one
+// that uses the library's built-in array: slots -> per-block lengths -> prefix sum -> bit-offset scatter.
+static int launch_encode_generic(const float* in, uint64_t nx, uint64_t ny, const ZfpParams& p, uint64_t blocks,
+                                 uint64_t* out, uint64_t out_bytes, void* scratch, uint64_t* block_bits,
+                                 cudaStream_t s) {
+  const int dim = ny ? 2 : 1;
+  const uint64_t wpb = (max_block_bits(p, dim) + 63) / 64;
+  uint64_t* slots = (uint64_t*)scratch;
+  uint32_t* lens = (uint32_t*)(slots + wpb * blocks);
+  uint64_t* tile_sums = (uint64_t*)((char*)lens + ((blocks * 4 + 7) & ~7ull));
+  const uint64_t tiles = (blocks + kScanTile - 1) / kScanTile;
+  cudaMemsetAsync(out, 0, out_bytes, s);   // the scatter pass ORs into the stream
+  const int g = grid_for(blocks);
+  if (dim == 1) encode_slots_kernel<1><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, slots, lens);
+  else encode_slots_kernel<2><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, slots, lens);
+  if (is_fixed_rate(p)) {
+    fixed_offsets_kernel<<<grid_for(blocks + 1), kThreads, 0, s>>>(blocks, p.maxbits, block_bits);
+  } else {
+    scan_tile_sums_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums);
+    scan_tile_offsets_kernel<<<1, kThreads, 0, s>>>(tile_sums, tiles);
+    scan_apply_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums, block_bits);
+  }
+  scatter_slots_kernel<<<g, kThreads, 0, s>>>(slots, lens, block_bits, blocks, (unsigned long long*)out);
+  return (int)cudaGetLastError();
+}
+
 // Scratch requirements of the generic encoder, in bytes, for `blocks` blocks.
 // Layout: slots (words_per_block * blocks u64) | lens (blocks u32, padded) |
 // tile sums (tiles u64).
@@ -556,29 +582,10 @@ uint64_t gcow_encode_generic_scratch_bytes(const int32_t* params, uint64_t block
 // ceil(total/64)*8.
 int gcow_encode_generic(const float* in, uint64_t nx, uint64_t ny, const int32_t* params, uint64_t* out,
                         uint64_t out_bytes, void* scratch, uint64_t* block_bits, void* stream) {
-  cudaStream_t s = (cudaStream_t)stream;
   ZfpParams p = load_params(params);
-  int dim = ny ? 2 : 1;
   uint64_t blocks = ny ? num_blocks_2d(nx, ny) : num_blocks_1d(nx);
   if (!blocks) return 0;
-  uint64_t wpb = (max_block_bits(p, dim) + 63) / 64;
-  uint64_t* slots = (uint64_t*)scratch;
-  uint32_t* lens = (uint32_t*)(slots + wpb * blocks);
-  uint64_t* tile_sums = (uint64_t*)((char*)lens + ((blocks * 4 + 7) & ~7ull));
-  uint64_t tiles = (blocks + kScanTile - 1) / kScanTile;
-  cudaMemsetAsync(out, 0, out_bytes, s);
-  int g = grid_for(blocks);
-  if (dim == 1) encode_slots_kernel<1><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, slots, lens);
-  else encode_slots_kernel<2><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, slots, lens);
-  if (is_fixed_rate(p)) {
-    fixed_offsets_kernel<<<grid_for(blocks + 1), kThreads, 0, s>>>(blocks, p.maxbits, block_bits);
-  } else {
-    scan_tile_sums_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums);
-    scan_tile_offsets_kernel<<<1, kThreads, 0, s>>>(tile_sums, tiles);
-    scan_apply_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums, block_bits);
-  }
-  scatter_slots_kernel<<<g, kThreads, 0, s>>>(slots, lens, block_bits, blocks, (unsigned long long*)out);
-  return (int)cudaGetLastError();
+  return launch_encode_generic(in, nx, ny, p, blocks, out, out_bytes, scratch, block_bits, (cudaStream_t)stream);
 }
 
 // Fixed-rate encode without scratch; maxbits must be a multiple of 64 (e.g. 2-D at
@@ -717,6 +724,15 @@ int gcow_encode_generic_static(const float* in, uint64_t nx, uint64_t ny, const 
     return static_fail(GCOW_STATIC_BAD_ARGS, "null argument");
   ZfpParams p = load_params(params);
   const int dim = ny ? 2 : 1;
+  // Every block needs at least 8 bytes of scratch, so a block count beyond capacity / 8 can be refused before
+  // any size is multiplied out; extents are bounded first so that the 2-D block count itself cannot wrap.
+  const uint64_t max_blocks = kStaticScratchBytes / 8;
+  const uint64_t bx = nx / 4 + (nx % 4 != 0), by = ny ? ny / 4 + (ny % 4 != 0) : 1;
+  if (bx > max_blocks || by > max_blocks || bx * by > max_blocks)
+    return static_fail(GCOW_STATIC_TOO_LARGE,
+                       "%llu x %llu values are far beyond what the built-in scratch array can hold; "
+                       "split the input or use gcow_encode_generic with your own scratch",
+                       (unsigned long long)nx, (unsigned long long)ny);
   const uint64_t blocks = ny ? num_blocks_2d(nx, ny) : num_blocks_1d(nx);
   if (!blocks) return GCOW_STATIC_OK;
   const uint64_t need = gcow_encode_generic_scratch_bytes(params, blocks, dim);
@@ -732,26 +748,8 @@ int gcow_encode_generic_static(const float* in, uint64_t nx, uint64_t ny, const 
   int rc = static_scratch_ptr(&scratch);
   if (rc != GCOW_STATIC_OK) return rc;
 
-  cudaStream_t s = (cudaStream_t)stream;
-  const uint64_t wpb = (max_block_bits(p, dim) + 63) / 64;
-  uint64_t* slots = (uint64_t*)scratch;
-  uint32_t* lens = (uint32_t*)(slots + wpb * blocks);
-  uint64_t* tile_sums = (uint64_t*)((char*)lens + ((blocks * 4 + 7) & ~7ull));
-  const uint64_t tiles = (blocks + kScanTile - 1) / kScanTile;
-  cudaMemsetAsync(out, 0, out_bytes, s);   // the scatter pass ORs into the stream
-  const int g = grid_for(blocks);
-  if (dim == 1) encode_slots_kernel<1><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, slots, lens);
-  else encode_slots_kernel<2><<<g, kThreads, 0, s>>>(in, nx, ny, p, blocks, slots, lens);
-  if (is_fixed_rate(p)) {
-    fixed_offsets_kernel<<<grid_for(blocks + 1), kThreads, 0, s>>>(blocks, p.maxbits, block_bits);
-  } else {
-    scan_tile_sums_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums);
-    scan_tile_offsets_kernel<<<1, kThreads, 0, s>>>(tile_sums, tiles);
-    scan_apply_kernel<<<(unsigned)tiles, kThreads, 0, s>>>(lens, blocks, tile_sums, block_bits);
-  }
-  scatter_slots_kernel<<<g, kThreads, 0, s>>>(slots, lens, block_bits, blocks, (unsigned long long*)out);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return static_fail((int)e, "kernel launch failed with cuda error %llu", (unsigned long long)e);
+  const int e = launch_encode_generic(in, nx, ny, p, blocks, out, out_bytes, scratch, block_bits, (cudaStream_t)stream);
+  if (e != 0) return static_fail(e, "kernel launch failed with cuda error %llu", (unsigned long long)e);
   return GCOW_STATIC_OK;
 }
 

@@ -37,15 +37,31 @@ def _error_word(device: torch.device) -> torch.Tensor:
     return w
 
 
-def check_errors(device: torch.device | None = None) -> None:
-    """Raise if any compute kernel gave up on an internal wait (synchronises)."""
+class KernelWaitAbandoned(RuntimeError):
+    """A tcgen05 GEMM / convolution kernel gave up on one of its bounded mbarrier waits, so a tile of its
+    output was not written."""
+
+
+def check_errors(device: torch.device | None = None, raise_on_error: bool = True) -> int:
+    """Read the error word of the compute kernels (synchronises). Raises KernelWaitAbandoned if a kernel gave up on
+    an internal wait, or returns the code when ``raise_on_error`` is false. The word is cleared."""
+    worst = 0
     for dev, w in _err_words.items():
         if device is not None and dev != device:
             continue
         code = int(w.item())
         if code:
             w.zero_()
-            raise RuntimeError(f"gcow compute kernel on {dev} abandoned a wait (role code {code})")
+            if raise_on_error:
+                raise KernelWaitAbandoned(f"gcow compute kernel on {dev} abandoned a wait (role code {code})")
+            worst = code
+    return worst
+
+
+def error_word(device: torch.device) -> torch.Tensor:
+    """The device word that the tensor-core kernels set when they abandon a wait (one int32). Training loops copy it
+    to the host next to the loss, so a kernel that gave up is noticed one step later without an extra synchronisation."""
+    return _error_word(device)
 
 
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,

@@ -36,7 +36,7 @@ class GcowDDPState:
     residual: dict = field(default_factory=dict)   # error-feedback memory per bucket index
     last_buckets: list = field(default_factory=list)
     side: dict = field(default_factory=dict)       # out-of-place result buffers per bucket index (safe mode)
-    pending: list = field(default_factory=list)    # (bucket buffer, verdict word) of this step (safe mode)
+    pending: list = field(default_factory=list)    # (bucket buffer, side buffer) of this step (safe mode)
     timeouts: int = 0
     fallbacks: int = 0
 
@@ -44,25 +44,47 @@ class GcowDDPState:
         self.last_buckets.clear()
         self.pending.clear()
 
+    def agree_on_failure(self, failed_here: bool) -> bool:
+        """True on every rank if the collective gave up on ANY rank in this step. A time-out can hit some
+        ranks only (a rank that arrives after its peers' deadline finds every flag set and succeeds), so the
+        decision to redo the step's buckets must not be taken by each rank alone: ranks that redo would call
+        NCCL while the others do not. One MAX all-reduce of a flag over the control group settles it."""
+        world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        if world == 1:
+            return failed_here
+        dev = self.pending[0][0].device if self.pending else torch.device("cpu")
+        flag = torch.tensor([1 if failed_here else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        return bool(int(flag.item()))
+
     def finish_step(self) -> None:
-        """Call after backward, before the optimizer step: waits for the communication
-        stream. If a bucket's collective gave up: with ``cfg.fallback_nccl`` every
-        bucket that was not committed is all-reduced again by NCCL in fp32 (its buffer
-        still holds the local gradient), otherwise CollectiveTimeout is raised."""
+        """Call after backward, before the optimizer step: waits for the communication stream and reads
+        the collective's status record. Default mode: a time-out raises CollectiveTimeout. Safe mode
+        (``cfg.fallback_nccl``): every bucket was reduced into a side buffer and its own buffer still holds
+        the local gradient; the ranks agree whether any of them saw a failure, then either all copy the
+        side buffers in, or all redo every bucket of the step with NCCL in fp32."""
+        failed, err = False, None
         try:
             self.ar.check(self.ar.stream)
-        except CollectiveTimeout:
+        except CollectiveTimeout as e:
+            failed, err = True, e
             self.timeouts += 1
-            if not (self.cfg.fallback_nccl and self.pending):
-                raise
-            world = dist.get_world_size(self.group)
-            for buf, verdict in self.pending:
-                if int(verdict.item()) != 1:
+        if not self.cfg.fallback_nccl:
+            if failed:
+                raise err
+            return
+        if self.agree_on_failure(failed):
+            world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+            for buf, _side in self.pending:
+                if world > 1:
                     dist.all_reduce(buf, group=self.group)
                     if self.cfg.average:
                         buf.div_(world)
-                    self.fallbacks += 1
-            torch.cuda.current_stream().synchronize()
+                self.fallbacks += 1
+            self.ar.reset_status()
+        else:
+            for buf, side in self.pending:
+                buf.copy_(side)
 
     def step_record(self) -> dict:
         """Metrics of the step that just finished, for the JSONL log."""
@@ -99,17 +121,15 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
             buf.add_(res)                      # re-inject what compression dropped last time
             sent = buf.clone()
         if state.cfg.fallback_nccl:
-            # safe mode: reduce into a side buffer; copy back on the device only if no
-            # collective has failed, so a failed bucket keeps its local gradient
+            # safe mode: reduce into a side buffer; finish_step copies it in once all ranks
+            # agree that the step's collectives succeeded, so until then the bucket keeps its local gradient
             idx = bucket.index()
             side = state.side.get(idx)
-            if side is None or side[0].numel() != buf.numel():
-                side = (torch.empty_like(buf), torch.zeros(1, dtype=torch.int32, device=buf.device))
+            if side is None or side.numel() != buf.numel():
+                side = torch.empty_like(buf)
                 state.side[idx] = side
-            ar(buf, out=side[0], stream=ar.stream)
-            ar.commit(side[0], buf, side[1], ar.stream)
-            state.pending.append((buf, side[1]))
-            state.launches += 1
+            ar(buf, out=side, stream=ar.stream)
+            state.pending.append((buf, side))
         else:
             ar(buf, stream=ar.stream)
         if state.cfg.error_feedback:

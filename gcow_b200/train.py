@@ -147,6 +147,7 @@ class Trainer:
         self.std = torch.tensor(IMAGENET_STD, device=self.device).view(1, 3, 1, 1) * 255.0
         self.copy_stream = torch.cuda.Stream(device=self.device)
         self.loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+        self.err_host = torch.zeros(2, dtype=torch.int32).pin_memory()    # compute kernels' error word, per slot
         self.loss_event: list[Optional[torch.cuda.Event]] = [None, None]
         self.steps = 0
         self.epoch = 0
@@ -228,6 +229,10 @@ class Trainer:
         loss = self.step_device(dev)
         slot = self.steps & 1
         self.loss_host[slot:slot + 1].copy_(loss.view(1), non_blocking=True)
+        if ops_backend.get_backend() == "own":
+            from .ops import kernels
+            self.err_host[slot:slot + 1].copy_(kernels.error_word(self.device), non_blocking=True)
+            self.d2h_bytes += 4
         ev = torch.cuda.Event()
         ev.record()
         self.loss_event[slot] = ev
@@ -237,14 +242,26 @@ class Trainer:
         if self.loss_event[pslot] is not None:
             self.loss_event[pslot].synchronize()
             prev = float(self.loss_host[pslot])
+            self._raise_on_kernel_error(int(self.err_host[pslot]))
             if math.isnan(prev):
                 raise FloatingPointError("loss is NaN: training diverged")   # train_imagenet.py:445-446
         if self.logger.enabled:
             self.logger.log(step=self.steps, loss=prev, **(self.hook_state.step_record() if self.hook_state else {}))
         return StepResult(prev, self.steps)
 
+    def _raise_on_kernel_error(self, code: int) -> None:
+        if code:
+            from .ops import kernels
+            kernels.error_word(self.device).zero_()
+            self.err_host.zero_()
+            raise kernels.KernelWaitAbandoned(
+                f"a tensor-core kernel on {self.device} abandoned a wait (role code {code}) in step {self.steps - 1}: "
+                f"that step's activations or gradients are incomplete")
+
     def last_loss(self) -> float:
+        """Loss of the latest ``step`` call (synchronises); raises if a compute kernel gave up during it."""
         torch.cuda.current_stream().synchronize()
+        self._raise_on_kernel_error(int(self.err_host[self.steps & 1]))
         return float(self.loss_host[self.steps & 1])
 
     # ------------------------------------------------------------ checkpoint

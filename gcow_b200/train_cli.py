@@ -118,6 +118,9 @@ def validate(tr: Trainer, loader, print_freq: int):
     for m in (top1, top5, losses):
         m.all_reduce(tr.device)
     tr.ddp.train()
+    if tr.device.type == "cuda":
+        from .ops import kernels
+        kernels.check_errors(tr.device)              # a tensor-core kernel that gave up would have skewed the metrics
     return top1.avg, top5.avg, losses.avg
 
 
@@ -195,6 +198,8 @@ def run_one(args, mode: str, variable) -> dict:
         stale = 0 if is_best else stale + 1
         save_checkpoint({"epoch": epoch + 1, "arch": args.arch, "best_acc1": best_acc1, "trainer": tr.state_dict()},
                         ckpt, is_best)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.barrier()      # rank 0 writes alone; the others must not start waiting on it inside a collective
         secs = time.time() - t_epoch
         row = {"mode": mode, "variable": variable, "epoch": epoch, "train_loss": losses.avg, "val_loss": vl,
                "acc1": a1, "acc5": a5, "epoch_sec": secs,

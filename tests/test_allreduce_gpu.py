@@ -31,9 +31,15 @@ def test_single_rank_equals_oracle(rate):
         x = gen(n, n)
         pieces = [x[i:i + (1 << 20)] for i in range(0, n, 1 << 20)]
         ref = np.concatenate([allreduce_oracle(q[None], p, "twoshot", 0) for q in pieces])
-        y = ar(torch.from_numpy(x).cuda())
+        y = ar(torch.from_numpy(x).cuda(), variant="twoshot")
         ar.check()
         assert np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+        # the default on one rank is a single round trip D(E(x)), as the reference applies to the local gradient
+        assert ar.pick_variant(n) == "oneshot"
+        one = np.concatenate([allreduce_oracle(q[None], p, "oneshot", 0) for q in pieces])
+        y1 = ar(torch.from_numpy(x).cuda())
+        ar.check()
+        assert np.array_equal(y1.cpu().numpy().view(np.uint32), one.view(np.uint32))
 
 
 @pytest.mark.gpu

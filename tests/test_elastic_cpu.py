@@ -54,3 +54,16 @@ def test_reference_launch_flags_map_to_ranks():
     import pytest
     with pytest.raises(SystemExit):
         train_cli.main(["--dummy", "--pretrained"])
+
+
+@pytest.mark.parametrize("failing", ["", "1", "0,2"])
+def test_safe_mode_redo_is_agreed_across_ranks(failing):
+    """The fused collective can time out on some ranks only. finish_step must then redo the step's buckets with the
+    plain all-reduce on EVERY rank (or on none), from the untouched local gradients, so the replicas stay equal and
+    no rank is left alone inside a collective."""
+    env = dict(os.environ, FAILING=failing, MASTER_ADDR="127.0.0.1")
+    port = 29450 + os.getpid() % 200 + len(failing)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_agree_worker.py")]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=180)
+    assert p.returncode == 0 and p.stdout.count("ok") == 3, p.stdout[-1500:] + p.stderr[-1500:]
