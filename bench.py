@@ -15,6 +15,7 @@ L2 flush is needed between steps.
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import sys
@@ -137,7 +138,8 @@ def reference_arm(args) -> int:
                 dist.barrier()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            diverged = ref.train(int(args.rate), batches, model, criterion, optimizer, 0, device, rargs)
+            with contextlib.redirect_stdout(sys.stderr):      # the script prints its progress meters; keep stdout for the JSON line
+                diverged = ref.train(int(args.rate), batches, model, criterion, optimizer, 0, device, rargs)
             torch.cuda.synchronize()
             dt = time.perf_counter() - t0
             if world > 1:

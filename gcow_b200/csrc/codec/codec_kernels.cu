@@ -24,6 +24,7 @@ constexpr int kThreads = 256;
 // gcow_codec_tables) and are copied into shared memory by every CTA.
 __device__ __align__(16) uint16_t g_enc_table[kEncTabSize];
 __device__ __align__(16) uint16_t g_dec_table[kDecBudgetTabSize];
+__device__ __align__(16) uint32_t g_enc_pair_table[kEncPairTabSize];
 
 __device__ __forceinline__ void load_enc_table(uint16_t* etab, const uint16_t* __restrict__ src) {
   for (int i = threadIdx.x; i < kEncTabSize / 2; i += blockDim.x)
@@ -32,6 +33,11 @@ __device__ __forceinline__ void load_enc_table(uint16_t* etab, const uint16_t* _
 __device__ __forceinline__ void load_dec_table(uint16_t* dtab, const uint16_t* __restrict__ src) {
   for (int i = threadIdx.x; i < kDecBudgetTabSize / 8; i += blockDim.x)
     reinterpret_cast<uint4*>(dtab)[i] = reinterpret_cast<const uint4*>(src)[i];
+}
+
+__device__ __forceinline__ void load_pair_table(uint32_t* epair, const uint32_t* __restrict__ src) {
+  for (int i = threadIdx.x; i < kEncPairTabSize / 4; i += blockDim.x)
+    reinterpret_cast<uint4*>(epair)[i] = reinterpret_cast<const uint4*>(src)[i];
 }
 
 // Load block b of a 1-D array of n floats (tail block padded).
@@ -88,17 +94,20 @@ template <> struct CodeIO<128> {
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
 encode_1d_fixed_kernel(const float* __restrict__ in, uint64_t n, void* __restrict__ out, int aligned,
-                       const uint16_t* __restrict__ tab) {
+                       const uint16_t* __restrict__ tab, const uint32_t* __restrict__ pair_tab) {
   __shared__ __align__(16) uint16_t etab[kEncTabSize];
+  __shared__ __align__(16) uint32_t epair[kEncPairTabSize];
   load_enc_table(etab, tab);
+  load_pair_table(epair, pair_tab);
   __syncthreads();
+  const LeanTables lt = {etab, nullptr, epair};
   const uint64_t blocks = num_blocks_1d(n);
   for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
        b += (uint64_t)gridDim.x * blockDim.x) {
     float f[4];
     load_block_1d(f, in, n, b, aligned);
     uint32_t w[CodeIO<BITS>::NW];
-    encode_block_1d_rate<BITS>(f, etab, w);
+    encode_block_1d_lean<BITS>(f, lt, w);
     CodeIO<BITS>::store(out, b, w);
   }
 }
@@ -110,13 +119,14 @@ decode_1d_fixed_kernel(const void* __restrict__ in, float* __restrict__ out, uin
   __shared__ __align__(16) uint16_t dtab[kDecBudgetTabSize];
   load_dec_table(dtab, tab);
   __syncthreads();
+  const LeanTables lt = {nullptr, dtab, nullptr};
   const uint64_t blocks = num_blocks_1d(n);
   for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
        b += (uint64_t)gridDim.x * blockDim.x) {
     uint32_t w[CodeIO<BITS>::NW];
     CodeIO<BITS>::load(in, b, w);
     float f[4];
-    decode_block_1d_rate<BITS>(f, dtab, w, shift);
+    decode_block_1d_lean<BITS>(f, lt, w, shift);
     store_block_1d(f, out, n, b, aligned);
   }
 }
@@ -476,28 +486,40 @@ extern "C" {
 // Device pointers of the coder tables on the current device; the tables are
 // built on the host and uploaded on the first call per device (a synchronous
 // copy, so make that first call outside any stream capture).
-int gcow_codec_tables(const void** etab, const void** dtab) {
+int gcow_codec_tables3(const void** etab, const void** dtab, const void** epair) {
   static std::mutex mu;
   static const void* e_addr[64] = {};
   static const void* d_addr[64] = {};
+  static const void* p_addr[64] = {};
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess || dev < 0 || dev >= 64) return err ? (int)err : -1;
   std::lock_guard<std::mutex> lock(mu);
   if (!e_addr[dev]) {
     static uint16_t he[kEncTabSize], hd[kDecBudgetTabSize];
+    static uint32_t hp[kEncPairTabSize];
     build_codec_tables(he, hd);
+    build_pair_table(hp);
     if ((err = cudaMemcpyToSymbol(g_enc_table, he, sizeof he)) != cudaSuccess) return (int)err;
     if ((err = cudaMemcpyToSymbol(g_dec_table, hd, sizeof hd)) != cudaSuccess) return (int)err;
-    void *pe = nullptr, *pd = nullptr;
+    if ((err = cudaMemcpyToSymbol(g_enc_pair_table, hp, sizeof hp)) != cudaSuccess) return (int)err;
+    void *pe = nullptr, *pd = nullptr, *pp = nullptr;
     if ((err = cudaGetSymbolAddress(&pe, g_enc_table)) != cudaSuccess) return (int)err;
     if ((err = cudaGetSymbolAddress(&pd, g_dec_table)) != cudaSuccess) return (int)err;
+    if ((err = cudaGetSymbolAddress(&pp, g_enc_pair_table)) != cudaSuccess) return (int)err;
+    p_addr[dev] = pp;
     d_addr[dev] = pd;
     e_addr[dev] = pe;
   }
   *etab = e_addr[dev];
   *dtab = d_addr[dev];
+  *epair = p_addr[dev];
   return 0;
+}
+
+int gcow_codec_tables(const void** etab, const void** dtab) {
+  const void* pair;
+  return gcow_codec_tables3(etab, dtab, &pair);
 }
 
 // Fixed-rate 1-D encode; maxbits in {16, 32, 64, 128}. `out` holds
@@ -508,14 +530,15 @@ int gcow_encode_1d_fixed(const float* in, uint64_t n, int maxbits, void* out, vo
   if (!blocks) return 0;
   int aligned = ((uintptr_t)in & 15) == 0;
   int g = grid_for(blocks);
-  const void *etp, *dtp;
-  if (int rc = gcow_codec_tables(&etp, &dtp)) return rc;
+  const void *etp, *dtp, *ptp;
+  if (int rc = gcow_codec_tables3(&etp, &dtp, &ptp)) return rc;
   const uint16_t* et = (const uint16_t*)etp;
+  const uint32_t* pt = (const uint32_t*)ptp;
   switch (maxbits) {
-    case 16: encode_1d_fixed_kernel<16><<<g, kThreads, 0, s>>>(in, n, out, aligned, et); break;
-    case 32: encode_1d_fixed_kernel<32><<<g, kThreads, 0, s>>>(in, n, out, aligned, et); break;
-    case 64: encode_1d_fixed_kernel<64><<<g, kThreads, 0, s>>>(in, n, out, aligned, et); break;
-    case 128: encode_1d_fixed_kernel<128><<<g, kThreads, 0, s>>>(in, n, out, aligned, et); break;
+    case 16: encode_1d_fixed_kernel<16><<<g, kThreads, 0, s>>>(in, n, out, aligned, et, pt); break;
+    case 32: encode_1d_fixed_kernel<32><<<g, kThreads, 0, s>>>(in, n, out, aligned, et, pt); break;
+    case 64: encode_1d_fixed_kernel<64><<<g, kThreads, 0, s>>>(in, n, out, aligned, et, pt); break;
+    case 128: encode_1d_fixed_kernel<128><<<g, kThreads, 0, s>>>(in, n, out, aligned, et, pt); break;
     default: return -1;
   }
   return (int)cudaGetLastError();

@@ -434,21 +434,40 @@ uint64_t gcow_header_decompress(const uint64_t* in, float* data, uint64_t nx, ui
   return src.pos;
 }
 
-// Table-driven 1-D fixed-rate paths (rate-specialised and general); both are run
-// and must agree (-2 otherwise). maxbits must be 16, 32, 64 or 128.
+// Table-driven 1-D fixed-rate paths (rate-specialised, general, and the warp-uniform
+// formulation the kernels run); all are run and must agree (-2 otherwise). maxbits
+// must be 16, 32, 64 or 128.
+namespace {
+struct HostLeanTables {
+  std::vector<uint16_t> etab, btab;
+  std::vector<uint32_t> epair;
+  gcow::LeanTables t;
+  HostLeanTables() : etab(gcow::kEncTabSize), btab(gcow::kDecBudgetTabSize), epair(gcow::kEncPairTabSize) {
+    gcow::build_codec_tables(etab.data(), btab.data());
+    gcow::build_pair_table(epair.data());
+    t.etab = etab.data(); t.dtab = btab.data(); t.epair = epair.data();
+  }
+};
+const gcow::LeanTables& host_lean_tables() {
+  static HostLeanTables h;
+  return h.t;
+}
+}  // namespace
+
 int gcow_fast1d_compress(const float* data, uint64_t n, const int32_t* params, void* out) {
   ZfpParams p = load_params(params);
   uint16_t etab[gcow::kEncTabSize];
   for (uint32_t i = 0; i < (uint32_t)gcow::kEncTabSize; i++) etab[i] = gcow::make_enc_entry(i / 16, i % 16);
+  const gcow::LeanTables& lt = host_lean_tables();
   uint64_t blocks = gcow::num_blocks_1d(n);
   float blk[4];
   for (uint64_t b = 0; b < blocks; b++) {
     o_gather(blk, data, n, 0, b);
     switch (p.maxbits) {
-      case 16: { uint32_t w[1], v[1]; gcow::encode_block_1d_rate<16>(blk, etab, w); gcow::encode_block_1d_fast<1>(blk, p, etab, v); if (w[0] != v[0]) return -2; ((uint16_t*)out)[b] = (uint16_t)w[0]; break; }
-      case 32: { uint32_t w[1], v[1]; gcow::encode_block_1d_rate<32>(blk, etab, w); gcow::encode_block_1d_fast<1>(blk, p, etab, v); if (w[0] != v[0]) return -2; ((uint32_t*)out)[b] = w[0]; break; }
-      case 64: { uint32_t w[2], v[2]; gcow::encode_block_1d_rate<64>(blk, etab, w); gcow::encode_block_1d_fast<2>(blk, p, etab, v); if (memcmp(w, v, 8)) return -2; memcpy((uint32_t*)out + 2 * b, w, 8); break; }
-      case 128: { uint32_t w[4], v[4]; gcow::encode_block_1d_rate<128>(blk, etab, w); gcow::encode_block_1d_fast<4>(blk, p, etab, v); if (memcmp(w, v, 16)) return -2; memcpy((uint32_t*)out + 4 * b, w, 16); break; }
+      case 16: { uint32_t w[1], v[1], l[1]; gcow::encode_block_1d_rate<16>(blk, etab, w); gcow::encode_block_1d_fast<1>(blk, p, etab, v); gcow::encode_block_1d_lean<16>(blk, lt, l); if (memcmp(w, v, 4) || memcmp(w, l, 4)) return -2; ((uint16_t*)out)[b] = (uint16_t)w[0]; break; }
+      case 32: { uint32_t w[1], v[1], l[1]; gcow::encode_block_1d_rate<32>(blk, etab, w); gcow::encode_block_1d_fast<1>(blk, p, etab, v); gcow::encode_block_1d_lean<32>(blk, lt, l); if (memcmp(w, v, 4) || memcmp(w, l, 4)) return -2; ((uint32_t*)out)[b] = w[0]; break; }
+      case 64: { uint32_t w[2], v[2], l[2]; gcow::encode_block_1d_rate<64>(blk, etab, w); gcow::encode_block_1d_fast<2>(blk, p, etab, v); gcow::encode_block_1d_lean<64>(blk, lt, l); if (memcmp(w, v, 8) || memcmp(w, l, 8)) return -2; memcpy((uint32_t*)out + 2 * b, w, 8); break; }
+      case 128: { uint32_t w[4], v[4], l[4]; gcow::encode_block_1d_rate<128>(blk, etab, w); gcow::encode_block_1d_fast<4>(blk, p, etab, v); gcow::encode_block_1d_lean<128>(blk, lt, l); if (memcmp(w, v, 16) || memcmp(w, l, 16)) return -2; memcpy((uint32_t*)out + 4 * b, w, 16); break; }
       default: return -1;
     }
   }
@@ -460,16 +479,17 @@ int gcow_fast1d_decompress(const void* in, float* data, uint64_t n, const int32_
   for (uint32_t i = 0; i < (uint32_t)gcow::kDecTabSize; i++) dtab[i] = gcow::make_dec_entry(i / 128, i % 128);
   gcow::build_codec_tables(etab.data(), btab.data());
   uint64_t blocks = gcow::num_blocks_1d(n);
-  float blk[4], alt[4];
+  float blk[4], alt[4], lean[4];
+  const gcow::LeanTables& lt = host_lean_tables();
   for (uint64_t b = 0; b < blocks; b++) {
     switch (p.maxbits) {
-      case 16: { uint32_t w[1] = {((const uint16_t*)in)[b]}; gcow::decode_block_1d_rate<16>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); break; }
-      case 32: { uint32_t w[1] = {((const uint32_t*)in)[b]}; gcow::decode_block_1d_rate<32>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); break; }
-      case 64: { uint32_t w[2]; memcpy(w, (const uint32_t*)in + 2 * b, 8); gcow::decode_block_1d_rate<64>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<2>(alt, p, dtab.data(), w, shift); break; }
-      case 128: { uint32_t w[4]; memcpy(w, (const uint32_t*)in + 4 * b, 16); gcow::decode_block_1d_rate<128>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<4>(alt, p, dtab.data(), w, shift); break; }
+      case 16: { uint32_t w[1] = {((const uint16_t*)in)[b]}; gcow::decode_block_1d_rate<16>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); gcow::decode_block_1d_lean<16>(lean, lt, w, shift); break; }
+      case 32: { uint32_t w[1] = {((const uint32_t*)in)[b]}; gcow::decode_block_1d_rate<32>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<1>(alt, p, dtab.data(), w, shift); gcow::decode_block_1d_lean<32>(lean, lt, w, shift); break; }
+      case 64: { uint32_t w[2]; memcpy(w, (const uint32_t*)in + 2 * b, 8); gcow::decode_block_1d_rate<64>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<2>(alt, p, dtab.data(), w, shift); gcow::decode_block_1d_lean<64>(lean, lt, w, shift); break; }
+      case 128: { uint32_t w[4]; memcpy(w, (const uint32_t*)in + 4 * b, 16); gcow::decode_block_1d_rate<128>(blk, btab.data(), w, shift); gcow::decode_block_1d_fast<4>(alt, p, dtab.data(), w, shift); gcow::decode_block_1d_lean<128>(lean, lt, w, shift); break; }
       default: return -1;
     }
-    if (memcmp(blk, alt, 16)) return -2;   // the two table-driven formulations must agree
+    if (memcmp(blk, alt, 16) || memcmp(blk, lean, 16)) return -2;   // the table-driven formulations must agree
     o_scatter(blk, data, n, 0, b);
   }
   return 0;

@@ -19,6 +19,7 @@
 // depends only on the plane and on the running count n), so encoding is
 // "concatenate per-plane codes, cut at the budget".
 #pragma once
+#include <math.h>
 #include <stdint.h>
 #include <string.h>
 #include "zfp_params.h"
@@ -781,6 +782,231 @@ inline void build_codec_tables(uint16_t* etab, uint16_t* dtab_budget) {
     const uint32_t n = i >> 10, a = (i >> 7) & 7, pk = i & 127;
     dtab_budget[i] = make_dec_budget_entry(n, a, pk & low_mask32(a));
   }
+}
+
+// ------------------------------------------- lean fixed-rate 1-D block codec
+// The coder above walks a block plane by plane with a data-dependent trip count, so
+// the 32 lanes of a warp (one block each) spend much of their time waiting for the
+// slowest lane. The functions below produce the same bits with warp-uniform control
+// flow and fewer integer instructions:
+//
+//  * encoder: the top eight bit planes are coded two planes per table lookup, four
+//    lookups for every lane. The table index (two planes of four coefficients) is
+//    gathered from the top bytes with one mask and one multiply, so no bit-matrix
+//    transpose is needed. A plane at significance count n >= 3 is always the four
+//    coefficient bits verbatim (with n = 3 the group-test bit IS bit 3), so longer
+//    blocks append the remaining planes as transposed nibbles.
+//  * decoder: planes are looked up one at a time only until n reaches 3; the rest of
+//    the block is verbatim nibbles taken from the stream in one shift.
+//
+// Inputs the fast path does not cover (a non-finite or vanishing block maximum, a NaN
+// member, data so smooth that eight planes do not reach n >= 3 or fill the budget)
+// return to encode_block_1d_rate / decode_block_1d_rate above, which stay the
+// definition. The serial oracle and the reference build are the tests' yardstick for
+// both (sw/src/encode.c:279-339,457-495; sw/src/decode.c:141-183,220-253).
+
+// Two planes per lookup: index n * 256 + g, where bit 7-2i of g is coefficient i's
+// bit in the first (higher) plane and bit 6-2i its bit in the second plane.
+// Entry: code (14 bits) | length << 16 | (n' - n) << 24, so that adding an entry to a
+// packed state [junk:16 | position:8 | n:8] advances position and n at once.
+constexpr int kEncPairTabSize = 5 * 256;
+GCOW_HD uint32_t make_enc_pair_entry(uint32_t n, uint32_t g) {
+  uint32_t x1 = 0, x2 = 0;
+  for (int i = 0; i < 4; i++) {
+    x1 |= ((g >> (7 - 2 * i)) & 1u) << i;
+    x2 |= ((g >> (6 - 2 * i)) & 1u) << i;
+  }
+  const uint32_t n0 = n;
+  uint64_t c1, c2; uint32_t l1, l2;
+  encode_plane<4>(x1, n, c1, l1);
+  encode_plane<4>(x2, n, c2, l2);
+  return (uint32_t)(c1 | (c2 << l1)) | ((l1 + l2) << 16) | ((n - n0) << 24);
+}
+
+GCOW_HD uint32_t shl_sat(uint32_t v, uint32_t s) {   // v << s, 0 for s >= 32
+#if defined(__CUDA_ARCH__)
+  uint32_t r; asm("shl.b32 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(s)); return r;
+#else
+  return s < 32 ? v << s : 0u;
+#endif
+}
+GCOW_HD uint32_t shr_sat(uint32_t v, uint32_t s) {   // v >> s, 0 for s >= 32
+#if defined(__CUDA_ARCH__)
+  uint32_t r; asm("shr.u32 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(s)); return r;
+#else
+  return s < 32 ? v >> s : 0u;
+#endif
+}
+
+// BITS bits held in registers, addressed by bit position.
+template <int NW> struct BitBuf;
+template <> struct BitBuf<1> {
+  uint32_t a;
+  GCOW_HD void clear() { a = 0; }
+  GCOW_HD void load(const uint32_t (&w)[1]) { a = w[0]; }
+  GCOW_HD void store(uint32_t (&w)[1]) const { w[0] = a; }
+  GCOW_HD void put(uint32_t pos, uint32_t v) { a |= shl_sat(v, pos); }
+  GCOW_HD uint32_t peek(uint32_t pos) const { return shr_sat(a, pos); }
+};
+template <> struct BitBuf<2> {
+  uint64_t a;
+  GCOW_HD void clear() { a = 0; }
+  GCOW_HD void load(const uint32_t (&w)[2]) { a = (uint64_t)w[0] | ((uint64_t)w[1] << 32); }
+  GCOW_HD void store(uint32_t (&w)[2]) const { w[0] = (uint32_t)a; w[1] = (uint32_t)(a >> 32); }
+  GCOW_HD void put(uint32_t pos, uint32_t v) { if (pos < 64) a |= (uint64_t)v << pos; }
+  GCOW_HD uint32_t peek(uint32_t pos) const { return pos < 64 ? (uint32_t)(a >> pos) : 0u; }
+};
+template <> struct BitBuf<4> {
+  uint64_t lo, hi;
+  GCOW_HD void clear() { lo = hi = 0; }
+  GCOW_HD void load(const uint32_t (&w)[4]) {
+    lo = (uint64_t)w[0] | ((uint64_t)w[1] << 32); hi = (uint64_t)w[2] | ((uint64_t)w[3] << 32);
+  }
+  GCOW_HD void store(uint32_t (&w)[4]) const {
+    w[0] = (uint32_t)lo; w[1] = (uint32_t)(lo >> 32); w[2] = (uint32_t)hi; w[3] = (uint32_t)(hi >> 32);
+  }
+  GCOW_HD void put(uint32_t pos, uint32_t v) {
+    if (pos < 64) {
+      lo |= (uint64_t)v << pos;
+      if (pos > 32) hi |= (uint64_t)v >> (64 - pos);
+    } else if (pos < 128) {
+      hi |= (uint64_t)v << (pos - 64);
+    }
+  }
+  GCOW_HD uint32_t peek(uint32_t pos) const {
+    if (pos < 64) {
+      uint64_t r = lo >> pos;
+      if (pos > 32) r |= hi << (64 - pos);
+      return (uint32_t)r;
+    }
+    return pos < 128 ? (uint32_t)(hi >> (pos - 64)) : 0u;
+  }
+};
+
+struct LeanTables {
+  const uint16_t* etab;    // kEncTabSize: one plane per lookup (definition path)
+  const uint16_t* dtab;    // kDecBudgetTabSize: budget-aware, one plane per lookup
+  const uint32_t* epair;   // kEncPairTabSize: two planes per lookup
+};
+
+template <int BITS>
+GCOW_HD void encode_block_1d_lean(const float* f, const LeanTables& t, uint32_t (&w)[(BITS + 31) / 32]) {
+  constexpr int NW = (BITS + 31) / 32;
+  const float a01 = fmaxf(fabsf(f[0]), fabsf(f[1])), a23 = fmaxf(fabsf(f[2]), fabsf(f[3]));
+  const uint32_t mb = f32_bits(fmaxf(a01, a23));
+  if (mb == 0) {
+#pragma unroll
+    for (int i = 0; i < NW; i++) w[i] = 0;
+    return;
+  }
+  const uint32_t ex = mb >> 23;
+  if (ex < 29 || ex > 254) { encode_block_1d_rate<BITS>(f, t.etab, w); return; }
+  const float scale = bits_f32((283u - ex) << 23);           // 2^(30 - emax), emax = ex - 126
+  const float p0 = scale * f[0], p1 = scale * f[1], p2 = scale * f[2], p3 = scale * f[3];
+  if (!(fabsf((p0 + p1) + (p2 + p3)) < 8.0e9f)) { encode_block_1d_rate<BITS>(f, t.etab, w); return; }   // a NaN member
+  int32_t q[4];
+#if defined(__CUDA_ARCH__)
+  q[0] = __float2int_rz(p0); q[1] = __float2int_rz(p1); q[2] = __float2int_rz(p2); q[3] = __float2int_rz(p3);
+#else
+  q[0] = (int32_t)p0; q[1] = (int32_t)p1; q[2] = (int32_t)p2; q[3] = (int32_t)p3;
+#endif
+  fwd_lift(q[0], q[1], q[2], q[3]);
+  uint32_t u[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) u[i] = int2nb(q[i]);
+  const uint32_t mm = u[0] | u[1] | u[2] | u[3];
+  uint32_t z = mm ? clz32(mm) : 32u;
+  if (z > 24) z = 24;                                         // further zero planes go through the table (one 0 bit each)
+  const uint32_t sh = 24 - z;
+  const uint32_t R = (u[0] >> sh) | ((u[1] >> sh) << 8) | ((u[2] >> sh) << 16) | ((u[3] >> sh) << 24);
+  BitBuf<NW> buf;
+  buf.clear();
+  buf.put(0, 2u * ex + 3u);                                   // flag bit + biased exponent (emax + 127 = ex + 1)
+  uint32_t S = (kHeaderBits + z) << 16;                       // [junk:16 | position:8 | n:8]
+  constexpr int kPairs = BITS == 16 ? 2 : 4;                  // 16-bit blocks: four planes always exceed 7 payload bits
+#pragma unroll
+  for (int j = 0; j < kPairs; j++) {
+    const uint32_t x = (R >> (6 - 2 * j)) & 0x03030303u;
+    const uint32_t g = (x * 0x40100401u) >> 24;               // the four 2-bit fields side by side
+    const uint32_t e = t.epair[(S >> 24) * 256u + g];
+    buf.put((S >> 16) & 0xffu, e & 0x3fffu);
+    S += e;
+  }
+  uint32_t pos = (S >> 16) & 0xffu, n = S >> 24, k = 32 - z - 2 * kPairs;
+  if (NW > 1) {
+    // the remaining planes are verbatim nibbles once n >= 3
+    while (n >= 3 && pos < (uint32_t)BITS && k > 0) {
+      buf.put(pos, plane_group8(u, k));
+      const uint32_t cnt = k < 8 ? k : 8;
+      pos += 4 * cnt;
+      k -= cnt;
+    }
+  }
+  if (pos < (uint32_t)BITS && k > 0) { encode_block_1d_rate<BITS>(f, t.etab, w); return; }   // very smooth block
+  buf.store(w);
+  if (BITS < 32 * NW) w[NW - 1] &= low_mask32(BITS - 32 * (NW - 1));
+}
+
+template <int BITS>
+GCOW_HD void decode_block_1d_lean(float* f, const LeanTables& t, const uint32_t (&w)[(BITS + 31) / 32],
+                                  int shift = 0) {
+  constexpr int NW = (BITS + 31) / 32;
+  if (!(w[0] & 1u)) {
+    f[0] = f[1] = f[2] = f[3] = 0;
+    return;
+  }
+  const int emax = (int)((w[0] >> 1) & 0xffu) - kEBias;
+  BitBuf<NW> buf;
+  buf.load(w);
+  constexpr uint32_t end = BITS;
+  uint32_t pos = kHeaderBits, n = 0, j4 = 0, T = 0;
+  {  // leading all-zero planes: one 0 bit each
+    const uint32_t avail = end - pos;
+    const uint32_t S = buf.peek(pos) & low_mask32(avail);
+    uint32_t z = S ? (uint32_t)ctz32(S) : 32u;
+    if (z > avail) z = avail;
+    pos += z;
+  }
+  const uint32_t ktop = 32 - (pos - kHeaderBits);             // planes ktop-1 .. 0 remain
+  // planes with n < 3: one budget-aware lookup each (at most eight of them here)
+  while (n < 3 && pos < end && j4 < 32 && j4 < 4 * ktop) {
+    const uint32_t avail = end - pos;
+    const uint32_t a = avail < 7 ? avail : 7;
+    const uint32_t e = t.dtab[((n * 8 + a) << 7) + (buf.peek(pos) & 127u)];   // bits past the block's end read as 0
+    T |= (e & 15u) << j4;
+    pos += (e >> 4) & 7u;
+    n = e >> 7;
+    j4 += 4;
+  }
+  if (n < 3 && pos < end && j4 < 4 * ktop) { decode_block_1d_rate<BITS>(f, t.dtab, w, shift); return; }   // very smooth block
+  uint32_t u[4] = {0, 0, 0, 0};
+  uint32_t k = ktop;
+  if (NW == 1) {
+    // the rest of the block is verbatim nibbles: at most 16 planes in all, two transposed words
+    const uint32_t tail = buf.peek(pos);
+    T |= shl_sat(tail, j4);
+    const uint32_t T1 = j4 ? shr_sat(tail, 32 - j4) : 0u;
+    deposit_group8(u, T, k);
+    if (T1 && k > 8) deposit_group8(u, T1, k - 8);
+  } else {
+    if (T) deposit_group8(u, T, k);
+    k -= j4 >> 2;
+    while (pos < end && k > 0) {
+      deposit_group8(u, buf.peek(pos), k);           // bits past the block's end read as 0
+      pos += 32;
+      k = k > 8 ? k - 8 : 0;
+    }
+  }
+  int32_t q[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) q[i] = nb2int(u[i]);
+  inv_lift(q[0], q[1], q[2], q[3]);
+  inv_cast<4>(f, q, emax, shift);
+}
+
+// Host-side construction of the pair table.
+inline void build_pair_table(uint32_t* epair) {
+  for (uint32_t i = 0; i < (uint32_t)kEncPairTabSize; i++) epair[i] = make_enc_pair_entry(i >> 8, i & 255u);
 }
 
 }  // namespace gcow

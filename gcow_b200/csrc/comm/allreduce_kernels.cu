@@ -47,8 +47,9 @@ struct ArArgs {
   uint32_t* status;           // 8 words, see record_failure
   uint32_t* abort_flag;       // local device word
   unsigned long long* stamps; // optional [gridDim.x][4] globaltimer stamps, or nullptr
-  const uint16_t* enc_table;  // coder tables in global memory (see gcow_codec_tables)
+  const uint16_t* enc_table;  // coder tables in global memory (see gcow_codec_tables3)
   const uint16_t* dec_table;
+  const uint32_t* pair_table;
   ArLayout L;
 };
 
@@ -186,19 +187,23 @@ __device__ __forceinline__ void stamp(const ArArgs& a, int slot) {
 }
 
 template <int BITS>
-__global__ void __launch_bounds__(kArThreads, 8)
+__global__ void __launch_bounds__(kArThreads, 6)
 allreduce_fused_kernel(const ArArgs a) {
   using C = Code<BITS>;
   constexpr int NW = C::NW;
   __shared__ __align__(16) uint16_t etab[kEncTabSize];
   __shared__ __align__(16) uint16_t dtab[kDecBudgetTabSize];
+  __shared__ __align__(16) uint32_t epair[kEncPairTabSize];
   __shared__ int s_ok;
   for (int i = threadIdx.x; i < kEncTabSize / 2; i += blockDim.x)
     reinterpret_cast<uint32_t*>(etab)[i] = reinterpret_cast<const uint32_t*>(a.enc_table)[i];
   for (int i = threadIdx.x; i < kDecBudgetTabSize / 8; i += blockDim.x)
     reinterpret_cast<uint4*>(dtab)[i] = reinterpret_cast<const uint4*>(a.dec_table)[i];
+  for (int i = threadIdx.x; i < kEncPairTabSize / 4; i += blockDim.x)
+    reinterpret_cast<uint4*>(epair)[i] = reinterpret_cast<const uint4*>(a.pair_table)[i];
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
+  const LeanTables lt = {etab, dtab, epair};
 
   const int P = a.world, r = a.rank, cta = blockIdx.x, tid = threadIdx.x;
   const ArLayout& L = a.L;
@@ -227,7 +232,7 @@ allreduce_fused_kernel(const ArArgs a) {
         float f[4];
         load_block(f, a.in, a.n, gb, in_al);
         uint32_t w[NW];
-        encode_block_1d_rate<BITS>(f, etab, w);
+        encode_block_1d_lean<BITS>(f, lt, w);
         for (int step = 0; step < P; step++) {
           int j = (r + 1 + step) % P;
           C::st(a.arena[j] + a.region_off + (uint64_t)r * L.slot_bytes, gb, w);
@@ -257,7 +262,7 @@ allreduce_fused_kernel(const ArArgs a) {
           uint32_t w[NW];
           C::ld(local + a.region_off + (uint64_t)s * L.slot_bytes, gb, w);
           float d[4];
-          decode_block_1d_rate<BITS>(d, dtab, w, 0);
+          decode_block_1d_lean<BITS>(d, lt, w, 0);
           if (s == 0) { acc[0] = d[0]; acc[1] = d[1]; acc[2] = d[2]; acc[3] = d[3]; }
           else { acc[0] += d[0]; acc[1] += d[1]; acc[2] += d[2]; acc[3] += d[3]; }
         }
@@ -282,7 +287,7 @@ allreduce_fused_kernel(const ArArgs a) {
       float f[4];
       load_block(f, a.in, a.n, gb, in_al);
       uint32_t w[NW];
-      encode_block_1d_rate<BITS>(f, etab, w);
+      encode_block_1d_lean<BITS>(f, lt, w);
       C::st(dst, b, w);
     }
   }
@@ -315,11 +320,11 @@ allreduce_fused_kernel(const ArArgs a) {
           uint32_t c[NW];
           C::ld(local + a.region_off + (uint64_t)s * L.slot_bytes, b, c);
           float d[4];
-          decode_block_1d_rate<BITS>(d, dtab, c, 0);
+          decode_block_1d_lean<BITS>(d, lt, c, 0);
           if (s == 0) { acc[0] = d[0]; acc[1] = d[1]; acc[2] = d[2]; acc[3] = d[3]; }
           else { acc[0] += d[0]; acc[1] += d[1]; acc[2] += d[2]; acc[3] += d[3]; }
         }
-        encode_block_1d_rate<BITS>(acc, etab, w);
+        encode_block_1d_lean<BITS>(acc, lt, w);
       }
       if (a.variant == kTwoShotNvls) {
         if (BITS == 16) {
@@ -368,7 +373,7 @@ allreduce_fused_kernel(const ArArgs a) {
       uint32_t w[NW];
       C::ld(src, b, w);
       float d[4];
-      decode_block_1d_rate<BITS>(d, dtab, w, a.shift);
+      decode_block_1d_lean<BITS>(d, lt, w, a.shift);
       if (a.postscale != 1.0f) {
 #pragma unroll
         for (int i = 0; i < 4; i++) d[i] *= a.postscale;
@@ -414,7 +419,7 @@ int max_coresident_ctas(int device) {
 
 using namespace gcow;
 
-extern "C" int gcow_codec_tables(const void** etab, const void** dtab);
+extern "C" int gcow_codec_tables3(const void** etab, const void** dtab, const void** epair);
 
 extern "C" {
 
@@ -464,10 +469,11 @@ int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world,
   a.status = status; a.abort_flag = abort_flag; a.stamps = stamps;
   a.L = ar_layout(n, world, ctas, bits, variant);
   if (a.L.region_bytes > region_cap) return -2;
-  const void *etp, *dtp;
-  if (int rc = gcow_codec_tables(&etp, &dtp)) return rc;
+  const void *etp, *dtp, *ptp;
+  if (int rc = gcow_codec_tables3(&etp, &dtp, &ptp)) return rc;
   a.enc_table = (const uint16_t*)etp;
   a.dec_table = (const uint16_t*)dtp;
+  a.pair_table = (const uint32_t*)ptp;
   if (n == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   switch (bits) {

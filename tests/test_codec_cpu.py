@@ -255,6 +255,44 @@ def test_fast1d_matches_oracle(rate):
             assert np.array_equal(ref.view(np.uint32), got.view(np.uint32))
 
 
+def _smooth_and_odd_1d():
+    """Inputs that leave the warp-uniform fast path: smooth ramps and constants (the significance count stays
+    below 3 for many planes), blocks whose members differ by many orders of magnitude, non-finite members, values
+    below the cast's scale range and an all-tiny block whose coefficients have more than 24 leading zero planes."""
+    rng = np.random.default_rng(11)
+    parts = [np.linspace(-1.0, 1.0, 4096, dtype=np.float32),                        # ramp
+             np.full(256, 0.3337, dtype=np.float32),                                # constant
+             np.sin(np.arange(4096, dtype=np.float32) * 1e-3),                      # very smooth
+             (rng.standard_normal(4096) * np.repeat(10.0 ** rng.integers(-12, 3, 1024), 4)).astype(np.float32),
+             (rng.standard_normal(4096) * 10.0 ** rng.integers(-9, 1, 4096)).astype(np.float32),   # mixed within blocks
+             np.array([1.0, 0, 0, 0, 0, 1.0, 0, 0, 0, 0, 1.0, 0, 0, 0, 0, 1.0], dtype=np.float32),
+             np.array([1.0, 1.0, 1e-7, -1e-7, 1.0, -1.0, 3e-8, 0.0, 5.0, 5.0, 5.0, 5.0000005], dtype=np.float32),
+             np.array([np.nan, 1.0, 2.0, 3.0, np.inf, 1.0, -1.0, 0.5, -np.inf, np.nan, 0.0, 1e-3,
+                       1e-30, 2e-31, -3e-32, 1e-33, 1e-38, 1e-39, 0.0, -1e-40, -0.0, 0.0, -0.0, 0.0], dtype=np.float32)]
+    return np.concatenate(parts)
+
+
+@pytest.mark.parametrize("rate", [4, 8, 16, 32])
+def test_lean_formulation_on_smooth_and_odd_data(rate):
+    """gcow_fast1d_compress / _decompress run the three table-driven formulations on every block and fail (-2) if
+    any two disagree; their common result must equal the serial oracle's."""
+    p = ZfpParams.from_rate(rate, 1)
+    with np.errstate(all="ignore"):
+        xs = (_smooth_and_odd_1d(), _rand(1 << 18, seed=21), (_rand(1 << 16, seed=22) * 1e3).astype(np.float32))
+    for x in xs:
+        c = g.compress(torch.from_numpy(x), params=p, dim=1)
+        blocks = (x.size + 3) // 4
+        out = np.zeros(c.nbytes + 16, dtype=np.uint8)
+        assert lib.gcow_fast1d_compress(x.ctypes.data, x.size, p.as_c(), out.ctypes.data) == 0
+        nb = blocks * p.maxbits // 8
+        assert out[:nb].tobytes() == c.stream.numpy().tobytes()[:nb]
+        ref = g.decompress(c).numpy()
+        got = np.zeros(x.size, dtype=np.float32)
+        assert lib.gcow_fast1d_decompress(out.ctypes.data, got.ctypes.data, x.size, p.as_c(), 1) == 0
+        assert np.array_equal(g.decompress(c, shift=1).numpy().view(np.uint32), got.view(np.uint32))
+        assert ref.shape == x.shape
+
+
 def test_fast1d_decoder_on_random_streams():
     # arbitrary bit patterns exercise budget exhaustion inside unary runs
     rng = np.random.default_rng(7)
@@ -266,7 +304,7 @@ def test_fast1d_decoder_on_random_streams():
         c = g.codec.Compressed(torch.from_numpy(raw.copy()), p, (n,), None)
         ref = g.decompress(c).numpy()
         got = np.zeros(n, dtype=np.float32)
-        lib.gcow_fast1d_decompress(raw.ctypes.data, got.ctypes.data, n, p.as_c(), 0)
+        assert lib.gcow_fast1d_decompress(raw.ctypes.data, got.ctypes.data, n, p.as_c(), 0) == 0
         assert np.array_equal(ref.view(np.uint32), got.view(np.uint32))
         hd = _header_decompress(raw.tobytes(), (n,), p)
         assert np.array_equal(ref.view(np.uint32), hd.view(np.uint32))
