@@ -1,0 +1,101 @@
+"""Every convolution of a ResNet, own kernels against cuDNN, layer shape by layer shape.
+
+    python -m gcow_b200.bench.conv_layers_bench [--arch resnet50] [--batch 256] [--json out.json]
+
+The distinct convolution configurations of the model (input channels, output channels, filter, stride,
+input extent) are collected with forward hooks on one forward pass; each is then timed as the model runs
+it: ``gcow_b200.ops.nn.Conv2d`` forward plus backward through autograd (forward, data gradient and weight
+gradient together, including the layout and weight-format work the module does around its kernels), once
+on the default own routing and once with every convolution sent to cuDNN (``GCOW_CONV=lib``). The
+table's last row sums ``count x time`` over the model: the convolution cost of one training step on
+either arm. The reference's models call nn.Conv2d at hw/models/resenet.py:11-17,79,113.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from collections import OrderedDict
+from pathlib import Path
+
+import torch
+
+from gcow_b200.bench.codec_bench import time_cuda
+from gcow_b200.models import MODELS
+from gcow_b200.ops import backend
+from gcow_b200.ops import nn as gnn
+
+
+def collect(arch: str, batch: int, image: int):
+    """OrderedDict {(cin, cout, k, stride, pad, h): count} of the model's convolutions."""
+    backend.set_backend("torch")
+    net = MODELS[arch]().cuda().to(memory_format=torch.channels_last).bfloat16()
+    seen: OrderedDict = OrderedDict()
+    first = []
+
+    def hook(m, inp, out):
+        x = inp[0]
+        key = (m.in_channels, m.out_channels, m.kernel_size[0], m.stride[0], m.padding[0], x.shape[2])
+        seen[key] = seen.get(key, 0) + 1
+        if not first:
+            first.append(key)
+    hs = [m.register_forward_hook(hook) for m in net.modules() if isinstance(m, gnn.Conv2d)]
+    with torch.no_grad():
+        net(torch.zeros(min(batch, 2), 3, image, image, device="cuda", dtype=torch.bfloat16)
+            .contiguous(memory_format=torch.channels_last))
+    for h in hs:
+        h.remove()
+    return seen, first[0]
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--arch", default="resnet50")
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--image", type=int, default=224)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", default="")
+    args = ap.parse_args(argv)
+    layers, stem = collect(args.arch, args.batch, args.image)
+    backend.set_backend("own")
+    rows, tot = [], {"own": 0.0, "cudnn": 0.0}
+    for (cin, cout, k, s, p, h), count in layers.items():
+        conv = gnn.Conv2d(cin, cout, k, stride=s, padding=p, bias=False).cuda().to(memory_format=torch.channels_last)
+        x = torch.randn(args.batch, cin, h, h, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+        x.requires_grad_((cin, cout, k, s, p, h) != stem)          # the stem's input needs no gradient
+        row = {"cin": cin, "cout": cout, "k": k, "stride": s, "h": h, "count": count}
+        gy = None
+        for arm, env in (("own", None), ("cudnn", "lib")):
+            if env is None:
+                os.environ.pop("GCOW_CONV", None)
+            else:
+                os.environ["GCOW_CONV"] = env
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                y = conv(x)
+            if gy is None:
+                gy = torch.randn_like(y)
+            row[f"{arm}_path"] = gnn.last_conv_path()
+
+            def step():
+                conv.weight.grad = None
+                x.grad = None
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    out = conv(x)
+                out.backward(gy)
+            ms, _ = time_cuda(step, args.iters)
+            row[f"{arm}_ms"] = round(ms, 4)
+            tot[arm] += ms * count
+        row["own_over_cudnn"] = round(row["own_ms"] / row["cudnn_ms"], 3)
+        os.environ.pop("GCOW_CONV", None)
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    summary = {"arch": args.arch, "batch": args.batch, "convolutions": sum(layers.values()),
+               "own_ms_per_step": round(tot["own"], 3), "cudnn_ms_per_step": round(tot["cudnn"], 3)}
+    print(json.dumps(summary), flush=True)
+    if args.json:
+        Path(args.json).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.json).write_text(json.dumps({"layers": rows, "summary": summary}, indent=1))
+
+
+if __name__ == "__main__":
+    main()

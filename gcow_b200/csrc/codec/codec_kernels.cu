@@ -25,6 +25,7 @@ constexpr int kThreads = 256;
 __device__ __align__(16) uint16_t g_enc_table[kEncTabSize];
 __device__ __align__(16) uint16_t g_dec_table[kDecBudgetTabSize];
 __device__ __align__(16) uint32_t g_enc_pair_table[kEncPairTabSize];
+__device__ __align__(16) uint32_t g_dec_loop_table[kDecLoopTabSize];
 
 __device__ __forceinline__ void load_enc_table(uint16_t* etab, const uint16_t* __restrict__ src) {
   for (int i = threadIdx.x; i < kEncTabSize / 2; i += blockDim.x)
@@ -38,6 +39,11 @@ __device__ __forceinline__ void load_dec_table(uint16_t* dtab, const uint16_t* _
 __device__ __forceinline__ void load_pair_table(uint32_t* epair, const uint32_t* __restrict__ src) {
   for (int i = threadIdx.x; i < kEncPairTabSize / 4; i += blockDim.x)
     reinterpret_cast<uint4*>(epair)[i] = reinterpret_cast<const uint4*>(src)[i];
+}
+
+__device__ __forceinline__ void load_loop_table(uint32_t* dloop, const uint32_t* __restrict__ src) {
+  for (int i = threadIdx.x; i < kDecLoopTabSize / 4; i += blockDim.x)
+    reinterpret_cast<uint4*>(dloop)[i] = reinterpret_cast<const uint4*>(src)[i];
 }
 
 // Load block b of a 1-D array of n floats (tail block padded).
@@ -95,12 +101,10 @@ template <int BITS>
 __global__ void __launch_bounds__(kThreads)
 encode_1d_fixed_kernel(const float* __restrict__ in, uint64_t n, void* __restrict__ out, int aligned,
                        const uint16_t* __restrict__ tab, const uint32_t* __restrict__ pair_tab) {
-  __shared__ __align__(16) uint16_t etab[kEncTabSize];
   __shared__ __align__(16) uint32_t epair[kEncPairTabSize];
-  load_enc_table(etab, tab);
   load_pair_table(epair, pair_tab);
   __syncthreads();
-  const LeanTables lt = {etab, nullptr, epair};
+  const LeanTables lt = {tab, nullptr, epair, nullptr};      // the plane-by-plane table is read from global memory (rare path)
   const uint64_t blocks = num_blocks_1d(n);
   for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
        b += (uint64_t)gridDim.x * blockDim.x) {
@@ -115,11 +119,11 @@ encode_1d_fixed_kernel(const float* __restrict__ in, uint64_t n, void* __restric
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
 decode_1d_fixed_kernel(const void* __restrict__ in, float* __restrict__ out, uint64_t n, int shift,
-                       int aligned, const uint16_t* __restrict__ tab) {
-  __shared__ __align__(16) uint16_t dtab[kDecBudgetTabSize];
-  load_dec_table(dtab, tab);
+                       int aligned, const uint16_t* __restrict__ tab, const uint32_t* __restrict__ loop_tab) {
+  __shared__ __align__(16) uint32_t dloop[kDecLoopTabSize];
+  load_loop_table(dloop, loop_tab);
   __syncthreads();
-  const LeanTables lt = {nullptr, dtab, nullptr};
+  const LeanTables lt = {nullptr, tab, nullptr, dloop};      // the plane-by-plane table is read from global memory (rare path)
   const uint64_t blocks = num_blocks_1d(n);
   for (uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks;
        b += (uint64_t)gridDim.x * blockDim.x) {
@@ -486,20 +490,26 @@ extern "C" {
 // Device pointers of the coder tables on the current device; the tables are
 // built on the host and uploaded on the first call per device (a synchronous
 // copy, so make that first call outside any stream capture).
-int gcow_codec_tables3(const void** etab, const void** dtab, const void** epair) {
+int gcow_codec_tables4(const void** etab, const void** dtab, const void** epair, const void** dloop) {
   static std::mutex mu;
   static const void* e_addr[64] = {};
   static const void* d_addr[64] = {};
   static const void* p_addr[64] = {};
+  static const void* l_addr[64] = {};
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess || dev < 0 || dev >= 64) return err ? (int)err : -1;
   std::lock_guard<std::mutex> lock(mu);
   if (!e_addr[dev]) {
     static uint16_t he[kEncTabSize], hd[kDecBudgetTabSize];
-    static uint32_t hp[kEncPairTabSize];
+    static uint32_t hp[kEncPairTabSize], hl[kDecLoopTabSize];
     build_codec_tables(he, hd);
     build_pair_table(hp);
+    build_dec_loop_table(hl);
+    if ((err = cudaMemcpyToSymbol(g_dec_loop_table, hl, sizeof hl)) != cudaSuccess) return (int)err;
+    void* pl = nullptr;
+    if ((err = cudaGetSymbolAddress(&pl, g_dec_loop_table)) != cudaSuccess) return (int)err;
+    l_addr[dev] = pl;
     if ((err = cudaMemcpyToSymbol(g_enc_table, he, sizeof he)) != cudaSuccess) return (int)err;
     if ((err = cudaMemcpyToSymbol(g_dec_table, hd, sizeof hd)) != cudaSuccess) return (int)err;
     if ((err = cudaMemcpyToSymbol(g_enc_pair_table, hp, sizeof hp)) != cudaSuccess) return (int)err;
@@ -514,12 +524,13 @@ int gcow_codec_tables3(const void** etab, const void** dtab, const void** epair)
   *etab = e_addr[dev];
   *dtab = d_addr[dev];
   *epair = p_addr[dev];
+  *dloop = l_addr[dev];
   return 0;
 }
 
 int gcow_codec_tables(const void** etab, const void** dtab) {
-  const void* pair;
-  return gcow_codec_tables3(etab, dtab, &pair);
+  const void *pair, *loop;
+  return gcow_codec_tables4(etab, dtab, &pair, &loop);
 }
 
 // Fixed-rate 1-D encode; maxbits in {16, 32, 64, 128}. `out` holds
@@ -530,8 +541,8 @@ int gcow_encode_1d_fixed(const float* in, uint64_t n, int maxbits, void* out, vo
   if (!blocks) return 0;
   int aligned = ((uintptr_t)in & 15) == 0;
   int g = grid_for(blocks);
-  const void *etp, *dtp, *ptp;
-  if (int rc = gcow_codec_tables3(&etp, &dtp, &ptp)) return rc;
+  const void *etp, *dtp, *ptp, *ltp;
+  if (int rc = gcow_codec_tables4(&etp, &dtp, &ptp, &ltp)) return rc;
   const uint16_t* et = (const uint16_t*)etp;
   const uint32_t* pt = (const uint32_t*)ptp;
   switch (maxbits) {
@@ -550,14 +561,15 @@ int gcow_decode_1d_fixed(const void* in, float* out, uint64_t n, int maxbits, in
   if (!blocks) return 0;
   int aligned = ((uintptr_t)out & 15) == 0;
   int g = grid_for(blocks);
-  const void *etp, *dtp;
-  if (int rc = gcow_codec_tables(&etp, &dtp)) return rc;
+  const void *etp, *dtp, *ptp, *ltp;
+  if (int rc = gcow_codec_tables4(&etp, &dtp, &ptp, &ltp)) return rc;
+  const uint32_t* lt = (const uint32_t*)ltp;
   const uint16_t* dt = (const uint16_t*)dtp;
   switch (maxbits) {
-    case 16: decode_1d_fixed_kernel<16><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt); break;
-    case 32: decode_1d_fixed_kernel<32><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt); break;
-    case 64: decode_1d_fixed_kernel<64><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt); break;
-    case 128: decode_1d_fixed_kernel<128><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt); break;
+    case 16: decode_1d_fixed_kernel<16><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt, lt); break;
+    case 32: decode_1d_fixed_kernel<32><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt, lt); break;
+    case 64: decode_1d_fixed_kernel<64><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt, lt); break;
+    case 128: decode_1d_fixed_kernel<128><<<g, kThreads, 0, s>>>(in, out, n, shift, aligned, dt, lt); break;
     default: return -1;
   }
   return (int)cudaGetLastError();

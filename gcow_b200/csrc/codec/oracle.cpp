@@ -440,12 +440,14 @@ uint64_t gcow_header_decompress(const uint64_t* in, float* data, uint64_t nx, ui
 namespace {
 struct HostLeanTables {
   std::vector<uint16_t> etab, btab;
-  std::vector<uint32_t> epair;
+  std::vector<uint32_t> epair, dloop;
   gcow::LeanTables t;
-  HostLeanTables() : etab(gcow::kEncTabSize), btab(gcow::kDecBudgetTabSize), epair(gcow::kEncPairTabSize) {
+  HostLeanTables() : etab(gcow::kEncTabSize), btab(gcow::kDecBudgetTabSize), epair(gcow::kEncPairTabSize),
+                     dloop(gcow::kDecLoopTabSize) {
     gcow::build_codec_tables(etab.data(), btab.data());
     gcow::build_pair_table(epair.data());
-    t.etab = etab.data(); t.dtab = btab.data(); t.epair = epair.data();
+    gcow::build_dec_loop_table(dloop.data());
+    t.etab = etab.data(); t.dtab = btab.data(); t.epair = epair.data(); t.dloop = dloop.data();
   }
 };
 const gcow::LeanTables& host_lean_tables() {

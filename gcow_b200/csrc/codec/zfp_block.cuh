@@ -883,10 +883,29 @@ template <> struct BitBuf<4> {
   }
 };
 
+// Decoder loop table: one plane per lookup while fewer than three coefficients are significant.
+// Byte offset n * 4096 + a * 512 + peek * 4 (n = 0..2, a = remaining budget capped at 7, peek = next 7
+// stream bits). Entry: plane nibble | bits used << 8 | (n' * 4096) << 16 - the last field is the row
+// offset of the next lookup, and n' >= 3 ends the loop.
+constexpr int kDecLoopTabSize = 3 * 8 * 128;
+GCOW_HD uint32_t make_dec_loop_entry(uint32_t n, uint32_t a, uint32_t peek) {
+  const uint32_t e = make_dec_budget_entry(n, a, peek & low_mask32(a));      // plane | used << 4 | n' << 7
+  return (e & 15u) | (((e >> 4) & 7u) << 8) | ((e >> 7) << 28);
+}
+
+GCOW_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, uint32_t s) {   // low word of (hi:lo) >> s, 0 < s < 32
+#if defined(__CUDA_ARCH__)
+  return __funnelshift_r(lo, hi, s);
+#else
+  return (lo >> s) | (hi << (32 - s));
+#endif
+}
+
 struct LeanTables {
-  const uint16_t* etab;    // kEncTabSize: one plane per lookup (definition path)
-  const uint16_t* dtab;    // kDecBudgetTabSize: budget-aware, one plane per lookup
+  const uint16_t* etab;    // kEncTabSize: one plane per lookup (definition path; rarely used, may be global memory)
+  const uint16_t* dtab;    // kDecBudgetTabSize: budget-aware, one plane per lookup (definition path, likewise)
   const uint32_t* epair;   // kEncPairTabSize: two planes per lookup
+  const uint32_t* dloop;   // kDecLoopTabSize: decoder loop while n < 3
 };
 
 template <int BITS>
@@ -955,30 +974,33 @@ GCOW_HD void decode_block_1d_lean(float* f, const LeanTables& t, const uint32_t 
     f[0] = f[1] = f[2] = f[3] = 0;
     return;
   }
-  const int emax = (int)((w[0] >> 1) & 0xffu) - kEBias;
+  const uint32_t e8 = (w[0] >> 1) & 0xffu;                     // biased exponent, emax + 127
   BitBuf<NW> buf;
   buf.load(w);
   constexpr uint32_t end = BITS;
-  uint32_t pos = kHeaderBits, n = 0, j4 = 0, T = 0;
-  {  // leading all-zero planes: one 0 bit each
-    const uint32_t avail = end - pos;
-    const uint32_t S = buf.peek(pos) & low_mask32(avail);
-    uint32_t z = S ? (uint32_t)ctz32(S) : 32u;
-    if (z > avail) z = avail;
-    pos += z;
-  }
-  const uint32_t ktop = 32 - (pos - kHeaderBits);             // planes ktop-1 .. 0 remain
-  // planes with n < 3: one budget-aware lookup each (at most eight of them here)
-  while (n < 3 && pos < end && j4 < 32 && j4 < 4 * ktop) {
+  // leading all-zero planes: one 0 bit each; a sentinel bit ends the count at the budget (or at 32 planes)
+  constexpr uint32_t kPayload = end - kHeaderBits;
+  const uint32_t lead = buf.peek(kHeaderBits);
+  const uint32_t z = kPayload < 32 ? (uint32_t)ctz32(lead | (1u << (kPayload < 32 ? kPayload : 0)))
+                                   : (lead ? (uint32_t)ctz32(lead) : 32u);
+  uint32_t pos = kHeaderBits + z;
+  const uint32_t ktop = 32 - z;                                // planes ktop-1 .. 0 remain
+  // planes with n < 3: one budget-aware lookup each, at most eight of them here
+  uint32_t nrow = 0, j4 = 0, T = 0;                            // nrow = n * 4096, the table row's byte offset
+#pragma unroll
+  for (int c = 0; c < 8; c++) {
+    if (!(nrow < 3u * 4096u && pos < end && (NW == 1 || (uint32_t)c < ktop))) break;
     const uint32_t avail = end - pos;
     const uint32_t a = avail < 7 ? avail : 7;
-    const uint32_t e = t.dtab[((n * 8 + a) << 7) + (buf.peek(pos) & 127u)];   // bits past the block's end read as 0
-    T |= (e & 15u) << j4;
-    pos += (e >> 4) & 7u;
-    n = e >> 7;
+    const uint32_t pk = buf.peek(pos) & 127u;                  // bits past the block's end read as 0
+    const uint32_t e = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(t.dloop) + nrow + a * 512u + pk * 4u);
+    T = funnel_r(T, e, 4);                                     // newest plane enters at the top nibble
+    pos += (e >> 8) & 0xffu;
+    nrow = e >> 16;
     j4 += 4;
   }
-  if (n < 3 && pos < end && j4 < 4 * ktop) { decode_block_1d_rate<BITS>(f, t.dtab, w, shift); return; }   // very smooth block
+  if (nrow < 3u * 4096u && pos < end && j4 < 4 * ktop) { decode_block_1d_rate<BITS>(f, t.dtab, w, shift); return; }   // very smooth block
+  T = shr_sat(T, 32 - j4);                                     // first plane in the low nibble
   uint32_t u[4] = {0, 0, 0, 0};
   uint32_t k = ktop;
   if (NW == 1) {
@@ -1001,12 +1023,19 @@ GCOW_HD void decode_block_1d_lean(float* f, const LeanTables& t, const uint32_t 
 #pragma unroll
   for (int i = 0; i < 4; i++) q[i] = nb2int(u[i]);
   inv_lift(q[0], q[1], q[2], q[3]);
-  inv_cast<4>(f, q, emax, shift);
+  // 2^(emax - 30 - shift): a normal float unless the block is tiny
+  const int ef = (int)e8 - 30 - shift;
+  const float scale = (ef >= 1 && ef <= 254) ? bits_f32((uint32_t)ef << 23) : pow2f((int)e8 - kEBias - 30 - shift);
+#pragma unroll
+  for (int i = 0; i < 4; i++) f[i] = scale * (float)q[i];
 }
 
 // Host-side construction of the pair table.
 inline void build_pair_table(uint32_t* epair) {
   for (uint32_t i = 0; i < (uint32_t)kEncPairTabSize; i++) epair[i] = make_enc_pair_entry(i >> 8, i & 255u);
+}
+inline void build_dec_loop_table(uint32_t* dloop) {
+  for (uint32_t i = 0; i < (uint32_t)kDecLoopTabSize; i++) dloop[i] = make_dec_loop_entry(i >> 10, (i >> 7) & 7u, i & 127u);
 }
 
 }  // namespace gcow

@@ -50,6 +50,7 @@ struct ArArgs {
   const uint16_t* enc_table;  // coder tables in global memory (see gcow_codec_tables3)
   const uint16_t* dec_table;
   const uint32_t* pair_table;
+  const uint32_t* loop_table;
   ArLayout L;
 };
 
@@ -191,19 +192,17 @@ __global__ void __launch_bounds__(kArThreads, 6)
 allreduce_fused_kernel(const ArArgs a) {
   using C = Code<BITS>;
   constexpr int NW = C::NW;
-  __shared__ __align__(16) uint16_t etab[kEncTabSize];
-  __shared__ __align__(16) uint16_t dtab[kDecBudgetTabSize];
   __shared__ __align__(16) uint32_t epair[kEncPairTabSize];
+  __shared__ __align__(16) uint32_t dloop[kDecLoopTabSize];
   __shared__ int s_ok;
-  for (int i = threadIdx.x; i < kEncTabSize / 2; i += blockDim.x)
-    reinterpret_cast<uint32_t*>(etab)[i] = reinterpret_cast<const uint32_t*>(a.enc_table)[i];
-  for (int i = threadIdx.x; i < kDecBudgetTabSize / 8; i += blockDim.x)
-    reinterpret_cast<uint4*>(dtab)[i] = reinterpret_cast<const uint4*>(a.dec_table)[i];
+  for (int i = threadIdx.x; i < kDecLoopTabSize / 4; i += blockDim.x)
+    reinterpret_cast<uint4*>(dloop)[i] = reinterpret_cast<const uint4*>(a.loop_table)[i];
   for (int i = threadIdx.x; i < kEncPairTabSize / 4; i += blockDim.x)
     reinterpret_cast<uint4*>(epair)[i] = reinterpret_cast<const uint4*>(a.pair_table)[i];
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
-  const LeanTables lt = {etab, dtab, epair};
+  // the plane-by-plane tables serve the rare blocks that leave the fast path and stay in global memory
+  const LeanTables lt = {a.enc_table, a.dec_table, epair, dloop};
 
   const int P = a.world, r = a.rank, cta = blockIdx.x, tid = threadIdx.x;
   const ArLayout& L = a.L;
@@ -419,7 +418,7 @@ int max_coresident_ctas(int device) {
 
 using namespace gcow;
 
-extern "C" int gcow_codec_tables3(const void** etab, const void** dtab, const void** epair);
+extern "C" int gcow_codec_tables4(const void** etab, const void** dtab, const void** epair, const void** dloop);
 
 extern "C" {
 
@@ -469,11 +468,12 @@ int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world,
   a.status = status; a.abort_flag = abort_flag; a.stamps = stamps;
   a.L = ar_layout(n, world, ctas, bits, variant);
   if (a.L.region_bytes > region_cap) return -2;
-  const void *etp, *dtp, *ptp;
-  if (int rc = gcow_codec_tables3(&etp, &dtp, &ptp)) return rc;
+  const void *etp, *dtp, *ptp, *ltp;
+  if (int rc = gcow_codec_tables4(&etp, &dtp, &ptp, &ltp)) return rc;
   a.enc_table = (const uint16_t*)etp;
   a.dec_table = (const uint16_t*)dtp;
   a.pair_table = (const uint32_t*)ptp;
+  a.loop_table = (const uint32_t*)ltp;
   if (n == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   switch (bits) {

@@ -74,6 +74,35 @@ __global__ void col2im_kernel(const bf16* __restrict__ dcol, bf16* __restrict__ 
   }
 }
 
+// Patch matrix for an input whose channel count is not a multiple of 8 (the 3-channel image in front of
+// the stem): row length Kp >= KH*KW*C is a multiple of 8, element kk of a row is tap kk / C, channel kk % C,
+// columns past KH*KW*C are zero. One thread gathers eight elements and stores them as 16 bytes.
+__global__ void im2col_anyc_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, Geo g, int Kp) {
+  const int groups = Kp / 8, K = g.KH * g.KW * g.C;
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * groups;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int k0 = (int)(t % groups) * 8;
+    int64_t p = t / groups;
+    const int ow = (int)(p % g.OW); p /= g.OW;
+    const int oh = (int)(p % g.OH);
+    const int n = (int)(p / g.OH);
+    const int h0 = oh * g.stride - g.pad, w0 = ow * g.stride - g.pad;
+    __align__(16) bf16 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int kk = k0 + i;
+      bf16 e = __float2bfloat16(0.0f);
+      if (kk < K) {
+        const int tap = kk / g.C, c = kk - tap * g.C;
+        const int ih = h0 + tap / g.KW, iw = w0 + tap % g.KW;
+        if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) e = x[(((int64_t)n * g.H + ih) * g.W + iw) * g.C + c];
+      }
+      v[i] = e;
+    }
+    *reinterpret_cast<uint4*>(col + t * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
 inline int grid1d(int64_t items) { int64_t b = (items + 255) / 256; return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b)); }
 
 }  // namespace conv
@@ -88,6 +117,16 @@ int gcow_im2col(const void* x, void* col, int N, int H, int W, int C, int KH, in
   Geo g{N, H, W, C, KH, KW, stride, pad, (H + 2 * pad - KH) / stride + 1, (W + 2 * pad - KW) / stride + 1};
   const int64_t total = (int64_t)N * g.OH * g.OW * KH * KW * (C / 8);
   im2col_kernel<<<grid1d(total), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)col, g);
+  return (int)cudaGetLastError();
+}
+
+// Any channel count; `Kp` (row length of col) is a multiple of 8 and at least KH*KW*C.
+int gcow_im2col_anyc(const void* x, void* col, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Kp,
+                     void* stream) {
+  if (Kp % 8 || Kp < KH * KW * C || stride < 1) return -1;
+  Geo g{N, H, W, C, KH, KW, stride, pad, (H + 2 * pad - KH) / stride + 1, (W + 2 * pad - KW) / stride + 1};
+  const int64_t total = (int64_t)N * g.OH * g.OW * (Kp / 8);
+  im2col_anyc_kernel<<<grid1d(total), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)col, g, Kp);
   return (int)cudaGetLastError();
 }
 

@@ -27,6 +27,7 @@
 //
 // Replaces the cuBLAS GEMMs behind nn.Linear / 1x1 convolutions in the
 // reference's models (hw/models/resenet.py:11,17,90).
+#include <stdio.h>
 #include <stdlib.h>
 #include <mutex>
 
@@ -358,6 +359,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // ------------------------------------------------------------------- host side
 static EncodeTiledFn encode_fn() { return encode_tiled_fn(); }
 
+// Says on stderr why a tensor map was refused (the launcher then returns -12): rank, extents, strides and box.
+static int map_refused(CUresult r, int rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
+  fprintf(stderr, "gcow gemm: cuTensorMapEncodeTiled failed with CUresult %d; rank %d, dims", (int)r, rank);
+  for (int i = 0; i < rank; i++) fprintf(stderr, " %llu", (unsigned long long)dims[i]);
+  fprintf(stderr, ", byte strides");
+  for (int i = 0; i + 1 < rank; i++) fprintf(stderr, " %llu", (unsigned long long)strides[i]);
+  fprintf(stderr, ", box");
+  for (int i = 0; i < rank; i++) fprintf(stderr, " %u", (unsigned)box[i]);
+  fprintf(stderr, "\n");
+  return -12;
+}
+
 // 2-D bf16 row-major [rows, cols] with leading dimension ld (elements); box = 64 columns x box_rows.
 static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -370,7 +383,7 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t c
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
+  return r == CUDA_SUCCESS ? 0 : map_refused(r, 2, dims, strides, box);
 }
 
 // 3-D variant: `batch` matrices, `bstride` elements apart; box = 64 columns x box_rows x 1.
@@ -386,7 +399,7 @@ static int make_map3(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t 
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
+  return r == CUDA_SUCCESS ? 0 : map_refused(r, 3, dims, strides, box);
 }
 
 // MN-major matrix [K][cols] (cols a multiple of 64) as {64, K, cols / 64 (, batch)}; box = 64 x 64 x chunks.
@@ -403,7 +416,7 @@ static int make_map_mn(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t c
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
+  return r == CUDA_SUCCESS ? 0 : map_refused(r, (int)rank, dims, strides, box);
 }
 
 template <int BM_> constexpr size_t smem_bytes() {

@@ -6,4 +6,7 @@ MODELS = {
     "resnet152": resnet152, "bert_large": bert_large, "bert_base": bert_base, "bert_tiny": bert_tiny,
 }
 
-__all__ = ["MODELS", "ResNet", "BertConfig", "BertForPreTraining"] + list(MODELS)
+from .zoo import build_model, swap_layers, torchvision_names  # noqa: E402
+
+__all__ = ["MODELS", "ResNet", "BertConfig", "BertForPreTraining", "build_model", "swap_layers",
+           "torchvision_names"] + list(MODELS)

@@ -375,15 +375,6 @@ class _Conv1x1Fn(torch.autograd.Function):
         return gx, gw, gb
 
 
-def conv1x1_enabled() -> bool:
-    """1x1 convolutions go through the tcgen05 GEMM only on request (GCOW_CONV1X1=own). They are products with a
-    short reduction and a large output, i.e. bound by memory; measured on ResNet-50 the own path costs 35.7 ms per
-    step against 29.2 ms with cuDNN (forward product 200704 x 256 x 64: 58 us against 38 us), so cuDNN stays the
-    default."""
-    import os
-    return os.environ.get("GCOW_CONV1X1", "lib") == "own"
-
-
 def conv1x1_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
     if not (x.is_cuda and x.dim() == 4 and _have("gcow_gemm_bf16")):
         return False
@@ -720,10 +711,19 @@ class _ConvGemmFn(torch.autograd.Function):
         lib = _native.cuda()
         if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
             x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
-        col = torch.empty((N * OH * OW, KH * KW * C), dtype=torch.bfloat16, device=x.device)
-        _chk(lib.gcow_im2col(x.data_ptr(), col.data_ptr(), N, H, W, C, KH, KW, stride, pad, _stream(x.device)), "gcow_im2col")
+        K = KH * KW * C
+        Kp = (K + 7) // 8 * 8          # row length of the patch matrix: a multiple of 8 (16-byte rows for TMA)
+        col = torch.empty((N * OH * OW, Kp), dtype=torch.bfloat16, device=x.device)
+        if C % 8 == 0:
+            _chk(lib.gcow_im2col(x.data_ptr(), col.data_ptr(), N, H, W, C, KH, KW, stride, pad, _stream(x.device)), "gcow_im2col")
+        else:                          # e.g. the 3-channel image in front of the stem; padded columns are zero
+            _chk(lib.gcow_im2col_anyc(x.data_ptr(), col.data_ptr(), N, H, W, C, KH, KW, stride, pad, Kp, _stream(x.device)),
+                 "gcow_im2col_anyc")
         _launches += 1
-        wr = w.permute(0, 2, 3, 1).reshape(Co, KH * KW * C).to(torch.bfloat16).contiguous()      # [Co, (kh,kw,c)]
+        wr = w.permute(0, 2, 3, 1).reshape(Co, K).to(torch.bfloat16)                             # [Co, (kh,kw,c)]
+        if Kp != K:
+            wr = torch.nn.functional.pad(wr, (0, Kp - K))
+        wr = wr.contiguous()
         y = gemm_bf16(col, wr, bias=b.float().contiguous() if b is not None else None)
         ctx.save_for_backward(col, wr)
         ctx.meta = (N, C, H, W, Co, KH, KW, OH, OW, stride, pad, w.dtype, b is not None)
@@ -739,31 +739,33 @@ class _ConvGemmFn(torch.autograd.Function):
             g = g.to(torch.bfloat16).contiguous()
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
+            if C % 8:
+                raise NotImplementedError("data gradient of a convolution whose input channels are not a multiple of 8")
             dcol = gemm_bf16(g, wr, b_t=True)                                   # [pixels, K]
             gx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=g.device, memory_format=torch.channels_last)
             _chk(_native.cuda().gcow_col2im(dcol.data_ptr(), gx.data_ptr(), N, H, W, C, KH, KW, stride, pad,
                                             _stream(g.device)), "gcow_col2im")
             _launches += 1
         if ctx.needs_input_grad[1]:
-            gw = wgrad_gemm(g, col)                                               # [Co, K]
-            gw = gw.view(Co, KH, KW, C).permute(0, 3, 1, 2).to(wdtype).contiguous(memory_format=torch.channels_last)
+            gw = wgrad_gemm(g, col)                                               # [Co, Kp]
+            if gw.shape[1] != KH * KW * C:
+                gw = gw[:, :KH * KW * C]
+            gw = gw.reshape(Co, KH, KW, C).permute(0, 3, 1, 2).to(wdtype).contiguous(memory_format=torch.channels_last)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)
         return gx, gw, gb, None, None
 
 
-def conv_gemm_enabled() -> bool:
-    """KxK convolutions run as own im2col + tcgen05 GEMM only on request (GCOW_CONV=own);
-    the explicit patch matrix costs KH*KW times the activation traffic, so cuDNN's
-    implicit GEMM stays the default."""
-    import os
-    return os.environ.get("GCOW_CONV", "lib") == "own"
-
-
-def conv_gemm_usable(x: torch.Tensor, w: torch.Tensor, groups: int, dilation) -> bool:
-    if not (x.is_cuda and x.dim() == 4 and _have("gcow_im2col") and groups == 1 and tuple(dilation) == (1, 1)):
+def conv_gemm_usable(x: torch.Tensor, w: torch.Tensor, stride: int, pad: int, groups: int, dilation) -> bool:
+    """im2col + GEMM covers any stride and filter size; an input whose channel count is not a multiple of 8 only
+    when no gradient flows into it (the image in front of the stem)."""
+    if not (x.is_cuda and x.dim() == 4 and _have("gcow_im2col_anyc") and groups == 1 and tuple(dilation) == (1, 1)):
         return False
-    return x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.shape[0] * x.shape[2] * x.shape[3] >= 128
+    if x.shape[1] % 8 and x.requires_grad:
+        return False
+    KH, KW = w.shape[2], w.shape[3]
+    OH, OW = (x.shape[2] + 2 * pad - KH) // stride + 1, (x.shape[3] + 2 * pad - KW) // stride + 1
+    return w.shape[0] % 8 == 0 and OH > 0 and OW > 0 and x.shape[0] * OH * OW >= 128
 
 
 def conv_gemm(x, w, b, stride, pad):
@@ -881,18 +883,53 @@ class _ConvIgemmFn(torch.autograd.Function):
         return gx, gw, gb, None, None
 
 
-def conv_igemm_mode() -> str:
-    """GCOW_CONV selects the KxK convolution path of the own backend: ``auto`` (default: implicit GEMM on the
-    tcgen05 kernel for stride-1 layers with at least 128 channels, where it is on par with cuDNN, and cuDNN for
-    the rest), ``igemm`` (implicit GEMM wherever it applies), ``own`` (im2col + GEMM, any stride) or ``lib``
-    (cuDNN everywhere)."""
+def conv_mode() -> str:
+    """GCOW_CONV selects the convolution routing of the own backend:
+    ``auto`` (default) - every convolution on this library's kernels: 1x1 layers on the tcgen05 GEMM (strided ones
+    after a pixel subsample), stride-1 KxK layers with whole 64-channel rows on the implicit-GEMM kernel, everything
+    else (strided KxK, the stem) as im2col + GEMM;
+    ``mixed`` - own kernels only where they are at least on par with cuDNN (stride-1 KxK with >= 128 channels), cuDNN
+    for the rest;
+    ``lib`` - cuDNN everywhere (the comparison arm)."""
     import os
     return os.environ.get("GCOW_CONV", "auto")
 
 
-def conv_igemm_wanted(w: torch.Tensor) -> bool:
-    mode = conv_igemm_mode()
-    return mode == "igemm" or (mode == "auto" and min(w.shape[0], w.shape[1]) >= 128)
+_conv_paths: dict = {}
+
+
+def conv_path_counts(reset: bool = False) -> dict:
+    """How many convolution calls took which path since the last reset: gemm1x1, gemm1x1_strided, igemm, im2col,
+    cudnn. Benchmarks report it; a test asserts that a ResNet-50 step sends nothing to cudnn."""
+    out = dict(_conv_paths)
+    if reset:
+        _conv_paths.clear()
+    return out
+
+
+def conv_route(x: torch.Tensor, m) -> str:
+    """Which kernel family serves this convolution call (see conv_mode)."""
+    from . import backend
+    mode = conv_mode()
+    path = "cudnn"
+    if (backend.get_backend() == "own" and mode != "lib" and m.groups == 1 and tuple(m.dilation) == (1, 1)
+            and all(isinstance(p, int) for p in m.padding) and m.stride[0] == m.stride[1]
+            and m.padding[0] == m.padding[1] and m.kernel_size[0] == m.kernel_size[1] and x.is_cuda and x.dim() == 4):
+        k, s, p, w = m.kernel_size[0], m.stride[0], m.padding[0], m.weight
+        if k == 1 and p == 0:
+            if mode == "auto":
+                oh, ow = (x.shape[2] - 1) // s + 1, (x.shape[3] - 1) // s + 1
+                rows = x.shape[0] * oh * ow
+                if (_have("gcow_gemm_bf16") and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and rows % 8 == 0 and rows >= 128
+                        and x.is_contiguous(memory_format=torch.channels_last)):
+                    path = "gemm1x1" if s == 1 else "gemm1x1_strided"
+        elif s == 1 and conv_igemm_usable(x, w, m.stride, m.padding, m.groups, m.dilation) and (
+                mode == "auto" or min(w.shape[0], w.shape[1]) >= 128):
+            path = "igemm"
+        elif mode == "auto" and conv_gemm_usable(x, w, s, p, m.groups, m.dilation):
+            path = "im2col"
+    _conv_paths[path] = _conv_paths.get(path, 0) + 1
+    return path
 
 
 def conv_igemm_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups: int, dilation) -> bool:

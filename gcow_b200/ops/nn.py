@@ -44,18 +44,30 @@ class Linear(nn.Linear):
         return linear(x, self.weight, self.bias)
 
 
+_last_conv_path = ""
+
+
+def last_conv_path() -> str:
+    """Path of the most recent Conv2d call (see kernels.conv_route); benchmarks print it per layer."""
+    return _last_conv_path
+
+
 class Conv2d(nn.Conv2d):
+    """Convolution routed to this library's kernels (kernels.conv_route): the tcgen05 GEMM for 1x1 layers, the
+    implicit-GEMM kernel for stride-1 KxK layers, im2col + GEMM for strided KxK layers and the stem; cuDNN only on
+    request (GCOW_CONV=lib / mixed) or for configurations no own kernel covers (groups, dilation, tiny inputs)."""
+
     def forward(self, x):
-        if (backend.get_backend() == "own" and self.kernel_size == (1, 1) and self.stride == (1, 1)
-                and self.padding == (0, 0) and self.groups == 1 and K.conv1x1_enabled()
-                and K.conv1x1_usable(x, self.weight)):
+        global _last_conv_path
+        path = _last_conv_path = K.conv_route(x, self)
+        if path == "gemm1x1":
             return K.conv1x1(x, self.weight, self.bias)
-        if (backend.get_backend() == "own" and K.conv_igemm_wanted(self.weight)
-                and K.conv_igemm_usable(x, self.weight, self.stride, self.padding, self.groups, self.dilation)):
+        if path == "gemm1x1_strided":
+            s = self.stride[0]          # a strided 1x1 convolution reads every s-th pixel: subsample, then the GEMM
+            return K.conv1x1(x[:, :, ::s, ::s].contiguous(memory_format=torch.channels_last), self.weight, self.bias)
+        if path == "igemm":
             return K.conv_igemm(x, self.weight, self.bias, self.padding)
-        if (backend.get_backend() == "own" and K.conv_gemm_enabled() and self.stride[0] == self.stride[1]
-                and self.padding[0] == self.padding[1] and isinstance(self.padding[0], int)
-                and K.conv_gemm_usable(x, self.weight, self.groups, self.dilation)):
+        if path == "im2col":
             return K.conv_gemm(x, self.weight, self.bias, self.stride[0], self.padding[0])
         return super().forward(x)
 

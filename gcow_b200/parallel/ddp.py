@@ -39,6 +39,8 @@ class GcowDDPState:
     pending: list = field(default_factory=list)    # (bucket buffer, side buffer) of this step (safe mode)
     timeouts: int = 0
     fallbacks: int = 0
+    timing: bool = False                           # record CUDA events around every bucket's collective
+    comm_events: list = field(default_factory=list)
 
     def begin_step(self) -> None:
         self.last_buckets.clear()
@@ -86,6 +88,14 @@ class GcowDDPState:
             for buf, side in self.pending:
                 buf.copy_(side)
 
+    def comm_seconds(self) -> float:
+        """Device time the communication stream spent in the buckets' collectives (codec and transfer are one
+        kernel here) since the last call; needs ``timing = True``. Synchronises with the communication stream."""
+        self.ar.stream.synchronize()
+        t = sum(a.elapsed_time(b) for a, b in self.comm_events) / 1e3
+        self.comm_events.clear()
+        return t
+
     def step_record(self) -> dict:
         """Metrics of the step that just finished, for the JSONL log."""
         ar = self.ar
@@ -112,6 +122,9 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
         torch.cuda.nvtx.range_push(f"gcow_allreduce bucket {bucket.index()} {buf.numel() * 4 >> 20} MB "
                                    f"{ar.pick_variant(buf.numel())}")
     with torch.cuda.stream(ar.stream):
+        if state.timing:
+            t0 = torch.cuda.Event(enable_timing=True)
+            t0.record(ar.stream)
         if state.cfg.error_feedback:
             idx = bucket.index()
             res = state.residual.get(idx)
@@ -137,6 +150,10 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
             from ..codec import compress, decompress
             kept = decompress(compress(sent, params=ar.params))
             torch.sub(sent, kept, out=state.residual[bucket.index()])
+        if state.timing and len(state.comm_events) < 100000:
+            t1 = torch.cuda.Event(enable_timing=True)
+            t1.record(ar.stream)
+            state.comm_events.append((t0, t1))
         buf.record_stream(ar.stream)
         fut = torch.futures.Future(devices=[buf.device])
         fut.set_result(buf)
@@ -163,8 +180,12 @@ def codec_roundtrip_nccl_hook(state: dict, bucket: dist.GradBucket) -> torch.fut
     ``params`` (ZfpParams) and the byte counters ``bytes_in`` / ``bytes_out``."""
     from ..codec import compress, decompress
     buf = bucket.buffer()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
     c = compress(buf, params=state["params"], dim=1, return_index=True)
     decompress(c, out=buf)
+    t1.record()
+    state.setdefault("codec_events", []).append((t0, t1))
     state["bytes_in"] += buf.numel() * 4
     state["bytes_out"] += c.nbytes
     world = dist.get_world_size()

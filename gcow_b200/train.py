@@ -29,7 +29,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 from .config import GcowConfig
-from .models import MODELS
+from .models import build_model
 from .ops import backend as ops_backend
 from .ops.optim import FusedAdamW, FusedSGD
 from .parallel.ddp import wrap_ddp
@@ -109,13 +109,15 @@ class SyntheticTokens:
 class StepResult:
     loss: Optional[float]      # loss of the PREVIOUS step (None on the first call)
     step: int
+    acc1: Optional[float] = None   # training top-1 / top-5 of the previous step in percent (with track_accuracy)
+    acc5: Optional[float] = None
 
 
 class Trainer:
     def __init__(self, model: str = "resnet50", batch_size: int = 256, cfg: GcowConfig | None = None,
                  ops: str = "own", lr: float | None = None, num_classes: int = 1000, seq_len: int = 512,
                  device: torch.device | None = None, log_path: str = "", seed: int = 0,
-                 model_kwargs: dict | None = None):
+                 model_kwargs: dict | None = None, pretrained: bool = False, track_accuracy: bool = False):
         self.device = device or torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
         torch.cuda.set_device(self.device)
         ensure_process_group(self.device)
@@ -128,7 +130,7 @@ class Trainer:
         kw = dict(model_kwargs or {})
         if self.kind == "resnet":
             kw.setdefault("num_classes", num_classes)
-        net = MODELS[model](**kw).to(self.device)
+        net = build_model(model, pretrained=pretrained, **kw).to(self.device)
         if self.kind == "resnet":
             net = net.to(memory_format=torch.channels_last)
         self.ddp, self.hook_state = wrap_ddp(net, self.cfg, self.device)
@@ -146,7 +148,12 @@ class Trainer:
         self.mean = torch.tensor(IMAGENET_MEAN, device=self.device).view(1, 3, 1, 1) * 255.0
         self.std = torch.tensor(IMAGENET_STD, device=self.device).view(1, 3, 1, 1) * 255.0
         self.copy_stream = torch.cuda.Stream(device=self.device)
-        self.loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+        self.track_accuracy = track_accuracy and self.kind == "resnet"
+        self.loss_host = torch.zeros((2, 4), dtype=torch.float32)      # per slot: loss, top-1, top-5, unused
+        if torch.cuda.is_available():
+            self.loss_host = self.loss_host.pin_memory()
+        self._stats = torch.zeros(4, dtype=torch.float32, device=self.device)
+        self.h2d_events: list = []          # (start, end) CUDA events of the batch copies, read by h2d_seconds()
         self.err_host = torch.zeros(2, dtype=torch.int32).pin_memory()    # compute kernels' error word, per slot
         self.loss_event: list[Optional[torch.cuda.Event]] = [None, None]
         self.steps = 0
@@ -160,6 +167,8 @@ class Trainer:
     def stage(self, inputs, targets):
         """Start the host->device copy of a batch on the prefetch stream."""
         with torch.cuda.stream(self.copy_stream):
+            t0 = torch.cuda.Event(enable_timing=True)
+            t0.record(self.copy_stream)
             if self.kind == "resnet":
                 x = inputs.to(self.device, non_blocking=True)
                 y = targets.to(self.device, non_blocking=True)
@@ -168,8 +177,10 @@ class Trainer:
             else:
                 dev = tuple(t.to(self.device, non_blocking=True) for t in inputs)
                 self.h2d_bytes += sum(t.numel() * t.element_size() for t in inputs)
-            ev = torch.cuda.Event()
+            ev = torch.cuda.Event(enable_timing=True)
             ev.record(self.copy_stream)
+            if len(self.h2d_events) < 100000:
+                self.h2d_events.append((t0, ev))
         self._staged = (dev, ev)
 
     def _take_staged(self):
@@ -197,7 +208,14 @@ class Trainer:
                 if x.dtype == torch.uint8:
                     x = self.preprocess(x)
                 out = self.ddp(x)
-                return F.cross_entropy(out.float(), y)
+                logits = out.float()
+                if self.track_accuracy:      # top-1 / top-5 as the reference's loop reports them (train_imagenet.py:437-440)
+                    with torch.no_grad():
+                        k = min(5, logits.shape[1])
+                        hit = logits.topk(k, 1).indices.eq(y.view(-1, 1))
+                        self._stats[1] = hit[:, :1].any(1).float().mean() * 100.0
+                        self._stats[2] = hit.any(1).float().mean() * 100.0
+                return F.cross_entropy(logits, y)
             ids, mlm, nsp = dev
             return self.ddp(ids, None, mlm, nsp)
 
@@ -228,7 +246,8 @@ class Trainer:
             self.stage(*prefetch)
         loss = self.step_device(dev)
         slot = self.steps & 1
-        self.loss_host[slot:slot + 1].copy_(loss.view(1), non_blocking=True)
+        self._stats[0] = loss
+        self.loss_host[slot].copy_(self._stats, non_blocking=True)
         if ops_backend.get_backend() == "own":
             from .ops import kernels
             self.err_host[slot:slot + 1].copy_(kernels.error_word(self.device), non_blocking=True)
@@ -236,18 +255,20 @@ class Trainer:
         ev = torch.cuda.Event()
         ev.record()
         self.loss_event[slot] = ev
-        self.d2h_bytes += 4
-        prev = None
+        self.d2h_bytes += 16
+        prev = a1 = a5 = None
         pslot = slot ^ 1
         if self.loss_event[pslot] is not None:
             self.loss_event[pslot].synchronize()
-            prev = float(self.loss_host[pslot])
+            prev = float(self.loss_host[pslot, 0])
+            if self.track_accuracy:
+                a1, a5 = float(self.loss_host[pslot, 1]), float(self.loss_host[pslot, 2])
             self._raise_on_kernel_error(int(self.err_host[pslot]))
             if math.isnan(prev):
                 raise FloatingPointError("loss is NaN: training diverged")   # train_imagenet.py:445-446
         if self.logger.enabled:
             self.logger.log(step=self.steps, loss=prev, **(self.hook_state.step_record() if self.hook_state else {}))
-        return StepResult(prev, self.steps)
+        return StepResult(prev, self.steps, a1, a5)
 
     def _raise_on_kernel_error(self, code: int) -> None:
         if code:
@@ -262,7 +283,14 @@ class Trainer:
         """Loss of the latest ``step`` call (synchronises); raises if a compute kernel gave up during it."""
         torch.cuda.current_stream().synchronize()
         self._raise_on_kernel_error(int(self.err_host[self.steps & 1]))
-        return float(self.loss_host[self.steps & 1])
+        return float(self.loss_host[self.steps & 1, 0])
+
+    def h2d_seconds(self) -> float:
+        """Device time of the host->device batch copies since the last call (synchronises with the copy stream)."""
+        self.copy_stream.synchronize()
+        t = sum(a.elapsed_time(b) for a, b in self.h2d_events) / 1e3
+        self.h2d_events.clear()
+        return t
 
     # ------------------------------------------------------------ checkpoint
     def state_dict(self) -> dict:

@@ -36,7 +36,10 @@ from .utils.logging import AverageMeter, ProgressMeter, accuracy, append_csv
 
 def parse(argv=None) -> argparse.Namespace:
     ap = argparse.ArgumentParser(prog="gcow-train", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("data", nargs="?", default="", help="directory with train_x.npy/train_y.npy/val_x.npy/val_y.npy (uint8 NHWC)")
+    ap.add_argument("data", nargs="?", default="",
+                    help="dataset directory: train/ and val/ class folders (as torchvision's ImageFolder reads them), the "
+                         "python version of CIFAR-10 with --cifar, or pre-decoded train_x.npy/train_y.npy/val_x.npy/val_y.npy "
+                         "(uint8 NHWC)")
     ap.add_argument("-a", "--arch", default="resnet18")
     ap.add_argument("--zfp-mode", default="", choices=["", "precision", "accuracy", "rate", "lossless"])
     ap.add_argument("--rates", type=float, nargs="+", default=[16])
@@ -54,14 +57,17 @@ def parse(argv=None) -> argparse.Namespace:
     ap.add_argument("-e", "--evaluate", action="store_true")
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--dummy", action="store_true", help="synthetic data")
+    ap.add_argument("--num-classes", type=int, default=0,
+                    help="0: 10 with --cifar, else the number of class folders under DATA/train, else 1000")
     ap.add_argument("--cifar", action="store_true", help="32x32 inputs, 10 classes, ReduceLROnPlateau (the CIFAR-10 study)")
     ap.add_argument("--steps-per-epoch", type=int, default=100, help="with --dummy")
     ap.add_argument("--patience", type=int, default=5, help="epochs without top-1 improvement before stopping")
     ap.add_argument("--out-dir", default="results")
     ap.add_argument("--ops", default="own", choices=["own", "torch"])
     # launch flags of the reference script (hw/models/train_imagenet.py:60-94); torchrun's environment wins when present
-    ap.add_argument("-j", "--workers", type=int, default=4, help="accepted for compatibility: batches are assembled in-process")
-    ap.add_argument("--pretrained", action="store_true", help="refused: no pretrained weights are available offline")
+    ap.add_argument("-j", "--workers", type=int, default=4, help="data loading worker processes per rank")
+    ap.add_argument("--pretrained", action="store_true",
+                    help="start from torchvision's weights (they must already be in the local torch hub cache)")
     ap.add_argument("--world-size", type=int, default=-1, help="number of nodes (with --multiprocessing-distributed) or of processes")
     ap.add_argument("--rank", type=int, default=-1, help="node rank (with --multiprocessing-distributed) or process rank")
     ap.add_argument("--dist-url", default="tcp://127.0.0.1:23456", help="rendezvous tcp://host:port when not started by torchrun")
@@ -132,10 +138,15 @@ def run_one(args, mode: str, variable) -> dict:
         cfg.mode, cfg.rate = "rate", float(variable)
     else:
         cfg.variant = "nccl"                     # DDP's own NCCL path; a hook is added below for the lossy modes
-    classes = 10 if args.cifar else 1000
+    classes = args.num_classes or (10 if args.cifar else 1000)
+    if not args.num_classes and not args.cifar and args.data and os.path.isdir(os.path.join(args.data, "train")):
+        classes = sum(e.is_dir() for e in os.scandir(os.path.join(args.data, "train"))) or classes
     image = 32 if args.cifar else 224
     tr = Trainer(args.arch, batch_size=args.batch_size, cfg=cfg, ops=args.ops, lr=args.lr, num_classes=classes,
-                 seed=args.seed, model_kwargs={"small_input": True} if args.cifar else None)
+                 seed=args.seed, model_kwargs={"small_input": True} if args.cifar else None, pretrained=args.pretrained,
+                 track_accuracy=True)
+    if tr.hook_state is not None:
+        tr.hook_state.timing = True
     for g in tr.opt.param_groups:
         g["momentum"], g["weight_decay"] = args.momentum, args.wd
     hook_state = None
@@ -151,11 +162,15 @@ def run_one(args, mode: str, variable) -> dict:
     if args.dummy or not args.data:
         train_loader = DummyLoader(tr.kind, args.batch_size, args.steps_per_epoch, image, classes, args.seed + tr.rank)
         val_loader = DummyLoader(tr.kind, args.batch_size, max(1, args.steps_per_epoch // 10), image, classes, 10_000 + tr.rank)
-    else:
+    elif os.path.exists(os.path.join(args.data, "train_x.npy")):
         train_loader = FileLoader(os.path.join(args.data, "train_x.npy"), os.path.join(args.data, "train_y.npy"),
                                   args.batch_size, tr.rank, tr.world, True, args.seed)
         val_loader = FileLoader(os.path.join(args.data, "val_x.npy"), os.path.join(args.data, "val_y.npy"),
                                 args.batch_size, tr.rank, tr.world, False, args.seed)
+    else:               # image folders / CIFAR-10 batches, decoded and augmented by worker processes
+        from .data import make_loaders
+        train_loader, val_loader = make_loaders(args.data, args.cifar, args.batch_size, tr.rank, tr.world, args.workers,
+                                                args.seed, image)
     tag = f"{args.arch}_{mode}_{variable}"
     ckpt = os.path.join(args.out_dir, "models", tag + "_ckp.tar")
     best_acc1, start_epoch, stale = 0.0, args.start_epoch, 0
@@ -171,8 +186,8 @@ def run_one(args, mode: str, variable) -> dict:
     result = {"mode": mode, "variable": variable, "diverged": False}
     for epoch in range(start_epoch, args.epochs):
         batch_time, data_time = AverageMeter("Time", ":6.3f"), AverageMeter("Data", ":6.3f")
-        losses = AverageMeter("Loss", ":.4e")
-        prog = ProgressMeter(len(train_loader), [batch_time, data_time, losses], prefix=f"Epoch: [{epoch}]")
+        losses, top1, top5 = AverageMeter("Loss", ":.4e"), AverageMeter("Acc@1", ":6.2f"), AverageMeter("Acc@5", ":6.2f")
+        prog = ProgressMeter(len(train_loader), [batch_time, data_time, losses, top1, top5], prefix=f"Epoch: [{epoch}]")
         t_epoch = end = time.time()
         try:
             for i, (x, y) in enumerate(train_loader):
@@ -180,6 +195,9 @@ def run_one(args, mode: str, variable) -> dict:
                 r = tr.step(x, y)
                 if r.loss is not None:
                     losses.update(r.loss, args.batch_size)
+                if r.acc1 is not None:
+                    top1.update(r.acc1, args.batch_size)
+                    top5.update(r.acc5, args.batch_size)
                 batch_time.update(time.time() - end)
                 end = time.time()
                 if rank == 0 and i % args.print_freq == 0:
@@ -201,8 +219,18 @@ def run_one(args, mode: str, variable) -> dict:
         if dist.is_initialized() and dist.get_world_size() > 1:
             dist.barrier()      # rank 0 writes alone; the others must not start waiting on it inside a collective
         secs = time.time() - t_epoch
-        row = {"mode": mode, "variable": variable, "epoch": epoch, "train_loss": losses.avg, "val_loss": vl,
-               "acc1": a1, "acc5": a5, "epoch_sec": secs,
+        # device seconds of this epoch: batch copies (the reference's "transfer" time, hw/models/train_imagenet.py:452-473),
+        # the compressed collectives (codec and wire are one kernel in rate mode) and the stand-alone codec (other modes)
+        h2d_sec = tr.h2d_seconds()
+        comm_sec = tr.hook_state.comm_seconds() if tr.hook_state else 0.0
+        codec_sec = 0.0
+        if hook_state and hook_state.get("codec_events"):
+            torch.cuda.synchronize()
+            codec_sec = sum(a.elapsed_time(b) for a, b in hook_state["codec_events"]) / 1e3
+            hook_state["codec_events"].clear()
+        row = {"mode": mode, "variable": variable, "epoch": epoch, "train_loss": losses.avg, "train_acc1": top1.avg,
+               "train_acc5": top5.avg, "val_loss": vl, "acc1": a1, "acc5": a5, "epoch_sec": secs,
+               "h2d_sec": h2d_sec, "allreduce_sec": comm_sec, "codec_sec": codec_sec,
                "samples_per_sec": len(train_loader) * args.batch_size * tr.world / secs,
                "wire_ratio": tr.hook_state.ar.wire_ratio() if tr.hook_state else 0.0,
                "codec_ratio": (hook_state["bytes_in"] / max(1, hook_state["bytes_out"])) if hook_state else 0.0}
@@ -239,8 +267,6 @@ def _spawned(local: int, ngpus: int, argv) -> None:
 
 def main(argv=None) -> int:
     args = parse(argv)
-    if args.pretrained:
-        raise SystemExit("--pretrained: no pretrained weights can be downloaded here; load a checkpoint with --resume")
     if "RANK" not in os.environ:                  # not under torchrun: honour the reference's launch flags
         ngpus = max(1, torch.cuda.device_count())
         if args.multiprocessing_distributed and ngpus > 1:

@@ -77,9 +77,9 @@ def test_conv_igemm_resnet_layer_shape():
     assert _rel(y, ref) < 2e-2 and _rel(xo.grad, xr.grad) < 2e-2 and _rel(wo.grad, wr.grad) < 5e-3
 
 
-def test_conv2d_module_uses_igemm_when_selected(monkeypatch):
+def test_conv2d_module_uses_igemm_by_default(monkeypatch):
     from gcow_b200.ops import kernels as K, nn as gnn, set_backend
-    monkeypatch.setenv("GCOW_CONV", "igemm")
+    monkeypatch.delenv("GCOW_CONV", raising=False)
     set_backend("own")
     torch.manual_seed(6)
     conv = gnn.Conv2d(64, 64, 3, padding=1, bias=False).cuda().to(memory_format=torch.channels_last)
@@ -87,6 +87,72 @@ def test_conv2d_module_uses_igemm_when_selected(monkeypatch):
     before = K.launch_count()
     with torch.autocast("cuda", dtype=torch.bfloat16):
         y = conv(x)
-    assert K.launch_count() == before + 1
+    assert K.launch_count() == before + 1 and gnn.last_conv_path() == "igemm"
     ref = F.conv2d(x.float(), conv.weight.bfloat16().float(), padding=1)
     assert _rel(y, ref) < 2e-2
+    monkeypatch.setenv("GCOW_CONV", "lib")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        conv(x)
+    assert gnn.last_conv_path() == "cudnn"
+
+
+# (Ci, Co, k, stride, pad, H, input needs a gradient, expected path): the layer kinds of a ResNet that the
+# implicit-GEMM kernel does not serve
+MODULE_CASES = [
+    (64, 256, 1, 1, 0, 14, True, "gemm1x1"),
+    (256, 64, 1, 1, 0, 14, True, "gemm1x1"),
+    (256, 512, 1, 2, 0, 14, True, "gemm1x1_strided"),
+    (128, 128, 3, 2, 1, 14, True, "im2col"),
+    (64, 128, 3, 2, 1, 15, True, "im2col"),
+    (3, 64, 7, 2, 3, 32, False, "im2col"),
+    (3, 64, 3, 1, 1, 16, False, "im2col"),
+]
+
+
+@pytest.mark.parametrize("case", MODULE_CASES)
+def test_conv2d_module_paths_match_fp32_reference(case, monkeypatch):
+    from gcow_b200.ops import kernels as K, nn as gnn, set_backend
+    monkeypatch.delenv("GCOW_CONV", raising=False)
+    set_backend("own")
+    Ci, Co, k, s, p, H, xgrad, path = case
+    torch.manual_seed(sum(case[:6]))
+    conv = gnn.Conv2d(Ci, Co, k, stride=s, padding=p, bias=False).cuda().to(memory_format=torch.channels_last)
+    with torch.no_grad():
+        conv.weight.copy_(conv.weight.bfloat16().float())
+    x = (torch.randn(8, Ci, H, H, device="cuda") * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    xo = x.clone().requires_grad_(xgrad)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = conv(xo)
+    assert gnn.last_conv_path() == path
+    xr = x.float().requires_grad_(xgrad)
+    wr = conv.weight.detach().clone().requires_grad_(True)
+    ref = F.conv2d(xr, wr, None, stride=s, padding=p)
+    assert y.shape == ref.shape and _rel(y, ref) < 2e-2
+    gy = (torch.randn_like(ref) * 0.5).bfloat16()
+    y.backward(gy.to(y.dtype))
+    ref.backward(gy.float())
+    K.check_errors()
+    assert _rel(conv.weight.grad, wr.grad) < 1e-2
+    if xgrad:
+        assert _rel(xo.grad, xr.grad) < 2e-2
+
+
+def test_resnet50_step_sends_no_convolution_to_cudnn(monkeypatch):
+    """All 53 convolutions of ResNet-50 (hw/models/resenet.py:11-17,79,113 in the reference) run on this library's
+    kernels by default, forward and backward."""
+    from gcow_b200.models import MODELS
+    from gcow_b200.ops import kernels as K, set_backend
+    monkeypatch.delenv("GCOW_CONV", raising=False)
+    set_backend("own")
+    torch.manual_seed(0)
+    net = MODELS["resnet50"](num_classes=16).cuda().to(memory_format=torch.channels_last)
+    x = torch.randn(8, 3, 224, 224, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    K.conv_path_counts(reset=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = net(x).float().square().mean()
+    loss.backward()
+    K.check_errors()
+    counts = K.conv_path_counts(reset=True)
+    assert sum(counts.values()) == 53 and counts.get("cudnn", 0) == 0, counts
+    assert counts["gemm1x1"] == 33 and counts["gemm1x1_strided"] == 3 and counts["igemm"] == 13 and counts["im2col"] == 4
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.parameters())
