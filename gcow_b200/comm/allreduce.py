@@ -109,6 +109,8 @@ class CompressedAllReduce:
     def __init__(self, max_numel: int, cfg: GcowConfig | None = None, group=None,
                  device: torch.device | None = None, backend: str = "auto"):
         self.cfg = cfg or GcowConfig.from_env()
+        if backend == "auto":      # GCOW_COMM_BACKEND=ipc|symm picks how peer memory is mapped when the caller does not
+            backend = os.environ.get("GCOW_COMM_BACKEND", "auto")
         if self.cfg.dim != 1 or self.cfg.mode != "rate":
             raise ValueError("the fused all-reduce uses the 1-D fixed-rate codec")
         self.params = ZfpParams.from_rate(self.cfg.rate, 1)

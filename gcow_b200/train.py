@@ -77,6 +77,29 @@ class SyntheticImages:
         return self.x[0].numel() * self.x[0].element_size() + self.y[0].numel() * 8
 
 
+class LearnableImages:
+    """A classification task that can be learned: every class has a fixed random low-resolution pattern, an image is
+    its class pattern plus pixel noise. Fresh batches every call (uint8 NHWC, pinned), the same patterns on every
+    rank, different samples per rank. Used to compare loss curves across compression rates."""
+
+    def __init__(self, batch: int, size: int = 64, classes: int = 10, seed: int = 0, noise: float = 48.0,
+                 pattern_seed: int = 1234):
+        g = torch.Generator().manual_seed(pattern_seed)
+        coarse = torch.rand((classes, 8, 8, 3), generator=g) * 160.0 + 48.0
+        rep = size // 8
+        self.patterns = coarse.repeat_interleave(rep, 1).repeat_interleave(rep, 2)          # [classes, size, size, 3]
+        self.batch, self.classes, self.noise = batch, classes, noise
+        self.gen = torch.Generator().manual_seed(seed)
+
+    def next(self):
+        y = torch.randint(0, self.classes, (self.batch,), generator=self.gen)
+        x = self.patterns[y] + torch.randn((self.batch,) + tuple(self.patterns.shape[1:]), generator=self.gen) * self.noise
+        x = x.clamp_(0, 255).to(torch.uint8)
+        if torch.cuda.is_available():
+            x, y = x.pin_memory(), y.pin_memory()
+        return x, y
+
+
 class SyntheticTokens:
     """Random token ids uniform over the vocabulary, 15 % masked-LM labels, NSP labels."""
 

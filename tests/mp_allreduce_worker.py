@@ -72,6 +72,30 @@ def main():
             fails.append(f"rate {rate} unaligned view wrote outside its range")
         ran += 1
         del ar
+    if os.environ.get("GCOW_TEST_BIG") == "1":
+        # One 256 MB fp32 buffer per rank (values ~N(0, 1e-3), seed = rank) at 4, 8 and 16 bit/value against the host
+        # model: rank 0 computes decode-sum-encode on the CPU and broadcasts it, every rank compares on the device.
+        n = 64 << 20
+        xs = None
+        if rank == 0:
+            xs = np.stack([gen(r, n) for r in range(world)])
+        mine = torch.from_numpy(gen(rank, n)).to(dev)
+        for rate in (8, 4, 16):
+            cfg = GcowConfig(rate=rate, comm_ctas=4096, timeout_ms=20000)
+            ar = CompressedAllReduce(n, cfg, device=dev, backend=backend)
+            p = ZfpParams.from_rate(rate, 1)
+            ref = torch.empty(n, device=dev)
+            if rank == 0:
+                ref.copy_(torch.from_numpy(allreduce_oracle(xs, p, "twoshot", shift)))
+            dist.broadcast(ref, 0)
+            for variant in ["twoshot"] + (["nvls"] if ar.arena.mc_ptr else []):
+                y = ar(mine.clone(), variant=variant)
+                ar.check()
+                bad = int((y.view(torch.int32) != ref.view(torch.int32)).sum())
+                if bad:
+                    fails.append(f"256 MB rate {rate} {variant}: {bad} words differ")
+                ran += 1
+            del ar
     allf = [None] * world
     dist.all_gather_object(allf, fails)
     if rank == 0:

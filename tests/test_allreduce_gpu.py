@@ -127,3 +127,26 @@ def test_multi_gpu_ipc_backend():
     proc, res = _run_workers(2, {"GCOW_COMM_BACKEND": "ipc"})
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert res["backend"] == "ipc" and not any(res["fails"])
+
+
+@pytest.mark.multigpu
+def test_multi_gpu_256mb_buffer_matches_host_model():
+    """One 256 MB gradient buffer per rank at 4/8/16 bit/value on every visible GPU (2, 4 or 8), bit for bit
+    against decode-sum-encode on the host."""
+    n = torch.cuda.device_count()
+    nproc = 8 if n >= 8 else 4 if n >= 4 else 2
+    proc, res = _run_workers(nproc, {"GCOW_TEST_BIG": "1"}, timeout=1500)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert res is not None and res["world"] == nproc and not any(res["fails"])
+
+
+@pytest.mark.multigpu
+def test_late_peer_times_out_on_both_ranks_then_recovers():
+    """A rank that reaches its launch 300 ms late, with 50 ms waits: both ranks get a time-out record instead of a
+    hang, the next call is bit-exact again, and the training hook's safe mode finishes the step with NCCL. Plain peer
+    loads and stores (IPC backend, no multicast object bound), NVLS off in NCCL."""
+    proc, res = _run_workers(2, {"GCOW_COMM_BACKEND": "ipc", "NCCL_NVLS_ENABLE": "0"}, script="mp_late_peer_worker.py")
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert res["timed_out"] == [True, True] and res["recovered_bit_exact"] == [True, True]
+    assert res["safe_mode_fallbacks"][0] > 0 and res["safe_mode_fallbacks"] == res["safe_mode_fallbacks"][::-1]
+    assert res["replicas_equal"]
