@@ -149,6 +149,10 @@ def _declare_conv(lib, proto):
             proto(lib, name, restype, *args)
     opt("gcow_im2col", i32, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, ptr)
     opt("gcow_col2im", i32, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, ptr)
+    opt("gcow_attention_supported", i32, i32, i32, i32, i32)
+    opt("gcow_attention_fwd", i32, ptr, ptr, ptr, i32, i32, i32, i32, C.c_float, ptr, ptr)
+    opt("gcow_attention_bwd", i32, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, i32, i32, C.c_float, ptr, ptr)
+    opt("gcow_subsample", i32, ptr, ptr, i32, i32, i32, i32, i32, i32, ptr)
     opt("gcow_im2col_anyc", i32, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, i32, ptr)
     opt("gcow_conv_fwd", i32, ptr, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, i32, ptr, ptr)
     opt("gcow_conv_wgrad_split", i32, i32, i32, i32, i32, i32, i32, i32, i32, i32)

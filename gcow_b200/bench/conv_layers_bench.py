@@ -55,6 +55,7 @@ def main(argv=None):
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default="")
+    ap.add_argument("--alt-1x1", action="store_true", help="also time the 1x1 layers on the implicit-GEMM kernel")
     args = ap.parse_args(argv)
     layers, stem = collect(args.arch, args.batch, args.image)
     backend.set_backend("own")
@@ -65,11 +66,15 @@ def main(argv=None):
         x.requires_grad_((cin, cout, k, s, p, h) != stem)          # the stem's input needs no gradient
         row = {"cin": cin, "cout": cout, "k": k, "stride": s, "h": h, "count": count}
         gy = None
-        for arm, env in (("own", None), ("cudnn", "lib")):
+        arms = [("own", None), ("cudnn", "lib")]
+        if args.alt_1x1 and k == 1 and s == 1:
+            arms.append(("igemm1x1", "auto"))
+        for arm, env in arms:
             if env is None:
                 os.environ.pop("GCOW_CONV", None)
             else:
                 os.environ["GCOW_CONV"] = env
+            os.environ["GCOW_CONV1X1"] = "igemm" if arm == "igemm1x1" else "gemm"
             with torch.autocast("cuda", dtype=torch.bfloat16):
                 y = conv(x)
             if gy is None:
@@ -84,7 +89,8 @@ def main(argv=None):
                 out.backward(gy)
             ms, _ = time_cuda(step, args.iters)
             row[f"{arm}_ms"] = round(ms, 4)
-            tot[arm] += ms * count
+            if arm in tot:
+                tot[arm] += ms * count
         row["own_over_cudnn"] = round(row["own_ms"] / row["cudnn_ms"], 3)
         os.environ.pop("GCOW_CONV", None)
         rows.append(row)

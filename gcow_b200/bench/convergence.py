@@ -29,12 +29,23 @@ def run_arm(name: str, cfg: GcowConfig, args, device) -> dict:
     data = LearnableImages(args.batch, args.image, 10, seed=100 + tr.rank)
     losses, accs = [], []
     nxt = data.next()
+    diverged = 0
     for _ in range(args.steps + 1):
         cur, nxt = nxt, data.next()
-        r = tr.step(cur[0], cur[1], prefetch=nxt)
+        try:
+            r = tr.step(cur[0], cur[1], prefetch=nxt)
+        except FloatingPointError:          # NaN loss: this arm has diverged; the sweep goes on (train_imagenet.py:445-446)
+            diverged = 1
+            break
         if r.loss is not None:
             losses.append(r.loss)
             accs.append(r.acc1)
+    flag = torch.tensor([diverged], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if int(flag):
+        del tr
+        torch.cuda.empty_cache()
+        return {"arm": name, "diverged": True, "steps": len(losses)}
     t = torch.tensor(losses, device=device, dtype=torch.float64)
     a = torch.tensor(accs, device=device, dtype=torch.float64)
     dist.all_reduce(t)
@@ -59,7 +70,7 @@ def main(argv=None):
     ap.add_argument("--lr", type=float, default=0.05)
     ap.add_argument("--window", type=int, default=25)
     ap.add_argument("--rates", type=float, nargs="+", default=[16, 8, 4])
-    ap.add_argument("--error-feedback-rates", type=float, nargs="*", default=[4])
+    ap.add_argument("--error-feedback-rates", type=float, nargs="*", default=[8])
     ap.add_argument("--json", default="")
     args = ap.parse_args(argv)
     local = int(os.environ.get("LOCAL_RANK", 0))

@@ -314,14 +314,18 @@ allreduce_fused_kernel(const ArArgs a) {
 #pragma unroll
       for (int i = 0; i < NW; i++) w[i] = 0;
       if (valid) {
+        // the next source's code is in flight while this one is decoded
         float acc[4];
+        uint32_t c[NW], nxt[NW];
+        C::ld(local + a.region_off, b, c);
         for (int s = 0; s < P; s++) {
-          uint32_t c[NW];
-          C::ld(local + a.region_off + (uint64_t)s * L.slot_bytes, b, c);
+          if (s + 1 < P) C::ld(local + a.region_off + (uint64_t)(s + 1) * L.slot_bytes, b, nxt);
           float d[4];
           decode_block_1d_lean<BITS>(d, lt, c, 0);
           if (s == 0) { acc[0] = d[0]; acc[1] = d[1]; acc[2] = d[2]; acc[3] = d[3]; }
           else { acc[0] += d[0]; acc[1] += d[1]; acc[2] += d[2]; acc[3] += d[3]; }
+#pragma unroll
+          for (int i = 0; i < NW; i++) c[i] = nxt[i];
         }
         encode_block_1d_lean<BITS>(acc, lt, w);
       }

@@ -76,30 +76,80 @@ __global__ void col2im_kernel(const bf16* __restrict__ dcol, bf16* __restrict__ 
 
 // Patch matrix for an input whose channel count is not a multiple of 8 (the 3-channel image in front of
 // the stem): row length Kp >= KH*KW*C is a multiple of 8, element kk of a row is tap kk / C, channel kk % C,
-// columns past KH*KW*C are zero. One thread gathers eight elements and stores them as 16 bytes.
-__global__ void im2col_anyc_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, Geo g, int Kp) {
-  const int groups = Kp / 8, K = g.KH * g.KW * g.C;
-  const int64_t total = (int64_t)g.N * g.OH * g.OW * groups;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int k0 = (int)(t % groups) * 8;
-    int64_t p = t / groups;
-    const int ow = (int)(p % g.OW); p /= g.OW;
-    const int oh = (int)(p % g.OH);
-    const int n = (int)(p / g.OH);
-    const int h0 = oh * g.stride - g.pad, w0 = ow * g.stride - g.pad;
+// columns past KH*KW*C are zero. A CTA serves kTileW consecutive output pixels of one output row: it stages the
+// KH input-row segments they touch in shared memory (coalesced reads, zero fill outside the image), then every
+// thread assembles eight elements of a patch row from there and stores them as 16 bytes, so the patch matrix -
+// by far the larger side - is written in whole, consecutive rows.
+constexpr int kTileW = 32;
+__global__ void __launch_bounds__(256)
+im2col_anyc_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, Geo g, int Kp, int tiles_w) {
+  extern __shared__ bf16 patch[];                          // [KH][span][C]
+  const int span = (kTileW - 1) * g.stride + g.KW;         // input pixels per row segment
+  const int rowlen = span * g.C, RC = g.KW * g.C, K = g.KH * RC;
+  int b = blockIdx.x;
+  const int tw = b % tiles_w; b /= tiles_w;
+  const int oh = b % g.OH;
+  const int n = b / g.OH;
+  const int ow0 = tw * kTileW;
+  const int h0 = oh * g.stride - g.pad, w0 = ow0 * g.stride - g.pad;
+  for (int i = threadIdx.x; i < g.KH * rowlen; i += blockDim.x) {
+    const int kh = i / rowlen, r = i - kh * rowlen;
+    const int ih = h0 + kh, iw = w0 + r / g.C;
+    bf16 e = __float2bfloat16(0.0f);
+    if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) e = x[(((int64_t)n * g.H + ih) * g.W + w0) * g.C + r];
+    patch[i] = e;
+  }
+  __syncthreads();
+  const int groups = Kp / 8;
+  const int npix = min(kTileW, g.OW - ow0);
+  bf16* out = col + (((int64_t)n * g.OH + oh) * g.OW + ow0) * Kp;
+  for (int t = threadIdx.x; t < npix * groups; t += blockDim.x) {
+    const int p = t / groups, k0 = (t - p * groups) * 8;
     __align__(16) bf16 v[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       const int kk = k0 + i;
       bf16 e = __float2bfloat16(0.0f);
       if (kk < K) {
-        const int tap = kk / g.C, c = kk - tap * g.C;
-        const int ih = h0 + tap / g.KW, iw = w0 + tap % g.KW;
-        if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) e = x[(((int64_t)n * g.H + ih) * g.W + iw) * g.C + c];
+        const int kh = kk / RC, j = kk - kh * RC;
+        e = patch[kh * rowlen + p * g.stride * g.C + j];
       }
       v[i] = e;
     }
-    *reinterpret_cast<uint4*>(col + t * 8) = *reinterpret_cast<const uint4*>(v);
+    *reinterpret_cast<uint4*>(out + (int64_t)t * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
+// Pixel subsample in front of a strided 1x1 convolution: y[n][oh][ow][:] = x[n][oh*s][ow*s][:], 16 bytes per thread;
+// and its gradient, which puts g back at the sampled pixels and zeros everywhere else in one pass.
+__global__ void subsample_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int N, int H, int W, int C, int s,
+                                 int OH, int OW) {
+  const int cg = C / 8;
+  const int64_t total = (int64_t)N * OH * OW * cg;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int c8 = (int)(t % cg);
+    int64_t p = t / cg;
+    const int ow = (int)(p % OW); p /= OW;
+    const int oh = (int)(p % OH);
+    const int n = (int)(p / OH);
+    *reinterpret_cast<uint4*>(y + t * 8) =
+        *reinterpret_cast<const uint4*>(x + ((((int64_t)n * H + (int64_t)oh * s) * W + (int64_t)ow * s) * cg + c8) * 8);
+  }
+}
+__global__ void subsample_grad_kernel(const bf16* __restrict__ g, bf16* __restrict__ dx, int N, int H, int W, int C, int s,
+                                      int OH, int OW) {
+  const int cg = C / 8;
+  const int64_t total = (int64_t)N * H * W * cg;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int c8 = (int)(t % cg);
+    int64_t p = t / cg;
+    const int w = (int)(p % W); p /= W;
+    const int h = (int)(p % H);
+    const int n = (int)(p / H);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (h % s == 0 && w % s == 0 && h / s < OH && w / s < OW)
+      v = *reinterpret_cast<const uint4*>(g + ((((int64_t)n * OH + h / s) * OW + w / s) * cg + c8) * 8);
+    *reinterpret_cast<uint4*>(dx + t * 8) = v;
   }
 }
 
@@ -125,8 +175,23 @@ int gcow_im2col_anyc(const void* x, void* col, int N, int H, int W, int C, int K
                      void* stream) {
   if (Kp % 8 || Kp < KH * KW * C || stride < 1) return -1;
   Geo g{N, H, W, C, KH, KW, stride, pad, (H + 2 * pad - KH) / stride + 1, (W + 2 * pad - KW) / stride + 1};
-  const int64_t total = (int64_t)N * g.OH * g.OW * (Kp / 8);
-  im2col_anyc_kernel<<<grid1d(total), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)col, g, Kp);
+  const int tiles_w = (g.OW + kTileW - 1) / kTileW;
+  const int64_t ctas = (int64_t)N * g.OH * tiles_w;
+  const size_t smem = (size_t)KH * ((kTileW - 1) * stride + KW) * C * sizeof(bf16);
+  if (ctas > 0x7fffffffLL || smem > 48 * 1024) return -1;
+  im2col_anyc_kernel<<<(unsigned)ctas, 256, smem, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)col, g, Kp, tiles_w);
+  return (int)cudaGetLastError();
+}
+
+// y[N][OH][OW][C] = x[N][::s][::s][C] with OH = ceil(H/s), OW = ceil(W/s); C a multiple of 8. grad != 0: the gradient
+// (x is then the [N][OH][OW][C] upstream gradient and y the [N][H][W][C] result, zero off the sampled pixels).
+int gcow_subsample(const void* x, void* y, int N, int H, int W, int C, int s, int grad, void* stream) {
+  if (C % 8 || s < 1) return -1;
+  const int OH = (H + s - 1) / s, OW = (W + s - 1) / s;
+  if (grad) subsample_grad_kernel<<<grid1d((int64_t)N * H * W * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)x, (bf16*)y, N, H, W, C, s, OH, OW);
+  else subsample_kernel<<<grid1d((int64_t)N * OH * OW * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)x, (bf16*)y, N, H, W, C, s, OH, OW);
   return (int)cudaGetLastError();
 }
 

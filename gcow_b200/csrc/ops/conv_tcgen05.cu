@@ -429,22 +429,6 @@ static double pick_box(int W, int H, int N, int rows, int exact, int* obw, int* 
   return best_eff;
 }
 
-// Tuning overrides for experiments: GCOW_CONV_TUNE="box=8x8x2,stages=3,rows=128"
-struct Tune { int bw = 0, bh = 0, bn = 0, stages = 0, rows = 0; };
-static const Tune& tune() {
-  static Tune t;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    const char* e = getenv("GCOW_CONV_TUNE");
-    if (!e) return;
-    const char* q;
-    if ((q = strstr(e, "box="))) sscanf(q, "box=%dx%dx%d", &t.bw, &t.bh, &t.bn);
-    if ((q = strstr(e, "stages="))) sscanf(q, "stages=%d", &t.stages);
-    if ((q = strstr(e, "rows="))) sscanf(q, "rows=%d", &t.rows);
-  });
-  return t;
-}
-
 static size_t smem_for(int halves, int bn_cols, int stages) {
   return (size_t)stages * (halves * HALF_BYTES + bn_cols * BK * 2) + sizeof(Smem) + 16 + EPI_WARPS * kStageWarpBytes + 1024;
 }
@@ -468,7 +452,6 @@ static int device_sms() {
 static int stages_for(int halves, int bn_cols) {
   int st = kSmemBudget / (halves * HALF_BYTES + bn_cols * BK * 2);
   st = st > MAX_STAGES ? MAX_STAGES : st;
-  if (tune().stages > 0 && tune().stages < st) st = tune().stages;
   return st;
 }
 
@@ -493,8 +476,6 @@ static int fwd_halves(int Wo, int Ho, int N, int tiles_c, int ksteps, int bn_col
   // 64 KB stages leave a ring of three (measured: 1.45 x the modelled step)
   if (bn_cols == 256) cost[2] *= 1.45;
   int halves = cost[2] < cost[1] ? 2 : 1;
-  if (tune().rows == 128) halves = 1;
-  if (tune().rows == 256) halves = 2;
   return halves;
 }
 
@@ -540,7 +521,6 @@ int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int 
   const int ksteps = kh * kw * (Ci / 64);
   const int halves = fwd_halves(Wo, Ho, N, tiles_c, ksteps, p.bn_cols, sms);
   pick_box(Wo, Ho, N, 128 * halves, 0, &p.bw, &p.bh, &p.bn);
-  if (tune().bw > 0 && tune().bw * tune().bh * tune().bn <= 128 * halves) { p.bw = tune().bw; p.bh = tune().bh; p.bn = tune().bn; }
   p.tiles_w = (Wo + p.bw - 1) / p.bw; p.tiles_h = (Ho + p.bh - 1) / p.bh; p.tiles_n = (N + p.bn - 1) / p.bn;
   p.stages = stages_for(halves, p.bn_cols);
   p.out = y; p.bias = bias; p.N = N; p.H = Ho; p.W = Wo; p.Ci = Ci; p.Co = Co;

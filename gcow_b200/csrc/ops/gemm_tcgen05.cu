@@ -436,6 +436,15 @@ EncodeTiledFn encode_tiled_fn() {
         q == cudaDriverEntryPointSuccess)
       fn = (EncodeTiledFn)p;
   });
+  // The encoder is a driver-API call and needs a current context on the calling thread. A thread that has made no
+  // runtime-API call yet has none (autograd's backward threads reach a launcher this way when their first
+  // allocation is served from PyTorch's cache), and the call fails with CUDA_ERROR_INVALID_CONTEXT. Binding the
+  // runtime's device once per thread makes its primary context current.
+  thread_local bool bound = false;
+  if (!bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) bound = true;
+  }
   return fn;
 }
 }  // namespace tc
@@ -487,8 +496,7 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
   int rc;
   // an MN-major operand whose row length is a multiple of 64 is fetched with one copy per stage
-  static const bool no_merge = getenv("GCOW_GEMM_NO_MERGE") != nullptr;
-  const int a_merged = a_mn && M % 64 == 0 && !no_merge, b_merged = b_mn && N % 64 == 0 && !no_merge;
+  const int a_merged = a_mn && M % 64 == 0, b_merged = b_mn && N % 64 == 0;
   if (a_merged || b_merged) {
     rc = a_merged ? make_map_mn(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)bm / 64)
          : batch == 1 ? (a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)

@@ -29,6 +29,30 @@ def _have(name: str) -> bool:
         return False
 
 
+_arena: dict = {}
+
+
+def _ws(tag: str, shape, dtype, device) -> torch.Tensor:
+    """Scratch tensor from a per-(device, stream, purpose) arena that grows to the largest request and is then
+    reused: partial sums of split reductions and similar buffers that live only between two kernels of one
+    operation. Operations on one stream run in order, so two of them never use the same scratch at the same time;
+    nothing that is returned to the caller or saved for the backward pass may come from here."""
+    n = 1
+    for d in (shape if isinstance(shape, (tuple, list)) else (shape,)):
+        n *= int(d)
+    key = (tag, dtype, device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _arena.get(key)
+    if buf is None or buf.numel() < n:
+        buf = torch.empty(max(n, 1), dtype=dtype, device=device)
+        _arena[key] = buf
+    return buf[:n].view(shape)
+
+
+def workspace_bytes() -> int:
+    """Bytes currently held by the scratch arena."""
+    return sum(b.numel() * b.element_size() for b in _arena.values())
+
+
 def _error_word(device: torch.device) -> torch.Tensor:
     w = _err_words.get(device)
     if w is None:
@@ -161,7 +185,7 @@ def wgrad_gemm(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     if s == 1 or g.stride(0) != N or x.stride(0) != K:
         return gemm_bf16(g, x, a_t=True, b_t=True, out_dtype=torch.float32)
     lib = _native.cuda()
-    part = torch.empty((s, N, K), dtype=torch.float32, device=g.device)
+    part = _ws("wgrad_part", (s, N, K), torch.float32, g.device)
     err = lib.gcow_gemm_bf16_batched(
         g.data_ptr(), x.data_ptr(), part.data_ptr(), N, K, M // s, N, K, K, s, (M // s) * N, (M // s) * K, N * K,
         None, None, OUT_F32, _error_word(g.device).data_ptr(), 1, 1, 0, _stream(g.device))
@@ -332,7 +356,7 @@ def colsum(g: torch.Tensor) -> torch.Tensor:
     if cols % 2 or g.stride(1) != 1 or g.stride(0) % 2:
         return g.float().sum(0)
     parts = lib.gcow_colsum_parts(rows)
-    part = torch.empty(parts * cols, dtype=torch.float32, device=g.device)
+    part = _ws("colsum_part", parts * cols, torch.float32, g.device)
     out = torch.empty(cols, dtype=torch.float32, device=g.device)
     _chk(lib.gcow_colsum(g.data_ptr(), part.data_ptr(), out.data_ptr(), rows, cols, g.stride(0), _stream(g.device)),
          "gcow_colsum")
@@ -373,6 +397,40 @@ class _Conv1x1Fn(torch.autograd.Function):
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)
         return gx, gw, gb
+
+
+class _SubsampleFn(torch.autograd.Function):
+    """x[:, :, ::s, ::s] of a channels-last bf16 tensor as a dense channels-last tensor (what a strided 1x1 convolution
+    reads); the backward writes the gradient at the sampled pixels and zeros elsewhere in one kernel."""
+
+    @staticmethod
+    def forward(ctx, x, s):
+        global _launches
+        N, C, H, W = x.shape
+        if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
+            x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        OH, OW = (H + s - 1) // s, (W + s - 1) // s
+        y = torch.empty((N, C, OH, OW), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
+        _chk(_native.cuda().gcow_subsample(x.data_ptr(), y.data_ptr(), N, H, W, C, s, 0, _stream(x.device)), "gcow_subsample")
+        _launches += 1
+        ctx.meta = (N, C, H, W, s)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        N, C, H, W, s = ctx.meta
+        if gy.dtype != torch.bfloat16 or not gy.is_contiguous(memory_format=torch.channels_last):
+            gy = gy.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        gx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=gy.device, memory_format=torch.channels_last)
+        _chk(_native.cuda().gcow_subsample(gy.data_ptr(), gx.data_ptr(), N, H, W, C, s, 1, _stream(gy.device)),
+             "gcow_subsample (gradient)")
+        _launches += 1
+        return gx, None
+
+
+def subsample(x: torch.Tensor, s: int) -> torch.Tensor:
+    return _SubsampleFn.apply(x, s)
 
 
 def conv1x1_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -417,7 +475,7 @@ class _LayerNormFn(torch.autograd.Function):
         lib = _native.cuda()
         dx = torch.empty_like(xb)
         parts = lib.gcow_layernorm_bwd_parts(rows)
-        part = torch.empty(parts * 2 * H, dtype=torch.float32, device=xb.device)
+        part = _ws("ln_part", parts * 2 * H, torch.float32, xb.device)
         dgb = torch.empty(2 * H, dtype=torch.float32, device=xb.device)
         _chk(lib.gcow_layernorm_bwd(g.data_ptr(), xb.data_ptr(), g32.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                                     dx.data_ptr(), part.data_ptr(), dgb.data_ptr(), rows, H, _stream(xb.device)),
@@ -552,7 +610,7 @@ class _BatchNormActFn(torch.autograd.Function):
         lib = _native.cuda()
         y = torch.empty_like(x, memory_format=torch.channels_last)
         stats = torch.empty(4 * C, dtype=torch.float32, device=x.device)
-        part = torch.empty(lib.gcow_bn_parts(R, C) * 2 * C, dtype=torch.float32, device=x.device)
+        part = _ws("bn_part", lib.gcow_bn_parts(R, C) * 2 * C, torch.float32, x.device)
         g32, b32 = gamma.float().contiguous(), beta.float().contiguous()
         mask = torch.empty(R * C // 8, dtype=torch.uint8, device=x.device) if relu else None
         _chk(lib.gcow_bn_fwd_train(x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
@@ -589,7 +647,7 @@ class _BatchNormActFn(torch.autograd.Function):
         # the masked (summed) gradient: the residual input's gradient, and what the second sweep reads
         dres = torch.empty_like(x, memory_format=torch.channels_last) if (has_res or gy2 is not None) else None
         dgb = torch.empty(2 * C, dtype=torch.float32, device=x.device)
-        part = torch.empty(lib.gcow_bn_parts(R, C) * 2 * C, dtype=torch.float32, device=x.device)
+        part = _ws("bn_part", lib.gcow_bn_parts(R, C) * 2 * C, torch.float32, x.device)
         _chk(lib.gcow_bn_bwd2(gy.data_ptr(), gy2.data_ptr() if gy2 is not None else None,
                               mask.data_ptr() if mask is not None else None, x.data_ptr(), g32.data_ptr(),
                               stats.data_ptr(), dx.data_ptr(),
@@ -802,7 +860,7 @@ class _Embed3Fn(torch.autograd.Function):
         dtok = torch.zeros((V, H), dtype=torch.float32, device=dev)
         dpos = torch.zeros((P, H), dtype=torch.float32, device=dev)
         parts = lib.gcow_embed_type_parts(B * S)
-        tpart = torch.empty((parts, NT * H), dtype=torch.float32, device=dev)
+        tpart = _ws("embed_type_part", (parts, NT * H), torch.float32, dev)
         dtyp = torch.empty((NT, H), dtype=torch.float32, device=dev)
         _chk(lib.gcow_embed3_bwd(g.data_ptr(), ids.data_ptr(), ty.data_ptr(), order.data_ptr(), dtok.data_ptr(), dpos.data_ptr(),
                                  tpart.data_ptr(), B, S, H, NT, _stream(dev)), "gcow_embed3_bwd")
@@ -867,7 +925,9 @@ class _ConvIgemmFn(torch.autograd.Function):
             _launches += 2
         if ctx.needs_input_grad[1]:
             split = lib.gcow_conv_wgrad_split(N, H, W, C, Co, KH, KW, pad_h, pad_w)
-            part = torch.empty((split, Co, KH * KW * C), dtype=torch.float32, device=dev)
+            # the partial sums are scratch when an ordered sum follows; a single part IS the result
+            part = (_ws("conv_wgrad_part", (split, Co, KH * KW * C), torch.float32, dev) if split > 1 else
+                    torch.empty((1, Co, KH * KW * C), dtype=torch.float32, device=dev))
             _chk(lib.gcow_conv_wgrad(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, KH, KW, pad_h, pad_w,
                                      err, st), "gcow_conv_wgrad")
             _launches += 1
@@ -916,7 +976,9 @@ def conv_route(x: torch.Tensor, m) -> str:
             and all(isinstance(p, int) for p in m.padding) and m.stride[0] == m.stride[1]
             and m.padding[0] == m.padding[1] and m.kernel_size[0] == m.kernel_size[1] and x.is_cuda and x.dim() == 4):
         k, s, p, w = m.kernel_size[0], m.stride[0], m.padding[0], m.weight
-        if k == 1 and p == 0:
+        if k == 1 and p == 0 and s == 1 and _onebyone_on_igemm() and conv_igemm_usable(x, w, m.stride, m.padding, 1, (1, 1), True):
+            path = "igemm"
+        elif k == 1 and p == 0:
             if mode == "auto":
                 oh, ow = (x.shape[2] - 1) // s + 1, (x.shape[3] - 1) // s + 1
                 rows = x.shape[0] * oh * ow
@@ -932,7 +994,12 @@ def conv_route(x: torch.Tensor, m) -> str:
     return path
 
 
-def conv_igemm_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups: int, dilation) -> bool:
+def _onebyone_on_igemm() -> bool:
+    import os
+    return os.environ.get("GCOW_CONV1X1", "gemm") == "igemm"
+
+
+def conv_igemm_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups: int, dilation, allow_1x1: bool = False) -> bool:
     """Stride 1, dense, input channels a multiple of 64 (whole 128-byte channel rows per filter tap),
     output channels a multiple of 8, padding below the filter size."""
     if not (x.is_cuda and x.dim() == 4 and _have("gcow_conv_fwd") and groups == 1 and tuple(dilation) == (1, 1)):
@@ -940,7 +1007,7 @@ def conv_igemm_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups:
     if tuple(stride) != (1, 1) or not all(isinstance(p, int) for p in padding):
         return False
     KH, KW = w.shape[2], w.shape[3]
-    if KH * KW == 1 or padding[0] >= KH or padding[1] >= KW:
+    if (KH * KW == 1 and not allow_1x1) or padding[0] >= KH or padding[1] >= KW:
         return False
     # the data gradient swaps the channel roles, so both counts must be whole 64-channel rows
     return x.shape[1] % 64 == 0 and w.shape[0] % 64 == 0
@@ -1008,11 +1075,59 @@ class _AttentionFn(torch.autograd.Function):
         return dq, dk, dv, None
 
 
-def attention_enabled() -> bool:
-    """The unfused own attention is opt-in (GCOW_ATTENTION=own): it materialises the S x S
-    score matrices, so the fused library kernel behind scaled_dot_product_attention is faster."""
+class _FusedAttentionFn(torch.autograd.Function):
+    """Fused self-attention on the tcgen05 kernels of csrc/ops/attention_tcgen05.cu: packed qkv [B, S, 3, H, 64] in,
+    context [B, S, H*64] out; the backward recomputes the probabilities from the stored log-sum-exp and writes
+    the packed gradient [B, S, 3, H, 64]."""
+
+    @staticmethod
+    def forward(ctx, qkv, scale):
+        global _launches
+        B, S, _, H, D = qkv.shape
+        q = qkv if (qkv.dtype == torch.bfloat16 and qkv.is_contiguous()) else qkv.to(torch.bfloat16).contiguous()
+        out = torch.empty((B, S, H * D), dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+        _chk(_native.cuda().gcow_attention_fwd(q.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, H, D, scale,
+                                               _error_word(q.device).data_ptr(), _stream(q.device)), "gcow_attention_fwd")
+        _launches += 1
+        ctx.save_for_backward(q, out, lse)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, go):
+        global _launches
+        q, out, lse = ctx.saved_tensors
+        B, S, _, H, D = q.shape
+        g = go if (go.dtype == torch.bfloat16 and go.is_contiguous()) else go.to(torch.bfloat16).contiguous()
+        dqkv = torch.empty_like(q)
+        delta = _ws("attn_delta", (B, H, S), torch.float32, q.device)
+        _chk(_native.cuda().gcow_attention_bwd(q.data_ptr(), out.data_ptr(), g.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                                               dqkv.data_ptr(), B, S, H, D, ctx.scale, _error_word(q.device).data_ptr(),
+                                               _stream(q.device)), "gcow_attention_bwd")
+        _launches += 3
+        return dqkv, None
+
+
+def fused_attention_usable(qkv: torch.Tensor) -> bool:
+    """Head dimension 64 and a sequence length that is a multiple of 128, at most 512."""
+    if not (qkv.is_cuda and qkv.dim() == 5 and _have("gcow_attention_fwd")):
+        return False
+    B, S, three, H, D = qkv.shape
+    return three == 3 and bool(_native.cuda().gcow_attention_supported(B, S, H, D))
+
+
+def fused_attention(qkv: torch.Tensor) -> torch.Tensor:
+    """qkv: [B, S, 3, H, 64] -> context [B, S, H*64]."""
+    return _FusedAttentionFn.apply(qkv, 1.0 / (qkv.shape[-1] ** 0.5))
+
+
+def attention_mode() -> str:
+    """GCOW_ATTENTION=lib sends self-attention to PyTorch's scaled_dot_product_attention (the comparison arm);
+    by default the own backend uses the fused tcgen05 kernels where they apply (head dimension 64, sequence a
+    multiple of 128 up to 512) and batched tcgen05 GEMMs with softmax kernels elsewhere."""
     import os
-    return os.environ.get("GCOW_ATTENTION", "lib") == "own"
+    return os.environ.get("GCOW_ATTENTION", "own")
 
 
 def attention_usable(qkv: torch.Tensor) -> bool:

@@ -64,7 +64,7 @@ class Conv2d(nn.Conv2d):
             return K.conv1x1(x, self.weight, self.bias)
         if path == "gemm1x1_strided":
             s = self.stride[0]          # a strided 1x1 convolution reads every s-th pixel: subsample, then the GEMM
-            return K.conv1x1(x[:, :, ::s, ::s].contiguous(memory_format=torch.channels_last), self.weight, self.bias)
+            return K.conv1x1(K.subsample(x, s), self.weight, self.bias)
         if path == "igemm":
             return K.conv_igemm(x, self.weight, self.bias, self.padding)
         if path == "im2col":
@@ -159,8 +159,10 @@ class _PackedSdpaFn(torch.autograd.Function):
 def attention(qkv: torch.Tensor) -> torch.Tensor:
     """qkv: [B, S, 3, heads, head_dim] -> context [B, S, heads*head_dim] (no mask, no dropout)."""
     B, S, _, H, D = qkv.shape
-    if backend.get_backend() == "own" and K.attention_enabled() and K.attention_usable(qkv):
-        return K.attention(qkv)
+    if backend.get_backend() == "own" and K.fused_attention_usable(qkv) and K.attention_mode() != "lib":
+        return K.fused_attention(qkv)           # one tcgen05 kernel forward, two backward
+    if backend.get_backend() == "own" and K.attention_mode() != "lib" and K.attention_usable(qkv):
+        return K.attention(qkv)                 # other shapes: batched tcgen05 GEMMs + softmax kernels
     if qkv.is_cuda and qkv.requires_grad and backend.get_backend() == "own":
         return _PackedSdpaFn.apply(qkv)
     q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))     # [B, H, S, D]

@@ -271,13 +271,52 @@ def test_batched_gemm_and_own_attention():
     assert (g - x.grad).abs().max().item() < 0.05 * x.grad.abs().max().item() + 0.02
 
 
-def test_packed_sdpa_matches_plain_autograd():
+@pytest.mark.parametrize("shape", [(2, 128, 2, 64), (1, 256, 3, 64), (2, 384, 2, 64), (1, 512, 4, 64)])
+def test_fused_attention_matches_fp32_reference(shape):
+    """Forward and the three gradients of the fused tcgen05 attention against softmax(QK^T / sqrt d) V in fp32 on
+    the same bf16-rounded inputs."""
+    from gcow_b200.ops import kernels as K
+    B, S, H, D = shape
+    torch.manual_seed(sum(shape))
+    qkv = (torch.randn(B, S, 3, H, D, device="cuda") * 0.8).bfloat16().requires_grad_(True)
+    assert K.fused_attention_usable(qkv)
+    w = torch.randn(B, S, H * D, device="cuda").bfloat16()
+    o = K.fused_attention(qkv)
+    (o.float() * w.float()).sum().backward()
+    K.check_errors()
+    g = qkv.grad.float().clone()
+    x = qkv.detach().float().requires_grad_(True)
+    q, k, v = (x[:, :, i].transpose(1, 2) for i in range(3))
+    p = torch.softmax(q @ k.transpose(-1, -2) / D ** 0.5, dim=-1)
+    oref = (p @ v).transpose(1, 2).reshape(B, S, H * D)
+    (oref * w.float()).sum().backward()
+    assert (o.float() - oref).abs().max().item() < 0.02
+    for i, name in enumerate(("dq", "dk", "dv")):
+        err = (g[:, :, i] - x.grad[:, :, i]).abs().max().item()
+        assert err < 0.03 * x.grad[:, :, i].abs().max().item() + 0.01, (name, err)
+
+
+def test_attention_module_routes_to_the_fused_kernel():
+    from gcow_b200.ops import kernels as K, nn as gnn, set_backend
+    set_backend("own")
+    qkv = (torch.randn(1, 128, 3, 2, 64, device="cuda") * 0.5).bfloat16()
+    before = K.launch_count()
+    o = gnn.attention(qkv)
+    assert K.launch_count() == before + 1 and o.shape == (1, 128, 128)      # one launch: the fused forward
+    small = (torch.randn(1, 64, 3, 2, 64, device="cuda") * 0.5).bfloat16()  # 64 positions: the batched-GEMM path
+    before = K.launch_count()
+    gnn.attention(small)
+    assert K.launch_count() == before + 3
+
+
+def test_packed_sdpa_matches_plain_autograd(monkeypatch):
     from gcow_b200.ops import nn as gnn, set_backend
     torch.manual_seed(10)
     B, S, H, D = 2, 64, 4, 64
     base = (torch.randn(B, S, 3, H, D, device="cuda") * 0.5).bfloat16()
     w = torch.randn(B, S, H * D, device="cuda").bfloat16()
     outs = {}
+    monkeypatch.setenv("GCOW_ATTENTION", "lib")          # the library arm of the own backend
     for be in ("torch", "own"):
         set_backend(be)
         qkv = base.clone().requires_grad_(True)

@@ -118,7 +118,8 @@ class _FakeBucket:
 
 def test_error_feedback_keeps_the_accumulated_error_bounded():
     """With the residual fed back, the sum of what is transmitted over T steps tracks T times the gradient: the
-    error stays the size of ONE step's quantisation error instead of growing with T."""
+    error stays the size of ONE step's quantisation error instead of growing with T. (At 8 bit/value; at 4 bit/value
+    the codec's error on noise-like blocks is as large as the block itself and the feedback loop does not contract.)"""
     from gcow_b200.comm import CompressedAllReduce
     from gcow_b200.config import GcowConfig
     from gcow_b200.parallel.ddp import GcowDDPState, compressed_allreduce_hook
@@ -127,7 +128,7 @@ def test_error_feedback_keeps_the_accumulated_error_bounded():
     T = 16
     errs = {}
     for ef in (False, True):
-        cfg = GcowConfig(rate=4, comm_ctas=16, error_feedback=ef)
+        cfg = GcowConfig(rate=8, comm_ctas=16, error_feedback=ef)
         st = GcowDDPState(CompressedAllReduce(1 << 16, cfg), cfg)
         total = torch.zeros_like(g)
         for _ in range(T):
@@ -137,4 +138,4 @@ def test_error_feedback_keeps_the_accumulated_error_bounded():
         torch.cuda.synchronize()
         errs[ef] = float((total - T * g).norm() / (T * g).norm())
     assert errs[True] < 0.25 * errs[False], errs
-    assert errs[True] < 0.1, errs
+    assert errs[True] < 0.02, errs
