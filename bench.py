@@ -359,6 +359,12 @@ def main() -> int:
     for _ in range(2):
         e2e_step()
     torch.cuda.synchronize()
+    # which kernel family served each convolution call of one step (forward pass of every layer)
+    from gcow_b200.ops import kernels as _kern
+    _kern.conv_path_counts(reset=True)
+    dev_step()
+    torch.cuda.synchronize()
+    conv_paths = _kern.conv_path_counts(reset=True)
 
     sampler = ClockSampler(local).start() if rank == 0 else None
     l0 = tr.gpu_launches()
@@ -404,6 +410,10 @@ def main() -> int:
                        "seq_len": args.seq_len if tr.kind == "bert" else None, "image": 224,
                        "parallelism": f"dp{world}", "bucket_mb": cfg.bucket_mb, "rate_bits_per_value": args.rate,
                        "variant": cfg.variant, "ops": args.ops, "comm_ctas": tr.hook_state.ar.ctas if tr.hook_state else 0,
+                       "conv_paths_per_step": conv_paths,
+                       "conv_backend": {"own": sum(v for k, v in conv_paths.items() if k != "cudnn"),
+                                        "cudnn": conv_paths.get("cudnn", 0)},
+                       "attention": ("fused tcgen05" if tr.kind == "bert" and args.ops == "own" else None),
                        "l2": "inputs+activations larger than L2, no flush"},
             "e2e": {"value": total * args.steps / (e2e_ms / 1e3), "unit": unit, "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},

@@ -5,7 +5,8 @@
 The distinct convolution configurations of the model (input channels, output channels, filter, stride,
 input extent) are collected with forward hooks on one forward pass; each is then timed as the model runs
 it: ``gcow_b200.ops.nn.Conv2d`` forward plus backward through autograd (forward, data gradient and weight
-gradient together, including the layout and weight-format work the module does around its kernels), once
+gradient together, including the layout and weight-format kernels the module runs around them; device time, with
+the calls enqueued behind a spin kernel so that host latency does not count), once
 on the default own routing and once with every convolution sent to cuDNN (``GCOW_CONV=lib``). The
 table's last row sums ``count x time`` over the model: the convolution cost of one training step on
 either arm. The reference's models call nn.Conv2d at hw/models/resenet.py:11-17,79,113.
@@ -20,10 +21,25 @@ from pathlib import Path
 
 import torch
 
-from gcow_b200.bench.codec_bench import time_cuda
 from gcow_b200.models import MODELS
 from gcow_b200.ops import backend
 from gcow_b200.ops import nn as gnn
+
+
+def time_queued(fn, iters: int, warmup: int = 2) -> float:
+    """Device milliseconds per call with the host out of the picture: a spin kernel keeps the GPU busy while all
+    ``iters`` calls are enqueued behind it, so the timed region (CUDA events) runs back to back on the device."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(int(6e7))          # about 30 ms at 1.9 GHz: far longer than enqueueing the calls takes
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
 
 
 def collect(arch: str, batch: int, image: int):
@@ -68,13 +84,16 @@ def main(argv=None):
         gy = None
         arms = [("own", None), ("cudnn", "lib")]
         if args.alt_1x1 and k == 1 and s == 1:
-            arms.append(("igemm1x1", "auto"))
+            arms.append(("igemm1x1", "auto"))      # forces the one-tap implicit GEMM whatever the pixel count
         for arm, env in arms:
             if env is None:
                 os.environ.pop("GCOW_CONV", None)
             else:
                 os.environ["GCOW_CONV"] = env
-            os.environ["GCOW_CONV1X1"] = "igemm" if arm == "igemm1x1" else "gemm"
+            if arm == "igemm1x1":
+                os.environ["GCOW_CONV1X1"] = "igemm"
+            else:
+                os.environ.pop("GCOW_CONV1X1", None)
             with torch.autocast("cuda", dtype=torch.bfloat16):
                 y = conv(x)
             if gy is None:
@@ -87,7 +106,7 @@ def main(argv=None):
                 with torch.autocast("cuda", dtype=torch.bfloat16):
                     out = conv(x)
                 out.backward(gy)
-            ms, _ = time_cuda(step, args.iters)
+            ms = time_queued(step, args.iters)
             row[f"{arm}_ms"] = round(ms, 4)
             if arm in tot:
                 tot[arm] += ms * count

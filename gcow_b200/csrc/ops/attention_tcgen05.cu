@@ -21,8 +21,9 @@
 //            gradients deterministic.
 //  delta = rowsum(dO * O) comes from a small elementwise kernel.
 //
-// One thread per accumulator row (128 threads per CTA); thread 0 issues the TMA loads and the
-// MMAs. Every mbarrier wait is bounded: after a fixed number of polls the CTA records an error
+// 512 threads per CTA: four threads share an accumulator row (the four warps that may read a
+// tensor-memory lane quarter each take a quarter of the columns), which is what hides the latency
+// of the exponentials; thread 0 issues the TMA loads and the MMAs. Every mbarrier wait is bounded: after a fixed number of polls the CTA records an error
 // code, leaves its loops, waits (bounded) for outstanding MMAs, frees its tensor memory and
 // returns. No load uses cluster multicast. The reference's models are CNNs
 // (hw/models/train_imagenet.py:199-202); this kernel serves the BERT configuration.
@@ -40,6 +41,7 @@ constexpr int D = 64;                 // head dimension: one 128-byte row
 constexpr int TILE = 128;             // rows of a query / key tile
 constexpr int TILE_BYTES = TILE * D * 2;   // 16 KB
 constexpr int MAX_S = 512;
+constexpr int NT = 512;               // threads per CTA: 4 column groups x 128 rows
 
 struct Params {
   __nv_bfloat16* out;      // forward: context [B][S][H][64]
@@ -56,6 +58,7 @@ struct Bars {
   uint64_t a, b, c, d, e[2], f[2], drain;
   uint32_t tmem_base;
   volatile uint32_t abort;
+  float red[4][TILE];      // per-row partial maxima / sums of the four column groups
 };
 
 __device__ __forceinline__ uint32_t idesc_f16(int n, bool a_mn, bool b_mn) {
@@ -128,7 +131,7 @@ __device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_smem, uint32_
 }
 
 // ------------------------------------------------------------------------------ forward
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(NT, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const Params p) {
   extern __shared__ uint8_t raw[];
@@ -139,6 +142,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   uint8_t* sP1 = sV + 4 * TILE_BYTES;       // P of keys 256..511
   Bars* bs = reinterpret_cast<Bars*>(sP1 + 4 * TILE_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = (warp & 3) * 32 + (tid & 31), cg = warp >> 2;      // accumulator row, column group 0..3
   const int q0 = blockIdx.x * TILE, h = blockIdx.y, b = blockIdx.z;
   const int nk = p.S, ntile = nk / TILE;
   const int half0 = nk < 256 ? nk : 256, half1 = nk - half0;
@@ -153,7 +157,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bs->tmem_base;
-  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   bool ok = true;
 
   if (tid == 0) {
@@ -174,15 +178,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   ok = __syncthreads_and(ok);
   if (ok) {
     tc_fence_after();
-    // pass 1: row maximum over every key
+    // pass 1: row maximum over every key; this thread scans its quarter of the columns
     float m = -INFINITY;
-    for (int c = 0; c < nk / 32; c++) {
+    for (int c = cg * (nk / 128); c < (cg + 1) * (nk / 128); c++) {
       uint32_t r[32];
       tc_ld32(lane_addr + c * 32, r);
       tc_wait_ld();
 #pragma unroll
       for (int j = 0; j < 32; j++) m = fmaxf(m, __uint_as_float(r[j]));
     }
+    bs->red[cg][row] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(bs->red[0][row], bs->red[1][row]), fmaxf(bs->red[2][row], bs->red[3][row]));
+    __syncthreads();                        // red is reused for the row sums below
     const float ms = m * p.scale_log2;
     float l = 0.0f;
     // pass 2: exponentials, row sum, P as bf16 in the A-operand layout; then O += P V for that half
@@ -190,7 +198,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const int keys = hf ? half1 : half0;
       if (!keys) break;
       uint8_t* sP = hf ? sP1 : sK;
-      for (int c = 0; c < keys / 32; c++) {
+      for (int c = cg * (keys / 128); c < (cg + 1) * (keys / 128); c++) {
         uint32_t r[32];
         tc_ld32(lane_addr + hf * 256 + c * 32, r);
         tc_wait_ld();
@@ -200,7 +208,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           v[j] = exp2f(fmaf(__uint_as_float(r[j]), p.scale_log2, -ms));
           l += v[j];
         }
-        store_kmajor32(sP, tid, c * 32, v);
+        store_kmajor32(sP, row, c * 32, v);
       }
       proxy_fence();
       tc_fence_before();
@@ -220,14 +228,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         }
       }
     }
+    bs->red[cg][row] = l;
     ok = ok && wait(bs, &bs->d, 0, p.error, 24);
     ok = __syncthreads_and(ok);
     if (ok) {
       tc_fence_after();
+      l = (bs->red[0][row] + bs->red[1][row]) + (bs->red[2][row] + bs->red[3][row]);
       const float inv = 1.0f / l;
-      const size_t row = (((size_t)b * p.S + q0 + tid) * p.H + h) * D;
-#pragma unroll
-      for (int c = 0; c < 2; c++) {
+      const size_t orow = (((size_t)b * p.S + q0 + row) * p.H + h) * D;
+      if (cg < 2) {                          // 64 output columns: column groups 0 and 1 take 32 each
+        const int c = cg;
         uint32_t r[32];
         tc_ld32(lane_addr + c * 32, r);
         tc_wait_ld();
@@ -237,10 +247,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
                                pack2(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv),
                                pack2(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv),
                                pack2(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv));
-          *reinterpret_cast<uint4*>(p.out + row + c * 32 + j * 8) = o;
+          *reinterpret_cast<uint4*>(p.out + orow + c * 32 + j * 8) = o;
         }
       }
-      p.lse[((size_t)b * p.H + h) * p.S + q0 + tid] = ms + log2f(l);
+      if (cg == 0) p.lse[((size_t)b * p.H + h) * p.S + q0 + row] = ms + log2f(l);
     }
   }
   if (tid == 0) drain(bs);
@@ -277,9 +287,9 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 // P and dS of one 128 x 128 tile from S (tensor-memory columns 0..127) and dP (columns 128..255): this thread's
 // row. WRITE_P: also emit P. MN: operands go to the MN-major layout (reduction over rows), else K-major.
 template <bool WRITE_P, bool MN>
-__device__ __forceinline__ void softmax_grad_tile(uint32_t lane_addr, int row, float lse, float delta, const Params& p,
+__device__ __forceinline__ void softmax_grad_tile(uint32_t lane_addr, int row, int c, float lse, float delta, const Params& p,
                                                   uint8_t* sP, uint8_t* sdS) {
-  for (int c = 0; c < 4; c++) {
+  {                                          // this thread's 32-column chunk c of the row
     uint32_t rs[32], rd[32];
     tc_ld32(lane_addr + c * 32, rs);
     tc_ld32(lane_addr + 128 + c * 32, rd);
@@ -301,9 +311,8 @@ __device__ __forceinline__ void softmax_grad_tile(uint32_t lane_addr, int row, f
 }
 
 // Write this thread's row of a 64-column fp32 accumulator (tensor-memory column `col`) as bf16 to `dst`.
-__device__ __forceinline__ void store_acc_row(uint32_t lane_addr, int col, __nv_bfloat16* dst) {
-#pragma unroll
-  for (int c = 0; c < 2; c++) {
+__device__ __forceinline__ void store_acc_row(uint32_t lane_addr, int col, int c, __nv_bfloat16* dst) {
+  {                                          // chunk c (0 or 1) of the 64 columns
     uint32_t r[32];
     tc_ld32(lane_addr + col + c * 32, r);
     tc_wait_ld();
@@ -319,7 +328,7 @@ __device__ __forceinline__ void store_acc_row(uint32_t lane_addr, int col, __nv_
 }
 
 // ------------------------------------------------------------------- backward: dK and dV
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(NT, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                      const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const Params p) {
   extern __shared__ uint8_t raw[];
@@ -332,6 +341,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   uint8_t* sdS = sP + 2 * TILE_BYTES;        // 32 KB, MN-major
   Bars* bs = reinterpret_cast<Bars*>(sdS + 2 * TILE_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = (warp & 3) * 32 + (tid & 31), cg = warp >> 2;
   const int k0 = blockIdx.x * TILE, h = blockIdx.y, b = blockIdx.z;
   const int nq = p.S / TILE;
 
@@ -346,7 +356,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bs->tmem_base;
-  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t COL_S = 0, COL_DV = 256, COL_DK = 320;      // dP sits at COL_S + 128
   bool ok = true;
 
@@ -382,7 +392,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tc_commit(&bs->c);
       }
     }
-    const size_t stat = ((size_t)b * p.H + h) * p.S + i * TILE + tid;
+    const size_t stat = ((size_t)b * p.H + h) * p.S + i * TILE + row;
     const float lse = p.lse[stat], delta = p.delta[stat];
     ok = wait(bs, &bs->c, i & 1, p.error, 34);
     // P / dS of iteration i-1 must have been consumed by its MMAs before they are overwritten
@@ -390,7 +400,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     ok = __syncthreads_and(ok);
     if (!ok) break;
     tc_fence_after();
-    softmax_grad_tile<true, true>(lane_addr + COL_S, tid, lse, delta, p, sP, sdS);
+    softmax_grad_tile<true, true>(lane_addr + COL_S, row, cg, lse, delta, p, sP, sdS);
     proxy_fence();
     tc_fence_before();
     __syncthreads();
@@ -415,9 +425,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   ok = __syncthreads_and(ok);
   if (ok) {
     tc_fence_after();
-    const size_t row = ((((size_t)b * p.S + k0 + tid) * 3) * p.H + h) * D;      // [b][s][which][h][d], which = 0
-    store_acc_row(lane_addr, COL_DK, p.dqkv + row + (size_t)1 * p.H * D);
-    store_acc_row(lane_addr, COL_DV, p.dqkv + row + (size_t)2 * p.H * D);
+    const size_t orow = ((((size_t)b * p.S + k0 + row) * 3) * p.H + h) * D;     // [b][s][which][h][d], which = 0
+    // column groups 0, 1: the two halves of dK's row; 2, 3: of dV's row
+    store_acc_row(lane_addr, cg < 2 ? COL_DK : COL_DV, cg & 1, p.dqkv + orow + (size_t)(cg < 2 ? 1 : 2) * p.H * D);
   }
   if (tid == 0) drain(bs);
   tc_fence_before();
@@ -426,7 +436,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
 }
 
 // ------------------------------------------------------------------------ backward: dQ
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(NT, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const Params p) {
   extern __shared__ uint8_t raw[];
@@ -438,6 +448,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   uint8_t* sdS = sV + 2 * TILE_BYTES;        // 32 KB, K-major: [128 queries][128 keys] as two 64-key blocks
   Bars* bs = reinterpret_cast<Bars*>(sdS + 2 * TILE_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = (warp & 3) * 32 + (tid & 31), cg = warp >> 2;
   const int q0 = blockIdx.x * TILE, h = blockIdx.y, b = blockIdx.z;
   const int nkv = p.S / TILE;
 
@@ -452,10 +463,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bs->tmem_base;
-  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t COL_S = 0, COL_DQ = 256;
   bool ok = true;
-  const size_t stat = ((size_t)b * p.H + h) * p.S + q0 + tid;
+  const size_t stat = ((size_t)b * p.H + h) * p.S + q0 + row;
   const float lse = p.lse[stat], delta = p.delta[stat];
 
   if (tid == 0) {
@@ -493,7 +504,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     ok = __syncthreads_and(ok);
     if (!ok) break;
     tc_fence_after();
-    softmax_grad_tile<false, false>(lane_addr + COL_S, tid, lse, delta, p, nullptr, sdS);
+    softmax_grad_tile<false, false>(lane_addr + COL_S, row, cg, lse, delta, p, nullptr, sdS);
     proxy_fence();
     tc_fence_before();
     __syncthreads();
@@ -513,8 +524,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   ok = __syncthreads_and(ok);
   if (ok) {
     tc_fence_after();
-    const size_t row = ((((size_t)b * p.S + q0 + tid) * 3) * p.H + h) * D;
-    store_acc_row(lane_addr, COL_DQ, p.dqkv + row);
+    const size_t orow = ((((size_t)b * p.S + q0 + row) * 3) * p.H + h) * D;
+    if (cg < 2) store_acc_row(lane_addr, COL_DQ, cg, p.dqkv + orow);
   }
   if (tid == 0) drain(bs);
   tc_fence_before();
@@ -586,7 +597,7 @@ int gcow_attention_fwd(const void* qkv, void* out, float* lse, int B, int S, int
   Params p = {};
   p.out = (__nv_bfloat16*)out; p.lse = lse; p.B = B; p.S = S; p.H = H;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.error = error;
-  attn_fwd_kernel<<<dim3(S / TILE, H, B), 128, kFwdSmem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  attn_fwd_kernel<<<dim3(S / TILE, H, B), NT, kFwdSmem, (cudaStream_t)stream>>>(tq, tk, tv, p);
   return (int)cudaGetLastError();
 }
 
@@ -606,8 +617,8 @@ int gcow_attention_bwd(const void* qkv, const void* out, const void* dout, const
   Params p = {};
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dqkv = (__nv_bfloat16*)dqkv; p.B = B; p.S = S; p.H = H;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.error = error;
-  attn_bwd_dkdv_kernel<<<dim3(S / TILE, H, B), 128, kBwdSmem, st>>>(tq, tk, tv, tdo, p);
-  attn_bwd_dq_kernel<<<dim3(S / TILE, H, B), 128, kDqSmem, st>>>(tq, tk, tv, tdo, p);
+  attn_bwd_dkdv_kernel<<<dim3(S / TILE, H, B), NT, kBwdSmem, st>>>(tq, tk, tv, tdo, p);
+  attn_bwd_dq_kernel<<<dim3(S / TILE, H, B), NT, kDqSmem, st>>>(tq, tk, tv, tdo, p);
   return (int)cudaGetLastError();
 }
 

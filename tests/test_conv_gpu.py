@@ -155,4 +155,7 @@ def test_resnet50_step_sends_no_convolution_to_cudnn(monkeypatch):
     counts = K.conv_path_counts(reset=True)
     assert sum(counts.values()) == 53 and counts.get("cudnn", 0) == 0, counts
     assert counts["gemm1x1"] == 33 and counts["gemm1x1_strided"] == 3 and counts["igemm"] == 13 and counts["im2col"] == 4
+    # at batch 256 the 1x1 layers of the 56 x 56 stage move to the one-tap implicit GEMM (a routing rule on the pixel count)
+    big = torch.empty(256, 64, 56, 56, device="meta")
+    assert K._onebyone_on_igemm(big) and not K._onebyone_on_igemm(x)
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.parameters())
