@@ -7,6 +7,10 @@ against the ``.zfp`` golden).
     python -m gcow_b200.cli 510 --tolerance 1e-3 --golden path/compressed_2d_510.zfp
     python -m gcow_b200.cli 4096 --rate 8 --dim 2 --out field.gcow --device cuda
     python -m gcow_b200.cli --input grad.npy --dim 1 --rate 8 --roundtrip
+    python -m gcow_b200.cli --input AEROD_v_1_1800_3600.dat --shape 1800 3600 --print 4     # a raw float32 field
+
+The last form is the counterpart of the reference's data probe (hw/tests/parse_dat.cpp:1-38), which reads a raw
+1800 x 3600 float field and prints a few values.
 """
 from __future__ import annotations
 
@@ -31,7 +35,9 @@ def reference_field(n: int) -> np.ndarray:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="gcow-codec", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("n", nargs="?", type=int, default=0, help="side of the generated n x n field")
-    ap.add_argument("--input", default="", help=".npy file to compress instead of the generated field")
+    ap.add_argument("--input", default="", help=".npy file, or with --shape a raw float32 file, to compress instead of the generated field")
+    ap.add_argument("--shape", type=int, nargs="+", default=None, metavar="N",
+                    help="rows [columns] of a raw little-endian float32 --input file (no header)")
     ap.add_argument("--dim", type=int, default=2, choices=[1, 2])
     m = ap.add_mutually_exclusive_group()
     m.add_argument("--rate", type=float)
@@ -49,7 +55,13 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     if not (args.rate or args.tolerance or args.precision):
         args.tolerance = 1e-3                      # the reference kernel's hard-wired setting (hw/src/gcow.cpp:44-45)
-    if args.input:
+    if args.input and args.shape:
+        arr = np.fromfile(args.input, dtype="<f4")
+        want = int(np.prod(args.shape))
+        if arr.size < want:
+            ap.error(f"{args.input} holds {arr.size} float32 values, --shape asks for {want}")
+        arr = arr[:want].reshape(args.shape)
+    elif args.input:
         arr = np.load(args.input).astype(np.float32)
     elif args.n > 0:
         arr = reference_field(args.n)

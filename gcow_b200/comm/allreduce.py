@@ -187,25 +187,34 @@ class CompressedAllReduce:
 
     # -------------------------------------------------------------------- call
     def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, stream: torch.cuda.Stream | None = None,
-                 variant: str | None = None) -> torch.Tensor:
+                 variant: str | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
         """Launch the all-reduce of ``x`` (in place unless ``out`` is given) on
-        ``stream`` (default: the current stream). Does not synchronise."""
+        ``stream`` (default: the current stream). Does not synchronise.
+        ``residual`` (float32, same size): error feedback inside the kernel - this rank contributes
+        ``x + residual`` and ``residual`` becomes what its compressed code of that sum dropped."""
         if x.dtype != torch.float32 or not x.is_cuda or not x.is_contiguous():
             raise TypeError("need a contiguous float32 CUDA tensor")
         out = x if out is None else out
         n = x.numel()
         s = stream or torch.cuda.current_stream(self.device)
+        if residual is not None and (residual.dtype != torch.float32 or residual.numel() != n or not residual.is_contiguous()
+                                     or residual.device != x.device):
+            raise TypeError("residual must be a contiguous float32 tensor of the input's size on the same device")
         for lo in range(0, n, self.max_numel):
             hi = min(n, lo + self.max_numel)
-            self._launch(x.view(-1)[lo:hi], out.view(-1)[lo:hi], s, variant)
+            self._launch(x.view(-1)[lo:hi], out.view(-1)[lo:hi], s, variant,
+                         residual.view(-1)[lo:hi] if residual is not None else None)
         return out
 
-    def _launch(self, x: torch.Tensor, out: torch.Tensor, s: torch.cuda.Stream, variant: str | None) -> None:
+    def _launch(self, x: torch.Tensor, out: torch.Tensor, s: torch.cuda.Stream, variant: str | None,
+                residual: torch.Tensor | None = None) -> None:
         n = x.numel()
         if n == 0:
             return
         if self.header_only:
             with torch.cuda.stream(s):
+                if residual is not None:          # everything is dropped: the residual keeps the whole input
+                    residual.add_(x)
                 out.zero_()
             self.calls += 1
             self.bytes_in += n * 4
@@ -219,11 +228,12 @@ class CompressedAllReduce:
         post = self._avg_scale
         if v == 1 and shift:          # one-shot has no final decode to fold the shift into
             post, shift = post * 2.0 ** (-shift), 0
-        err = self.lib.gcow_ar_launch(
+        err = self.lib.gcow_ar_launch_ef(
             x.data_ptr(), out.data_ptr(), n, self.rank, self.world, v, self.bits, self.ctas_for(n), shift,
             C.c_float(post), self._peer_array, C.c_void_p(self.arena.mc_ptr), self.region_cap, self.epoch,
             int(self.cfg.timeout_ms) * 1_000_000, self.status.data_ptr(), self.status[8:].data_ptr(),
-            self.stamps.data_ptr() if self.stamps is not None else None, s.cuda_stream)
+            self.stamps.data_ptr() if self.stamps is not None else None,
+            residual.data_ptr() if residual is not None else None, s.cuda_stream)
         if err:
             raise RuntimeError(f"gcow_ar_launch failed: {err}")
         self.calls += 1

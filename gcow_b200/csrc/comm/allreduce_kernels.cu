@@ -51,6 +51,7 @@ struct ArArgs {
   const uint16_t* dec_table;
   const uint32_t* pair_table;
   const uint32_t* loop_table;
+  float* residual;            // error feedback: added to the input before encoding, then set to x - D(E(x)); or nullptr
   ArLayout L;
 };
 
@@ -183,6 +184,27 @@ __device__ __forceinline__ void store_block(const float* f, float* __restrict__ 
   }
 }
 
+// Error feedback around the encoder: f += r, and after encoding r = f - D(E(f)) (what this rank's code lost).
+template <int BITS, int NW>
+__device__ __forceinline__ void encode_with_feedback(float (&f)[4], const ArArgs& a, uint64_t gb, const LeanTables& lt,
+                                                     uint32_t (&w)[NW]) {
+  const bool al = ((uintptr_t)a.residual & 15) == 0;
+  float r[4];
+  load_block(r, a.residual, a.n, gb, al);
+  const uint64_t x0 = 4 * gb;
+  if (x0 + 4 > a.n) {          // load_block pads a partial block with copies; the residual of the padding is not data
+    for (uint64_t i = a.n > x0 ? a.n - x0 : 0; i < 4; i++) r[i] = 0;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) f[i] += r[i];
+  encode_block_1d_lean<BITS>(f, lt, w);
+  float d[4];
+  decode_block_1d_lean<BITS>(d, lt, w, 0);
+#pragma unroll
+  for (int i = 0; i < 4; i++) r[i] = f[i] - d[i];
+  store_block(r, a.residual, a.n, gb, al);
+}
+
 __device__ __forceinline__ void stamp(const ArArgs& a, int slot) {
   if (a.stamps && threadIdx.x == 0) a.stamps[(uint64_t)blockIdx.x * 4 + slot] = global_ns();
 }
@@ -231,7 +253,8 @@ allreduce_fused_kernel(const ArArgs a) {
         float f[4];
         load_block(f, a.in, a.n, gb, in_al);
         uint32_t w[NW];
-        encode_block_1d_lean<BITS>(f, lt, w);
+        if (a.residual) encode_with_feedback<BITS, NW>(f, a, gb, lt, w);
+        else encode_block_1d_lean<BITS>(f, lt, w);
         for (int step = 0; step < P; step++) {
           int j = (r + 1 + step) % P;
           C::st(a.arena[j] + a.region_off + (uint64_t)r * L.slot_bytes, gb, w);
@@ -286,7 +309,8 @@ allreduce_fused_kernel(const ArArgs a) {
       float f[4];
       load_block(f, a.in, a.n, gb, in_al);
       uint32_t w[NW];
-      encode_block_1d_lean<BITS>(f, lt, w);
+      if (a.residual) encode_with_feedback<BITS, NW>(f, a, gb, lt, w);
+      else encode_block_1d_lean<BITS>(f, lt, w);
       C::st(dst, b, w);
     }
   }
@@ -449,15 +473,16 @@ int gcow_ar_max_ctas(int bits) {
   return m < kMaxCtas ? m : kMaxCtas;
 }
 
-// Launch the fused all-reduce on `stream`.
+// Launch the fused all-reduce on `stream`. `residual` (n floats, or null) enables error feedback inside the kernel: the
+// encoder sees in + residual, and residual becomes what this rank's code of that sum dropped.
 //   arenas: `world` device pointers (every rank's arena as mapped in this process)
 //   mc_arena: multicast mapping or null; region_cap: bytes of one parity's data region
 //   status: 8 u32 (device-visible); abort_flag: 1 u32; stamps: optional ctas*4 u64
 // Returns 0, a CUDA error code, or -1 / -2 for bad arguments / insufficient arena.
-int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world, int variant, int bits,
-                   int ctas, int shift, float postscale, void* const* arenas, void* mc_arena,
-                   uint64_t region_cap, uint32_t epoch, uint64_t timeout_ns, uint32_t* status,
-                   uint32_t* abort_flag, unsigned long long* stamps, void* stream) {
+int gcow_ar_launch_ef(const float* in, float* out, uint64_t n, int rank, int world, int variant, int bits,
+                      int ctas, int shift, float postscale, void* const* arenas, void* mc_arena,
+                      uint64_t region_cap, uint32_t epoch, uint64_t timeout_ns, uint32_t* status,
+                      uint32_t* abort_flag, unsigned long long* stamps, float* residual, void* stream) {
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || ctas < 1 || ctas > kMaxCtas) return -1;
   if (variant == kTwoShotNvls && !mc_arena) return -1;
   ArArgs a;
@@ -470,6 +495,7 @@ int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world,
   a.epoch = epoch;
   a.timeout_ns = timeout_ns;
   a.status = status; a.abort_flag = abort_flag; a.stamps = stamps;
+  a.residual = residual;
   a.L = ar_layout(n, world, ctas, bits, variant);
   if (a.L.region_bytes > region_cap) return -2;
   const void *etp, *dtp, *ptp, *ltp;
@@ -488,6 +514,14 @@ int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world,
     default: return -1;
   }
   return (int)cudaGetLastError();
+}
+
+int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world, int variant, int bits,
+                   int ctas, int shift, float postscale, void* const* arenas, void* mc_arena,
+                   uint64_t region_cap, uint32_t epoch, uint64_t timeout_ns, uint32_t* status,
+                   uint32_t* abort_flag, unsigned long long* stamps, void* stream) {
+  return gcow_ar_launch_ef(in, out, n, rank, world, variant, bits, ctas, shift, postscale, arenas, mc_arena, region_cap,
+                           epoch, timeout_ns, status, abort_flag, stamps, nullptr, stream);
 }
 
 // Conditional commit of an out-of-place all-reduce result (see commit_kernel).

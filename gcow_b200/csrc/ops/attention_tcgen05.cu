@@ -180,12 +180,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     tc_fence_after();
     // pass 1: row maximum over every key; this thread scans its quarter of the columns
     float m = -INFINITY;
-    for (int c = cg * (nk / 128); c < (cg + 1) * (nk / 128); c++) {
-      uint32_t r[32];
-      tc_ld32(lane_addr + c * 32, r);
-      tc_wait_ld();
+    {
+      // tensor-memory loads two chunks ahead of the arithmetic
+      const int c0 = cg * (nk / 128), c1 = (cg + 1) * (nk / 128);
+      uint32_t ra[32], rb[32];
+      tc_ld32(lane_addr + c0 * 32, ra);
+      for (int c = c0; c < c1; c += 2) {
+        tc_wait_ld();
+        if (c + 1 < c1) tc_ld32(lane_addr + (c + 1) * 32, rb);
 #pragma unroll
-      for (int j = 0; j < 32; j++) m = fmaxf(m, __uint_as_float(r[j]));
+        for (int j = 0; j < 32; j++) m = fmaxf(m, __uint_as_float(ra[j]));
+        if (c + 1 < c1) {
+          tc_wait_ld();
+          if (c + 2 < c1) tc_ld32(lane_addr + (c + 2) * 32, ra);
+#pragma unroll
+          for (int j = 0; j < 32; j++) m = fmaxf(m, __uint_as_float(rb[j]));
+        }
+      }
     }
     bs->red[cg][row] = m;
     __syncthreads();
@@ -198,17 +209,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const int keys = hf ? half1 : half0;
       if (!keys) break;
       uint8_t* sP = hf ? sP1 : sK;
-      for (int c = cg * (keys / 128); c < (cg + 1) * (keys / 128); c++) {
-        uint32_t r[32];
-        tc_ld32(lane_addr + hf * 256 + c * 32, r);
+      {
+        // this thread's one or two chunks of the half: both loads are issued before the first is used
+        const int c0 = cg * (keys / 128), two = keys / 128 == 2;
+        uint32_t ra[32], rb[32];
+        tc_ld32(lane_addr + hf * 256 + c0 * 32, ra);
+        if (two) tc_ld32(lane_addr + hf * 256 + (c0 + 1) * 32, rb);
         tc_wait_ld();
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; j++) {
-          v[j] = exp2f(fmaf(__uint_as_float(r[j]), p.scale_log2, -ms));
+          v[j] = exp2f(fmaf(__uint_as_float(ra[j]), p.scale_log2, -ms));
           l += v[j];
         }
-        store_kmajor32(sP, row, c * 32, v);
+        store_kmajor32(sP, row, c0 * 32, v);
+        if (two) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            v[j] = exp2f(fmaf(__uint_as_float(rb[j]), p.scale_log2, -ms));
+            l += v[j];
+          }
+          store_kmajor32(sP, row, (c0 + 1) * 32, v);
+        }
       }
       proxy_fence();
       tc_fence_before();

@@ -125,14 +125,15 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
         if state.timing:
             t0 = torch.cuda.Event(enable_timing=True)
             t0.record(ar.stream)
+        res = None
         if state.cfg.error_feedback:
+            # the kernel's encode phase adds the residual to this rank's contribution and leaves behind what the
+            # code of that sum dropped - no copy of the bucket and no separate codec pass
             idx = bucket.index()
             res = state.residual.get(idx)
             if res is None or res.numel() != buf.numel():
                 res = torch.zeros_like(buf)
                 state.residual[idx] = res
-            buf.add_(res)                      # re-inject what compression dropped last time
-            sent = buf.clone()
         if state.cfg.fallback_nccl:
             # safe mode: reduce into a side buffer; finish_step copies it in once all ranks
             # agree that the step's collectives succeeded, so until then the bucket keeps its local gradient
@@ -141,15 +142,10 @@ def compressed_allreduce_hook(state: GcowDDPState, bucket: dist.GradBucket) -> t
             if side is None or side.numel() != buf.numel():
                 side = torch.empty_like(buf)
                 state.side[idx] = side
-            ar(buf, out=side, stream=ar.stream)
+            ar(buf, out=side, stream=ar.stream, residual=res)
             state.pending.append((buf, side))
         else:
-            ar(buf, stream=ar.stream)
-        if state.cfg.error_feedback:
-            # residual = what this rank wanted to send minus what the codec kept of it
-            from ..codec import compress, decompress
-            kept = decompress(compress(sent, params=ar.params))
-            torch.sub(sent, kept, out=state.residual[bucket.index()])
+            ar(buf, stream=ar.stream, residual=res)
         if state.timing and len(state.comm_events) < 100000:
             t1 = torch.cuda.Event(enable_timing=True)
             t1.record(ar.stream)

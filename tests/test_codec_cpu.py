@@ -374,3 +374,21 @@ def test_cli_matches_golden_and_prints(tmp_path, capsys):
     padded = tmp_path / "p.gcow"
     assert cli.main(["100", "--device", "cpu", "--out", str(padded), "--pad64", "--iters", "1"]) == 0
     assert len(padded.read_bytes()) % 64 == 0
+
+
+def test_cli_reads_a_raw_float32_field(tmp_path, capsys):
+    """A header-less float32 dump with --shape, as the reference's data probe reads its climate field
+    (hw/tests/parse_dat.cpp:1-38): same stream as the same array given as .npy."""
+    import json
+    from gcow_b200 import cli
+    a = field(36)[:20]                                   # 20 rows x 36 columns
+    raw, npy = tmp_path / "f.dat", tmp_path / "f.npy"
+    a.astype("<f4").tofile(raw)
+    np.save(npy, a)
+    o1, o2 = tmp_path / "a.gcow", tmp_path / "b.gcow"
+    assert cli.main(["--input", str(raw), "--shape", "20", "36", "--device", "cpu", "--out", str(o1), "--iters", "1",
+                     "--print", "3"]) == 0
+    first = capsys.readouterr().out.strip().splitlines()
+    assert first[0].split()[0].startswith("1.0") and json.loads(first[-1])["values"] == 720
+    assert cli.main(["--input", str(npy), "--device", "cpu", "--out", str(o2), "--iters", "1"]) == 0
+    assert o1.read_bytes() == o2.read_bytes()
