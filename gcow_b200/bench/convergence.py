@@ -4,7 +4,7 @@
 
 The question the reference's two study scripts exist to answer (sweeps over rates and tolerances,
 hw/models/train_resnet_cifar10.py:38-42,190-217; hw/models/train_imagenet.py:154-155,372-393), asked here of the
-on-the-wire path: ResNet-18 on a learnable synthetic 10-class task (class patterns plus pixel noise), the same
+on-the-wire path: ResNet-18 on a learnable synthetic 100-class task (class patterns plus heavy pixel noise), the same
 initial weights and sample stream in every arm; the lossless arm is the NCCL fp32 all-reduce, the others the fused
 compressed all-reduce at the given bits per value. Prints one JSON line per arm with the mean loss of every
 window of 25 steps and the training accuracy of the last window.
@@ -24,9 +24,9 @@ from gcow_b200.train import LearnableImages, Trainer
 
 
 def run_arm(name: str, cfg: GcowConfig, args, device) -> dict:
-    tr = Trainer(args.arch, batch_size=args.batch, cfg=cfg, lr=args.lr, num_classes=10, device=device, seed=0,
+    tr = Trainer(args.arch, batch_size=args.batch, cfg=cfg, lr=args.lr, num_classes=args.classes, device=device, seed=0,
                  track_accuracy=True)
-    data = LearnableImages(args.batch, args.image, 10, seed=100 + tr.rank)
+    data = LearnableImages(args.batch, args.image, args.classes, seed=100 + tr.rank, noise=args.noise)
     losses, accs = [], []
     nxt = data.next()
     diverged = 0
@@ -68,6 +68,8 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--image", type=int, default=64)
     ap.add_argument("--lr", type=float, default=0.05)
+    ap.add_argument("--classes", type=int, default=100)
+    ap.add_argument("--noise", type=float, default=96.0, help="standard deviation of the pixel noise (patterns span 48..208)")
     ap.add_argument("--window", type=int, default=25)
     ap.add_argument("--rates", type=float, nargs="+", default=[16, 8, 4])
     ap.add_argument("--error-feedback-rates", type=float, nargs="*", default=[8])
