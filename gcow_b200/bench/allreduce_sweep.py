@@ -24,7 +24,19 @@ import torch.distributed as dist
 from gcow_b200.comm import CompressedAllReduce
 from gcow_b200.config import GcowConfig
 
-NVLINK_GBS = 770.0   # measured peer copy, per direction per GPU
+NVLINK_GBS = 770.0   # peer copy per direction per GPU as measured on this pool; --peer-copy re-measures it (row "peer_copy")
+
+
+def peer_copy_gbs(dev, rank, P, nbytes=1 << 30, iters=5):
+    """One-directional peer copy bandwidth: every rank copies `nbytes` from its right neighbour's symmetric buffer
+    into local memory (plain device-to-device copy over NVLink), device-timed, minimum over ranks."""
+    import torch.distributed._symmetric_memory as symm
+    t = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+    hdl = symm.rendezvous(t, dist.group.WORLD)
+    src = hdl.get_buffer((rank + 1) % P, (nbytes,), torch.uint8)
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    ms = time_calls(lambda: dst.copy_(src), iters)       # time_calls takes the MAX time over ranks
+    return nbytes / ms / 1e6
 
 
 def hbm_gbs():
@@ -68,11 +80,13 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes-kb", type=int, nargs="+",
                     default=[1, 16, 256, 1024, 4096, 25600, 65536, 262144, 1048576])
-    ap.add_argument("--rates", type=float, nargs="+", default=[4, 8, 16])
+    ap.add_argument("--rates", type=float, nargs="+", default=[2, 4, 8, 16],
+                    help="bits per value; 2 is floored to the 9-bit block header, decodes to zeros and moves no data")
     ap.add_argument("--variants", nargs="+", default=["twoshot", "oneshot", "nvls"])
     ap.add_argument("--ctas", type=int, default=0, help="0 = as many as are co-resident")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default="")
+    ap.add_argument("--peer-copy", action="store_true", help="also measure the NVLink peer-copy bandwidth (1 GiB, one direction)")
     args = ap.parse_args(argv)
 
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -86,6 +100,14 @@ def main(argv=None):
     max_numel = max(args.sizes_kb) * 256
     rows = []
     pool_bytes = 192 << 20
+    if args.peer_copy and P > 1:
+        try:
+            gbs = peer_copy_gbs(dev, rank, P)
+            rows.append({"impl": "peer_copy", "kb": 1 << 20, "gbs": gbs, "P": P})
+        except Exception as e:  # noqa: BLE001 - symmetric memory may be unavailable; the sweep goes on
+            rows.append({"impl": "peer_copy", "error": repr(e)[:200], "P": P})
+        if rank == 0:
+            print(json.dumps(rows[-1]), flush=True)
 
     # NCCL fp32 baseline
     for kb in args.sizes_kb:
@@ -113,7 +135,7 @@ def main(argv=None):
             n = kb * 256
             copies = max(1, min(8, pool_bytes // (n * 4)))
             bufs = [torch.randn(n, device=dev) * 1e-3 for _ in range(copies)]
-            for variant in args.variants:
+            for variant in (["twoshot"] if ar.header_only else args.variants):   # header-only blocks: zeros, no traffic
                 if variant == "nvls" and not ar.arena.mc_ptr:
                     continue
                 if variant == "oneshot" and (n > ar.oneshot_numel or P == 1):
@@ -127,7 +149,8 @@ def main(argv=None):
                 ms = time_calls(call, iters)
                 ar.check()
                 roof = roofline_ms(n * 4, rate, P, variant, hbm)
-                rows.append({"impl": variant, "rate": rate, "kb": kb, "ms": ms, "eff_gbs": n * 4 / ms / 1e6,
+                rows.append({"impl": "header_only" if ar.header_only else variant, "rate": rate, "kb": kb, "ms": ms,
+                             "eff_gbs": n * 4 / ms / 1e6,
                              "roofline_ms": roof, "frac": roof / ms, "roofline": f"{how} HBM {hbm:.0f} GB/s, NVLink {NVLINK_GBS:.0f} GB/s",
                              "P": P, "ctas": ar.ctas})
                 if rank == 0:
