@@ -244,8 +244,8 @@ def side_metrics(device, rank, world) -> dict:
     p8 = ZfpParams.from_rate(8, 1)
     c = g.compress(x, params=p8)
     y = torch.empty_like(x)
-    enc = time_calls(lambda: g.compress(x, params=p8), 5)
-    dec = time_calls(lambda: g.decompress(c, out=y), 5)
+    enc = time_calls(lambda: g.compress(x, params=p8), 10, warmup=50)
+    dec = time_calls(lambda: g.decompress(c, out=y), 10, warmup=50)
     out["codec_rate8_256MB"] = {"enc_ms": enc, "dec_ms": dec, "enc_gbs": n * 4 / enc / 1e6, "dec_gbs": n * 4 / dec / 1e6,
                                 "max_abs_err": float((x - y).abs().max())}
     del c, y
@@ -256,7 +256,7 @@ def side_metrics(device, rank, world) -> dict:
         def nccl():
             dist.all_reduce(bufs[k["i"] & 1])
             k["i"] += 1
-        out["allreduce_256MB_ms"] = {"nccl_fp32": time_calls(nccl, 5)}
+        out["allreduce_256MB_ms"] = {"nccl_fp32": time_calls(nccl, 10, warmup=50)}
         exact = True
         for rate in (4, 8, 16):
             cfg = GcowConfig(rate=rate, comm_ctas=4096, timeout_ms=20000, average=True)
@@ -266,7 +266,8 @@ def side_metrics(device, rank, world) -> dict:
             def fused():
                 ar(bufs[k["i"] & 1])
                 k["i"] += 1
-            out["allreduce_256MB_ms"][f"fused_rate{rate}"] = time_calls(fused, 5)
+            # the host-side check of the previous rate left the GPU idle and its clocks low: 100 calls bring them back
+            out["allreduce_256MB_ms"][f"fused_rate{rate}"] = time_calls(fused, 10, warmup=100)
             ar.check()
             # bit-exactness on 1 M values: every rank gathers all inputs and runs the host model
             m = 1 << 20
