@@ -36,6 +36,9 @@ def _declare_comm(lib, proto):
         ptr, ptr, ptr, ptr)
     opt("gcow_ar_launch_ef", i32, ptr, ptr, u64, i32, i32, i32, i32, i32, i32, f32, ptr, ptr, u64, u32, u64,
         ptr, ptr, ptr, ptr, ptr)
+    opt("gcow_ar_max_ctas_v", i32, i32, i32)
+    opt("gcow_ar_launch_sparse", i32, ptr, ptr, u64, i32, i32, i32, i32, i32, f32, ptr, u64, u32, u64,
+        ptr, ptr, ptr, ptr, i32, ptr, ptr)
     opt("gcow_ar_wait_probe", i32, ptr, u32, u64, ptr, ptr, ptr)
     opt("gcow_ar_commit", i32, ptr, ptr, ptr, u64, ptr, i32, ptr)
     opt("gcow_ipc_alloc", i32, u64, ptr)

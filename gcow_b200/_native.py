@@ -43,6 +43,7 @@ def cpu() -> C.CDLL:
             _proto(lib, "gcow_header_decompress", u64, ptr, ptr, u64, u64, ptr, i32)
             _proto(lib, "gcow_fast1d_compress", i32, ptr, u64, ptr, ptr)
             _proto(lib, "gcow_fast1d_decompress", i32, ptr, ptr, u64, ptr, i32)
+            _proto(lib, "gcow_lean_accuracy_check", C.c_int64, ptr, u64, i32, i32, ptr)
             _proto(lib, "gcow_stage_emax", i32, ptr, i32, i32)
             _proto(lib, "gcow_stage_cast", None, ptr, ptr, i32, i32, i32)
             _proto(lib, "gcow_stage_inv_cast", None, ptr, ptr, i32, i32, i32, i32)
@@ -56,6 +57,8 @@ def cpu() -> C.CDLL:
             _proto(lib, "gcow_oracle_allreduce", None, ptr, i32, u64, ptr, i32, i32, ptr, i32)
             _proto(lib, "gcow_protocol_model", i32, ptr, ptr, i32, u64, i32, i32, i32, i32, i32, i32, i32,
                    i32, i32, i32, i32, i32, i32, i32, ptr)
+            _proto(lib, "gcow_protocol_model2", i32, ptr, ptr, i32, u64, i32, i32, i32, i32, i32, i32, i32,
+                   i32, i32, i32, i32, i32, i32, i32, ptr, i32)
             _cpu = lib
     return _cpu
 

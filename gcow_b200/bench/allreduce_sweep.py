@@ -86,6 +86,9 @@ def main(argv=None):
     ap.add_argument("--ctas", type=int, default=0, help="0 = as many as are co-resident")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default="")
+    ap.add_argument("--accuracy", nargs="*", default=["1e-3:8", "1e-2:8", "1e-3:8:0.5"],
+                    help="fixed-accuracy rows as tolerance:cap[:fraction] (cap in bits/value; `fraction` of the buffer, "
+                         "its tail, is scaled to 1e-8, far below the tolerance); the wire bytes per call are measured")
     ap.add_argument("--peer-copy", action="store_true", help="also measure the NVLink peer-copy bandwidth (1 GiB, one direction)")
     args = ap.parse_args(argv)
 
@@ -156,6 +159,44 @@ def main(argv=None):
                 if rank == 0:
                     print(json.dumps(rows[-1]), flush=True)
             del bufs
+        del ar
+    # fixed accuracy with a bit cap (sparse variant): the bytes on the wire follow the data
+    for spec in args.accuracy:
+        tol, cap, *rest = spec.split(":")
+        tiny = float(rest[0]) if rest else 0.0
+
+        def fresh_values(n):
+            t = torch.randn(n, device=dev) * 1e-3
+            if tiny:
+                t[int(n * (1 - tiny)):] *= 1e-5
+            return t
+        cfg = GcowConfig(mode="accuracy", tolerance=float(tol), rate=float(cap), comm_ctas=args.ctas or 4096,
+                         timeout_ms=10000, average=True)
+        ar = CompressedAllReduce(max_numel, cfg, device=dev)
+        for kb in args.sizes_kb:
+            n = kb * 256
+            copies = max(1, min(8, pool_bytes // (n * 4)))
+            bufs = [fresh_values(n) for _ in range(copies)]
+            k = {"i": 0}
+
+            def call():
+                ar(bufs[k["i"] % copies])
+                k["i"] += 1
+            iters = args.iters if kb >= 1024 else args.iters * 10
+            ms = time_calls(call, iters)
+            ar.check()
+            w0 = ar.wire_bytes()
+            fresh = fresh_values(n)
+            ar(fresh)
+            ar.check()
+            wire = ar.wire_bytes() - w0
+            rows.append({"impl": "sparse", "tolerance": float(tol), "cap_rate": float(cap), "tiny_fraction": tiny,
+                         "kb": kb, "ms": ms,
+                         "eff_gbs": n * 4 / ms / 1e6, "wire_bytes_per_call": wire,
+                         "fp32_ring_bytes": int(2 * (P - 1) / P * n * 4), "P": P, "ctas": ar.ctas})
+            if rank == 0:
+                print(json.dumps(rows[-1]), flush=True)
+            del bufs, fresh
         del ar
     if rank == 0 and args.json:
         Path(args.json).parent.mkdir(parents=True, exist_ok=True)

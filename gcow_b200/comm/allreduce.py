@@ -27,7 +27,7 @@ from .. import _native
 from ..codec import ZfpParams
 from ..config import GcowConfig
 
-VARIANTS = {"twoshot": 0, "oneshot": 1, "nvls": 2}
+VARIANTS = {"twoshot": 0, "oneshot": 1, "nvls": 2, "sparse": 3}
 _FUSED_BITS = (16, 32, 64, 128)
 
 
@@ -104,6 +104,13 @@ class CompressedAllReduce:
 
     ``max_numel`` fixes the arena size; larger tensors are processed in pieces.
     Calls must be issued in the same order on every rank (as DDP does).
+
+    ``cfg.mode == "rate"``: fixed rate, every block is ``4 * rate`` bits on the wire.
+    ``cfg.mode == "accuracy"``: fixed accuracy with a bit cap (ZFP's expert mode: ``minexp`` from ``cfg.tolerance``,
+    ``maxbits = 4 * cfg.rate``, ``minbits = 1``) on the sparse variant of the kernel: bit planes below the tolerance
+    are dropped, and a block whose values all lie below it sends one bitmap bit and no code, so the bytes on the wire
+    follow the data (``wire_bytes()``). The reference's accuracy mode is the host round trip of
+    hw/models/train_imagenet.py:449-475 with ``tolerance=``.
     """
 
     def __init__(self, max_numel: int, cfg: GcowConfig | None = None, group=None,
@@ -111,13 +118,19 @@ class CompressedAllReduce:
         self.cfg = cfg or GcowConfig.from_env()
         if backend == "auto":      # GCOW_COMM_BACKEND=ipc|symm picks how peer memory is mapped when the caller does not
             backend = os.environ.get("GCOW_COMM_BACKEND", "auto")
-        if self.cfg.dim != 1 or self.cfg.mode != "rate":
-            raise ValueError("the fused all-reduce uses the 1-D fixed-rate codec")
+        if self.cfg.dim != 1 or self.cfg.mode not in ("rate", "accuracy"):
+            raise ValueError("the fused all-reduce uses the 1-D codec at fixed rate or fixed accuracy")
         self.params = ZfpParams.from_rate(self.cfg.rate, 1)
+        self.sparse = self.cfg.mode == "accuracy"
+        if self.sparse:
+            acc = ZfpParams.from_accuracy(self.cfg.tolerance)
+            if self.params.maxbits not in _FUSED_BITS:
+                raise ValueError("accuracy mode needs a cap of 4, 8, 16 or 32 bits/value in cfg.rate")
+            self.params = ZfpParams(1, self.params.maxbits, acc.maxprec, acc.minexp)
         # A 1-D block can never be shorter than its 9-bit header, so rates below 2.25 are floored
         # to 9 bits/block: the header alone, no bit plane. Every such block decodes to zeros, hence
         # the "all-reduce" at that rate is the zero vector on every rank and needs no traffic at all.
-        self.header_only = self.params.maxbits == 9
+        self.header_only = self.params.maxbits == 9 and not self.sparse
         if self.params.maxbits not in _FUSED_BITS and not self.header_only:
             raise ValueError(f"fused all-reduce supports 4, 8, 16 or 32 bits/value (or the 9-bit floor), "
                              f"not rate {self.cfg.rate}")
@@ -131,13 +144,15 @@ class CompressedAllReduce:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.lib = _native.cuda()
         with torch.cuda.device(self.device):
-            self.max_ctas = int(self.lib.gcow_ar_max_ctas(self.bits))
+            self.max_ctas = int(self.lib.gcow_ar_max_ctas_v(self.bits, 3 if self.sparse else 0))
         self.ctas = max(1, min(self.cfg.comm_ctas, self.max_ctas))
         self.max_numel = int(max_numel)
-        two = self.lib.gcow_ar_region_bytes(self.max_numel, self.world, self.ctas, self.bits, 0)
+        two = self.lib.gcow_ar_region_bytes(self.max_numel, self.world, self.ctas, self.bits, 3 if self.sparse else 0)
         # A single rank always takes the one-shot path: y = D(E(x)), ONE lossy round trip, which is what the
         # reference does to the local gradient on one GPU (hw/models/train_imagenet.py:449-475).
         one_n = self.max_numel if self.world == 1 else min(self.max_numel, max(1, self.cfg.oneshot_max_bytes // 4))
+        if self.sparse:
+            one_n = 0               # the sparse variant is two-shot at every size and world
         one = self.lib.gcow_ar_region_bytes(one_n, self.world, self.ctas, self.bits, 1)
         self.region_cap = int(max(two, one))
         self.oneshot_numel = one_n
@@ -154,6 +169,8 @@ class CompressedAllReduce:
         self.calls = 0
         self.bytes_in = 0
         self.bytes_wire = 0
+        self.wire_codes = torch.zeros(1, dtype=torch.int64, device=self.device)   # sparse variant: codes sent to peers
+        self._bitmap_bytes = 0
         pow2 = self.world & (self.world - 1) == 0
         self._avg_shift = int(math.log2(self.world)) if (self.cfg.average and pow2) else 0
         self._avg_scale = 1.0 if (not self.cfg.average or pow2) else 1.0 / self.world
@@ -162,6 +179,8 @@ class CompressedAllReduce:
     def pick_variant(self, numel: int) -> str:
         """Deterministic in (numel, config, world) so that all ranks agree."""
         v = self.cfg.variant
+        if self.sparse:
+            return "sparse"
         if v == "auto":
             if self.world == 1:
                 return "oneshot"
@@ -179,7 +198,7 @@ class CompressedAllReduce:
         warps then handles one destination), capped by the configured grid.
         Depends only on (numel, world, configuration): identical on every rank."""
         shard_blocks = -(-((numel + 3) // 4) // self.world)
-        return max(1, min(self.ctas, -(-shard_blocks // 64)))
+        return max(1, min(self.ctas, -(-shard_blocks // (256 if self.sparse else 64))))
 
     def enable_tracing(self, on: bool = True) -> None:
         """Per-CTA globaltimer stamps at the four phase boundaries of the last call."""
@@ -221,11 +240,29 @@ class CompressedAllReduce:
             return
         vname = variant or self.pick_variant(n)
         v = VARIANTS[vname]
+        if (v == 3) != self.sparse:
+            raise ValueError("the sparse variant goes with cfg.mode == 'accuracy', the others with 'rate'")
         if v == 2 and not self.arena.mc_ptr:
             raise RuntimeError("NVLS variant needs a multicast mapping")
         self.epoch += 1
         shift = self._avg_shift
         post = self._avg_scale
+        if v == 3:
+            err = self.lib.gcow_ar_launch_sparse(
+                x.data_ptr(), out.data_ptr(), n, self.rank, self.world, self.bits, self.ctas_for(n), shift,
+                C.c_float(post), self._peer_array, self.region_cap, self.epoch, int(self.cfg.timeout_ms) * 1_000_000,
+                self.status.data_ptr(), self.status[8:].data_ptr(),
+                self.stamps.data_ptr() if self.stamps is not None else None,
+                residual.data_ptr() if residual is not None else None, self.params.minexp,
+                self.wire_codes.data_ptr(), s.cuda_stream)
+            if err:
+                raise RuntimeError(f"gcow_ar_launch_sparse failed: {err}")
+            self.calls += 1
+            self.bytes_in += n * 4
+            P = self.world
+            shard_blocks = -(-(-(-((n + 3) // 4) // P)) // 64) * 64
+            self._bitmap_bytes += 2 * (P - 1) * shard_blocks // 8       # one bit per block, both phases
+            return
         if v == 1 and shift:          # one-shot has no final decode to fold the shift into
             post, shift = post * 2.0 ** (-shift), 0
         err = self.lib.gcow_ar_launch_ef(
@@ -275,12 +312,20 @@ class CompressedAllReduce:
         """[ctas, 4] device nanosecond stamps (start, pushed, reduced, done) of the last call."""
         return None if self.stamps is None else self.stamps.view(self.ctas, 4).cpu()
 
+    def wire_bytes(self) -> int:
+        """Bytes this rank has stored into other ranks' memory so far. Fixed rate: known from the sizes. Accuracy mode:
+        the kernel's count of codes sent plus the bitmaps (reads the device counter, so it synchronises)."""
+        if self.sparse:
+            return int(self.wire_codes.item()) * self.bits // 8 + self._bitmap_bytes
+        return self.bytes_wire
+
     def wire_ratio(self) -> float:
         """fp32 bytes a ring all-reduce would move per rank over compressed bytes moved."""
         P = self.world
-        if P == 1 or not self.bytes_wire:
+        wire = self.wire_bytes()
+        if P == 1 or not wire:
             return 0.0
-        return (2.0 * (P - 1) / P * self.bytes_in) / self.bytes_wire
+        return (2.0 * (P - 1) / P * self.bytes_in) / wire
 
 
 def nccl_allreduce_mean(x: torch.Tensor, group=None) -> torch.Tensor:

@@ -30,14 +30,15 @@ def allreduce_oracle(xs: np.ndarray, params: ZfpParams, variant: str = "twoshot"
 
 def protocol_model(xs: np.ndarray, bits: int, variant: str = "twoshot", ctas: int = 4, shift: int = 0,
                    timeout_ms: int = 2000, fault_call: int = -1, skip_rank: int = -1, delay_rank: int = -1,
-                   delay_ms: int = 0, drop: tuple = (-1, -1, -1), stale_epoch: int = -1):
-    """xs: float32 [calls, P, n]. Returns (outs [calls, P, n], status [P, 8], failed_ranks)."""
+                   delay_ms: int = 0, drop: tuple = (-1, -1, -1), stale_epoch: int = -1, minexp: int = -1074):
+    """xs: float32 [calls, P, n]. Returns (outs [calls, P, n], status [P, 8], failed_ranks).
+    ``variant="sparse"`` is the fixed-accuracy variant: planes below ``2**minexp`` are dropped, ``bits`` caps a block."""
     xs = np.ascontiguousarray(xs, dtype=np.float32)
     calls, P, n = xs.shape
     outs = np.zeros_like(xs)
     status = np.zeros((P, 8), dtype=np.uint32)
-    v = {"twoshot": 0, "oneshot": 1, "nvls": 0}[variant]
-    failed = _native.cpu().gcow_protocol_model(
+    v = {"twoshot": 0, "oneshot": 1, "nvls": 0, "sparse": 3}[variant]
+    failed = _native.cpu().gcow_protocol_model2(
         xs.ctypes.data, outs.ctypes.data, P, n, ctas, bits, v, shift, calls, timeout_ms, fault_call,
-        skip_rank, delay_rank, delay_ms, drop[0], drop[1], drop[2], stale_epoch, status.ctypes.data)
+        skip_rank, delay_rank, delay_ms, drop[0], drop[1], drop[2], stale_epoch, status.ctypes.data, int(minexp))
     return outs, status, int(failed)

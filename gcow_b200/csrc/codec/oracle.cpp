@@ -456,6 +456,41 @@ const gcow::LeanTables& host_lean_tables() {
 }
 }  // namespace
 
+// Fixed accuracy with a bit cap through the lean coders (as the sparse all-reduce kernel uses them) against the
+// definition path: out = D(E(x)) from the lean pair, and the return value counts the blocks whose result differs from
+// decode_block(encode_block(x)) at {minbits 1, maxbits bits, maxprec 64, minexp}. 0 means they agree everywhere.
+int64_t gcow_lean_accuracy_check(const float* data, uint64_t n, int bits, int minexp, float* out) {
+  const gcow::LeanTables& lt = host_lean_tables();
+  ZfpParams p;
+  p.minbits = 1; p.maxbits = (uint32_t)bits; p.maxprec = 64; p.minexp = minexp;
+  uint64_t blocks = gcow::num_blocks_1d(n);
+  int64_t bad = 0;
+  std::vector<uint64_t> buf(8);
+  for (uint64_t b = 0; b < blocks; b++) {
+    float blk[4], want[4], got[4] = {0, 0, 0, 0};
+    o_gather(blk, data, n, 0, b);
+    std::fill(buf.begin(), buf.end(), 0);
+    BitStream s(buf.data());
+    o_encode_block(s, blk, p, 1);
+    s.flush();
+    BitReader rd(buf.data());
+    o_decode_block(rd, want, p, 1, 0);
+    const uint32_t kmin = gcow::accuracy_kmin_of(blk, minexp);
+    if (kmin < 32) {
+      switch (bits) {
+        case 16: { uint32_t w[1]; gcow::encode_block_1d_lean<16>(blk, lt, w, kmin); gcow::decode_block_1d_lean<16>(got, lt, w, 0, gcow::accuracy_kmin(w[0], minexp)); break; }
+        case 32: { uint32_t w[1]; gcow::encode_block_1d_lean<32>(blk, lt, w, kmin); gcow::decode_block_1d_lean<32>(got, lt, w, 0, gcow::accuracy_kmin(w[0], minexp)); break; }
+        case 64: { uint32_t w[2]; gcow::encode_block_1d_lean<64>(blk, lt, w, kmin); gcow::decode_block_1d_lean<64>(got, lt, w, 0, gcow::accuracy_kmin(w[0], minexp)); break; }
+        case 128: { uint32_t w[4]; gcow::encode_block_1d_lean<128>(blk, lt, w, kmin); gcow::decode_block_1d_lean<128>(got, lt, w, 0, gcow::accuracy_kmin(w[0], minexp)); break; }
+        default: return -1;
+      }
+    }
+    bad += memcmp(want, got, sizeof(want)) != 0;
+    o_scatter(got, out, n, 0, b);
+  }
+  return bad;
+}
+
 int gcow_fast1d_compress(const float* data, uint64_t n, const int32_t* params, void* out) {
   ZfpParams p = load_params(params);
   uint16_t etab[gcow::kEncTabSize];

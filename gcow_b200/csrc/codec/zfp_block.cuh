@@ -728,12 +728,13 @@ GCOW_HD void encode_block_1d_rate(const float* f, const uint16_t* etab, uint32_t
 // `dtab` is the budget-aware table (kDecBudgetTabSize entries).
 template <int BITS>
 GCOW_HD void decode_block_1d_rate(float* f, const uint16_t* dtab, const uint32_t (&w)[(BITS + 31) / 32],
-                                  int shift = 0) {
+                                  int shift = 0, uint32_t kmin = 0) {
   constexpr int NW = (BITS + 31) / 32;
   if (!(w[0] & 1u)) {
     f[0] = f[1] = f[2] = f[3] = 0;
     return;
   }
+  const uint32_t planemask = 0xffffffffu << kmin;               // planes below kmin are not part of the block
   const int emax = (int)((w[0] >> 1) & 0xffu) - kEBias;
   uint32_t u[4] = {0, 0, 0, 0};
   uint32_t pos = kHeaderBits, n = 0, k = 32;
@@ -770,7 +771,7 @@ GCOW_HD void decode_block_1d_rate(float* f, const uint16_t* dtab, const uint32_t
   }
   int32_t q[4];
 #pragma unroll
-  for (int i = 0; i < 4; i++) q[i] = nb2int(u[i]);
+  for (int i = 0; i < 4; i++) q[i] = nb2int(u[i] & planemask);
   inv_lift(q[0], q[1], q[2], q[3]);
   inv_cast<4>(f, q, emax, shift);
 }
@@ -909,7 +910,8 @@ struct LeanTables {
 };
 
 template <int BITS>
-GCOW_HD void encode_block_1d_lean(const float* f, const LeanTables& t, uint32_t (&w)[(BITS + 31) / 32]) {
+GCOW_HD void encode_block_1d_lean(const float* f, const LeanTables& t, uint32_t (&w)[(BITS + 31) / 32],
+                                  uint32_t kmin = 0) {   // planes below kmin need not be coded (what follows them is ignored)
   constexpr int NW = (BITS + 31) / 32;
   const float a01 = fmaxf(fabsf(f[0]), fabsf(f[1])), a23 = fmaxf(fabsf(f[2]), fabsf(f[3]));
   const uint32_t mb = f32_bits(fmaxf(a01, a23));
@@ -954,26 +956,27 @@ GCOW_HD void encode_block_1d_lean(const float* f, const LeanTables& t, uint32_t 
   uint32_t pos = (S >> 16) & 0xffu, n = S >> 24, k = 32 - z - 2 * kPairs;
   if (NW > 1) {
     // the remaining planes are verbatim nibbles once n >= 3
-    while (n >= 3 && pos < (uint32_t)BITS && k > 0) {
+    while (n >= 3 && pos < (uint32_t)BITS && k > kmin) {
       buf.put(pos, plane_group8(u, k));
       const uint32_t cnt = k < 8 ? k : 8;
       pos += 4 * cnt;
       k -= cnt;
     }
   }
-  if (pos < (uint32_t)BITS && k > 0) { encode_block_1d_rate<BITS>(f, t.etab, w); return; }   // very smooth block
+  if (pos < (uint32_t)BITS && k > kmin) { encode_block_1d_rate<BITS>(f, t.etab, w); return; }   // very smooth block
   buf.store(w);
   if (BITS < 32 * NW) w[NW - 1] &= low_mask32(BITS - 32 * (NW - 1));
 }
 
 template <int BITS>
 GCOW_HD void decode_block_1d_lean(float* f, const LeanTables& t, const uint32_t (&w)[(BITS + 31) / 32],
-                                  int shift = 0) {
+                                  int shift = 0, uint32_t kmin = 0) {
   constexpr int NW = (BITS + 31) / 32;
   if (!(w[0] & 1u)) {
     f[0] = f[1] = f[2] = f[3] = 0;
     return;
   }
+  const uint32_t planemask = 0xffffffffu << kmin;               // planes below kmin are not part of the block
   const uint32_t e8 = (w[0] >> 1) & 0xffu;                     // biased exponent, emax + 127
   BitBuf<NW> buf;
   buf.load(w);
@@ -999,7 +1002,10 @@ GCOW_HD void decode_block_1d_lean(float* f, const LeanTables& t, const uint32_t 
     nrow = e >> 16;
     j4 += 4;
   }
-  if (nrow < 3u * 4096u && pos < end && j4 < 4 * ktop) { decode_block_1d_rate<BITS>(f, t.dtab, w, shift); return; }   // very smooth block
+  if (nrow < 3u * 4096u && pos < end && j4 < 4 * ktop && ktop - (j4 >> 2) > kmin) {   // very smooth block
+    decode_block_1d_rate<BITS>(f, t.dtab, w, shift, kmin);
+    return;
+  }
   T = shr_sat(T, 32 - j4);                                     // first plane in the low nibble
   uint32_t u[4] = {0, 0, 0, 0};
   uint32_t k = ktop;
@@ -1013,7 +1019,7 @@ GCOW_HD void decode_block_1d_lean(float* f, const LeanTables& t, const uint32_t 
   } else {
     if (T) deposit_group8(u, T, k);
     k -= j4 >> 2;
-    while (pos < end && k > 0) {
+    while (pos < end && k > kmin) {
       deposit_group8(u, buf.peek(pos), k);           // bits past the block's end read as 0
       pos += 32;
       k = k > 8 ? k - 8 : 0;
@@ -1021,13 +1027,30 @@ GCOW_HD void decode_block_1d_lean(float* f, const LeanTables& t, const uint32_t 
   }
   int32_t q[4];
 #pragma unroll
-  for (int i = 0; i < 4; i++) q[i] = nb2int(u[i]);
+  for (int i = 0; i < 4; i++) q[i] = nb2int(u[i] & planemask);
   inv_lift(q[0], q[1], q[2], q[3]);
   // 2^(emax - 30 - shift): a normal float unless the block is tiny
   const int ef = (int)e8 - 30 - shift;
   const float scale = (ef >= 1 && ef <= 254) ? bits_f32((uint32_t)ef << 23) : pow2f((int)e8 - kEBias - 30 - shift);
 #pragma unroll
   for (int i = 0; i < 4; i++) f[i] = scale * (float)q[i];
+}
+
+// Fixed accuracy with a bit cap (minexp from the tolerance, maxbits = BITS, minbits = 1): a block keeps the planes
+// 31 .. 32 - prec, prec = block_precision(emax, ., minexp, 1), as far as the cap allows. The embedded code of those
+// planes is a prefix of the fixed-rate code, so the fixed-rate encoder serves unchanged and the decoder only has to
+// drop what it read of the planes below: `kmin` of the coders above (which also keeps them on their fast path when
+// the planes that count end before the bit budget does). A block with prec = 0 (everything below
+// the tolerance) or all zeros is a single 0 bit in the stream; callers send nothing for it.
+// Lowest plane kept, from a kept block's header word (32 - prec, at most 31).
+GCOW_HD uint32_t accuracy_kmin(uint32_t w0, int minexp) {
+  const int emax = (int)((w0 >> 1) & 0xffu) - kEBias;
+  return 32u - block_precision(emax, 32, minexp, 1);
+}
+// Lowest plane kept for the block f, or 32 when the block is dropped.
+GCOW_HD uint32_t accuracy_kmin_of(const float* f, int minexp) {
+  const int emax = block_emax<4>(f);
+  return emax == -kEBias ? 32u : 32u - block_precision(emax, 32, minexp, 1);
 }
 
 // Host-side construction of the pair table.

@@ -15,6 +15,9 @@
 //            output, folding the division by P into the block exponent.
 // The one-shot variant pushes every block to every rank in phase 1 and sums the
 // P decoded copies locally (no re-encode, one network hop).
+// The sparse variant is the two-shot protocol at fixed accuracy with a bit cap: a block whose values all lie below the
+// tolerance is one bit in a bitmap and sends no code, the others are packed behind one another (ballot + popcount
+// give each its position), so the bytes on the wire follow the data.
 //
 // Every wait is bounded by a globaltimer deadline and an iteration count; a CTA
 // that gives up records {code, phase, peer, cta, expected, seen}, raises the
@@ -52,6 +55,8 @@ struct ArArgs {
   const uint32_t* pair_table;
   const uint32_t* loop_table;
   float* residual;            // error feedback: added to the input before encoding, then set to x - D(E(x)); or nullptr
+  int minexp;                 // sparse variant: smallest bit-plane exponent kept (fixed-accuracy rule)
+  unsigned long long* wire;   // sparse variant: += codes this rank stored into other ranks' memory, or nullptr
   ArLayout L;
 };
 
@@ -411,6 +416,203 @@ allreduce_fused_kernel(const ArArgs a) {
   stamp(a, 3);
 }
 
+
+// ------------------------------------------------- sparse two-shot (fixed accuracy with a bit cap)
+// Encodes one block under the accuracy rule; false = dropped (decodes to zeros, nothing is sent). With error feedback
+// the residual is added first and then set to what the code (or the drop) lost.
+template <int BITS, int NW>
+__device__ __forceinline__ bool sparse_encode(float (&f)[4], const ArArgs& a, uint64_t gb, const LeanTables& lt,
+                                              uint32_t (&w)[NW]) {
+  float r[4];
+  const bool al = ((uintptr_t)a.residual & 15) == 0;
+  if (a.residual) {
+    load_block(r, a.residual, a.n, gb, al);
+    const uint64_t x0 = 4 * gb;
+    if (x0 + 4 > a.n) {
+      for (uint64_t i = a.n > x0 ? a.n - x0 : 0; i < 4; i++) r[i] = 0;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) f[i] += r[i];
+  }
+  const uint32_t kmin = accuracy_kmin_of(f, a.minexp);
+  const bool keep = kmin < 32;
+  if (keep) encode_block_1d_lean<BITS>(f, lt, w, kmin);
+  if (a.residual) {
+    float d[4] = {0, 0, 0, 0};
+    if (keep) decode_block_1d_lean<BITS>(d, lt, w, 0, kmin);
+#pragma unroll
+    for (int i = 0; i < 4; i++) r[i] = f[i] - d[i];
+    store_block(r, a.residual, a.n, gb, al);
+  }
+  return keep;
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kArThreads, 4)
+allreduce_sparse_kernel(const ArArgs a) {
+  using C = Code<BITS>;
+  constexpr int NW = C::NW;
+  static_assert(kSparseChunks == kArThreads / 32, "one chunk per warp of the owner's CTA");
+  __shared__ __align__(16) uint32_t epair[kEncPairTabSize];
+  __shared__ __align__(16) uint32_t dloop[kDecLoopTabSize];
+  __shared__ int s_ok;
+  for (int i = threadIdx.x; i < kDecLoopTabSize / 4; i += blockDim.x)
+    reinterpret_cast<uint4*>(dloop)[i] = reinterpret_cast<const uint4*>(a.loop_table)[i];
+  for (int i = threadIdx.x; i < kEncPairTabSize / 4; i += blockDim.x)
+    reinterpret_cast<uint4*>(epair)[i] = reinterpret_cast<const uint4*>(a.pair_table)[i];
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  const LeanTables lt = {a.enc_table, a.dec_table, epair, dloop};
+
+  const int P = a.world, r = a.rank, cta = blockIdx.x, tid = threadIdx.x;
+  const ArLayout& L = a.L;
+  const uint64_t SB = L.shard_blocks, NB = L.blocks;
+  const uint64_t s0 = (uint64_t)cta * L.slice_blocks;
+  const uint64_t s1 = s0 + L.slice_blocks < SB ? s0 + L.slice_blocks : SB;
+  const uint64_t CL = L.slice_blocks / kSparseChunks;          // chunk length, a multiple of 32
+  const bool in_al = ((uintptr_t)a.in & 15) == 0, out_al = ((uintptr_t)a.out & 15) == 0;
+  const int warp = tid >> 5, lane = tid & 31, nwarps = kArThreads / 32;
+  const uint32_t below = (1u << lane) - 1u;                    // lanes before this one
+  // phases 1 and 3: warp w works on shard slot w % P and on a contiguous run of the slice's chunks
+  const int wps = (nwarps % P == 0) ? nwarps / P : 1;
+  const int slot = warp % P, sub = warp / P;
+  const bool has_slot = warp < P * wps;
+  const int cpp = kSparseChunks / wps;                         // chunks per warp: wps is 1, 2, 4 or 8
+  uint8_t* const local = a.arena[r];
+  unsigned long long sent = 0;
+  stamp(a, 0);
+
+  // ---- phase 1: encode shard j; kept blocks go, packed per chunk, into owner j's slot for source r
+  if (has_slot) {
+    const int j = (r + 1 + slot) % P;
+    uint8_t* dst = a.arena[j] + a.region_off + (uint64_t)r * L.slot_bytes;
+    uint32_t* dst_bm = reinterpret_cast<uint32_t*>(dst + L.bitmap_off);
+    for (int c = sub * cpp; c < (sub + 1) * cpp; c++) {
+      const uint64_t c0 = s0 + (uint64_t)c * CL;
+      if (c0 >= s1) break;
+      const uint64_t c1 = c0 + CL < s1 ? c0 + CL : s1;
+      uint64_t run = 0;
+      for (uint64_t base = c0; base < c1; base += 32) {
+        const uint64_t b = base + lane, gb = (uint64_t)j * SB + b;
+        bool keep = false;
+        uint32_t w[NW];
+        if (b < c1 && gb < NB) {
+          float f[4];
+          load_block(f, a.in, a.n, gb, in_al);
+          keep = sparse_encode<BITS, NW>(f, a, gb, lt, w);
+        }
+        const uint32_t word = __ballot_sync(0xffffffffu, keep);
+        if (keep) C::st(dst, c0 + run + __popc(word & below), w);
+        if (lane == 0) dst_bm[base >> 5] = word;
+        run += __popc(word);
+      }
+      if (j != r) sent += run;
+    }
+  }
+  __syncthreads();
+  if (tid < P) {
+    __threadfence_system();
+    st_release_sys(flag_ptr(a.arena[tid], a.parity, 0, r, cta), a.epoch);
+  }
+  stamp(a, 1);
+
+  // ---- phase 2: warp w reduces chunk w of my shard's slice and sends the re-encoded result to every rank
+  if (tid < P) {
+    if (!wait_flag(a, flag_ptr(local, a.parity, 0, tid, cta), 1, tid)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  {
+    const uint64_t goff = a.region_off + L.recv_bytes + (uint64_t)r * L.slot_bytes;
+    const uint64_t c0 = s0 + (uint64_t)warp * CL;
+    if (c0 < s1) {
+      const uint64_t c1 = c0 + CL < s1 ? c0 + CL : s1;
+      uint32_t run_in[kMaxRanks];
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; s++) run_in[s] = 0;
+      uint64_t run_out = 0;
+      for (uint64_t base = c0; base < c1; base += 32) {
+        const uint64_t b = base + lane, gb = (uint64_t)r * SB + b;
+        float acc[4] = {0, 0, 0, 0};                            // 0 + d is d: the sum is in ascending rank order
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; s++) {
+          if (s < P) {
+            const uint8_t* src = local + a.region_off + (uint64_t)s * L.slot_bytes;
+            const uint32_t word = __ldcg(reinterpret_cast<const uint32_t*>(src + L.bitmap_off) + (base >> 5));
+            if ((word >> lane) & 1u) {
+              uint32_t w[NW];
+              C::ld(src, c0 + run_in[s] + __popc(word & below), w);
+              float d[4];
+              decode_block_1d_lean<BITS>(d, lt, w, 0, accuracy_kmin(w[0], a.minexp));
+#pragma unroll
+              for (int i = 0; i < 4; i++) acc[i] += d[i];
+            }
+            run_in[s] += __popc(word);
+          }
+        }
+        bool keep = false;
+        uint32_t w[NW];
+        if (b < c1 && gb < NB) {
+          const uint32_t kmin = accuracy_kmin_of(acc, a.minexp);
+          keep = kmin < 32;
+          if (keep) encode_block_1d_lean<BITS>(acc, lt, w, kmin);
+        }
+        const uint32_t word = __ballot_sync(0xffffffffu, keep);
+        const uint64_t at = c0 + run_out + __popc(word & below);
+        for (int step = 0; step < P; step++) {
+          uint8_t* g = a.arena[(r + 1 + step) % P] + goff;
+          if (keep) C::st(g, at, w);
+          if (lane == 0) reinterpret_cast<uint32_t*>(g + L.bitmap_off)[base >> 5] = word;
+        }
+        run_out += __popc(word);
+      }
+      sent += run_out * (uint64_t)(P - 1);
+    }
+    __syncthreads();
+    if (tid < P) {
+      __threadfence_system();
+      st_release_sys(flag_ptr(a.arena[tid], a.parity, 1, r, cta), a.epoch);
+    }
+  }
+  stamp(a, 2);
+
+  // ---- phase 3: decode every shard's slice into the output (dropped blocks are zeros)
+  if (tid < P) {
+    if (!wait_flag(a, flag_ptr(local, a.parity, 1, tid, cta), 2, tid)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  if (has_slot) {
+    const int j = slot;
+    const uint8_t* src = local + a.region_off + L.recv_bytes + (uint64_t)j * L.slot_bytes;
+    const uint32_t* bm = reinterpret_cast<const uint32_t*>(src + L.bitmap_off);
+    for (int c = sub * cpp; c < (sub + 1) * cpp; c++) {
+      const uint64_t c0 = s0 + (uint64_t)c * CL;
+      if (c0 >= s1) break;
+      const uint64_t c1 = c0 + CL < s1 ? c0 + CL : s1;
+      uint64_t run = 0;
+      for (uint64_t base = c0; base < c1; base += 32) {
+        const uint64_t b = base + lane, gb = (uint64_t)j * SB + b;
+        const uint32_t word = __ldcg(bm + (base >> 5));
+        float d[4] = {0, 0, 0, 0};
+        if ((word >> lane) & 1u) {
+          uint32_t w[NW];
+          C::ld(src, c0 + run + __popc(word & below), w);
+          decode_block_1d_lean<BITS>(d, lt, w, a.shift, accuracy_kmin(w[0], a.minexp));
+          if (a.postscale != 1.0f) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) d[i] *= a.postscale;
+          }
+        }
+        if (b < c1 && gb < NB) store_block(d, a.out, a.n, gb, out_al);
+        run += __popc(word);
+      }
+    }
+  }
+  if (a.wire && lane == 0 && sent) atomicAdd(a.wire, sent);
+  stamp(a, 3);
+}
+
 // Copy src -> dst only if no call so far has failed (status word still 0), and
 // record the verdict for the host. With the all-reduce writing to a side buffer,
 // a bucket whose collective gave up keeps its original local gradient.
@@ -435,9 +637,10 @@ __global__ void wait_probe_kernel(const ArArgs a, const uint32_t* flag) {
 }
 
 template <int BITS>
-int max_coresident_ctas(int device) {
+int max_coresident_ctas(int device, bool sparse = false) {
   int per_sm = 0, sms = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_fused_kernel<BITS>, kArThreads, 0);
+  if (sparse) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_sparse_kernel<BITS>, kArThreads, 0);
+  else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_fused_kernel<BITS>, kArThreads, 0);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   return per_sm * sms;
 }
@@ -459,19 +662,21 @@ uint64_t gcow_ar_region_bytes(uint64_t n, int world, int ctas, int bits, int var
 }
 
 // Largest grid that is guaranteed co-resident (the flag protocol needs it).
-int gcow_ar_max_ctas(int bits) {
+int gcow_ar_max_ctas_v(int bits, int variant) {
   int dev = 0;
   cudaGetDevice(&dev);
+  const bool sp = variant == kTwoShotSparse;
   int m = 0;
   switch (bits) {
-    case 16: m = max_coresident_ctas<16>(dev); break;
-    case 32: m = max_coresident_ctas<32>(dev); break;
-    case 64: m = max_coresident_ctas<64>(dev); break;
-    case 128: m = max_coresident_ctas<128>(dev); break;
+    case 16: m = max_coresident_ctas<16>(dev, sp); break;
+    case 32: m = max_coresident_ctas<32>(dev, sp); break;
+    case 64: m = max_coresident_ctas<64>(dev, sp); break;
+    case 128: m = max_coresident_ctas<128>(dev, sp); break;
     default: return -1;
   }
   return m < kMaxCtas ? m : kMaxCtas;
 }
+int gcow_ar_max_ctas(int bits) { return gcow_ar_max_ctas_v(bits, kTwoShot); }
 
 // Launch the fused all-reduce on `stream`. `residual` (n floats, or null) enables error feedback inside the kernel: the
 // encoder sees in + residual, and residual becomes what this rank's code of that sum dropped.
@@ -479,10 +684,11 @@ int gcow_ar_max_ctas(int bits) {
 //   mc_arena: multicast mapping or null; region_cap: bytes of one parity's data region
 //   status: 8 u32 (device-visible); abort_flag: 1 u32; stamps: optional ctas*4 u64
 // Returns 0, a CUDA error code, or -1 / -2 for bad arguments / insufficient arena.
-int gcow_ar_launch_ef(const float* in, float* out, uint64_t n, int rank, int world, int variant, int bits,
-                      int ctas, int shift, float postscale, void* const* arenas, void* mc_arena,
-                      uint64_t region_cap, uint32_t epoch, uint64_t timeout_ns, uint32_t* status,
-                      uint32_t* abort_flag, unsigned long long* stamps, float* residual, void* stream) {
+static int ar_launch_impl(const float* in, float* out, uint64_t n, int rank, int world, int variant, int bits,
+                          int ctas, int shift, float postscale, void* const* arenas, void* mc_arena,
+                          uint64_t region_cap, uint32_t epoch, uint64_t timeout_ns, uint32_t* status,
+                          uint32_t* abort_flag, unsigned long long* stamps, float* residual, int minexp,
+                          unsigned long long* wire, void* stream) {
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || ctas < 1 || ctas > kMaxCtas) return -1;
   if (variant == kTwoShotNvls && !mc_arena) return -1;
   ArArgs a;
@@ -496,6 +702,8 @@ int gcow_ar_launch_ef(const float* in, float* out, uint64_t n, int rank, int wor
   a.timeout_ns = timeout_ns;
   a.status = status; a.abort_flag = abort_flag; a.stamps = stamps;
   a.residual = residual;
+  a.minexp = minexp;
+  a.wire = wire;
   a.L = ar_layout(n, world, ctas, bits, variant);
   if (a.L.region_bytes > region_cap) return -2;
   const void *etp, *dtp, *ptp, *ltp;
@@ -506,6 +714,16 @@ int gcow_ar_launch_ef(const float* in, float* out, uint64_t n, int rank, int wor
   a.loop_table = (const uint32_t*)ltp;
   if (n == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  if (variant == kTwoShotSparse) {
+    switch (bits) {
+      case 16: allreduce_sparse_kernel<16><<<ctas, kArThreads, 0, s>>>(a); break;
+      case 32: allreduce_sparse_kernel<32><<<ctas, kArThreads, 0, s>>>(a); break;
+      case 64: allreduce_sparse_kernel<64><<<ctas, kArThreads, 0, s>>>(a); break;
+      case 128: allreduce_sparse_kernel<128><<<ctas, kArThreads, 0, s>>>(a); break;
+      default: return -1;
+    }
+    return (int)cudaGetLastError();
+  }
   switch (bits) {
     case 16: allreduce_fused_kernel<16><<<ctas, kArThreads, 0, s>>>(a); break;
     case 32: allreduce_fused_kernel<32><<<ctas, kArThreads, 0, s>>>(a); break;
@@ -514,6 +732,25 @@ int gcow_ar_launch_ef(const float* in, float* out, uint64_t n, int rank, int wor
     default: return -1;
   }
   return (int)cudaGetLastError();
+}
+
+int gcow_ar_launch_ef(const float* in, float* out, uint64_t n, int rank, int world, int variant, int bits,
+                      int ctas, int shift, float postscale, void* const* arenas, void* mc_arena,
+                      uint64_t region_cap, uint32_t epoch, uint64_t timeout_ns, uint32_t* status,
+                      uint32_t* abort_flag, unsigned long long* stamps, float* residual, void* stream) {
+  if (variant == kTwoShotSparse) return -1;
+  return ar_launch_impl(in, out, n, rank, world, variant, bits, ctas, shift, postscale, arenas, mc_arena, region_cap,
+                        epoch, timeout_ns, status, abort_flag, stamps, residual, 0, nullptr, stream);
+}
+
+// The sparse variant: fixed accuracy (planes below 2^minexp are dropped, blocks wholly below it send nothing) with a cap
+// of `bits` per block. `wire` (device, or null) is incremented by the number of codes stored into other ranks' memory.
+int gcow_ar_launch_sparse(const float* in, float* out, uint64_t n, int rank, int world, int bits, int ctas, int shift,
+                          float postscale, void* const* arenas, uint64_t region_cap, uint32_t epoch,
+                          uint64_t timeout_ns, uint32_t* status, uint32_t* abort_flag, unsigned long long* stamps,
+                          float* residual, int minexp, unsigned long long* wire, void* stream) {
+  return ar_launch_impl(in, out, n, rank, world, kTwoShotSparse, bits, ctas, shift, postscale, arenas, nullptr,
+                        region_cap, epoch, timeout_ns, status, abort_flag, stamps, residual, minexp, wire, stream);
 }
 
 int gcow_ar_launch(const float* in, float* out, uint64_t n, int rank, int world, int variant, int bits,

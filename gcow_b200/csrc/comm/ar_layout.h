@@ -13,6 +13,9 @@
 //   [ data region, parity 0 ][ data region, parity 1 ]
 // Data region, two-shot:  recv slots [P][SB codes] then gather slots [P][SB codes]
 //              one-shot:  recv slots [P][P*SB codes]
+//              sparse two-shot (fixed accuracy with a bit cap): the same recv and gather slots, each followed by a
+//              bitmap of SB bits. A slice is cut into kSparseChunks chunks; a chunk's kept blocks ("1" in the bitmap)
+//              are packed from the chunk's first code position on, dropped blocks send nothing.
 // Calls alternate parity. A rank that starts call k+2 has finished call k+1,
 // whose last phase waited for every peer's phase 2 of call k+1, which a peer
 // only reaches after its call k has fully completed - so parity k%2 is free.
@@ -35,7 +38,8 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxCtas = 2048;
 constexpr uint64_t kFlagBytes = 2ull * 2 * kMaxRanks * kMaxCtas * 4;
 
-enum ArVariant : int { kTwoShot = 0, kOneShot = 1, kTwoShotNvls = 2 };
+enum ArVariant : int { kTwoShot = 0, kOneShot = 1, kTwoShotNvls = 2, kTwoShotSparse = 3 };
+constexpr int kSparseChunks = 8;   // packed ranges per slice: one per warp of the owner's CTA
 
 // status codes written by a kernel that gave up waiting
 enum ArStatus : uint32_t { kArOk = 0, kArTimeout = 1, kArAborted = 2, kArBadArgs = 3 };
@@ -43,12 +47,13 @@ enum ArStatus : uint32_t { kArOk = 0, kArTimeout = 1, kArAborted = 2, kArBadArgs
 struct ArLayout {
   uint64_t blocks;        // NB
   uint64_t shard_blocks;  // SB, multiple of 64
-  uint64_t slice_blocks;  // blocks per CTA slice, multiple of 32
+  uint64_t slice_blocks;  // blocks per CTA slice, multiple of 32 (of 32 * kSparseChunks in the sparse variant)
   uint32_t code_bytes;    // bytes per compressed block
   uint64_t slot_bytes;    // bytes of one source's slot in the recv area
   uint64_t recv_bytes;    // P * slot_bytes
   uint64_t gather_bytes;  // P * SB * code_bytes (two-shot), 0 (one-shot)
   uint64_t region_bytes;  // recv + gather
+  uint64_t bitmap_off;    // sparse variant: byte offset of a slot's bitmap (after its SB code positions), else 0
 };
 
 GCOW_LAYOUT_HD uint64_t round_up_u64(uint64_t v, uint64_t m) { return (v + m - 1) / m * m; }
@@ -58,9 +63,15 @@ GCOW_LAYOUT_HD ArLayout ar_layout(uint64_t n, int P, int G, int bits, int varian
   L.blocks = (n + 3) / 4;
   L.shard_blocks = round_up_u64((L.blocks + P - 1) / P, 64);
   if (L.shard_blocks == 0) L.shard_blocks = 64;
-  L.slice_blocks = round_up_u64((L.shard_blocks + G - 1) / G, 32);
+  const bool sparse = variant == kTwoShotSparse;
+  L.slice_blocks = round_up_u64((L.shard_blocks + G - 1) / G, sparse ? 32 * kSparseChunks : 32);
   L.code_bytes = (uint32_t)bits / 8;
   uint64_t shard_bytes = L.shard_blocks * L.code_bytes;
+  L.bitmap_off = 0;
+  if (sparse) {
+    L.bitmap_off = shard_bytes;
+    shard_bytes += round_up_u64(L.shard_blocks / 8, 16);
+  }
   if (variant == kOneShot) {
     L.slot_bytes = shard_bytes * P;
     L.gather_bytes = 0;

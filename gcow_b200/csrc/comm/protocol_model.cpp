@@ -34,7 +34,7 @@ struct Fault {
 };
 
 struct Model {
-  int P, G, bits, variant, shift;
+  int P, G, bits, variant, shift, minexp;
   uint64_t n, region_cap;
   ArLayout L;
   std::vector<std::vector<uint8_t>> arena;  // one per rank
@@ -190,6 +190,121 @@ void run_rank(Model& m, int r, const float* in, float* out, uint32_t epoch, int 
   }
 }
 
+// The sparse variant (fixed accuracy with a bit cap): the same flags, with the kept blocks of every chunk packed
+// behind one another and a bitmap beside them, exactly as allreduce_sparse_kernel lays them out.
+template <int BITS>
+void run_rank_sparse(Model& m, int r, const float* in, float* out, uint32_t epoch, int timeout_ms,
+                     const Fault& ft, uint32_t* status) {
+  constexpr int NW = (BITS + 31) / 32;
+  const int P = m.P, G = m.G, parity = (int)(epoch & 1), bytes = m.bits / 8;
+  const ArLayout& L = m.L;
+  const uint64_t SB = L.shard_blocks, NB = L.blocks, CL = L.slice_blocks / kSparseChunks;
+  const uint64_t roff = region_offset(parity, m.region_cap);
+  auto fail = [&](int phase, int peer, int cta, uint32_t seen) {
+    if (status[0] == 0) { status[0] = kArTimeout; status[1] = phase; status[2] = peer; status[3] = cta; status[4] = epoch; status[5] = seen; }
+  };
+  auto signal = [&](int dst, int phase, int cta) {
+    if (ft.drop_src == r && ft.drop_dst == dst && ft.drop_phase == phase) return;
+    flag_at(m, dst, parity, phase, r, cta)->store(epoch, std::memory_order_release);
+  };
+  auto set_bit = [](uint8_t* slot_bitmap, uint64_t b, bool v) {
+    uint32_t* wd = reinterpret_cast<uint32_t*>(slot_bitmap) + (b >> 5);
+    if ((b & 31) == 0) *wd = 0;
+    if (v) *wd |= 1u << (b & 31);
+  };
+  auto get_bit = [](const uint8_t* slot_bitmap, uint64_t b) {
+    return (reinterpret_cast<const uint32_t*>(slot_bitmap)[b >> 5] >> (b & 31)) & 1u;
+  };
+  // phase 1
+  for (int cta = 0; cta < G; cta++) {
+    uint64_t s0 = (uint64_t)cta * L.slice_blocks, s1 = std::min<uint64_t>(s0 + L.slice_blocks, SB);
+    for (int step = 0; step < P; step++) {
+      int j = (r + 1 + step) % P;
+      uint8_t* dst = m.arena[j].data() + roff + (uint64_t)r * L.slot_bytes;
+      for (uint64_t c0 = s0; c0 < s1; c0 += CL) {
+        uint64_t c1 = std::min<uint64_t>(c0 + CL, s1), run = 0;
+        for (uint64_t b = c0; b < c1; b++) {
+          uint64_t gb = (uint64_t)j * SB + b;
+          bool keep = false;
+          uint32_t w[NW];
+          if (gb < NB) {
+            float f[4];
+            load_block(f, in, m.n, gb);
+            keep = accuracy_kmin_of(f, m.minexp) < 32;
+            if (keep) encode_block_1d_rate<BITS>(f, m.etab.data(), w);
+          }
+          if (keep) put_code<NW>(dst, c0 + run++, w, bytes);
+          set_bit(dst + L.bitmap_off, b, keep);
+        }
+      }
+      signal(j, 0, cta);
+    }
+  }
+  // phase 2
+  for (int cta = 0; cta < G; cta++) {
+    uint64_t s0 = (uint64_t)cta * L.slice_blocks, s1 = std::min<uint64_t>(s0 + L.slice_blocks, SB);
+    for (int s = 0; s < P; s++) {
+      uint32_t seen;
+      if (!wait_flag(flag_at(m, r, parity, 0, s, cta), epoch, timeout_ms, &seen)) { fail(1, s, cta, seen); return; }
+    }
+    const uint8_t* local = m.arena[r].data();
+    const uint64_t goff = roff + L.recv_bytes + (uint64_t)r * L.slot_bytes;
+    for (uint64_t c0 = s0; c0 < s1; c0 += CL) {
+      uint64_t c1 = std::min<uint64_t>(c0 + CL, s1), run_out = 0;
+      std::vector<uint64_t> run_in(P, 0);
+      for (uint64_t b = c0; b < c1; b++) {
+        uint64_t gb = (uint64_t)r * SB + b;
+        float acc[4] = {0, 0, 0, 0};
+        for (int s = 0; s < P; s++) {
+          const uint8_t* src = local + roff + (uint64_t)s * L.slot_bytes;
+          if (!get_bit(src + L.bitmap_off, b)) continue;
+          uint32_t w[NW]; float d[4];
+          get_code<NW>(src, c0 + run_in[s]++, w, bytes);
+          decode_block_1d_rate<BITS>(d, m.dtab.data(), w, 0, accuracy_kmin(w[0], m.minexp));
+          for (int i = 0; i < 4; i++) acc[i] += d[i];
+        }
+        bool keep = false;
+        uint32_t w[NW];
+        if (gb < NB) {
+          keep = accuracy_kmin_of(acc, m.minexp) < 32;
+          if (keep) encode_block_1d_rate<BITS>(acc, m.etab.data(), w);
+        }
+        for (int j = 0; j < P; j++) {
+          uint8_t* g = m.arena[j].data() + goff;
+          if (keep) put_code<NW>(g, c0 + run_out, w, bytes);
+          set_bit(g + L.bitmap_off, b, keep);
+        }
+        run_out += keep;
+      }
+    }
+    for (int j = 0; j < P; j++) signal(j, 1, cta);
+  }
+  // phase 3
+  for (int cta = 0; cta < G; cta++) {
+    uint64_t s0 = (uint64_t)cta * L.slice_blocks, s1 = std::min<uint64_t>(s0 + L.slice_blocks, SB);
+    for (int j = 0; j < P; j++) {
+      uint32_t seen;
+      if (!wait_flag(flag_at(m, r, parity, 1, j, cta), epoch, timeout_ms, &seen)) { fail(2, j, cta, seen); return; }
+    }
+    for (int j = 0; j < P; j++) {
+      const uint8_t* src = m.arena[r].data() + roff + L.recv_bytes + (uint64_t)j * L.slot_bytes;
+      for (uint64_t c0 = s0; c0 < s1; c0 += CL) {
+        uint64_t c1 = std::min<uint64_t>(c0 + CL, s1), run = 0;
+        for (uint64_t b = c0; b < c1; b++) {
+          uint64_t gb = (uint64_t)j * SB + b;
+          float d[4] = {0, 0, 0, 0};
+          if (get_bit(src + L.bitmap_off, b)) {
+            uint32_t w[NW];
+            get_code<NW>(src, c0 + run++, w, bytes);
+            decode_block_1d_rate<BITS>(d, m.dtab.data(), w, m.shift, accuracy_kmin(w[0], m.minexp));
+          }
+          if (gb < NB) store_block(d, out, m.n, gb);
+        }
+      }
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -199,12 +314,13 @@ extern "C" {
 // (first failure per rank over all calls). The fault applies to call
 // `fault_call` only; stale_epoch >= 0 pre-seeds every flag with that value
 // before the first call. Returns the number of ranks that reported a failure.
-int gcow_protocol_model(const float* xs, float* outs, int P, uint64_t n, int G, int bits, int variant,
-                        int shift, int calls, int timeout_ms, int fault_call, int skip_rank,
-                        int delay_rank, int delay_ms, int drop_src, int drop_dst, int drop_phase,
-                        int stale_epoch, uint32_t* status) {
+// `minexp` matters to the sparse variant (3) only: the fixed-accuracy rule's smallest bit-plane exponent.
+int gcow_protocol_model2(const float* xs, float* outs, int P, uint64_t n, int G, int bits, int variant,
+                         int shift, int calls, int timeout_ms, int fault_call, int skip_rank,
+                         int delay_rank, int delay_ms, int drop_src, int drop_dst, int drop_phase,
+                         int stale_epoch, uint32_t* status, int minexp) {
   Model m;
-  m.P = P; m.G = G; m.bits = bits; m.variant = variant; m.shift = shift; m.n = n;
+  m.P = P; m.G = G; m.bits = bits; m.variant = variant; m.shift = shift; m.n = n; m.minexp = minexp;
   m.L = ar_layout(n, P, G, bits, variant);
   m.region_cap = m.L.region_bytes;
   m.arena.assign(P, std::vector<uint8_t>(arena_bytes_for(m.region_cap), 0));
@@ -227,6 +343,15 @@ int gcow_protocol_model(const float* xs, float* outs, int P, uint64_t n, int G, 
         const float* in = xs + ((uint64_t)c * P + r) * n;
         float* out = outs + ((uint64_t)c * P + r) * n;
         uint32_t epoch = first_epoch + (uint32_t)c;
+        if (variant == kTwoShotSparse) {
+          switch (bits) {
+            case 16: run_rank_sparse<16>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+            case 32: run_rank_sparse<32>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+            case 64: run_rank_sparse<64>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+            default: run_rank_sparse<128>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
+          }
+          return;
+        }
         switch (bits) {
           case 16: run_rank<16>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
           case 32: run_rank<32>(m, r, in, out, epoch, timeout_ms, ft, status + 8 * r); break;
@@ -240,6 +365,14 @@ int gcow_protocol_model(const float* xs, float* outs, int P, uint64_t n, int G, 
   int failed = 0;
   for (int r = 0; r < P; r++) failed += status[8 * r] != 0;
   return failed;
+}
+
+int gcow_protocol_model(const float* xs, float* outs, int P, uint64_t n, int G, int bits, int variant,
+                        int shift, int calls, int timeout_ms, int fault_call, int skip_rank,
+                        int delay_rank, int delay_ms, int drop_src, int drop_dst, int drop_phase,
+                        int stale_epoch, uint32_t* status) {
+  return gcow_protocol_model2(xs, outs, P, n, G, bits, variant, shift, calls, timeout_ms, fault_call, skip_rank,
+                              delay_rank, delay_ms, drop_src, drop_dst, drop_phase, stale_epoch, status, -1074);
 }
 
 }  // extern "C"

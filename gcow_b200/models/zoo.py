@@ -48,6 +48,7 @@ def torchvision_names() -> list:
 def build_model(name: str, pretrained: bool = False, **kw) -> nn.Module:
     """Model ``name`` from this package's zoo or from torchvision (layers swapped to own kernels)."""
     from . import MODELS
+    name = name.replace("-", "_")
     if name in MODELS and not pretrained:
         return MODELS[name](**kw)
     import torchvision.models as tvm

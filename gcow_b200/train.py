@@ -147,6 +147,7 @@ class Trainer:
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         self.cfg = cfg or GcowConfig.from_env()
         ops_backend.set_backend(ops)
+        model = model.replace("-", "_")
         self.kind = "bert" if model.startswith("bert") else "resnet"
         self.model_name, self.batch_size, self.seq_len = model, batch_size, seq_len
         torch.manual_seed(seed)                       # same initial weights on every rank

@@ -12,9 +12,11 @@ the GPU and, in rate mode, inside the gradient all-reduce itself.
 
 Codec modes (hw/models/train_imagenet.py:449-475):
   rate       fused compressed all-reduce at `rate` bits/value (compression on the wire)
-  accuracy   every bucket is round-tripped through the fixed-accuracy codec on the GPU,
-  precision  / fixed-precision codec, then all-reduced by NCCL in fp32 (variable-rate
-             streams cannot be summed block by block by the fused kernel)
+  accuracy   with --accuracy-cap-rate R (4, 8, 16 or 32): inside the fused all-reduce too - bit planes below the
+             tolerance are dropped, a block wholly below it sends nothing, no block exceeds 4R bits (ZFP expert
+             mode). Without the cap: every bucket is round-tripped through the uncapped fixed-accuracy codec on the
+             GPU and then all-reduced by NCCL in fp32
+  precision  fixed-precision codec round trip on the GPU, then NCCL fp32
   lossless   plain NCCL fp32 all-reduce (the control arm)
 """
 from __future__ import annotations
@@ -44,6 +46,8 @@ def parse(argv=None) -> argparse.Namespace:
     ap.add_argument("--zfp-mode", default="", choices=["", "precision", "accuracy", "rate", "lossless"])
     ap.add_argument("--rates", type=float, nargs="+", default=[16])
     ap.add_argument("--tolerances", type=float, nargs="+", default=[1e-6])
+    ap.add_argument("--accuracy-cap-rate", type=float, default=0,
+                    help="accuracy mode on the wire: cap of 4, 8, 16 or 32 bits/value per block (0: codec round trip + NCCL)")
     ap.add_argument("--precisions", type=int, nargs="+", default=[16])
     ap.add_argument("--reversed", action="store_true", help="walk the sweep variables in reverse order")
     ap.add_argument("--epochs", type=int, default=90)
@@ -134,8 +138,11 @@ def run_one(args, mode: str, variable) -> dict:
     rank = int(os.environ.get("RANK", 0))
     cfg_over = dict(rate=float(variable) if mode == "rate" else None)
     cfg = GcowConfig.from_cli(args)
+    wire_accuracy = mode == "accuracy" and args.accuracy_cap_rate > 0
     if mode == "rate":
         cfg.mode, cfg.rate = "rate", float(variable)
+    elif wire_accuracy:      # fixed accuracy inside the all-reduce: planes below the tolerance dropped, blocks capped
+        cfg.mode, cfg.tolerance, cfg.rate = "accuracy", float(variable), float(args.accuracy_cap_rate)
     else:
         cfg.variant = "nccl"                     # DDP's own NCCL path; a hook is added below for the lossy modes
     classes = args.num_classes or (10 if args.cifar else 1000)
@@ -150,7 +157,7 @@ def run_one(args, mode: str, variable) -> dict:
     for g in tr.opt.param_groups:
         g["momentum"], g["weight_decay"] = args.momentum, args.wd
     hook_state = None
-    if mode in ("accuracy", "precision"):
+    if mode in ("accuracy", "precision") and not wire_accuracy:
         from .codec import ZfpParams
         p = ZfpParams.from_accuracy(float(variable)) if mode == "accuracy" else ZfpParams.from_precision(int(variable))
         hook_state = {"params": p, "bytes_in": 0, "bytes_out": 0}

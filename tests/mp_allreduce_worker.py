@@ -72,6 +72,31 @@ def main():
             fails.append(f"rate {rate} unaligned view wrote outside its range")
         ran += 1
         del ar
+    # fixed accuracy with a bit cap (the sparse variant): half of every input lies far below the tolerance, so the
+    # blocks there send nothing; results against the host model at the same parameters, wire bytes against the count
+    for cap, tol in ((8, 1e-3), (4, 1e-2), (16, 1e-6), (32, 1e-4)):
+        cfg = GcowConfig(mode="accuracy", tolerance=tol, rate=cap, comm_ctas=int(os.environ.get("GCOW_TEST_CTAS", "24")),
+                         timeout_ms=5000)
+        ar = CompressedAllReduce(1 << 21, cfg, device=dev, backend=backend)
+        for n in sizes:
+            xs = np.stack([gen(7000 * n + 31 * cap + r, n) for r in range(world)])
+            xs[:, n // 2:] *= np.float32(1e-5)
+            ref = allreduce_oracle(xs, ar.params, "twoshot", shift)
+            x = torch.from_numpy(xs[rank]).to(dev)
+            y1 = ar(x.clone())
+            y2 = ar(x.clone())
+            ar.check()
+            ran += 1
+            for y in (y1, y2):
+                if not np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32)):
+                    bad = int((y.cpu().numpy().view(np.uint32) != ref.view(np.uint32)).sum())
+                    fails.append(f"accuracy tol {tol} cap {cap} n {n}: {bad} words differ")
+                    break
+        if world > 1:
+            dense = ar.bytes_in * cap / 32.0 * 2.0 * (world - 1) / world
+            if not (0 < ar.wire_bytes() < 0.8 * dense):
+                fails.append(f"accuracy tol {tol} cap {cap}: {ar.wire_bytes()} wire bytes, dense would be {dense:.0f}")
+        del ar
     if os.environ.get("GCOW_TEST_BIG") == "1":
         # One 256 MB fp32 buffer per rank (values ~N(0, 1e-3), seed = rank) at 4, 8 and 16 bit/value against the host
         # model: rank 0 computes decode-sum-encode on the CPU and broadcasts it, every rank compares on the device.

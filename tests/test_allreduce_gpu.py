@@ -43,6 +43,33 @@ def test_single_rank_equals_oracle(rate):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("cap,tol", [(4, 1e-2), (8, 1e-3), (16, 1e-6), (32, 1e-4)])
+def test_accuracy_mode_single_rank_equals_oracle(cap, tol):
+    """Fixed accuracy with a bit cap (the sparse variant): bit-exact against the host model at the same four codec
+    parameters; blocks below the tolerance come back as zeros; error feedback keeps what was dropped."""
+    ar = CompressedAllReduce(1 << 20, GcowConfig(mode="accuracy", tolerance=tol, rate=cap, comm_ctas=64))
+    assert ar.pick_variant(123) == "sparse" and ar.params.minbits == 1 and ar.params.maxbits == 4 * cap
+    for n in (3, 4099, 1 << 20, (1 << 20) + 77):
+        x = gen(n + cap, n)
+        x[n // 2:] *= np.float32(1e-5)                       # far below every tolerance used here
+        pieces = [x[i:i + (1 << 20)] for i in range(0, n, 1 << 20)]
+        ref = np.concatenate([allreduce_oracle(q[None], ar.params, "twoshot", 0) for q in pieces])
+        y = ar(torch.from_numpy(x).cuda())
+        ar.check()
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+        if n > 8:
+            assert not ref[n // 2 + 4:].any() and ref[: n // 2].any()
+    x = torch.from_numpy(gen(5, 4096)).cuda()
+    res = torch.zeros_like(x)
+    y = ar(x.clone(), residual=res)
+    ar.check()
+    p1 = ZfpParams(ar.params.minbits, ar.params.maxbits, ar.params.maxprec, ar.params.minexp)
+    once = allreduce_oracle(x.cpu().numpy()[None], p1, "oneshot", 0)        # D(E(x)): what this rank's code kept
+    assert np.array_equal(res.cpu().numpy(), x.cpu().numpy() - once)
+    assert ar.wire_bytes() == 0                                               # one rank: nothing leaves the GPU
+
+
+@pytest.mark.gpu
 def test_rate_2_is_the_header_only_floor():
     """9 bits per block keep no bit plane: D(E(x)) = 0, and so is the reduced result (as in the host model)."""
     p = ZfpParams.from_rate(2, 1)

@@ -392,3 +392,30 @@ def test_cli_reads_a_raw_float32_field(tmp_path, capsys):
     assert first[0].split()[0].startswith("1.0") and json.loads(first[-1])["values"] == 720
     assert cli.main(["--input", str(npy), "--device", "cpu", "--out", str(o2), "--iters", "1"]) == 0
     assert o1.read_bytes() == o2.read_bytes()
+
+
+@pytest.mark.parametrize("bits", [16, 32, 64, 128])
+@pytest.mark.parametrize("tol", [1e-1, 1e-2, 1e-3, 1e-6, 1e-9])
+def test_lean_coders_under_the_accuracy_rule(bits, tol):
+    """Fixed accuracy with a bit cap on the lean (table-driven) coders, as the sparse all-reduce uses them, against
+    the plane-by-plane definition: noise, quantised values (few planes set), smooth ramps, tiny and huge blocks."""
+    import ctypes as C
+    from gcow_b200 import _native
+    rng = np.random.default_rng(bits)
+    n = 40000
+    minexp = ZfpParams.from_accuracy(tol).minexp
+    cases = [
+        rng.standard_normal(n) * 1e-3,
+        np.round(rng.standard_normal(n) * 8) / 8 * 1e-3,             # few significant planes
+        np.linspace(0, 1e-2, n),                                     # smooth
+        rng.standard_normal(n) * 10.0 ** rng.integers(-12, 3, n),    # every magnitude
+        np.where(rng.random(n) < 0.7, 0.0, rng.standard_normal(n)),  # mostly zeros
+    ]
+    for x in cases:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty_like(x)
+        bad = _native.cpu().gcow_lean_accuracy_check(x.ctypes.data, n, bits, minexp, out.ctypes.data)
+        assert bad == 0
+        kept = np.abs(out).reshape(-1, 4).max(axis=1) > 0
+        if kept.any() and bits == 128 and tol >= 1e-3 and np.abs(x).max() < 1:   # where the cap never cuts, the bound holds
+            assert np.abs(out - x).max() <= tol

@@ -109,3 +109,28 @@ def test_oracle_error_vs_exact_sum():
     for rate, lim in ((8, 2e-4), (16, 1e-6)):
         y = allreduce_oracle(xs, ZfpParams.from_rate(rate, 1), "twoshot", 3)
         assert np.sqrt(np.mean((y - exact) ** 2)) < lim
+
+
+@pytest.mark.parametrize("P", [1, 2, 3, 8])
+@pytest.mark.parametrize("bits,tol", [(16, 1e-2), (32, 1e-3), (64, 1e-6), (128, 1e-4)])
+def test_sparse_variant_matches_oracle(P, bits, tol):
+    """Fixed accuracy with a bit cap: packed codes plus a bitmap per chunk give what the host model gives at the
+    same four parameters, for sizes around the chunk and slice bounds."""
+    acc = ZfpParams.from_accuracy(tol)
+    p = ZfpParams(1, bits, acc.maxprec, acc.minexp)
+    rng = np.random.default_rng(bits + P)
+    for n in (1, 7, 1023, 4 * 256 * 3 + 5, 70001):
+        xs = (rng.standard_normal((1, P, n)) * 1e-3).astype(np.float32)
+        xs[:, :, n // 2:] *= np.float32(1e-5)
+        for shift in (0, 2):
+            outs, status, failed = protocol_model(xs, bits, "sparse", ctas=3, shift=shift, minexp=acc.minexp)
+            assert failed == 0
+            want = allreduce_oracle(xs[0], p, "twoshot", shift)
+            for r in range(P):
+                assert np.array_equal(outs[0, r].view(np.uint32), want.view(np.uint32))
+
+
+def test_sparse_variant_times_out_like_the_others():
+    xs = np.zeros((1, 3, 4096), np.float32)
+    outs, status, failed = protocol_model(xs, 32, "sparse", ctas=2, timeout_ms=150, fault_call=0, skip_rank=1, minexp=-10)
+    assert failed == 2 and status[0, 0] == 1 and status[2, 0] == 1
