@@ -297,7 +297,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="gcow", choices=["gcow", "reference", "nccl"])
     ap.add_argument("--model", default="resnet50")
-    ap.add_argument("--batch", type=int, default=256, help="per-GPU batch")
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: 256 images for a ResNet, 32 sequences for BERT)")
     ap.add_argument("--rate", type=float, default=8.0)
     ap.add_argument("--ops", default="own", choices=["own", "torch"])
     ap.add_argument("--variant", default="auto")
@@ -308,6 +308,7 @@ def main() -> int:
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the NCCL arm and the codec / all-reduce side measurements after the timed loops")
     args = ap.parse_args()
+    args.batch = args.batch or (32 if args.model.replace("-", "_").startswith("bert") else 256)
     if args.impl == "reference":
         return reference_arm(args)
     if args.warmup < 3:

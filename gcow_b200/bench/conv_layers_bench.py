@@ -71,7 +71,8 @@ def main(argv=None):
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default="")
-    ap.add_argument("--alt-1x1", action="store_true", help="also time the 1x1 layers on the implicit-GEMM kernel")
+    ap.add_argument("--alt-1x1", action="store_true",
+                    help="also time every stride-1 1x1 layer on the path the routing did NOT choose (GEMM or one-tap implicit GEMM)")
     args = ap.parse_args(argv)
     layers, stem = collect(args.arch, args.batch, args.image)
     backend.set_backend("own")
@@ -84,14 +85,14 @@ def main(argv=None):
         gy = None
         arms = [("own", None), ("cudnn", "lib")]
         if args.alt_1x1 and k == 1 and s == 1:
-            arms.append(("igemm1x1", "auto"))      # forces the one-tap implicit GEMM whatever the pixel count
+            arms.append(("alt1x1", "auto"))        # forces the other 1x1 path, whatever the pixel count
         for arm, env in arms:
             if env is None:
                 os.environ.pop("GCOW_CONV", None)
             else:
                 os.environ["GCOW_CONV"] = env
-            if arm == "igemm1x1":
-                os.environ["GCOW_CONV1X1"] = "igemm"
+            if arm == "alt1x1":
+                os.environ["GCOW_CONV1X1"] = "gemm" if row["own_path"] == "igemm" else "igemm"
             else:
                 os.environ.pop("GCOW_CONV1X1", None)
             with torch.autocast("cuda", dtype=torch.bfloat16):

@@ -162,6 +162,7 @@ class CompressedAllReduce:
                                                [C.c_void_p(0)] * (8 - len(self.arena.peer_ptrs))))
         self.status = torch.zeros(16, dtype=torch.int32, device=self.device)   # [0:8] record, [8] abort
         self.status_host = torch.zeros(16, dtype=torch.int32).pin_memory()
+        self._lag_host = None          # check_lagged's two pinned slots, made on first use
         self.stamps = None
         self.epoch = 0
         self.stream = torch.cuda.Stream(device=self.device, priority=-1)
@@ -307,6 +308,34 @@ class CompressedAllReduce:
                 self.status.zero_()
             s.synchronize()
             raise CollectiveTimeout(self.rank, rec)
+
+    def check_lagged(self, stream: torch.cuda.Stream | None = None) -> None:
+        """As ``check`` without stalling the host: enqueue a copy of the status record on ``stream`` and raise for the
+        record copied by the PREVIOUS call (whose copy finished a step ago). A time-out is therefore reported one
+        call late; callers that must act on it before using the result (safe mode) use ``check``."""
+        s = stream or torch.cuda.current_stream(self.device)
+        if self._lag_host is None:
+            self._lag_host = torch.zeros(2, 16, dtype=torch.int32).pin_memory()
+            self._lag_events = [None, None]
+            self._lag_calls = 0
+        slot = self._lag_calls & 1
+        self._lag_calls += 1
+        with torch.cuda.stream(s):
+            self._lag_host[slot].copy_(self.status, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(s)
+        self._lag_events[slot] = ev
+        prev = slot ^ 1
+        if self._lag_events[prev] is not None:
+            self._lag_events[prev].synchronize()
+            self._lag_events[prev] = None
+            if int(self._lag_host[prev, 0]) != 0:
+                rec = dict(zip(("code", "phase", "peer", "cta", "expected", "seen", "epoch"),
+                               (int(v) for v in self._lag_host[prev, :7])))
+                with torch.cuda.stream(s):
+                    self.status.zero_()
+                self._lag_events = [None, None]
+                raise CollectiveTimeout(self.rank, rec)
 
     def phase_stamps(self) -> torch.Tensor | None:
         """[ctas, 4] device nanosecond stamps (start, pushed, reduced, done) of the last call."""

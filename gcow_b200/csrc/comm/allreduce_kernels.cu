@@ -448,7 +448,7 @@ __device__ __forceinline__ bool sparse_encode(float (&f)[4], const ArArgs& a, ui
 }
 
 template <int BITS>
-__global__ void __launch_bounds__(kArThreads, 4)
+__global__ void __launch_bounds__(kArThreads, 5)
 allreduce_sparse_kernel(const ArArgs a) {
   using C = Code<BITS>;
   constexpr int NW = C::NW;
@@ -456,6 +456,7 @@ allreduce_sparse_kernel(const ArArgs a) {
   __shared__ __align__(16) uint32_t epair[kEncPairTabSize];
   __shared__ __align__(16) uint32_t dloop[kDecLoopTabSize];
   __shared__ int s_ok;
+  __shared__ uint32_t s_run[kArThreads / 32][kMaxRanks];
   for (int i = threadIdx.x; i < kDecLoopTabSize / 4; i += blockDim.x)
     reinterpret_cast<uint4*>(dloop)[i] = reinterpret_cast<const uint4*>(a.loop_table)[i];
   for (int i = threadIdx.x; i < kEncPairTabSize / 4; i += blockDim.x)
@@ -527,29 +528,31 @@ allreduce_sparse_kernel(const ArArgs a) {
     const uint64_t c0 = s0 + (uint64_t)warp * CL;
     if (c0 < s1) {
       const uint64_t c1 = c0 + CL < s1 ? c0 + CL : s1;
-      uint32_t run_in[kMaxRanks];
-#pragma unroll
-      for (int s = 0; s < kMaxRanks; s++) run_in[s] = 0;
+      // packed position reached in every source's chunk: one counter per (warp, source) in shared memory, so that the
+      // loop over the sources stays a loop (eight inlined copies of the decoder would not fit the instruction cache)
+      if (lane < kMaxRanks) s_run[warp][lane] = 0;
+      __syncwarp();
       uint64_t run_out = 0;
       for (uint64_t base = c0; base < c1; base += 32) {
         const uint64_t b = base + lane, gb = (uint64_t)r * SB + b;
         float acc[4] = {0, 0, 0, 0};                            // 0 + d is d: the sum is in ascending rank order
+#pragma unroll 1
+        for (int s = 0; s < P; s++) {
+          const uint8_t* src = local + a.region_off + (uint64_t)s * L.slot_bytes;
+          const uint32_t word = __ldcg(reinterpret_cast<const uint32_t*>(src + L.bitmap_off) + (base >> 5));
+          const uint32_t run = s_run[warp][s];
+          if ((word >> lane) & 1u) {
+            uint32_t w[NW];
+            C::ld(src, c0 + run + __popc(word & below), w);
+            float d[4];
+            decode_block_1d_lean<BITS>(d, lt, w, 0, accuracy_kmin(w[0], a.minexp));
 #pragma unroll
-        for (int s = 0; s < kMaxRanks; s++) {
-          if (s < P) {
-            const uint8_t* src = local + a.region_off + (uint64_t)s * L.slot_bytes;
-            const uint32_t word = __ldcg(reinterpret_cast<const uint32_t*>(src + L.bitmap_off) + (base >> 5));
-            if ((word >> lane) & 1u) {
-              uint32_t w[NW];
-              C::ld(src, c0 + run_in[s] + __popc(word & below), w);
-              float d[4];
-              decode_block_1d_lean<BITS>(d, lt, w, 0, accuracy_kmin(w[0], a.minexp));
-#pragma unroll
-              for (int i = 0; i < 4; i++) acc[i] += d[i];
-            }
-            run_in[s] += __popc(word);
+            for (int i = 0; i < 4; i++) acc[i] += d[i];
           }
+          __syncwarp();
+          if (lane == 0) s_run[warp][s] = run + __popc(word);
         }
+        __syncwarp();
         bool keep = false;
         uint32_t w[NW];
         if (b < c1 && gb < NB) {

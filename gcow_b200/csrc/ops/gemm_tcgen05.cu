@@ -28,6 +28,7 @@
 // Replaces the cuBLAS GEMMs behind nn.Linear / 1x1 convolutions in the
 // reference's models (hw/models/resenet.py:11,17,90).
 #include <stdio.h>
+#include <string.h>
 #include <stdlib.h>
 #include <mutex>
 
@@ -63,6 +64,7 @@ struct Params {
   int M, N, K, ldc, flags;
   int batch;               // number of independent products (operands are 3-D tensor maps when > 1)
   int a_merged, b_merged;  // MN-major operand fetched as ONE box per stage (its row length is a multiple of 64)
+  int tma_store;           // bf16 C without residual / aux: the epilogue hands 32 x 32 boxes to the TMA (tmap_c is valid)
   long long stride_c;      // elements between consecutive C (and residual) matrices
   uint32_t* error;         // device word, set non-zero when a wait gave up
 };
@@ -90,7 +92,7 @@ __device__ __forceinline__ bool mbar_wait(Smem* sm, uint64_t* bar, uint32_t pari
 template <int BM_, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(Shape<BM_>::THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const Params p) {
+                 const __grid_constant__ CUtensorMap tmap_c, const Params p) {
   using S = Shape<BM_>;
   constexpr int BM = S::BM, STAGES = S::STAGES, A_BYTES = S::A_BYTES, HALVES = S::HALVES, EPI_WARPS = S::EPI_WARPS;
   extern __shared__ uint8_t smem_raw[];
@@ -98,8 +100,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t* smA = base;
   uint8_t* smB = base + STAGES * A_BYTES;
   Smem* sm = reinterpret_cast<Smem*>(base + STAGES * (A_BYTES + B_BYTES));
-  // per-warp staging buffers of the epilogue, 16-byte aligned behind the barriers
-  uint8_t* stage_base = reinterpret_cast<uint8_t*>(((uintptr_t)(sm + 1) + 15) & ~(uintptr_t)15);
+  // per-warp staging buffers of the epilogue (two each) behind the barriers; 512-byte aligned, because their layout
+  // (tc::stage_offset) is the 64-byte swizzle of the output tensor map, which is a function of the address
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>(((uintptr_t)(sm + 1) + 511) & ~(uintptr_t)511);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
@@ -213,6 +216,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     constexpr int COLS = BN / (EPI_WARPS / 4);    // columns of each accumulator this warp drains
     const int col0 = (ew / 4) * COLS;
     uint32_t t = 0;
+    int sbuf = 0;                                 // staging buffer of the next TMA store
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
       const int bz = tile / tiles_mn, tmn = tile - bz * tiles_mn;
@@ -230,10 +234,46 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // while chunk c is converted and stored.
         auto process = [&](const uint32_t (&r)[32], int c) {
           const int n = n0 + col0 + c * 32;
+          if (p.tma_store && n + 32 <= p.N && m0 + h * 128 + q * 32 < p.M) {
+            // The warp's 32 x 32 block goes to its staging buffer in the output map's swizzle and one lane hands it to
+            // the TMA, which clips rows past M. Two buffers alternate: a buffer is rewritten only after the store
+            // issued from it two blocks ago has finished reading it.
+            uint8_t* stg = stage_base + (ew * 2 + sbuf) * kStageWarpBytes;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+            if (p.flags & kBias) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] += __ldg(p.bias + n + j);
+            }
+            if (p.flags & kGelu) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              uint4 o;
+              __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; e++) ob[e] = __floats2bfloat162_rn(v[8 * k + 2 * e], v[8 * k + 2 * e + 1]);
+              *reinterpret_cast<uint4*>(stg + stage_offset(lane, k)) = o;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                           ::"l"((uint64_t)&tmap_c), "r"(smem_u32(stg)), "r"(n), "r"(m0 + h * 128 + q * 32), "r"(bz) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            }
+            __syncwarp();
+            sbuf ^= 1;
+            return;
+          }
           if (!(p.flags & kOutF32) && n + 32 <= p.N && m0 + h * 128 + q * 32 < p.M) {
             // bf16 output, whole 32-column chunk (warp-uniform): every global access goes through the
             // warp's staging buffer so that it is coalesced
-            uint8_t* stg = stage_base + ew * kStageWarpBytes;
+            uint8_t* stg = stage_base + ew * 2 * kStageWarpBytes;
             const bool row_ok = m < p.M;
             const size_t off = (size_t)bz * (size_t)p.stride_c + (size_t)m * p.ldc + n;
             float v[32];
@@ -344,6 +384,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         mbar_arrive(&sm->tmem_empty[acc0 + h]);
       }
     }
+    // the stores this lane handed to the TMA have completed before the CTA's shared memory goes away
+    if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   __syncwarp();
@@ -402,6 +444,21 @@ static int make_map3(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : map_refused(r, 3, dims, strides, box);
 }
 
+// Output map of the TMA-store epilogue: bf16 [batch][rows][cols], box = 32 columns x 32 rows in the 64-byte swizzle.
+static int make_map_store(CUtensorMap* map, void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint64_t batch,
+                          uint64_t bstride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  if (((uintptr_t)ptr & 15) || (ld * 2) % 16 || (bstride * 2) % 16) return -11;
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {ld * 2, bstride * 2};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : map_refused(r, 3, dims, strides, box);
+}
+
 // MN-major matrix [K][cols] (cols a multiple of 64) as {64, K, cols / 64 (, batch)}; box = 64 x 64 x chunks.
 static int make_map_mn(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t cols, uint64_t ld, uint64_t batch,
                        uint64_t bstride, uint32_t chunks) {
@@ -420,7 +477,7 @@ static int make_map_mn(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t c
 }
 
 template <int BM_> constexpr size_t smem_bytes() {
-  return Shape<BM_>::SMEM + sizeof(Smem) + 16 + (size_t)Shape<BM_>::EPI_WARPS * kStageWarpBytes + 1024;
+  return Shape<BM_>::SMEM + sizeof(Smem) + 512 + (size_t)Shape<BM_>::EPI_WARPS * 2 * kStageWarpBytes + 1024;
 }
 
 }  // namespace gemm
@@ -475,7 +532,8 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   if ((flags & kResidual) && (!residual || ((uintptr_t)residual & 15))) return -1;
   if ((flags & (kAuxOut | kGeluGrad)) && (!aux || ((uintptr_t)aux & 15) || N % 32 || (flags & kOutF32))) return -1;
   if ((flags & kAuxOut) && (flags & kGeluGrad)) return -1;
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mc;
+  memset(&mc, 0, sizeof(mc));
   static std::once_flag once;
   static int sms = 148;
   std::call_once(once, [] {
@@ -491,8 +549,10 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   const int tiles256 = ((M + 255) / 256) * ((N + BN - 1) / BN) * batch;
   // ... and for short reductions, where the epilogue of a 256-row tile (which cannot overlap the next tile's
   // first MMAs) would dominate
+  // ... and for very short reductions or few output columns, where the step is bound by memory and the 256-row tile
+  // fetches the B tile half as often (measured on the 1x1 layers of ResNet-50)
   const int bm = (tile_rows == 128 || tile_rows == 256) ? tile_rows
-                                                          : ((tiles256 >= (sms * 4) / 5 && K >= 2048) ? 256 : 128);
+                 : ((tiles256 >= (sms * 4) / 5 && (K >= 2048 || K <= 128 || N <= 64)) ? 256 : 128);
   // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
   int rc;
   // an MN-major operand whose row length is a multiple of 64 is fetched with one copy per stage
@@ -528,11 +588,17 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags; p.error = error;
   p.batch = batch; p.stride_c = batch > 1 ? stride_c : 0;
   p.a_merged = a_merged; p.b_merged = b_merged;
+  // plain bf16 results (bias and GELU allowed) leave through the TMA; N must be whole 32-column blocks
+  p.tma_store = !(flags & (kOutF32 | kResidual | kAccumulate | kAuxOut | kGeluGrad)) && N % 32 == 0;
+  if (p.tma_store) {
+    const uint64_t bs = batch > 1 ? (uint64_t)stride_c : (uint64_t)M * (uint64_t)ldc;
+    if (make_map_store(&mc, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, (uint64_t)batch, bs)) p.tma_store = 0;
+  }
   const int tiles = ((M + bm - 1) / bm) * ((N + BN - 1) / BN) * batch;
   int grid = tiles < sms ? tiles : sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   cudaStream_t st = (cudaStream_t)stream;
-#define GCOW_GEMM_LAUNCH(BM_, A, B) gemm_bf16_kernel<BM_, A, B><<<grid, Shape<BM_>::THREADS, smem_bytes<BM_>(), st>>>(ma, mb, p)
+#define GCOW_GEMM_LAUNCH(BM_, A, B) gemm_bf16_kernel<BM_, A, B><<<grid, Shape<BM_>::THREADS, smem_bytes<BM_>(), st>>>(ma, mb, mc, p)
   if (bm == 256) {
     if (!a_mn && !b_mn) GCOW_GEMM_LAUNCH(256, false, false);
     else if (!a_mn && b_mn) GCOW_GEMM_LAUNCH(256, false, true);

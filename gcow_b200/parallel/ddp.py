@@ -60,21 +60,28 @@ class GcowDDPState:
         return bool(int(flag.item()))
 
     def finish_step(self) -> None:
-        """Call after backward, before the optimizer step: waits for the communication stream and reads
-        the collective's status record. Default mode: a time-out raises CollectiveTimeout. Safe mode
+        """Call after backward, before the optimizer step: reads the collective's status record. Default mode: a
+        time-out raises CollectiveTimeout, one step late (see below). Safe mode
         (``cfg.fallback_nccl``): every bucket was reduced into a side buffer and its own buffer still holds
         the local gradient; the ranks agree whether any of them saw a failure, then either all copy the
         side buffers in, or all redo every bucket of the step with NCCL in fp32."""
-        failed, err = False, None
+        if not self.cfg.fallback_nccl:
+            # The status record is read one step late, so that the host never waits for the device here (a wait at
+            # this point drains the launch queue every step and the short kernels of the next forward pass then run
+            # at the pace of the host). A failed bucket leaves the local gradient in place (the kernel writes its
+            # output only after its last wait), the optimiser applies it, and the next step raises.
+            try:
+                self.ar.check_lagged(self.ar.stream)
+            except CollectiveTimeout:
+                self.timeouts += 1
+                raise
+            return
+        failed = False
         try:
             self.ar.check(self.ar.stream)
-        except CollectiveTimeout as e:
-            failed, err = True, e
+        except CollectiveTimeout:
+            failed = True
             self.timeouts += 1
-        if not self.cfg.fallback_nccl:
-            if failed:
-                raise err
-            return
         if self.agree_on_failure(failed):
             world = dist.get_world_size(self.group) if dist.is_initialized() else 1
             for buf, _side in self.pending:

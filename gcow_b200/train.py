@@ -306,6 +306,8 @@ class Trainer:
     def last_loss(self) -> float:
         """Loss of the latest ``step`` call (synchronises); raises if a compute kernel gave up during it."""
         torch.cuda.current_stream().synchronize()
+        if self.hook_state is not None:          # the per-step check of the collective lags by one step: settle it here
+            self.hook_state.ar.check()
         self._raise_on_kernel_error(int(self.err_host[self.steps & 1]))
         return float(self.loss_host[self.steps & 1, 0])
 

@@ -83,22 +83,25 @@ def test_safe_mode_commits_and_falls_back_to_nccl():
 
 def test_train_cli_modes_and_jsonl_log(tmp_path):
     """The study driver end to end on tiny synthetic CIFAR-like data: fused rate mode,
-    accuracy mode (codec round trip + NCCL) and the lossless control; CSV and JSONL outputs."""
+    accuracy mode (codec round trip + NCCL, and inside the fused all-reduce with a bit cap) and the lossless control;
+    CSV and JSONL outputs."""
     import json
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     log = tmp_path / "steps.jsonl"
-    for mode, extra in (("rate", ["--rates", "8"]), ("accuracy", ["--tolerances", "1e-3"]), ("lossless", [])):
+    for tag, mode, extra in (("rate", "rate", ["--rates", "8"]), ("accuracy", "accuracy", ["--tolerances", "1e-3"]),
+                             ("wire", "accuracy", ["--tolerances", "1e-3", "--accuracy-cap-rate", "8"]),
+                             ("lossless", "lossless", [])):
         cmd = [sys.executable, "-m", "gcow_b200.train_cli", "-a", "resnet18", "--cifar", "--dummy", "--epochs", "1",
-               "--steps-per-epoch", "6", "-b", "8", "--zfp-mode", mode, "--out-dir", str(tmp_path / mode),
+               "--steps-per-epoch", "6", "-b", "8", "--zfp-mode", mode, "--out-dir", str(tmp_path / tag),
                "--gcow-bucket-mb", "1", "--gcow-comm-ctas", "16", "--gcow-log-path", str(log)] + extra
         env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29900 + os.getpid() % 50))
         proc = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=600)
         assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
-        csv = (tmp_path / mode / "resnet18.csv").read_text().splitlines()
+        csv = (tmp_path / tag / "resnet18.csv").read_text().splitlines()
         assert len(csv) == 2 and "samples_per_sec" in csv[0]
-        assert (tmp_path / mode / "models" / f"resnet18_{mode}_{'8.0' if mode == 'rate' else ('0.001' if mode == 'accuracy' else '0')}_ckp.tar").exists()
+        assert (tmp_path / tag / "models" / f"resnet18_{mode}_{'8.0' if mode == 'rate' else ('0.001' if mode == 'accuracy' else '0')}_ckp.tar").exists()
     recs = [json.loads(l) for l in log.read_text().splitlines()]
     assert any(r.get("buckets", 0) > 0 and r.get("wire_bytes_per_rank", 0) > 0 for r in recs)
 
