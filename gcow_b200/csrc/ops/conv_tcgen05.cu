@@ -1,5 +1,5 @@
 // Implicit-GEMM convolution on the 5th-generation tensor cores (sm_100a), NHWC bf16,
-// stride 1, any odd or even filter size with zero padding. No im2col matrix is ever
+// stride 1 or 2, any odd or even filter size with zero padding. No im2col matrix is ever
 // written: the TMA unit gathers the shifted input window of every filter tap
 // straight from the activation tensor, and its out-of-bounds zero fill IS the padding.
 //
@@ -9,8 +9,12 @@
 //             map {C, W, H, N}; for tap (r,s) the same box is fetched at (w0+s-pw, h0+r-ph).
 //             Rows of the box land in shared memory as 128-byte channel rows with the
 //             128-byte swizzle, exactly the K-major operand layout of tcgen05.mma.
+//             Stride 2: the tensor map steps two elements along W and H (elementStrides), so the box holds every
+//             second input pixel and the same code runs on the half-size output grid.
 //   dgrad     the same kernel on dY with the filter flipped and its channel roles swapped
-//             (flip_weights_kernel), padding k-1-p.
+//             (flip_weights_kernel), padding k-1-p. Stride 2 (3x3, padding 1): the input gradient splits by the
+//             parity of its pixel coordinates into four stride-1 convolutions of dY with 1, 2, 2 and 4 of the nine
+//             taps (phase_weights_kernel); each writes every second pixel of every second row of dX.
 //   wgrad     dW[co, (r,s,ci)] = sum_pixels dY[pixel, co] * X[pixel + (r,s) - p, ci]
 //             GEMM view: M = Co, N = taps*Ci, K = pixels. Both operands are MN-major:
 //             64-pixel boxes of dY (A) and of the shifted X (B, one 64-channel box per
@@ -65,6 +69,9 @@ struct Params {
   int split, chunks_per_split;     // wgrad: CTA groups over the pixel range
   int b_chunks;         // wgrad: 64-channel groups of X fetched by one copy (1, 2 or 4)
   int flags;
+  int stride;           // step of the input window per output pixel (forward) / per dY pixel (wgrad): 1 or 2
+  int out_step, out_off_h, out_off_w, out_H, out_W;   // forward: tile pixel (h, w) is stored at (h * out_step + out_off_h,
+                                                      // w * out_step + out_off_w) of a [N, out_H, out_W, Co] tensor
   uint32_t* error;
 };
 
@@ -152,7 +159,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               mbar_expect_tx(&sm->full[s], a_tx + (uint32_t)b_bytes);
               const uint32_t bar = smem_u32(&sm->full[s]);
               uint8_t* st = base + s * stage_bytes;
-              tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0);
+              tma_load_4d(smem_u32(st), &map_a, bar, cc * BK, w0 * p.stride + sx - p.pad_w, h0 * p.stride + r - p.pad_h, n0);
               tma_load_2d(smem_u32(st + A_BYTES), &map_b, bar, tap * p.Ci + cc * BK, co0);
               if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
             }
@@ -179,7 +186,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               int tap = g / cchunks, ch = g - tap * cchunks;
               if (g >= col_groups) { tap = 0; ch = cchunks; }     // past the last column group: zeros
               const int r = tap / p.kw, sx = tap - r * p.kw;
-              tma_load_5d(smem_u32(st + A_BYTES + i * 8192), &map_b, bar, 0, w0 + sx - p.pad_w, h0 + r - p.pad_h, n0, ch);
+              tma_load_5d(smem_u32(st + A_BYTES + i * 8192), &map_b, bar, 0, w0 * p.stride + sx - p.pad_w,
+                          h0 * p.stride + r - p.pad_h, n0, ch);
             }
             if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
           }
@@ -256,10 +264,11 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const int iw = row % p.bw, ih = (row / p.bw) % p.bh, in = row / (p.bw * p.bh);
           const int w = (pt % p.tiles_w) * p.bw + iw, hh = ((pt / p.tiles_w) % p.tiles_h) * p.bh + ih;
           const int n = (pt / (p.tiles_w * p.tiles_h)) * p.bn + in;
-          row_ok = in < p.bn && w < p.W && hh < p.H && n < p.N;
+          const int oh = hh * p.out_step + p.out_off_h, ow = w * p.out_step + p.out_off_w;
+          row_ok = in < p.bn && w < p.W && hh < p.H && n < p.N && oh < p.out_H && ow < p.out_W;
           n_first = tcn * p.bn_cols;
           n_limit = p.Co;
-          row_off = (((size_t)n * p.H + hh) * p.W + w) * (size_t)p.Co;
+          row_off = (((size_t)n * p.out_H + oh) * p.out_W + ow) * (size_t)p.Co;
         } else {
           const int tcol = tile % tiles_col;
           int rest = tile / tiles_col;
@@ -370,20 +379,47 @@ __global__ void flip_weights_kernel(const __nv_bfloat16* __restrict__ w, __nv_bf
   }
 }
 
+// Filters of the four parity phases of the input gradient of a 3x3, stride-2, padding-1 convolution.
+// w [Co][3][3][Ci] -> wp: phase (a, b) (a = row parity of the dX pixel, b = column parity) is a dense
+// (1 + a) x (1 + b) filter [Ci][1 + a][1 + b][Co], its tap (u, v) reading dY at offset (+u, +v); the four
+// filters lie behind one another at element offsets {0, 1, 3, 5} * Ci * Co.
+__global__ void __launch_bounds__(256)
+phase_weights_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wp, int Co, int Ci) {
+  const size_t per = (size_t)Ci * Co;
+  const size_t total = 9 * per;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    // i indexes wp: find the phase, then (ci, u, v, co)
+    const size_t blk = i / per;                       // 0 | 1,2 | 3,4 | 5..8
+    const int ph = blk < 1 ? 0 : (blk < 3 ? 1 : (blk < 5 ? 2 : 3));
+    const int a = ph >> 1, b = ph & 1, kh = 1 + a, kw = 1 + b;
+    const size_t base = (ph == 0 ? 0 : (ph == 1 ? 1 : (ph == 2 ? 3 : 5))) * per;
+    size_t j = i - base;
+    const int co = (int)(j % Co); j /= Co;
+    const int v = (int)(j % kw); j /= kw;
+    const int u = (int)(j % kh); j /= kh;
+    const int ci = (int)j;
+    const int r = a == 0 ? 1 : (u == 0 ? 2 : 0), sx = b == 0 ? 1 : (v == 0 ? 2 : 0);
+    wp[i] = w[(((size_t)co * 3 + r) * 3 + sx) * Ci + ci];
+  }
+}
+
 // ------------------------------------------------------------------- host side
 // bf16 NHWC tensor as {C, W, H, N}; box = 64 channels x bw x bh x bn pixels.
 // chunks > 0: five dimensions {64, W, H, N, C / 64}, the box also spans `chunks` 64-channel groups,
 // which land 64 * bw * bh * bn * 2 bytes apart in shared memory (C must be a multiple of 64).
+// step > 1: the box holds every step-th pixel along W and H (the map's element strides); its traversed extent is then
+// (bw - 1) * step + 1 by (bh - 1) * step + 1.
 static int make_map_nhwc(CUtensorMap* map, const void* ptr, uint64_t N, uint64_t H, uint64_t W, uint64_t C, uint32_t bw,
-                         uint32_t bh, uint32_t bn, uint32_t chunks) {
+                         uint32_t bh, uint32_t bn, uint32_t chunks, uint32_t step = 1) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return -10;
   if (((uintptr_t)ptr & 15) || (C * 2) % 16) return -11;
-  if (bw > 256 || bh > 256 || bn > 256 || (chunks && C % 64)) return -11;
+  const uint32_t tw = (bw - 1) * step + 1, th = (bh - 1) * step + 1;
+  if (tw > 256 || th > 256 || bn > 256 || (chunks && C % 64) || step < 1 || step > 8) return -11;
   cuuint64_t dims[5] = {chunks ? 64 : C, W, H, N, C / 64};
   cuuint64_t strides[4] = {C * 2, W * C * 2, H * W * C * 2, 128};
-  cuuint32_t box[5] = {(cuuint32_t)BK, bw, bh, bn, chunks};
-  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  cuuint32_t box[5] = {(cuuint32_t)BK, tw, th, bn, chunks};
+  cuuint32_t estr[5] = {1, step, step, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, chunks ? 5 : 4, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -505,14 +541,13 @@ using namespace gcow::conv;
 
 extern "C" {
 
-// y[N,Ho,Wo,Co] = conv(x[N,Hin,Win,Ci], w[Co,kh,kw,Ci]) (+ bias), stride 1, zero padding (pad_h, pad_w);
-// Ho = Hin + 2*pad_h - kh + 1. bf16, NHWC; Ci a multiple of 64, Co a multiple of 8.
-// `error` is a device word that stays 0 unless a wait gave up. Returns 0, a negative argument error or a CUDA error.
-int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int N, int Hin, int Win, int Ci, int Co,
-                  int kh, int kw, int pad_h, int pad_w, uint32_t* error, void* stream) {
-  const int Ho = Hin + 2 * pad_h - kh + 1, Wo = Win + 2 * pad_w - kw + 1;
+// The forward kernel in full generality: input window step `stride` (1 or 2), an output grid of Ho x Wo tile pixels
+// whose pixel (h, w) is stored at (h * out_step + out_off_h, w * out_step + out_off_w) of y [N, out_H, out_W, Co].
+static int conv_fwd_launch(const void* x, const void* w, void* y, const float* bias, int N, int Hin, int Win, int Ci, int Co,
+                           int kh, int kw, int pad_h, int pad_w, int stride, int Ho, int Wo, int out_step, int out_off_h,
+                           int out_off_w, int out_H, int out_W, uint32_t* error, void* stream) {
   if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
-  if (Ci % 64 || Co % 8 || kh < 1 || kw < 1 || pad_h < 0 || pad_w < 0) return -1;
+  if (Ci % 64 || Co % 8 || kh < 1 || kw < 1 || pad_h < 0 || pad_w < 0 || stride < 1 || stride > 2 || out_step < 1) return -1;
   if ((uintptr_t)y & 15) return -1;
   const int sms = device_sms();
   Params p{};
@@ -527,9 +562,11 @@ int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int 
   p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w;
   p.split = 1; p.chunks_per_split = 0; p.b_chunks = 1;
   p.flags = bias ? kBias : 0;
+  p.stride = stride;
+  p.out_step = out_step; p.out_off_h = out_off_h; p.out_off_w = out_off_w; p.out_H = out_H; p.out_W = out_W;
   p.error = error;
   CUtensorMap ma, mb;
-  int rc = make_map_nhwc(&ma, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, p.bw, p.bh, p.bn, 0);
+  int rc = make_map_nhwc(&ma, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, p.bw, p.bh, p.bn, 0, (uint32_t)stride);
   if (rc) return rc;
   rc = make_map_2d(&mb, w, (uint64_t)Co, (uint64_t)kh * kw * Ci, (uint32_t)p.bn_cols);
   if (rc) return rc;
@@ -541,18 +578,64 @@ int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int 
   return (int)cudaGetLastError();
 }
 
-// Number of fp32 partial results gcow_conv_wgrad writes for these extents (the first dimension of `part`).
-int gcow_conv_wgrad_split(int N, int Hin, int Win, int Ci, int Co, int kh, int kw, int pad_h, int pad_w) {
+// y[N,Ho,Wo,Co] = conv(x[N,Hin,Win,Ci], w[Co,kh,kw,Ci]) (+ bias), stride 1, zero padding (pad_h, pad_w);
+// Ho = Hin + 2*pad_h - kh + 1. bf16, NHWC; Ci a multiple of 64, Co a multiple of 8.
+// `error` is a device word that stays 0 unless a wait gave up. Returns 0, a negative argument error or a CUDA error.
+int gcow_conv_fwd(const void* x, const void* w, void* y, const float* bias, int N, int Hin, int Win, int Ci, int Co,
+                  int kh, int kw, int pad_h, int pad_w, uint32_t* error, void* stream) {
   const int Ho = Hin + 2 * pad_h - kh + 1, Wo = Win + 2 * pad_w - kw + 1;
+  return conv_fwd_launch(x, w, y, bias, N, Hin, Win, Ci, Co, kh, kw, pad_h, pad_w, 1, Ho, Wo, 1, 0, 0, Ho, Wo, error, stream);
+}
+
+// The same with the window moved `stride` (1 or 2) input pixels per output pixel: Ho = (Hin + 2*pad_h - kh) / stride + 1.
+int gcow_conv_fwd_strided(const void* x, const void* w, void* y, const float* bias, int N, int Hin, int Win, int Ci, int Co,
+                          int kh, int kw, int pad_h, int pad_w, int stride, uint32_t* error, void* stream) {
+  if (stride < 1 || stride > 2) return -1;
+  const int Ho = (Hin + 2 * pad_h - kh) / stride + 1, Wo = (Win + 2 * pad_w - kw) / stride + 1;
+  return conv_fwd_launch(x, w, y, bias, N, Hin, Win, Ci, Co, kh, kw, pad_h, pad_w, stride, Ho, Wo, 1, 0, 0, Ho, Wo, error, stream);
+}
+
+// Input gradient of a 3x3, stride-2, padding-1 convolution with even input extents: dx[N,Hin,Win,Ci] from
+// dy[N,Hin/2,Win/2,Co] and w[Co,3,3,Ci]. `wp` is scratch of 9*Ci*Co bf16 for the four phase filters. Four launches of
+// the forward kernel, one per parity of the dx pixel; together they write every pixel of dx exactly once.
+int gcow_conv_dgrad_s2(const void* dy, const void* w, void* wp, void* dx, int N, int Hin, int Win, int Ci, int Co,
+                       uint32_t* error, void* stream) {
+  if (Hin % 2 || Win % 2 || Ci % 64 || Co % 64 || N <= 0) return -1;
+  const int Ho = Hin / 2, Wo = Win / 2;
+  const size_t per = (size_t)Ci * Co;
+  int blocks = (int)((9 * per + 255) / 256);
+  if (blocks > 1184) blocks = 1184;
+  phase_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wp, Co, Ci);
+  int rc = (int)cudaGetLastError();
+  if (rc) return rc;
+  const size_t off[4] = {0, 1, 3, 5};
+  for (int ph = 0; ph < 4; ph++) {
+    const int a = ph >> 1, b = ph & 1;
+    // dY is the input (its channels Co are reduced), dX's channels Ci are the outputs; taps read dY at (+u, +v)
+    rc = conv_fwd_launch(dy, (const __nv_bfloat16*)wp + off[ph] * per, dx, nullptr, N, Ho, Wo, Co, Ci, 1 + a, 1 + b, 0, 0, 1,
+                         Ho, Wo, 2, a, b, Hin, Win, error, stream);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// Number of fp32 partial results gcow_conv_wgrad writes for these extents (the first dimension of `part`).
+int gcow_conv_wgrad_split_strided(int N, int Hin, int Win, int Ci, int Co, int kh, int kw, int pad_h, int pad_w, int stride) {
+  if (stride < 1 || stride > 2) return 0;
+  const int Ho = (Hin + 2 * pad_h - kh) / stride + 1, Wo = (Win + 2 * pad_w - kw) / stride + 1;
   if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
   return wgrad_plan(N, Ho, Wo, Ci, Co, kh * kw, device_sms()).split;
+}
+int gcow_conv_wgrad_split(int N, int Hin, int Win, int Ci, int Co, int kh, int kw, int pad_h, int pad_w) {
+  return gcow_conv_wgrad_split_strided(N, Hin, Win, Ci, Co, kh, kw, pad_h, pad_w, 1);
 }
 
 // part[split][Co][kh*kw*Ci] (fp32) = partial sums over pixel ranges of dy[N,Ho,Wo,Co]^T * shifted x[N,Hin,Win,Ci];
 // the caller adds the `split` slices (gcow_reduce_partials). Ci and Co multiples of 64.
-int gcow_conv_wgrad(const void* dy, const void* x, float* part, int N, int Hin, int Win, int Ci, int Co, int kh, int kw,
-                    int pad_h, int pad_w, uint32_t* error, void* stream) {
-  const int Ho = Hin + 2 * pad_h - kh + 1, Wo = Win + 2 * pad_w - kw + 1;
+int gcow_conv_wgrad_strided(const void* dy, const void* x, float* part, int N, int Hin, int Win, int Ci, int Co, int kh, int kw,
+                            int pad_h, int pad_w, int stride, uint32_t* error, void* stream) {
+  if (stride < 1 || stride > 2) return -1;
+  const int Ho = (Hin + 2 * pad_h - kh) / stride + 1, Wo = (Win + 2 * pad_w - kw) / stride + 1;
   if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
   if (Ci % 64 || Co % 64 || kh < 1 || kw < 1 || pad_h < 0 || pad_w < 0) return -1;
   if ((uintptr_t)part & 15) return -1;
@@ -566,11 +649,14 @@ int gcow_conv_wgrad(const void* dy, const void* x, float* part, int N, int Hin, 
   p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w;
   p.split = q.split; p.chunks_per_split = q.per; p.b_chunks = q.b_chunks;
   p.flags = 0;
+  p.stride = stride;
+  p.out_step = 1; p.out_off_h = 0; p.out_off_w = 0; p.out_H = Ho; p.out_W = Wo;
   p.error = error;
   CUtensorMap ma, mb;
   int rc = make_map_nhwc(&ma, dy, (uint64_t)N, (uint64_t)Ho, (uint64_t)Wo, (uint64_t)Co, q.bw, q.bh, q.bn, 2u * q.halves);
   if (rc) return rc;
-  rc = make_map_nhwc(&mb, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, q.bw, q.bh, q.bn, (uint32_t)q.b_chunks);
+  rc = make_map_nhwc(&mb, x, (uint64_t)N, (uint64_t)Hin, (uint64_t)Win, (uint64_t)Ci, q.bw, q.bh, q.bn, (uint32_t)q.b_chunks,
+                     (uint32_t)stride);
   if (rc) return rc;
   const long long tiles = (long long)q.split * ((Co + 128 * q.halves - 1) / (128 * q.halves)) * ((kh * kw * Ci + 255) / 256);
   const int grid = (int)(tiles < sms ? tiles : sms);
@@ -578,6 +664,11 @@ int gcow_conv_wgrad(const void* dy, const void* x, float* part, int N, int Hin, 
   if (q.halves == 2) conv_igemm_kernel<true, 2><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
   else conv_igemm_kernel<true, 1><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
   return (int)cudaGetLastError();
+}
+
+int gcow_conv_wgrad(const void* dy, const void* x, float* part, int N, int Hin, int Win, int Ci, int Co, int kh, int kw,
+                    int pad_h, int pad_w, uint32_t* error, void* stream) {
+  return gcow_conv_wgrad_strided(dy, x, part, N, Hin, Win, Ci, Co, kh, kw, pad_h, pad_w, 1, error, stream);
 }
 
 // wt[Ci][kh][kw][Co] = w[Co][kh][kw][Ci] rotated by 180 degrees: with it, the gradient with respect to the input of a

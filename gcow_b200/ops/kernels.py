@@ -945,11 +945,82 @@ class _ConvIgemmFn(torch.autograd.Function):
         return gx, gw, gb, None, None
 
 
+class _ConvStride2Fn(torch.autograd.Function):
+    """3x3 convolution with stride 2 and padding 1 over even extents (the down-sampling layer of every ResNet stage)
+    on the implicit-GEMM kernel: the forward and the weight gradient read every second input pixel through a tensor
+    map with element strides; the input gradient is four stride-1 convolutions of dY, one per parity of the dX pixel,
+    with 1, 2, 2 and 4 of the nine taps. No patch matrix and no col2im scatter."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        global _launches
+        N, C, H, W = x.shape
+        Co = w.shape[0]
+        lib = _native.cuda()
+        if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
+            x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        wr = w.detach().permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()                        # [Co, 3, 3, Ci]
+        y = torch.empty((N, Co, H // 2, W // 2), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
+        bias = b.detach().float().contiguous() if b is not None else None
+        _chk(lib.gcow_conv_fwd_strided(x.data_ptr(), wr.data_ptr(), y.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                       N, H, W, C, Co, 3, 3, 1, 1, 2, _error_word(x.device).data_ptr(), _stream(x.device)),
+             "gcow_conv_fwd_strided")
+        _launches += 1
+        ctx.save_for_backward(x, wr)
+        ctx.meta = (N, C, H, W, Co, b is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        x, wr = ctx.saved_tensors
+        N, C, H, W, Co, has_bias = ctx.meta
+        lib = _native.cuda()
+        if gy.dtype != torch.bfloat16 or not gy.is_contiguous(memory_format=torch.channels_last):
+            gy = gy.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        dev, st, err = gy.device, _stream(gy.device), _error_word(gy.device).data_ptr()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            wp = _ws("conv_s2_phase_w", (9 * C * Co,), torch.bfloat16, dev)
+            gx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=dev, memory_format=torch.channels_last)
+            _chk(lib.gcow_conv_dgrad_s2(gy.data_ptr(), wr.data_ptr(), wp.data_ptr(), gx.data_ptr(), N, H, W, C, Co, err, st),
+                 "gcow_conv_dgrad_s2")
+            _launches += 5
+        if ctx.needs_input_grad[1]:
+            split = lib.gcow_conv_wgrad_split_strided(N, H, W, C, Co, 3, 3, 1, 1, 2)
+            part = (_ws("conv_wgrad_part", (split, Co, 9 * C), torch.float32, dev) if split > 1 else
+                    torch.empty((1, Co, 9 * C), dtype=torch.float32, device=dev))
+            _chk(lib.gcow_conv_wgrad_strided(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, 3, 3, 1, 1, 2,
+                                             err, st), "gcow_conv_wgrad_strided")
+            _launches += 1
+            if split > 1:
+                out = torch.empty((Co, 9 * C), dtype=torch.float32, device=dev)
+                _chk(lib.gcow_reduce_partials(part.data_ptr(), out.data_ptr(), split, out.numel(), st), "gcow_reduce_partials")
+                _launches += 1
+            else:
+                out = part[0]
+            gw = out.view(Co, 3, 3, C).permute(0, 3, 1, 2)
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(gy.permute(0, 2, 3, 1).reshape(-1, Co))
+        return gx, gw, gb
+
+
+def conv_igemm_s2_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups: int, dilation) -> bool:
+    """3x3, stride 2, padding 1, dense, even input extents, both channel counts whole 64-channel rows."""
+    return (x.is_cuda and x.dim() == 4 and _have("gcow_conv_dgrad_s2") and groups == 1 and tuple(dilation) == (1, 1)
+            and tuple(stride) == (2, 2) and tuple(padding) == (1, 1) and tuple(w.shape[2:]) == (3, 3)
+            and x.shape[2] % 2 == 0 and x.shape[3] % 2 == 0 and x.shape[1] % 64 == 0 and w.shape[0] % 64 == 0)
+
+
+def conv_igemm_s2(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+    return _ConvStride2Fn.apply(x, w, b)
+
+
 def conv_mode() -> str:
     """GCOW_CONV selects the convolution routing of the own backend:
     ``auto`` (default) - every convolution on this library's kernels: 1x1 layers on the tcgen05 GEMM (strided ones
-    after a pixel subsample), stride-1 KxK layers with whole 64-channel rows on the implicit-GEMM kernel, everything
-    else (strided KxK, the stem) as im2col + GEMM;
+    after a pixel subsample), stride-1 KxK layers with whole 64-channel rows and 3x3 stride-2 layers on the
+    implicit-GEMM kernel, everything else (other strided KxK, the stem) as im2col + GEMM;
     ``mixed`` - own kernels only where they are at least on par with cuDNN (stride-1 KxK with >= 128 channels), cuDNN
     for the rest;
     ``lib`` - cuDNN everywhere (the comparison arm)."""
@@ -961,8 +1032,8 @@ _conv_paths: dict = {}
 
 
 def conv_path_counts(reset: bool = False) -> dict:
-    """How many convolution calls took which path since the last reset: gemm1x1, gemm1x1_strided, igemm, im2col,
-    cudnn. Benchmarks report it; a test asserts that a ResNet-50 step sends nothing to cudnn."""
+    """How many convolution calls took which path since the last reset: gemm1x1, gemm1x1_strided, igemm, igemm_s2,
+    im2col, cudnn. Benchmarks report it; a test asserts that a ResNet-50 step sends nothing to cudnn."""
     out = dict(_conv_paths)
     if reset:
         _conv_paths.clear()
@@ -978,7 +1049,7 @@ def conv_route(x: torch.Tensor, m) -> str:
             and all(isinstance(p, int) for p in m.padding) and m.stride[0] == m.stride[1]
             and m.padding[0] == m.padding[1] and m.kernel_size[0] == m.kernel_size[1] and x.is_cuda and x.dim() == 4):
         k, s, p, w = m.kernel_size[0], m.stride[0], m.padding[0], m.weight
-        if (k == 1 and p == 0 and s == 1 and mode == "auto" and _onebyone_on_igemm(x)
+        if (k == 1 and p == 0 and s == 1 and mode == "auto" and _onebyone_on_igemm(x, w.shape[0])
                 and conv_igemm_usable(x, w, m.stride, m.padding, 1, (1, 1), True)):
             path = "igemm"
         elif k == 1 and p == 0:
@@ -991,21 +1062,24 @@ def conv_route(x: torch.Tensor, m) -> str:
         elif s == 1 and conv_igemm_usable(x, w, m.stride, m.padding, m.groups, m.dilation) and (
                 mode == "auto" or min(w.shape[0], w.shape[1]) >= 128):
             path = "igemm"
+        elif mode == "auto" and conv_igemm_s2_usable(x, w, m.stride, m.padding, m.groups, m.dilation):
+            path = "igemm_s2"
         elif mode == "auto" and conv_gemm_usable(x, w, s, p, m.groups, m.dilation):
             path = "im2col"
     _conv_paths[path] = _conv_paths.get(path, 0) + 1
     return path
 
 
-def _onebyone_on_igemm(x: torch.Tensor) -> bool:
-    """1x1 layers over very many pixels (the 56 x 56 stage of a ResNet at batch 256) are bound by memory and run
-    about 10 % faster as a one-tap implicit GEMM, whose tile is as wide as the layer's output channels, than on the
-    256-column GEMM tile; smaller layers are faster on the GEMM. GCOW_CONV1X1=gemm|igemm forces either."""
+def _onebyone_on_igemm(x: torch.Tensor, out_channels: int = 64) -> bool:
+    """A 1x1 layer with at most 64 output channels over very many pixels (64 -> 64 in the 56 x 56 stage of a ResNet at
+    batch 256) runs about 10 % faster as a one-tap implicit GEMM, whose tile is as wide as the layer's output
+    channels, than on the 256-column GEMM tile; every other 1x1 layer is faster on the GEMM (whose plain bf16
+    results leave through the TMA). GCOW_CONV1X1=gemm|igemm forces either."""
     import os
     forced = os.environ.get("GCOW_CONV1X1", "")
     if forced in ("gemm", "igemm"):
         return forced == "igemm"
-    return x.shape[0] * x.shape[2] * x.shape[3] >= 500_000
+    return out_channels <= 64 and x.shape[0] * x.shape[2] * x.shape[3] >= 500_000
 
 
 def conv_igemm_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups: int, dilation, allow_1x1: bool = False) -> bool:

@@ -54,7 +54,8 @@ def last_conv_path() -> str:
 
 class Conv2d(nn.Conv2d):
     """Convolution routed to this library's kernels (kernels.conv_route): the tcgen05 GEMM for 1x1 layers, the
-    implicit-GEMM kernel for stride-1 KxK layers, im2col + GEMM for strided KxK layers and the stem; cuDNN only on
+    implicit-GEMM kernel for stride-1 KxK layers and 3x3 stride-2 layers, im2col + GEMM for other strided KxK layers and
+    the stem; cuDNN only on
     request (GCOW_CONV=lib / mixed) or for configurations no own kernel covers (groups, dilation, tiny inputs)."""
 
     def forward(self, x):
@@ -67,6 +68,8 @@ class Conv2d(nn.Conv2d):
             return K.conv1x1(K.subsample(x, s), self.weight, self.bias)
         if path == "igemm":
             return K.conv_igemm(x, self.weight, self.bias, self.padding)
+        if path == "igemm_s2":
+            return K.conv_igemm_s2(x, self.weight, self.bias)
         if path == "im2col":
             return K.conv_gemm(x, self.weight, self.bias, self.stride[0], self.padding[0])
         return super().forward(x)

@@ -60,6 +60,39 @@ def test_conv_igemm_forward_and_gradients(case):
     assert _rel(bo.grad, br.grad) < 5e-3
 
 
+# (N, Ci, H, W, Co): whole boxes, ragged pixel boxes, more output than input channels and the reverse
+S2_CASES = [(4, 64, 16, 16, 64), (3, 64, 10, 14, 128), (2, 128, 28, 28, 128), (5, 256, 6, 8, 64), (2, 64, 2, 2, 64)]
+
+
+@pytest.mark.parametrize("case", S2_CASES)
+def test_conv_igemm_stride2_forward_and_gradients(case):
+    """3x3, stride 2, padding 1 on the implicit-GEMM kernel (strided tensor maps; the input gradient as four parity
+    phases) against an fp32 PyTorch convolution of the same bf16-rounded operands."""
+    from gcow_b200.ops import kernels as K
+    N, Ci, H, W, Co = case
+    torch.manual_seed(sum(case))
+    x, w, b = _mk(N, Ci, H, W, Co, 3, 3)
+    xr = x.float().requires_grad_(True)
+    wr = w.clone().requires_grad_(True)
+    br = b.clone().requires_grad_(True)
+    ref = F.conv2d(xr, wr, br, stride=2, padding=1)
+    gy = (torch.randn_like(ref) * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    ref.backward(gy.float())
+    xo = x.clone().requires_grad_(True)
+    wo = w.clone().requires_grad_(True)
+    bo = b.clone().requires_grad_(True)
+    assert K.conv_igemm_s2_usable(xo, wo, (2, 2), (1, 1), 1, (1, 1))
+    y = K.conv_igemm_s2(xo, wo, bo)
+    K.check_errors()
+    assert y.shape == ref.shape and y.dtype == torch.bfloat16
+    assert _rel(y, ref) < 2e-2
+    y.backward(gy)
+    K.check_errors()
+    assert _rel(xo.grad, xr.grad) < 2e-2
+    assert _rel(wo.grad, wr.grad) < 5e-3
+    assert _rel(bo.grad, br.grad) < 5e-3
+
+
 def test_conv_igemm_resnet_layer_shape():
     """One ResNet-50 3x3 layer at a batch that needs several waves of tiles and every split of the weight gradient."""
     from gcow_b200.ops import kernels as K
@@ -102,8 +135,9 @@ MODULE_CASES = [
     (64, 256, 1, 1, 0, 14, True, "gemm1x1"),
     (256, 64, 1, 1, 0, 14, True, "gemm1x1"),
     (256, 512, 1, 2, 0, 14, True, "gemm1x1_strided"),
-    (128, 128, 3, 2, 1, 14, True, "im2col"),
-    (64, 128, 3, 2, 1, 15, True, "im2col"),
+    (128, 128, 3, 2, 1, 14, True, "igemm_s2"),
+    (64, 128, 3, 2, 1, 15, True, "im2col"),          # odd extent: not covered by the stride-2 implicit GEMM
+    (96, 128, 3, 2, 1, 14, True, "im2col"),          # 96 input channels: not whole 64-channel rows
     (3, 64, 7, 2, 3, 32, False, "im2col"),
     (3, 64, 3, 1, 1, 16, False, "im2col"),
 ]
@@ -154,7 +188,8 @@ def test_resnet50_step_sends_no_convolution_to_cudnn(monkeypatch):
     K.check_errors()
     counts = K.conv_path_counts(reset=True)
     assert sum(counts.values()) == 53 and counts.get("cudnn", 0) == 0, counts
-    assert counts["gemm1x1"] == 33 and counts["gemm1x1_strided"] == 3 and counts["igemm"] == 13 and counts["im2col"] == 4
+    assert (counts["gemm1x1"] == 33 and counts["gemm1x1_strided"] == 3 and counts["igemm"] == 13
+            and counts["igemm_s2"] == 3 and counts["im2col"] == 1)
     # at batch 256 the 1x1 layers of the 56 x 56 stage move to the one-tap implicit GEMM (a routing rule on the pixel count)
     big = torch.empty(256, 64, 56, 56, device="meta")
     assert K._onebyone_on_igemm(big) and not K._onebyone_on_igemm(x)
