@@ -1071,7 +1071,7 @@ def conv_route(x: torch.Tensor, m) -> str:
 
 
 def _onebyone_on_igemm(x: torch.Tensor, out_channels: int = 64) -> bool:
-    """A 1x1 layer with at most 64 output channels over very many pixels (64 -> 64 in the 56 x 56 stage of a ResNet at
+    """A 1x1 layer with at most 64 input and output channels over very many pixels (64 -> 64 in the 56 x 56 stage of a ResNet at
     batch 256) runs about 10 % faster as a one-tap implicit GEMM, whose tile is as wide as the layer's output
     channels, than on the 256-column GEMM tile; every other 1x1 layer is faster on the GEMM (whose plain bf16
     results leave through the TMA). GCOW_CONV1X1=gemm|igemm forces either."""
@@ -1079,7 +1079,7 @@ def _onebyone_on_igemm(x: torch.Tensor, out_channels: int = 64) -> bool:
     forced = os.environ.get("GCOW_CONV1X1", "")
     if forced in ("gemm", "igemm"):
         return forced == "igemm"
-    return out_channels <= 64 and x.shape[0] * x.shape[2] * x.shape[3] >= 500_000
+    return out_channels <= 64 and x.shape[1] <= 64 and x.shape[0] * x.shape[2] * x.shape[3] >= 500_000
 
 
 def conv_igemm_usable(x: torch.Tensor, w: torch.Tensor, stride, padding, groups: int, dilation, allow_1x1: bool = False) -> bool:
