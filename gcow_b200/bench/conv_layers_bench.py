@@ -73,8 +73,14 @@ def main(argv=None):
     ap.add_argument("--json", default="")
     ap.add_argument("--alt-1x1", action="store_true",
                     help="also time every stride-1 1x1 layer on the path the routing did NOT choose (GEMM or one-tap implicit GEMM)")
+    ap.add_argument("--layer", type=int, nargs=5, default=None, metavar=("CI", "CO", "K", "STRIDE", "H"),
+                    help="time this one layer shape only (padding K // 2), e.g. for a profiler capture")
     args = ap.parse_args(argv)
-    layers, stem = collect(args.arch, args.batch, args.image)
+    if args.layer:
+        ci, co, k, st, h = args.layer
+        layers, stem = OrderedDict({(ci, co, k, st, k // 2, h): 1}), None
+    else:
+        layers, stem = collect(args.arch, args.batch, args.image)
     backend.set_backend("own")
     rows, tot = [], {"own": 0.0, "cudnn": 0.0}
     for (cin, cout, k, s, p, h), count in layers.items():
