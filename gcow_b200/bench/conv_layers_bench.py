@@ -78,7 +78,8 @@ def main(argv=None):
     args = ap.parse_args(argv)
     if args.layer:
         ci, co, k, st, h = args.layer
-        layers, stem = OrderedDict({(ci, co, k, st, k // 2, h): 1}), None
+        layers = OrderedDict({(ci, co, k, st, k // 2, h): 1})
+        stem = next(iter(layers)) if ci < 8 else None        # an image layer: its input needs no gradient
     else:
         layers, stem = collect(args.arch, args.batch, args.image)
     backend.set_backend("own")

@@ -120,6 +120,46 @@ im2col_anyc_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, Geo g, in
   }
 }
 
+// The same for a geometry known at compile time (the 7x7 / 2 stem over 3-channel images): every division and
+// remainder of the generic kernel has a run-time divisor and costs about twenty integer instructions, which made that
+// kernel instruction-bound at an eighth of the memory roofline; here they are multiplications by constants.
+template <int C, int KH, int KW, int S, int TILEW>
+__global__ void __launch_bounds__(256)
+im2col_fixed_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, Geo g, int tiles_w) {
+  constexpr int SPAN = (TILEW - 1) * S + KW, ROWLEN = SPAN * C, RC = KW * C, K = KH * RC, KP = (K + 7) / 8 * 8;
+  constexpr int GROUPS = KP / 8;
+  __shared__ bf16 patch[KH * ROWLEN];
+  int b = blockIdx.x;
+  const int tw = b % tiles_w; b /= tiles_w;
+  const int oh = b % g.OH;
+  const int n = b / g.OH;
+  const int ow0 = tw * TILEW;
+  const int h0 = oh * S - g.pad, w0 = ow0 * S - g.pad;
+  const bf16 zero = __float2bfloat16(0.0f);
+  for (int i = threadIdx.x; i < KH * ROWLEN; i += 256) {
+    const int kh = i / ROWLEN, r = i - kh * ROWLEN;
+    const int ih = h0 + kh, iw = w0 + r / C;
+    bf16 e = zero;
+    if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) e = x[(((int64_t)n * g.H + ih) * g.W + w0) * C + r];
+    patch[i] = e;
+  }
+  __syncthreads();
+  const int npix = min(TILEW, g.OW - ow0);
+  bf16* out = col + (((int64_t)n * g.OH + oh) * g.OW + ow0) * KP;
+  for (int t = threadIdx.x; t < npix * GROUPS; t += 256) {
+    const int p = t / GROUPS, k0 = (t - p * GROUPS) * 8;
+    const bf16* src = patch + p * S * C;
+    __align__(16) bf16 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int kk = k0 + i;
+      const int kh = kk / RC, j = kk - kh * RC;
+      v[i] = kk < K ? src[kh * ROWLEN + j] : zero;
+    }
+    *reinterpret_cast<uint4*>(out + (int64_t)t * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
 // Pixel subsample in front of a strided 1x1 convolution: y[n][oh][ow][:] = x[n][oh*s][ow*s][:], 16 bytes per thread;
 // and its gradient, which puts g back at the sampled pixels and zeros everywhere else in one pass.
 __global__ void subsample_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int N, int H, int W, int C, int s,
@@ -179,6 +219,17 @@ int gcow_im2col_anyc(const void* x, void* col, int N, int H, int W, int C, int K
   const int64_t ctas = (int64_t)N * g.OH * tiles_w;
   const size_t smem = (size_t)KH * ((kTileW - 1) * stride + KW) * C * sizeof(bf16);
   if (ctas > 0x7fffffffLL || smem > 48 * 1024) return -1;
+  if (C == 3 && KH == 7 && KW == 7 && stride == 2 && Kp == 152) {
+    constexpr int TW = 112;                                            // a whole output row of the 224 x 224 stem per CTA
+    const int tw = (g.OW + TW - 1) / TW;
+    im2col_fixed_kernel<3, 7, 7, 2, TW><<<(unsigned)((int64_t)N * g.OH * tw), 256, 0, (cudaStream_t)stream>>>(
+        (const bf16*)x, (bf16*)col, g, tw);
+    return (int)cudaGetLastError();
+  }
+  if (C == 3 && KH == 3 && KW == 3 && stride == 1 && Kp == 32) {       // the 3x3 stem of the CIFAR variant
+    im2col_fixed_kernel<3, 3, 3, 1, kTileW><<<(unsigned)ctas, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)col, g, tiles_w);
+    return (int)cudaGetLastError();
+  }
   im2col_anyc_kernel<<<(unsigned)ctas, 256, smem, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)col, g, Kp, tiles_w);
   return (int)cudaGetLastError();
 }

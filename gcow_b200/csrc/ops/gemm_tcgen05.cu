@@ -64,6 +64,8 @@ struct Params {
   int M, N, K, ldc, flags;
   int batch;               // number of independent products (operands are 3-D tensor maps when > 1)
   int a_merged, b_merged;  // MN-major operand fetched as ONE box per stage (its row length is a multiple of 64)
+  int a_chunks, b_chunks;  // 64-row groups of the A / B tile that exist in the matrix (a narrow operand is fetched with
+  uint32_t stage_tx;       // a smaller box: the rest of its tile is never read back); bytes both copies of a stage bring
   int tma_store;           // bf16 C without residual / aux: the epilogue hands 32 x 32 boxes to the TMA (tmap_c is valid)
   long long stride_c;      // elements between consecutive C (and residual) matrices
   uint32_t* error;         // device word, set non-zero when a wait gave up
@@ -140,15 +142,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int m0 = (tmn % tiles_m) * BM, n0 = (tmn / tiles_m) * BN;
         for (int kb = 0; kb < kblocks; kb++) {
           if (!(ok = mbar_wait(sm, &sm->empty[s], phase ^ 1, p.error, 1))) break;
-          mbar_expect_tx(&sm->full[s], A_BYTES + B_BYTES);
+          mbar_expect_tx(&sm->full[s], p.stage_tx);
           const uint32_t bar = smem_u32(&sm->full[s]);
           if (!A_MN) {
             tma_load(smem_u32(smA + s * A_BYTES), &tmap_a, bar, kb * BK, m0, bz, batched);
           } else if (p.a_merged) {
             tma_load_mn(smem_u32(smA + s * A_BYTES), &tmap_a, bar, kb * BK, m0 / 64, bz, batched);
           } else {
-#pragma unroll
-            for (int i = 0; i < BM / 64; i++)
+            for (int i = 0; i < p.a_chunks; i++)
               tma_load(smem_u32(smA + s * A_BYTES + i * 8192), &tmap_a, bar, m0 + 64 * i, kb * BK, bz, batched);
           }
           if (!B_MN) {
@@ -156,8 +157,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else if (p.b_merged) {
             tma_load_mn(smem_u32(smB + s * B_BYTES), &tmap_b, bar, kb * BK, n0 / 64, bz, batched);
           } else {
-#pragma unroll
-            for (int i = 0; i < BN / 64; i++)
+            for (int i = 0; i < p.b_chunks; i++)
               tma_load(smem_u32(smB + s * B_BYTES + i * 8192), &tmap_b, bar, n0 + 64 * i, kb * BK, bz, batched);
           }
           if (++s == STAGES) { s = 0; phase ^= 1; }
@@ -549,38 +549,43 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   const int tiles256 = ((M + 255) / 256) * ((N + BN - 1) / BN) * batch;
   // ... and for short reductions, where the epilogue of a 256-row tile (which cannot overlap the next tile's
   // first MMAs) would dominate
-  // ... and for very short reductions or few output columns, where the step is bound by memory and the 256-row tile
-  // fetches the B tile half as often (measured on the 1x1 layers of ResNet-50)
+  // ... and for very short reductions, where the step is bound by memory and the 256-row tile fetches the B tile
+  // half as often (measured on the 1x1 layers of ResNet-50)
   const int bm = (tile_rows == 128 || tile_rows == 256) ? tile_rows
-                 : ((tiles256 >= (sms * 4) / 5 && (K >= 2048 || K <= 128 || N <= 64)) ? 256 : 128);
+                 : ((tiles256 >= (sms * 4) / 5 && (K >= 2048 || K <= 128)) ? 256 : 128);
   // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
+  // An operand with fewer rows than its tile (64 output channels against the 256-column B tile) is fetched with a box of
+  // its own height: the rest of the tile's shared memory keeps stale bytes, which only reach accumulator rows or
+  // columns that are never stored.
+  const int a_rows = bm < (M + 63) / 64 * 64 ? bm : (M + 63) / 64 * 64;
+  const int b_rows = BN < (N + 63) / 64 * 64 ? BN : (N + 63) / 64 * 64;
   int rc;
   // an MN-major operand whose row length is a multiple of 64 is fetched with one copy per stage
   const int a_merged = a_mn && M % 64 == 0, b_merged = b_mn && N % 64 == 0;
   if (a_merged || b_merged) {
-    rc = a_merged ? make_map_mn(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)bm / 64)
+    rc = a_merged ? make_map_mn(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)a_rows / 64)
          : batch == 1 ? (a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
-                              : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)bm))
+                              : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)a_rows))
                       : (a_mn ? make_map3(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, 64)
-                              : make_map3(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)bm));
+                              : make_map3(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)a_rows));
     if (rc) return rc;
-    rc = b_merged ? make_map_mn(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, BN / 64)
+    rc = b_merged ? make_map_mn(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, (uint32_t)b_rows / 64)
          : batch == 1 ? (b_mn ? make_map(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64)
-                              : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN))
+                              : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)b_rows))
                       : (b_mn ? make_map3(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, 64)
-                              : make_map3(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, BN));
+                              : make_map3(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, (uint32_t)b_rows));
   } else if (batch == 1) {
     rc = a_mn ? make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64)
-              : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)bm);
+              : make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)a_rows);
     if (rc) return rc;
     rc = b_mn ? make_map(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64)
-              : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
+              : make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)b_rows);
   } else {
     rc = a_mn ? make_map3(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, 64)
-              : make_map3(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)bm);
+              : make_map3(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint64_t)batch, (uint64_t)stride_a, (uint32_t)a_rows);
     if (rc) return rc;
     rc = b_mn ? make_map3(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, 64)
-              : make_map3(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, BN);
+              : make_map3(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint64_t)batch, (uint64_t)stride_b, (uint32_t)b_rows);
   }
   if (rc) return rc;
   Params p;
@@ -588,6 +593,8 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags; p.error = error;
   p.batch = batch; p.stride_c = batch > 1 ? stride_c : 0;
   p.a_merged = a_merged; p.b_merged = b_merged;
+  p.a_chunks = a_rows / 64; p.b_chunks = b_rows / 64;
+  p.stage_tx = (uint32_t)(a_rows + b_rows) * 128u;
   // plain bf16 results (bias and GELU allowed) leave through the TMA; N must be whole 32-column blocks
   p.tma_store = !(flags & (kOutF32 | kResidual | kAccumulate | kAuxOut | kGeluGrad)) && N % 32 == 0;
   if (p.tma_store) {
