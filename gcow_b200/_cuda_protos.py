@@ -161,6 +161,7 @@ def _declare_conv(lib, proto):
     opt("gcow_im2col_anyc", i32, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, i32, ptr)
     opt("gcow_conv_fwd", i32, ptr, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, i32, ptr, ptr)
     opt("gcow_conv_fwd_strided", i32, ptr, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, ptr, ptr)
+    opt("gcow_conv_dgrad_1x1_s2", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, ptr, ptr)
     opt("gcow_conv_dgrad_s2", i32, ptr, ptr, ptr, ptr, i32, i32, i32, i32, i32, ptr, ptr)
     opt("gcow_conv_wgrad_split_strided", i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32)
     opt("gcow_conv_wgrad_strided", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, ptr, ptr)

@@ -146,17 +146,26 @@ im2col_fixed_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, Geo g, i
   __syncthreads();
   const int npix = min(TILEW, g.OW - ow0);
   bf16* out = col + (((int64_t)n * g.OH + oh) * g.OW + ow0) * KP;
-  for (int t = threadIdx.x; t < npix * GROUPS; t += 256) {
-    const int p = t / GROUPS, k0 = (t - p * GROUPS) * 8;
-    const bf16* src = patch + p * S * C;
-    __align__(16) bf16 v[8];
+  // Every thread keeps ONE group of eight patch-row elements for its whole life: where they sit relative to the pixel's
+  // first staged element is fixed, so the offsets are computed once; threads then stride over the pixels. Consecutive
+  // threads write consecutive 16-byte groups of consecutive rows.
+  constexpr int SLOTS = 256 / GROUPS;                        // pixels in flight per pass
+  const int grp = threadIdx.x % GROUPS, slot = threadIdx.x / GROUPS;
+  if (slot < SLOTS) {
+    int off[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const int kk = k0 + i;
+      const int kk = grp * 8 + i;
       const int kh = kk / RC, j = kk - kh * RC;
-      v[i] = kk < K ? src[kh * ROWLEN + j] : zero;
+      off[i] = kk < K ? kh * ROWLEN + j : -1;
     }
-    *reinterpret_cast<uint4*>(out + (int64_t)t * 8) = *reinterpret_cast<const uint4*>(v);
+    for (int p = slot; p < npix; p += SLOTS) {
+      const bf16* src = patch + p * S * C;
+      __align__(16) bf16 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = off[i] >= 0 ? src[off[i]] : zero;
+      *reinterpret_cast<uint4*>(out + ((int64_t)p * GROUPS + grp) * 8) = *reinterpret_cast<const uint4*>(v);
+    }
   }
 }
 

@@ -619,6 +619,17 @@ int gcow_conv_dgrad_s2(const void* dy, const void* w, void* wp, void* dx, int N,
   return 0;
 }
 
+// Input gradient of a 1x1 convolution with stride 2: dx[N,Hin,Win,Ci] is dy[N,Ho,Wo,Co] * wt at the sampled pixels
+// (every second pixel of every second row) and zero elsewhere. wt [Ci][Co] is the transposed filter.
+int gcow_conv_dgrad_1x1_s2(const void* dy, const void* wt, void* dx, int N, int Hin, int Win, int Ci, int Co,
+                           uint32_t* error, void* stream) {
+  if (Ci % 8 || Co % 64 || N <= 0 || Hin <= 0 || Win <= 0) return -1;
+  const int Ho = (Hin - 1) / 2 + 1, Wo = (Win - 1) / 2 + 1;
+  int rc = (int)cudaMemsetAsync(dx, 0, (size_t)N * Hin * Win * Ci * 2, (cudaStream_t)stream);
+  if (rc) return rc;
+  return conv_fwd_launch(dy, wt, dx, nullptr, N, Ho, Wo, Co, Ci, 1, 1, 0, 0, 1, Ho, Wo, 2, 0, 0, Hin, Win, error, stream);
+}
+
 // Number of fp32 partial results gcow_conv_wgrad writes for these extents (the first dimension of `part`).
 int gcow_conv_wgrad_split_strided(int N, int Hin, int Win, int Ci, int Co, int kh, int kw, int pad_h, int pad_w, int stride) {
   if (stride < 1 || stride > 2) return 0;

@@ -552,7 +552,7 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   // ... and for very short reductions, where the step is bound by memory and the 256-row tile fetches the B tile
   // half as often (measured on the 1x1 layers of ResNet-50)
   const int bm = (tile_rows == 128 || tile_rows == 256) ? tile_rows
-                 : ((tiles256 >= (sms * 4) / 5 && (K >= 2048 || K <= 128)) ? 256 : 128);
+                 : ((tiles256 >= (sms * 4) / 5 && (K >= 2048 || K < 256)) ? 256 : 128);
   // K-major: matrix [rows][K], box 64 x tile rows. MN-major: matrix [K][rows], box 64 x 64.
   // An operand with fewer rows than its tile (64 output channels against the 256-column B tile) is fetched with a box of
   // its own height: the rest of the tile's shared memory keeps stale bytes, which only reach accumulator rows or

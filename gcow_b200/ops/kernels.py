@@ -945,6 +945,78 @@ class _ConvIgemmFn(torch.autograd.Function):
         return gx, gw, gb, None, None
 
 
+class _Conv1x1Stride2Fn(torch.autograd.Function):
+    """1x1 convolution with stride 2 (the down-sampling shortcut of a ResNet stage) on the implicit-GEMM kernel with
+    one tap: forward and weight gradient read every second pixel through a tensor map with element strides, the input
+    gradient is one launch that stores to the sampled pixels of a zero-filled tensor. No subsampled copy of the input
+    and no scatter pass."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        global _launches
+        N, C, H, W = x.shape
+        Co = w.shape[0]
+        lib = _native.cuda()
+        if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
+            x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        wr = w.detach().reshape(Co, C).to(torch.bfloat16).contiguous()                              # [Co, Ci]
+        OH, OW = (H - 1) // 2 + 1, (W - 1) // 2 + 1
+        y = torch.empty((N, Co, OH, OW), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
+        bias = b.detach().float().contiguous() if b is not None else None
+        _chk(lib.gcow_conv_fwd_strided(x.data_ptr(), wr.data_ptr(), y.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                       N, H, W, C, Co, 1, 1, 0, 0, 2, _error_word(x.device).data_ptr(), _stream(x.device)),
+             "gcow_conv_fwd_strided")
+        _launches += 1
+        ctx.save_for_backward(x, wr)
+        ctx.meta = (N, C, H, W, Co, b is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        global _launches
+        x, wr = ctx.saved_tensors
+        N, C, H, W, Co, has_bias = ctx.meta
+        lib = _native.cuda()
+        if gy.dtype != torch.bfloat16 or not gy.is_contiguous(memory_format=torch.channels_last):
+            gy = gy.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        dev, st, err = gy.device, _stream(gy.device), _error_word(gy.device).data_ptr()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            wt = torch.empty((C, Co), dtype=torch.bfloat16, device=dev)
+            _chk(lib.gcow_conv_flip_weights(wr.data_ptr(), wt.data_ptr(), Co, 1, 1, C, st), "gcow_conv_flip_weights")
+            gx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=dev, memory_format=torch.channels_last)
+            _chk(lib.gcow_conv_dgrad_1x1_s2(gy.data_ptr(), wt.data_ptr(), gx.data_ptr(), N, H, W, C, Co, err, st),
+                 "gcow_conv_dgrad_1x1_s2")
+            _launches += 2
+        if ctx.needs_input_grad[1]:
+            split = lib.gcow_conv_wgrad_split_strided(N, H, W, C, Co, 1, 1, 0, 0, 2)
+            part = (_ws("conv_wgrad_part", (split, Co, C), torch.float32, dev) if split > 1 else
+                    torch.empty((1, Co, C), dtype=torch.float32, device=dev))
+            _chk(lib.gcow_conv_wgrad_strided(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, 1, 1, 0, 0, 2,
+                                             err, st), "gcow_conv_wgrad_strided")
+            _launches += 1
+            if split > 1:
+                out = torch.empty((Co, C), dtype=torch.float32, device=dev)
+                _chk(lib.gcow_reduce_partials(part.data_ptr(), out.data_ptr(), split, out.numel(), st), "gcow_reduce_partials")
+                _launches += 1
+            else:
+                out = part[0]
+            gw = out.view(Co, C, 1, 1)
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(gy.permute(0, 2, 3, 1).reshape(-1, Co))
+        return gx, gw, gb
+
+
+def conv1x1_s2_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Both channel counts whole 64-channel rows (the kernel's reduction rows forward, backward and in the weight gradient)."""
+    return (x.is_cuda and x.dim() == 4 and _have("gcow_conv_dgrad_1x1_s2") and tuple(w.shape[2:]) == (1, 1)
+            and x.shape[1] % 64 == 0 and w.shape[0] % 64 == 0)
+
+
+def conv1x1_s2(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+    return _Conv1x1Stride2Fn.apply(x, w, b)
+
+
 class _ConvStride2Fn(torch.autograd.Function):
     """3x3 convolution with stride 2 and padding 1 over even extents (the down-sampling layer of every ResNet stage)
     on the implicit-GEMM kernel: the forward and the weight gradient read every second input pixel through a tensor
@@ -1032,8 +1104,8 @@ _conv_paths: dict = {}
 
 
 def conv_path_counts(reset: bool = False) -> dict:
-    """How many convolution calls took which path since the last reset: gemm1x1, gemm1x1_strided, igemm, igemm_s2,
-    im2col, cudnn. Benchmarks report it; a test asserts that a ResNet-50 step sends nothing to cudnn."""
+    """How many convolution calls took which path since the last reset: gemm1x1, gemm1x1_strided, igemm1x1_s2, igemm,
+    igemm_s2, im2col, cudnn. Benchmarks report it; a test asserts that a ResNet-50 step sends nothing to cudnn."""
     out = dict(_conv_paths)
     if reset:
         _conv_paths.clear()
@@ -1052,6 +1124,8 @@ def conv_route(x: torch.Tensor, m) -> str:
         if (k == 1 and p == 0 and s == 1 and mode == "auto" and _onebyone_on_igemm(x, w.shape[0])
                 and conv_igemm_usable(x, w, m.stride, m.padding, 1, (1, 1), True)):
             path = "igemm"
+        elif k == 1 and p == 0 and s == 2 and mode == "auto" and conv1x1_s2_usable(x, w):
+            path = "igemm1x1_s2"
         elif k == 1 and p == 0:
             if mode == "auto":
                 oh, ow = (x.shape[2] - 1) // s + 1, (x.shape[3] - 1) // s + 1

@@ -68,6 +68,8 @@ class Conv2d(nn.Conv2d):
             return K.conv1x1(K.subsample(x, s), self.weight, self.bias)
         if path == "igemm":
             return K.conv_igemm(x, self.weight, self.bias, self.padding)
+        if path == "igemm1x1_s2":
+            return K.conv1x1_s2(x, self.weight, self.bias)
         if path == "igemm_s2":
             return K.conv_igemm_s2(x, self.weight, self.bias)
         if path == "im2col":

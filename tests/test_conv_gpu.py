@@ -134,7 +134,9 @@ def test_conv2d_module_uses_igemm_by_default(monkeypatch):
 MODULE_CASES = [
     (64, 256, 1, 1, 0, 14, True, "gemm1x1"),
     (256, 64, 1, 1, 0, 14, True, "gemm1x1"),
-    (256, 512, 1, 2, 0, 14, True, "gemm1x1_strided"),
+    (256, 512, 1, 2, 0, 14, True, "igemm1x1_s2"),
+    (64, 128, 1, 2, 0, 15, True, "igemm1x1_s2"),         # odd extent: the last sampled pixel is the last pixel
+    (72, 128, 1, 2, 0, 14, True, "gemm1x1_strided"),     # 72 channels: not whole 64-channel rows
     (128, 128, 3, 2, 1, 14, True, "igemm_s2"),
     (64, 128, 3, 2, 1, 15, True, "im2col"),          # odd extent: not covered by the stride-2 implicit GEMM
     (96, 128, 3, 2, 1, 14, True, "im2col"),          # 96 input channels: not whole 64-channel rows
@@ -188,7 +190,7 @@ def test_resnet50_step_sends_no_convolution_to_cudnn(monkeypatch):
     K.check_errors()
     counts = K.conv_path_counts(reset=True)
     assert sum(counts.values()) == 53 and counts.get("cudnn", 0) == 0, counts
-    assert (counts["gemm1x1"] == 33 and counts["gemm1x1_strided"] == 3 and counts["igemm"] == 13
+    assert (counts["gemm1x1"] == 33 and counts["igemm1x1_s2"] == 3 and counts["igemm"] == 13
             and counts["igemm_s2"] == 3 and counts["im2col"] == 1)
     # at batch 256 the 1x1 layers of the 56 x 56 stage move to the one-tap implicit GEMM (a routing rule on the pixel count)
     big = torch.empty(256, 64, 56, 56, device="meta")
