@@ -34,6 +34,11 @@ __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
 #pragma unroll
   for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(b[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
 }
+__device__ __forceinline__ void unpack8(const uint4& u, float (&v)[8]) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(b[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
 __device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
   uint4 u;
   __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&u);
@@ -106,45 +111,75 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
     for (int c = lane; c < H; c += 32) { dg[c] = 0; db[c] = 0; }
     __syncwarp();
   }
-  for (int r = blockIdx.x * 4 + warp; r < rows; r += gridDim.x * 4) {
-    const bf16* xr = x + (size_t)r * H;
-    const bf16* gr = dy + (size_t)r * H;
-    const float mu = mean[r], rs = rstd[r];
-    float s1 = 0, s2 = 0;
-    if (CH > 0) {
-      float xh[NR][8], gg[NR][8];
+  if (CH > 0) {
+    // One row per warp and turn; the next row's 2 x CH 16-byte loads are issued before this row's arithmetic, so a
+    // warp always has a row in flight (without that the kernel ran at a quarter of the memory roofline: load, reduce
+    // across the warp, store, and only then the next load).
+    const int stride = gridDim.x * 4;
+    int r = blockIdx.x * 4 + warp;
+    uint4 nx[NR], ng[NR];
+    float nmu = 0.0f, nrs = 0.0f;
+    auto fetch = [&](int row) {
+      const bf16* xr = x + (size_t)row * H;
+      const bf16* gr = dy + (size_t)row * H;
+#pragma unroll
+      for (int k = 0; k < NR; k++) {
+        const int c = lane * 8 + 256 * k;
+        if (c < H) {
+          nx[k] = *reinterpret_cast<const uint4*>(xr + c);
+          ng[k] = *reinterpret_cast<const uint4*>(gr + c);
+        }
+      }
+      nmu = mean[row]; nrs = rstd[row];
+    };
+    if (r < rows) fetch(r);
+    for (; r < rows; r += stride) {
+      uint4 cx[NR], cgv[NR];
+#pragma unroll
+      for (int k = 0; k < NR; k++) { cx[k] = nx[k]; cgv[k] = ng[k]; }
+      const float mu = nmu, rs = nrs;
+      if (r + stride < rows) fetch(r + stride);
+      float s1 = 0, s2 = 0;
 #pragma unroll
       for (int k = 0; k < NR; k++) {
         const int c = lane * 8 + 256 * k;
         if (c < H) {
           float xv[8], gv[8], gam[8];
-          load8(xr + c, xv); load8(gr + c, gv);
+          unpack8(cx[k], xv); unpack8(cgv[k], gv);
           *reinterpret_cast<float4*>(gam) = *reinterpret_cast<const float4*>(sm + c);
           *reinterpret_cast<float4*>(gam + 4) = *reinterpret_cast<const float4*>(sm + c + 4);
 #pragma unroll
           for (int i = 0; i < 8; i++) {
-            xh[k][i] = (xv[i] - mu) * rs;
-            gg[k][i] = gv[i] * gam[i];
-            s1 += gg[k][i]; s2 += gg[k][i] * xh[k][i];
-            rg[k][i] += gv[i] * xh[k][i];
+            const float xh = (xv[i] - mu) * rs, gg = gv[i] * gam[i];
+            s1 += gg; s2 += gg * xh;
+            rg[k][i] += gv[i] * xh;
             rb[k][i] += gv[i];
           }
         }
       }
       s1 = warp_sum(s1) / H; s2 = warp_sum(s2) / H;
       bf16* dr = dx + (size_t)r * H;
+      // the row is still in registers as packed bf16: unpacking it again is cheaper than keeping 2 x 8 x CH floats
 #pragma unroll
       for (int k = 0; k < NR; k++) {
         const int c = lane * 8 + 256 * k;
         if (c < H) {
-          float o[8];
+          float xv[8], gv[8], gam[8], o[8];
+          unpack8(cx[k], xv); unpack8(cgv[k], gv);
+          *reinterpret_cast<float4*>(gam) = *reinterpret_cast<const float4*>(sm + c);
+          *reinterpret_cast<float4*>(gam + 4) = *reinterpret_cast<const float4*>(sm + c + 4);
 #pragma unroll
-          for (int i = 0; i < 8; i++) o[i] = rs * (gg[k][i] - s1 - xh[k][i] * s2);
+          for (int i = 0; i < 8; i++) o[i] = rs * (gv[i] * gam[i] - s1 - (xv[i] - mu) * rs * s2);
           store8(dr + c, o);
         }
       }
-      continue;
     }
+  }
+  for (int r = blockIdx.x * 4 + warp; CH == 0 && r < rows; r += gridDim.x * 4) {
+    const bf16* xr = x + (size_t)r * H;
+    const bf16* gr = dy + (size_t)r * H;
+    const float mu = mean[r], rs = rstd[r];
+    float s1 = 0, s2 = 0;
     for (int c = lane * 8; c < H; c += 256) {
       float xv[8], gv[8];
       load8(xr + c, xv); load8(gr + c, gv);
