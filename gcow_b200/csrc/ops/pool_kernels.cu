@@ -28,64 +28,73 @@ __device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
-__global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ idx,
-                                   int N, int H, int W, int C, int OH, int OW) {
+// One CTA per output row (forward) or input row (backward): the row's base addresses are computed once, and the
+// position inside the row splits into (pixel, channel group) with a shift when the group count is a power of two.
+// The earlier flat index with three run-time divisions per element made both kernels instruction-bound.
+__device__ __forceinline__ void split_index(int i, int groups, int& pix, int& g) {
+  if ((groups & (groups - 1)) == 0) { const int sh = 31 - __clz(groups); pix = i >> sh; g = i & (groups - 1); }
+  else { pix = i / groups; g = i - pix * groups; }
+}
+
+__global__ void __launch_bounds__(256)
+maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ idx,
+                   int N, int H, int W, int C, int OH, int OW) {
   const int groups = C / 8;
-  const int64_t total = (int64_t)N * OH * OW * groups;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int g = (int)(t % groups);
-    int64_t p = t / groups;
-    const int ow = (int)(p % OW); p /= OW;
-    const int oh = (int)(p % OH);
-    const int n = (int)(p / OH);
+  const int oh = blockIdx.x % OH, n = blockIdx.x / OH;
+  const bf16* xin = x + (int64_t)n * H * W * C;
+  const int64_t orow = ((int64_t)n * OH + oh) * OW * C;
+  for (int i = threadIdx.x; i < OW * groups; i += blockDim.x) {
+    int ow, g;
+    split_index(i, groups, ow, g);
     float best[8];
     uint8_t arg[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) { best[i] = -INFINITY; arg[i] = 0; }
+    for (int k = 0; k < 8; k++) { best[k] = -INFINITY; arg[k] = 0; }
 #pragma unroll
     for (int k = 0; k < 9; k++) {
       const int ih = oh * 2 - 1 + k / 3, iw = ow * 2 - 1 + k % 3;
       if (ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
       float v[8];
-      load8(x + (((int64_t)n * H + ih) * W + iw) * C + g * 8, v);
+      load8(xin + ((int64_t)ih * W + iw) * C + g * 8, v);
 #pragma unroll
-      for (int i = 0; i < 8; i++) if (v[i] > best[i] || best[i] == -INFINITY) { best[i] = v[i]; arg[i] = (uint8_t)k; }
+      for (int e = 0; e < 8; e++) if (v[e] > best[e] || best[e] == -INFINITY) { best[e] = v[e]; arg[e] = (uint8_t)k; }
     }
-    const int64_t off = (((int64_t)n * OH + oh) * OW + ow) * C + g * 8;
+    const int64_t off = orow + (int64_t)ow * C + g * 8;
     store8(y + off, best);
     *reinterpret_cast<uint2*>(idx + off) = *reinterpret_cast<const uint2*>(arg);
   }
 }
 
-__global__ void maxpool_bwd_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ idx, bf16* __restrict__ dx,
-                                   int N, int H, int W, int C, int OH, int OW) {
+__global__ void __launch_bounds__(256)
+maxpool_bwd_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ idx, bf16* __restrict__ dx,
+                   int N, int H, int W, int C, int OH, int OW) {
   const int groups = C / 8;
-  const int64_t total = (int64_t)N * H * W * groups;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int g = (int)(t % groups);
-    int64_t p = t / groups;
-    const int iw = (int)(p % W); p /= W;
-    const int ih = (int)(p % H);
-    const int n = (int)(p / H);
+  const int ih = blockIdx.x % H, n = blockIdx.x / H;
+  const int64_t obase = (int64_t)n * OH * OW * C;
+  bf16* drow = dx + ((int64_t)n * H + ih) * W * C;
+  // the one or two output rows whose windows cover this input row
+  const int oh0 = ih / 2, oh1 = (ih + 1) / 2;
+  for (int i = threadIdx.x; i < W * groups; i += blockDim.x) {
+    int iw, g;
+    split_index(i, groups, iw, g);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    // output windows (oh, ow) with oh*2-1 <= ih <= oh*2+1
-    for (int oh = ih / 2; oh <= (ih + 1) / 2 && oh < OH; oh++) {
+    for (int oh = oh0; oh <= oh1 && oh < OH; oh++) {
       const int kh = ih - (oh * 2 - 1);
       if (kh < 0 || kh > 2) continue;
       for (int ow = iw / 2; ow <= (iw + 1) / 2 && ow < OW; ow++) {
         const int kw = iw - (ow * 2 - 1);
         if (kw < 0 || kw > 2) continue;
-        const int64_t off = (((int64_t)n * OH + oh) * OW + ow) * C + g * 8;
+        const int64_t off = obase + ((int64_t)oh * OW + ow) * C + g * 8;
         float gv[8];
         load8(dy + off, gv);
         const uint2 a = *reinterpret_cast<const uint2*>(idx + off);
         const uint8_t* arg = reinterpret_cast<const uint8_t*>(&a);
         const uint8_t k = (uint8_t)(kh * 3 + kw);
 #pragma unroll
-        for (int i = 0; i < 8; i++) if (arg[i] == k) acc[i] += gv[i];
+        for (int e = 0; e < 8; e++) if (arg[e] == k) acc[e] += gv[e];
       }
     }
-    store8(dx + (((int64_t)n * H + ih) * W + iw) * C + g * 8, acc);
+    store8(drow + (int64_t)iw * C + g * 8, acc);
   }
 }
 
@@ -140,14 +149,16 @@ extern "C" {
 int gcow_maxpool3x3s2_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C, void* stream) {
   if (C % 8) return -1;
   const int OH = (H + 2 - 3) / 2 + 1, OW = (W + 2 - 3) / 2 + 1;
-  maxpool_fwd_kernel<<<grid1d((int64_t)N * OH * OW * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+  if ((int64_t)N * OH > 0x7fffffffLL) return -1;
+  maxpool_fwd_kernel<<<(unsigned)(N * OH), 256, 0, (cudaStream_t)stream>>>(
       (const bf16*)x, (bf16*)y, (uint8_t*)idx, N, H, W, C, OH, OW);
   return (int)cudaGetLastError();
 }
 int gcow_maxpool3x3s2_bwd(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, void* stream) {
   if (C % 8) return -1;
   const int OH = (H + 2 - 3) / 2 + 1, OW = (W + 2 - 3) / 2 + 1;
-  maxpool_bwd_kernel<<<grid1d((int64_t)N * H * W * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+  if ((int64_t)N * H > 0x7fffffffLL) return -1;
+  maxpool_bwd_kernel<<<(unsigned)(N * H), 256, 0, (cudaStream_t)stream>>>(
       (const bf16*)dy, (const uint8_t*)idx, (bf16*)dx, N, H, W, C, OH, OW);
   return (int)cudaGetLastError();
 }
