@@ -11,6 +11,7 @@
 //   g += wd * p;  buf = first ? g : mu * buf + (1 - damp) * g;
 //   g  = nesterov ? g + mu * buf : buf;  p -= lr * g
 // AdamW is the decoupled-weight-decay Adam used for BERT pre-training.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -23,9 +24,20 @@ struct OptChunk {
   float* s1;   // exp_avg_sq (AdamW) or nullptr
   uint32_t n;
   uint32_t pad;
+  __nv_bfloat16* shadow;   // bf16 copy of the updated parameter in the same element order, or nullptr: what the
+                           // GEMM and convolution kernels read, so no cast kernel runs in the next forward pass
 };
 
 constexpr int kOptThreads = 256;
+
+// four consecutive bf16 values (the chunk starts 16-byte aligned in fp32, so 8-byte aligned here)
+__device__ __forceinline__ void store_shadow4(__nv_bfloat16* dst, const float4& p) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&lo);
+  u.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = u;
+}
 
 template <class F>
 __device__ __forceinline__ void for_each4(const OptChunk& c, F f) {
@@ -57,6 +69,7 @@ sgd_kernel(const OptChunk* __restrict__ chunks, uint32_t nchunks, float lr, floa
         }
         *reinterpret_cast<float4*>(c.p + i) = p;
         if (c.s0) *reinterpret_cast<float4*>(c.s0 + i) = b;
+        if (c.shadow) store_shadow4(c.shadow + i, p);
       } else {
         float gk = c.g[i] * grad_scale + wd * c.p[i];
         if (c.s0) {
@@ -65,6 +78,7 @@ sgd_kernel(const OptChunk* __restrict__ chunks, uint32_t nchunks, float lr, floa
           gk = nesterov ? gk + mu * b : b;
         }
         c.p[i] -= lr * gk;
+        if (c.shadow) c.shadow[i] = __float2bfloat16(c.p[i]);
       }
     });
   }
@@ -94,8 +108,10 @@ adamw_kernel(const OptChunk* __restrict__ chunks, uint32_t nchunks, float lr, fl
         *reinterpret_cast<float4*>(c.p + i) = p;
         *reinterpret_cast<float4*>(c.s0 + i) = m;
         *reinterpret_cast<float4*>(c.s1 + i) = v;
+        if (c.shadow) store_shadow4(c.shadow + i, p);
       } else {
         upd(c.p[i], c.g[i], c.s0[i], c.s1[i]);
+        if (c.shadow) c.shadow[i] = __float2bfloat16(c.p[i]);
       }
     });
   }

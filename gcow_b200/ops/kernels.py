@@ -88,6 +88,20 @@ def error_word(device: torch.device) -> torch.Tensor:
     return _error_word(device)
 
 
+def bf16_weight(w: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of a float32 weight in the same element order. The fused optimizers keep one up to date in their
+    update kernel (``w._gcow_bf16``, valid while ``w._version`` has not moved since), so a training step runs no cast
+    kernel per layer; a stale or missing copy is refreshed or made here."""
+    sh = getattr(w, "_gcow_bf16", None)          # Python attributes live on the parameter object, not on a detached view
+    if sh is None or sh.shape != w.shape or sh.device != w.device or w.dtype != torch.float32:
+        w = w.detach()
+        return w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+    if w._gcow_bf16_version != w._version:
+        sh.copy_(w.detach())
+        w._gcow_bf16_version = w._version
+    return sh
+
+
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, gelu: bool = False, out_dtype=torch.bfloat16,
               out: torch.Tensor | None = None, accumulate: bool = False, max_ctas: int = 0,
@@ -221,7 +235,7 @@ class _LinearFn(torch.autograd.Function):
         N = w.shape[0]
         N8 = (N + 7) // 8 * 8
         xb = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
-        wb = _pad_rows(w.to(torch.bfloat16).contiguous(), N8)
+        wb = _pad_rows(bf16_weight(w).contiguous(), N8)
         bias = _pad_rows(b.float().contiguous(), N8) if b is not None else None
         y = gemm_bf16(xb, wb, bias=bias)
         ctx.save_for_backward(xb, wb)
@@ -263,7 +277,7 @@ class _LinearResidualFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, b, r):
         xb = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
-        wb = w.to(torch.bfloat16).contiguous()
+        wb = bf16_weight(w).contiguous()
         rb = r.reshape(-1, r.shape[-1]).to(torch.bfloat16).contiguous()
         y = gemm_bf16(xb, wb, bias=b.float().contiguous() if b is not None else None, residual=rb)
         ctx.save_for_backward(xb, wb)
@@ -293,7 +307,7 @@ class _FfnResidualFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w1, b1, w2, b2):
         xb = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
-        w1b, w2b = w1.to(torch.bfloat16).contiguous(), w2.to(torch.bfloat16).contiguous()
+        w1b, w2b = bf16_weight(w1).contiguous(), bf16_weight(w2).contiguous()
         M, F = xb.shape[0], w1b.shape[0]
         pre = torch.empty((M, F), dtype=torch.bfloat16, device=xb.device)
         act = gemm_bf16(xb, w1b, bias=b1.float().contiguous(), gelu=True, pre_gelu_out=pre)
@@ -377,7 +391,7 @@ class _Conv1x1Fn(torch.autograd.Function):
         xm = x.permute(0, 2, 3, 1).reshape(-1, C)          # a view for channels-last input
         if xm.dtype != torch.bfloat16 or not xm.is_contiguous():
             xm = xm.to(torch.bfloat16).contiguous()
-        wb = w.reshape(w.shape[0], C).to(torch.bfloat16).contiguous()
+        wb = bf16_weight(w).reshape(w.shape[0], C).contiguous()
         y = gemm_bf16(xm, wb, bias=b.float().contiguous() if b is not None else None)
         ctx.save_for_backward(xm, wb)
         ctx.meta = (N, C, H, W, w.shape, w.dtype, b is not None)
@@ -676,7 +690,9 @@ def batchnorm_act(x, mod, residual=None, relu=False, fork=False):
     global _launches
     if mod.training or not mod.track_running_stats:
         if mod.training and mod.track_running_stats and mod.num_batches_tracked is not None:
-            mod.num_batches_tracked += 1
+            # counted on the host and added to the tensor when somebody looks (state_dict, ops.nn.BatchNorm2d): one
+            # tiny kernel per layer and step otherwise, 53 of them in a ResNet-50 step
+            mod._gcow_pending_batches = getattr(mod, "_gcow_pending_batches", 0) + 1
         mom = mod.momentum if mod.momentum is not None else 0.1
         rm = mod.running_mean if (mod.training and mod.track_running_stats) else None
         rv = mod.running_var if (mod.training and mod.track_running_stats) else None
@@ -780,7 +796,7 @@ class _ConvGemmFn(torch.autograd.Function):
             _chk(lib.gcow_im2col_anyc(x.data_ptr(), col.data_ptr(), N, H, W, C, KH, KW, stride, pad, Kp, _stream(x.device)),
                  "gcow_im2col_anyc")
         _launches += 1
-        wr = w.permute(0, 2, 3, 1).reshape(Co, K).to(torch.bfloat16)                             # [Co, (kh,kw,c)]
+        wr = bf16_weight(w).permute(0, 2, 3, 1).reshape(Co, K)                                   # [Co, (kh,kw,c)]
         if Kp != K:
             wr = torch.nn.functional.pad(wr, (0, Kp - K))
         wr = wr.contiguous()
@@ -896,7 +912,7 @@ class _ConvIgemmFn(torch.autograd.Function):
         lib = _native.cuda()
         if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
             x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
-        wr = w.detach().permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()                        # [Co, kh, kw, Ci]
+        wr = bf16_weight(w).permute(0, 2, 3, 1).contiguous()                                       # [Co, kh, kw, Ci]
         OH, OW = H + 2 * pad_h - KH + 1, W + 2 * pad_w - KW + 1
         y = torch.empty((N, Co, OH, OW), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
         bias = b.detach().float().contiguous() if b is not None else None
@@ -959,7 +975,7 @@ class _Conv1x1Stride2Fn(torch.autograd.Function):
         lib = _native.cuda()
         if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
             x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
-        wr = w.detach().reshape(Co, C).to(torch.bfloat16).contiguous()                              # [Co, Ci]
+        wr = bf16_weight(w).reshape(Co, C).contiguous()                                             # [Co, Ci]
         OH, OW = (H - 1) // 2 + 1, (W - 1) // 2 + 1
         y = torch.empty((N, Co, OH, OW), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
         bias = b.detach().float().contiguous() if b is not None else None
@@ -1031,7 +1047,7 @@ class _ConvStride2Fn(torch.autograd.Function):
         lib = _native.cuda()
         if x.dtype != torch.bfloat16 or not x.is_contiguous(memory_format=torch.channels_last):
             x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
-        wr = w.detach().permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()                        # [Co, 3, 3, Ci]
+        wr = bf16_weight(w).permute(0, 2, 3, 1).contiguous()                                       # [Co, 3, 3, Ci]
         y = torch.empty((N, Co, H // 2, W // 2), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
         bias = b.detach().float().contiguous() if b is not None else None
         _chk(lib.gcow_conv_fwd_strided(x.data_ptr(), wr.data_ptr(), y.data_ptr(), bias.data_ptr() if bias is not None else None,

@@ -85,9 +85,25 @@ class BatchNorm2d(nn.BatchNorm2d):
     backward kernel receives the two gradients separately and adds them while reading (otherwise the pair is just
     the same tensor twice)."""
 
+    def flush_batch_count(self):
+        """Add the training steps counted on the host (kernels.batchnorm_act) to ``num_batches_tracked``."""
+        n = getattr(self, "_gcow_pending_batches", 0)
+        if n and self.num_batches_tracked is not None:
+            self.num_batches_tracked += n
+        self._gcow_pending_batches = 0
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        self.flush_batch_count()
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+
+    def _load_from_state_dict(self, *args, **kw):
+        self._gcow_pending_batches = 0
+        super()._load_from_state_dict(*args, **kw)
+
     def forward(self, x, residual=None, relu=False, fork=False):
         if backend.get_backend() == "own" and K.batchnorm_usable(x, self, residual):
             return K.batchnorm_act(x, self, residual, relu, fork)
+        self.flush_batch_count()           # PyTorch's own path reads and increments the tensor itself
         y = super().forward(x)
         if residual is not None:
             y = y + residual

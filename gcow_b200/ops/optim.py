@@ -42,12 +42,19 @@ class _FusedBase(torch.optim.Optimizer):
         params = [p for p in group["params"] if p.grad is not None]
         for p in params:
             self._ensure_state(p)
-        key = tuple((p.data_ptr(), p.grad.data_ptr(), self.state[p]["s0"].data_ptr()) for p in params)
+        for p in params:                 # bf16 copies of the matrices and filters, written by the update kernel
+            if p.is_cuda and p.dim() >= 2 and getattr(p, "_gcow_bf16", None) is None and _dense(p) and p.dtype == torch.float32:
+                p._gcow_bf16 = torch.empty_like(p, dtype=torch.bfloat16, memory_format=torch.preserve_format)
+                p._gcow_bf16_version = -1
+        key = tuple((p.data_ptr(), p.grad.data_ptr(), self.state[p]["s0"].data_ptr(),
+                     p._gcow_bf16.data_ptr() if getattr(p, "_gcow_bf16", None) is not None else 0) for p in params)
         cache = self.__dict__.setdefault("_tables", {})
         ent = cache.get(id(group))
         if ent is not None and ent[0] == key:
             return ent[1], ent[2], params
         rows = []
+        if params and params[0].is_cuda and _native.cuda().gcow_opt_chunk_bytes() != struct.calcsize("<QQQQIIQ"):
+            raise RuntimeError("the optimizer library's chunk layout differs from this file's")
         for p in params:
             if not (_dense(p) and p.grad.stride() == p.stride() and p.dtype == torch.float32
                     and p.grad.dtype == torch.float32):
@@ -57,8 +64,10 @@ class _FusedBase(torch.optim.Optimizer):
             for lo in range(0, n, _CHUNK):
                 c = min(_CHUNK, n - lo)
                 s1 = st["s1"].data_ptr() + 4 * lo if self.n_states == 2 else 0
-                rows.append(struct.pack("<QQQQII", p.data_ptr() + 4 * lo, p.grad.data_ptr() + 4 * lo,
-                                        st["s0"].data_ptr() + 4 * lo, s1, c, 0))
+                sh = getattr(p, "_gcow_bf16", None)
+                rows.append(struct.pack("<QQQQIIQ", p.data_ptr() + 4 * lo, p.grad.data_ptr() + 4 * lo,
+                                        st["s0"].data_ptr() + 4 * lo, s1, c, 0,
+                                        sh.data_ptr() + 2 * lo if sh is not None else 0))
         raw = b"".join(rows)
         dev = params[0].device if params else torch.device("cpu")
         table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev) if rows else None
@@ -94,6 +103,8 @@ class FusedSGD(_FusedBase):
             self.launches += 1
             for p in ps:
                 self.state[p]["step"] += 1
+                if getattr(p, "_gcow_bf16", None) is not None:
+                    p._gcow_bf16_version = p._version        # the kernel wrote through raw pointers: no version bump
         return loss
 
     def _step_cpu(self, group, ps, grad_scale):
@@ -147,4 +158,6 @@ class FusedAdamW(_FusedBase):
             self.launches += 1
             for p in ps:
                 self.state[p]["step"] = t
+                if getattr(p, "_gcow_bf16", None) is not None:
+                    p._gcow_bf16_version = p._version
         return loss

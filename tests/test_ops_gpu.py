@@ -427,3 +427,20 @@ def test_batchnorm_fork_adds_the_two_gradients_in_the_kernel():
     xf = x0.float().requires_grad_(True)
     (F.relu(F.batch_norm(xf, None, None, bn.weight.detach(), bn.bias.detach(), True, 0.1, bn.eps)) * w2.float()).sum().backward()
     assert (x.grad.float() - xf.grad).abs().max().item() / xf.grad.abs().max().item() < 3e-2
+
+
+def test_batchnorm_counts_training_steps_lazily():
+    """num_batches_tracked is counted on the host by the own path and lands in the tensor when the state is saved,
+    when PyTorch's own path runs, and not twice."""
+    from gcow_b200.ops import nn as gnn, set_backend
+    set_backend("own")
+    bn = gnn.BatchNorm2d(64).cuda()
+    x = torch.randn(4, 64, 8, 8, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    for _ in range(5):
+        bn(x, relu=True)
+    assert int(bn.state_dict()["num_batches_tracked"]) == 5
+    assert int(bn.state_dict()["num_batches_tracked"]) == 5
+    set_backend("torch")
+    bn(x.float())
+    set_backend("own")
+    assert int(bn.num_batches_tracked) == 6
