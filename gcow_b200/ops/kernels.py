@@ -187,10 +187,52 @@ def _pair_gemm_enabled() -> bool:
     return _pair_gemm
 
 
-def wgrad_gemm(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+def take_grad_view(w: torch.Tensor):
+    """The float32 tensor this step's gradient of ``w`` may be written into, or None. A trainer that knows where the
+    gradient will end up (DDP's bucket view, i.e. last step's ``w.grad``) leaves it in ``w._gcow_grad_view`` before it
+    drops the gradients; the first layer to use ``w`` in a forward pass takes it, so two uses of one weight never share
+    it. The weight-gradient kernels then write there and the backward returns an alias of that memory: autograd adopts
+    it as ``w.grad`` and DDP, seeing its own bucket memory, copies nothing."""
+    gv = getattr(w, "_gcow_grad_view", None)
+    if gv is None:
+        return None
+    w._gcow_grad_view = None
+    if gv.dtype != torch.float32 or gv.shape != w.shape or gv.device != w.device:
+        return None
+    return (gv, w)
+
+
+def _grad_target(taken, rows: int, cols: int):
+    """(flat [rows, cols] view to write into, tensor to return as the gradient) or (None, None)."""
+    if taken is None:
+        return None, None
+    gv, w = taken
+    if w.grad is not None:                       # gradients are being accumulated: that memory is in use
+        return None, None
+    flat = gv.permute(0, 2, 3, 1) if gv.dim() == 4 else gv
+    if not flat.is_contiguous() or flat.numel() != rows * cols:
+        return None, None
+    flat = flat.reshape(rows, cols)
+    if flat.data_ptr() != gv.data_ptr() or gv.data_ptr() % 16:      # the kernels store 16 bytes at a time
+        return None, None
+    global _grad_view_hits
+    _grad_view_hits += 1
+    return flat, gv.as_strided(gv.shape, gv.stride())
+
+
+_grad_view_hits = 0
+
+
+def grad_view_hits() -> int:
+    """How many weight gradients were written straight into the tensor the trainer pointed at (see take_grad_view)."""
+    return _grad_view_hits
+
+
+def wgrad_gemm(g: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """dW[N, K] = g^T x for g [M, N], x [M, K] (both stored with the reduction dimension M outermost), fp32.
     The output has few tiles while M is long, so the reduction is split across CTAs: the rows are cut into
-    ``s`` slabs that run as one batched launch, and the ``s`` partial products are added in a fixed order."""
+    ``s`` slabs that run as one batched launch, and the ``s`` partial products are added in a fixed order.
+    ``out`` (contiguous fp32 [N, K]): where the result goes."""
     global _launches
     M, N = g.shape
     K = x.shape[1]
@@ -199,14 +241,15 @@ def wgrad_gemm(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     while s < 64 and tiles * s * 2 <= 148 and M % (2 * s) == 0 and (M // (2 * s)) % 64 == 0 and M // (2 * s) >= 512:
         s *= 2
     if s == 1 or g.stride(0) != N or x.stride(0) != K:
-        return gemm_bf16(g, x, a_t=True, b_t=True, out_dtype=torch.float32)
+        return gemm_bf16(g, x, a_t=True, b_t=True, out_dtype=torch.float32, out=out)
     lib = _native.cuda()
     part = _ws("wgrad_part", (s, N, K), torch.float32, g.device)
     err = lib.gcow_gemm_bf16_batched(
         g.data_ptr(), x.data_ptr(), part.data_ptr(), N, K, M // s, N, K, K, s, (M // s) * N, (M // s) * K, N * K,
         None, None, OUT_F32, _error_word(g.device).data_ptr(), 1, 1, 0, _stream(g.device))
     _chk(err, "gcow_gemm_bf16_batched")
-    out = torch.empty((N, K), dtype=torch.float32, device=g.device)
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.float32, device=g.device)
     _chk(lib.gcow_reduce_partials(part.data_ptr(), out.data_ptr(), s, N * K, _stream(g.device)), "gcow_reduce_partials")
     _launches += 2
     return out
@@ -240,6 +283,7 @@ class _LinearFn(torch.autograd.Function):
         y = gemm_bf16(xb, wb, bias=bias)
         ctx.save_for_backward(xb, wb)
         ctx.meta = (x.shape, w.dtype, b is not None, N, N8)
+        ctx.grad_view = take_grad_view(w) if (N == N8 and w.dtype == torch.float32) else None
         return y[:, :N].view(*x.shape[:-1], N) if N == N8 else y[:, :N].unflatten(0, x.shape[:-1])
 
     @staticmethod
@@ -265,7 +309,12 @@ class _LinearFn(torch.autograd.Function):
             gx = gemm_bf16(g, wb, b_t=True).view(x_shape)
         if ctx.needs_input_grad[1]:
             # dW[N,K] = g^T @ x: both g [M,N] and x [M,K] are stored [reduction M][rows]
-            gw = wgrad_gemm(g, xb)[:N].to(w_dtype)
+            flat, alias = _grad_target(ctx.grad_view, N, xb.shape[1])
+            if flat is not None:
+                wgrad_gemm(g, xb, out=flat)
+                gw = alias
+            else:
+                gw = wgrad_gemm(g, xb)[:N].to(w_dtype)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)[:N]
         return gx, gw, gb
@@ -282,6 +331,7 @@ class _LinearResidualFn(torch.autograd.Function):
         y = gemm_bf16(xb, wb, bias=b.float().contiguous() if b is not None else None, residual=rb)
         ctx.save_for_backward(xb, wb)
         ctx.meta = (x.shape, r.shape, b is not None)
+        ctx.grad_view = take_grad_view(w)
         return y.view(r.shape)
 
     @staticmethod
@@ -293,7 +343,10 @@ class _LinearResidualFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             gx = gemm_bf16(g, wb, b_t=True).view(x_shape)
         if ctx.needs_input_grad[1]:
-            gw = wgrad_gemm(g, xb)
+            flat, alias = _grad_target(ctx.grad_view, wb.shape[0], wb.shape[1])
+            gw = wgrad_gemm(g, xb, out=flat)
+            if flat is not None:
+                gw = alias
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)
         return gx, gw, gb, (gy if ctx.needs_input_grad[3] else None)
@@ -314,6 +367,7 @@ class _FfnResidualFn(torch.autograd.Function):
         y = gemm_bf16(act, w2b, bias=b2.float().contiguous(), residual=xb)
         ctx.save_for_backward(xb, w1b, w2b, pre, act)
         ctx.shape = x.shape
+        ctx.grad_views = (take_grad_view(w1), take_grad_view(w2))
         return y.view(x.shape)
 
     @staticmethod
@@ -321,10 +375,19 @@ class _FfnResidualFn(torch.autograd.Function):
         xb, w1b, w2b, pre, act = ctx.saved_tensors
         g = gy.reshape(-1, gy.shape[-1]).to(torch.bfloat16).contiguous()
         dpre = gemm_bf16(g, w2b, b_t=True, gelu_grad_of=pre)                 # (g W2) * GELU'(pre)
-        gw2 = wgrad_gemm(g, act) if ctx.needs_input_grad[3] else None
+        gw1 = gw2 = None
+        if ctx.needs_input_grad[3]:
+            flat, alias = _grad_target(ctx.grad_views[1], w2b.shape[0], w2b.shape[1])
+            gw2 = wgrad_gemm(g, act, out=flat)
+            if flat is not None:
+                gw2 = alias
         gb2 = colsum(g) if ctx.needs_input_grad[4] else None
         gx = gemm_bf16(dpre, w1b, b_t=True, residual=g).view(ctx.shape) if ctx.needs_input_grad[0] else None
-        gw1 = wgrad_gemm(dpre, xb) if ctx.needs_input_grad[1] else None
+        if ctx.needs_input_grad[1]:
+            flat, alias = _grad_target(ctx.grad_views[0], w1b.shape[0], w1b.shape[1])
+            gw1 = wgrad_gemm(dpre, xb, out=flat)
+            if flat is not None:
+                gw1 = alias
         gb1 = colsum(dpre) if ctx.needs_input_grad[2] else None
         return gx, gw1, gb1, gw2, gb2
 
@@ -395,6 +458,7 @@ class _Conv1x1Fn(torch.autograd.Function):
         y = gemm_bf16(xm, wb, bias=b.float().contiguous() if b is not None else None)
         ctx.save_for_backward(xm, wb)
         ctx.meta = (N, C, H, W, w.shape, w.dtype, b is not None)
+        ctx.grad_view = take_grad_view(w) if w.dtype == torch.float32 else None
         return y.view(N, H, W, w.shape[0]).permute(0, 3, 1, 2)
 
     @staticmethod
@@ -408,8 +472,13 @@ class _Conv1x1Fn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             gx = gemm_bf16(g, wb, b_t=True).view(N, H, W, C).permute(0, 3, 1, 2)
         if ctx.needs_input_grad[1]:
-            gw = wgrad_gemm(g, xm)
-            gw = gw.view(wshape).to(wdtype).contiguous(memory_format=torch.channels_last)
+            flat, alias = _grad_target(ctx.grad_view, wshape[0], C)
+            if flat is not None:
+                wgrad_gemm(g, xm, out=flat)
+                gw = alias
+            else:
+                gw = wgrad_gemm(g, xm)
+                gw = gw.view(wshape).to(wdtype).contiguous(memory_format=torch.channels_last)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g)
         return gx, gw, gb
@@ -922,6 +991,7 @@ class _ConvIgemmFn(torch.autograd.Function):
         _launches += 1
         ctx.save_for_backward(x, wr)
         ctx.meta = (N, C, H, W, Co, KH, KW, OH, OW, pad_h, pad_w, b is not None)
+        ctx.grad_view = take_grad_view(w)
         return y
 
     @staticmethod
@@ -943,19 +1013,21 @@ class _ConvIgemmFn(torch.autograd.Function):
             _launches += 2
         if ctx.needs_input_grad[1]:
             split = lib.gcow_conv_wgrad_split(N, H, W, C, Co, KH, KW, pad_h, pad_w)
+            flat, alias = _grad_target(ctx.grad_view, Co, KH * KW * C)
             # the partial sums are scratch when an ordered sum follows; a single part IS the result
             part = (_ws("conv_wgrad_part", (split, Co, KH * KW * C), torch.float32, dev) if split > 1 else
-                    torch.empty((1, Co, KH * KW * C), dtype=torch.float32, device=dev))
+                    (flat.unsqueeze(0) if flat is not None else torch.empty((1, Co, KH * KW * C), dtype=torch.float32, device=dev)))
             _chk(lib.gcow_conv_wgrad(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, KH, KW, pad_h, pad_w,
                                      err, st), "gcow_conv_wgrad")
             _launches += 1
             if split > 1:
-                out = torch.empty((Co, KH * KW * C), dtype=torch.float32, device=dev)
+                out = flat if flat is not None else torch.empty((Co, KH * KW * C), dtype=torch.float32, device=dev)
                 _chk(lib.gcow_reduce_partials(part.data_ptr(), out.data_ptr(), split, out.numel(), st), "gcow_reduce_partials")
                 _launches += 1
             else:
                 out = part[0]
-            gw = out.view(Co, KH, KW, C).permute(0, 3, 1, 2)          # logical [Co, Ci, kh, kw], channels-last memory
+            # logical [Co, Ci, kh, kw], channels-last memory
+            gw = alias if flat is not None else out.view(Co, KH, KW, C).permute(0, 3, 1, 2)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(gy.permute(0, 2, 3, 1).reshape(-1, Co))
         return gx, gw, gb, None, None
@@ -985,6 +1057,7 @@ class _Conv1x1Stride2Fn(torch.autograd.Function):
         _launches += 1
         ctx.save_for_backward(x, wr)
         ctx.meta = (N, C, H, W, Co, b is not None)
+        ctx.grad_view = take_grad_view(w)
         return y
 
     @staticmethod
@@ -1006,18 +1079,19 @@ class _Conv1x1Stride2Fn(torch.autograd.Function):
             _launches += 2
         if ctx.needs_input_grad[1]:
             split = lib.gcow_conv_wgrad_split_strided(N, H, W, C, Co, 1, 1, 0, 0, 2)
+            flat, alias = _grad_target(ctx.grad_view, Co, C)
             part = (_ws("conv_wgrad_part", (split, Co, C), torch.float32, dev) if split > 1 else
-                    torch.empty((1, Co, C), dtype=torch.float32, device=dev))
+                    (flat.unsqueeze(0) if flat is not None else torch.empty((1, Co, C), dtype=torch.float32, device=dev)))
             _chk(lib.gcow_conv_wgrad_strided(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, 1, 1, 0, 0, 2,
                                              err, st), "gcow_conv_wgrad_strided")
             _launches += 1
             if split > 1:
-                out = torch.empty((Co, C), dtype=torch.float32, device=dev)
+                out = flat if flat is not None else torch.empty((Co, C), dtype=torch.float32, device=dev)
                 _chk(lib.gcow_reduce_partials(part.data_ptr(), out.data_ptr(), split, out.numel(), st), "gcow_reduce_partials")
                 _launches += 1
             else:
                 out = part[0]
-            gw = out.view(Co, C, 1, 1)
+            gw = alias if flat is not None else out.view(Co, C, 1, 1)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(gy.permute(0, 2, 3, 1).reshape(-1, Co))
         return gx, gw, gb
@@ -1056,6 +1130,7 @@ class _ConvStride2Fn(torch.autograd.Function):
         _launches += 1
         ctx.save_for_backward(x, wr)
         ctx.meta = (N, C, H, W, Co, b is not None)
+        ctx.grad_view = take_grad_view(w)
         return y
 
     @staticmethod
@@ -1076,18 +1151,19 @@ class _ConvStride2Fn(torch.autograd.Function):
             _launches += 5
         if ctx.needs_input_grad[1]:
             split = lib.gcow_conv_wgrad_split_strided(N, H, W, C, Co, 3, 3, 1, 1, 2)
+            flat, alias = _grad_target(ctx.grad_view, Co, 9 * C)
             part = (_ws("conv_wgrad_part", (split, Co, 9 * C), torch.float32, dev) if split > 1 else
-                    torch.empty((1, Co, 9 * C), dtype=torch.float32, device=dev))
+                    (flat.unsqueeze(0) if flat is not None else torch.empty((1, Co, 9 * C), dtype=torch.float32, device=dev)))
             _chk(lib.gcow_conv_wgrad_strided(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, 3, 3, 1, 1, 2,
                                              err, st), "gcow_conv_wgrad_strided")
             _launches += 1
             if split > 1:
-                out = torch.empty((Co, 9 * C), dtype=torch.float32, device=dev)
+                out = flat if flat is not None else torch.empty((Co, 9 * C), dtype=torch.float32, device=dev)
                 _chk(lib.gcow_reduce_partials(part.data_ptr(), out.data_ptr(), split, out.numel(), st), "gcow_reduce_partials")
                 _launches += 1
             else:
                 out = part[0]
-            gw = out.view(Co, 3, 3, C).permute(0, 3, 1, 2)
+            gw = alias if flat is not None else out.view(Co, 3, 3, C).permute(0, 3, 1, 2)
         if has_bias and ctx.needs_input_grad[2]:
             gb = colsum(gy.permute(0, 2, 3, 1).reshape(-1, Co))
         return gx, gw, gb

@@ -159,6 +159,8 @@ class Trainer:
             net = net.to(memory_format=torch.channels_last)
         self.ddp, self.hook_state = wrap_ddp(net, self.cfg, self.device)
         params = [p for p in net.parameters() if p.requires_grad]
+        self._grad_view_hints = ops == "own" and self.device.type == "cuda"
+        self._hint_params = [p for p in params if p.dim() >= 2]
         if self.kind == "resnet":
             opt_cls = FusedSGD if ops == "own" else torch.optim.SGD
             self.opt = opt_cls(params, lr=lr or 0.1, momentum=0.9, weight_decay=1e-4)
@@ -247,6 +249,12 @@ class Trainer:
         """One optimisation step on device-resident inputs. Returns the loss tensor."""
         if self.hook_state is not None:
             self.hook_state.begin_step()
+        # Last step's gradients are DDP's bucket views, which is where this step's gradients will end up again: the
+        # weight-gradient kernels may write there directly (kernels.take_grad_view, taken during the forward pass, at
+        # most once per weight and step) and DDP then has nothing to copy.
+        if self._grad_view_hints:
+            for p in self._hint_params:
+                p._gcow_grad_view = p.grad
         loss = self.compute_loss(dev)
         # gradients are dropped rather than zeroed: autograd then assigns instead of accumulating, and DDP points
         # .grad back at its bucket views during backward

@@ -47,6 +47,33 @@ def test_checkpoint_resume_is_bit_identical(trainer, tmp_path):
     assert torch.equal(trainer.ddp.module.fc.weight, ref_w)
 
 
+def test_gradients_written_into_the_bucket_views_equal_the_copied_ones(trainer, tmp_path):
+    """The weight-gradient kernels may write straight into DDP's bucket views (kernels.take_grad_view). Same state,
+    same batch, with and without that: every gradient is bit-identical, and the direct path was really taken."""
+    from gcow_b200.ops import kernels as K
+    from gcow_b200.train import SyntheticImages
+    from gcow_b200.utils import save_checkpoint, load_checkpoint
+    x, y = SyntheticImages(8, 64, 10, pool=1, seed=9).next()
+    trainer.step(x, y)                                   # .grad now points at the bucket views
+    path = str(tmp_path / "g.tar")
+    save_checkpoint(trainer.state_dict(), path)
+    dev = (x.cuda(), y.cuda())
+    params = [p for p in trainer.ddp.module.parameters() if p.requires_grad]
+    grads = {}
+    for hints in (True, False):
+        trainer.load_state_dict(load_checkpoint(path, map_location="cuda:0"))
+        trainer._grad_view_hints = hints
+        for p in params:
+            p._gcow_grad_view = None
+        before = K.grad_view_hits()
+        trainer.step_device(dev)
+        torch.cuda.synchronize()
+        grads[hints] = [p.grad.clone() for p in params]
+        assert (K.grad_view_hits() > before) == hints
+    trainer._grad_view_hints = True
+    assert all(torch.equal(a, b) for a, b in zip(grads[True], grads[False]))
+
+
 def test_smoke_entry():
     import __graft_entry__ as ge
     # the trainer fixture already owns the process group; smoke() reuses it
