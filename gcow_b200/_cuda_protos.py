@@ -133,6 +133,7 @@ def _declare_bn_pool(lib, proto):
     opt("gcow_bn_fwd_train", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, f32, f32, i32, ptr)
     opt("gcow_bn_fwd_eval", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, f32, i32, ptr)
     opt("gcow_bn_bwd", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, i32, ptr)
+    opt("gcow_bn_bwd3", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, i32, ptr)
     opt("gcow_bn_bwd2", i32, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i32, i32, ptr)
     opt("gcow_maxpool3x3s2_fwd", i32, ptr, ptr, ptr, i32, i32, i32, i32, ptr)
     opt("gcow_maxpool3x3s2_bwd", i32, ptr, ptr, ptr, i32, i32, i32, i32, ptr)

@@ -304,19 +304,25 @@ int gcow_bn_fwd_eval(const void* x, const void* residual, void* y, const float* 
 // of the residual input (the ReLU-masked dy). dgb: 2*C floats out (dgamma, dbeta).
 // dy2 (nullable): a second gradient of the same output, added to dy on the fly; it needs dres (any buffer of the
 // tensor's size) to carry the masked sum to the second sweep.
-int gcow_bn_bwd2(const void* dy, const void* dy2, const void* mask, const void* x, const float* gamma, const float* stats,
-                 void* dx, void* dres, float* dgb, float* part, int64_t R, int C, int relu, void* stream) {
+// dgamma and dbeta (C floats each) may lie anywhere, e.g. in the two parameters' gradient tensors.
+int gcow_bn_bwd3(const void* dy, const void* dy2, const void* mask, const void* x, const float* gamma, const float* stats,
+                 void* dx, void* dres, float* dgamma, float* dbeta, float* part, int64_t R, int C, int relu, void* stream) {
   if (!shape_ok(C) || R <= 0 || (dy2 && !dres)) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   const int g = grid_for(R, C);
   const float *mean = stats, *rstd = stats + C;
   bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const bf16*)dy2, (const uint8_t*)mask, (const bf16*)x, mean, rstd,
                                            (bf16*)dres, part, R, C, relu);
-  gcow::launch_dependent(finalize_bwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), 0, s, (const float*)part, g, C, dgb, dgb + C);
+  gcow::launch_dependent(finalize_bwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), 0, s, (const float*)part, g, C, dgamma, dbeta);
   // the second sweep applies the mask again, or reads the masked gradient if it was written
   gcow::launch_dependent(bwd_dx_kernel, dim3(g), dim3(kThreads), 0, s, (const bf16*)(dres ? dres : dy), (const uint8_t*)mask, (const bf16*)x,
-                   gamma, mean, rstd, (const float*)dgb, (const float*)(dgb + C), (bf16*)dx, R, C, dres ? 0 : relu);
+                   gamma, mean, rstd, (const float*)dgamma, (const float*)dbeta, (bf16*)dx, R, C, dres ? 0 : relu);
   return (int)cudaGetLastError();
+}
+
+int gcow_bn_bwd2(const void* dy, const void* dy2, const void* mask, const void* x, const float* gamma, const float* stats,
+                 void* dx, void* dres, float* dgb, float* part, int64_t R, int C, int relu, void* stream) {
+  return gcow_bn_bwd3(dy, dy2, mask, x, gamma, stats, dx, dres, dgb, dgb + C, part, R, C, relu, stream);
 }
 
 int gcow_bn_bwd(const void* dy, const void* mask, const void* x, const float* gamma, const float* stats, void* dx,

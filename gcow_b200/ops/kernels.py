@@ -202,8 +202,9 @@ def take_grad_view(w: torch.Tensor):
     return (gv, w)
 
 
-def _grad_target(taken, rows: int, cols: int):
-    """(flat [rows, cols] view to write into, tensor to return as the gradient) or (None, None)."""
+def _grad_target(taken, rows: int, cols: int, align: int = 16):
+    """(flat [rows, cols] view to write into, tensor to return as the gradient) or (None, None). ``align``: what the
+    writing kernel needs of the address (the GEMM and convolution epilogues store 16 bytes at a time)."""
     if taken is None:
         return None, None
     gv, w = taken
@@ -213,7 +214,7 @@ def _grad_target(taken, rows: int, cols: int):
     if not flat.is_contiguous() or flat.numel() != rows * cols:
         return None, None
     flat = flat.reshape(rows, cols)
-    if flat.data_ptr() != gv.data_ptr() or gv.data_ptr() % 16:      # the kernels store 16 bytes at a time
+    if flat.data_ptr() != gv.data_ptr() or gv.data_ptr() % align:
         return None, None
     global _grad_view_hits
     _grad_view_hits += 1
@@ -706,6 +707,7 @@ class _BatchNormActFn(torch.autograd.Function):
              "gcow_bn_fwd_train")
         _launches += 3
         ctx.save_for_backward(x, mask, g32, stats)      # the ReLU bit mask stands in for y in the backward
+        ctx.grad_views = (take_grad_view(gamma), take_grad_view(beta)) if gamma.dtype == torch.float32 else (None, None)
         ctx.meta = (R, C, bool(relu), residual is not None, gamma.dtype)
         if not fork:
             return y
@@ -731,15 +733,24 @@ class _BatchNormActFn(torch.autograd.Function):
         dx = torch.empty_like(x, memory_format=torch.channels_last)
         # the masked (summed) gradient: the residual input's gradient, and what the second sweep reads
         dres = torch.empty_like(x, memory_format=torch.channels_last) if (has_res or gy2 is not None) else None
-        dgb = torch.empty(2 * C, dtype=torch.float32, device=x.device)
         part = _ws("bn_part", lib.gcow_bn_parts(R, C) * 2 * C, torch.float32, x.device)
-        _chk(lib.gcow_bn_bwd2(gy.data_ptr(), gy2.data_ptr() if gy2 is not None else None,
+        # dgamma and dbeta go straight into the two parameters' gradient tensors when the trainer pointed at them
+        fg, ag = _grad_target(ctx.grad_views[0], 1, C, align=4)
+        fb, ab = _grad_target(ctx.grad_views[1], 1, C, align=4) if fg is not None else (None, None)
+        if fb is not None and _have("gcow_bn_bwd3"):
+            dgamma, dbeta = ag, ab
+            pg, pb = fg.data_ptr(), fb.data_ptr()
+        else:
+            dgb = torch.empty(2 * C, dtype=torch.float32, device=x.device)
+            dgamma, dbeta = dgb[:C].to(pdtype), dgb[C:].to(pdtype)
+            pg, pb = dgb.data_ptr(), dgb.data_ptr() + 4 * C
+        _chk(lib.gcow_bn_bwd3(gy.data_ptr(), gy2.data_ptr() if gy2 is not None else None,
                               mask.data_ptr() if mask is not None else None, x.data_ptr(), g32.data_ptr(),
                               stats.data_ptr(), dx.data_ptr(),
-                              dres.data_ptr() if dres is not None else None, dgb.data_ptr(), part.data_ptr(), R, C,
-                              int(relu), _stream(x.device)), "gcow_bn_bwd2")
+                              dres.data_ptr() if dres is not None else None, pg, pb, part.data_ptr(), R, C,
+                              int(relu), _stream(x.device)), "gcow_bn_bwd3")
         _launches += 3
-        return dx, dgb[:C].to(pdtype), dgb[C:].to(pdtype), None, None, (dres if has_res else None), None, None, None, None
+        return dx, dgamma, dbeta, None, None, (dres if has_res else None), None, None, None, None
 
 
 def batchnorm_usable(x: torch.Tensor, mod, residual=None) -> bool:

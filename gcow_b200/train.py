@@ -160,7 +160,7 @@ class Trainer:
         self.ddp, self.hook_state = wrap_ddp(net, self.cfg, self.device)
         params = [p for p in net.parameters() if p.requires_grad]
         self._grad_view_hints = ops == "own" and self.device.type == "cuda"
-        self._hint_params = [p for p in params if p.dim() >= 2]
+        self._hint_params = params
         if self.kind == "resnet":
             opt_cls = FusedSGD if ops == "own" else torch.optim.SGD
             self.opt = opt_cls(params, lr=lr or 0.1, momentum=0.9, weight_decay=1e-4)
