@@ -91,7 +91,8 @@ def error_word(device: torch.device) -> torch.Tensor:
 def bf16_weight(w: torch.Tensor) -> torch.Tensor:
     """bf16 copy of a float32 weight in the same element order. The fused optimizers keep one up to date in their
     update kernel (``w._gcow_bf16``, valid while ``w._version`` has not moved since), so a training step runs no cast
-    kernel per layer; a stale or missing copy is refreshed or made here."""
+    kernel per layer; a stale or missing copy is refreshed or made here. (Writes that bypass the version counter,
+    i.e. through ``w.data``, are not seen: such code has to drop ``w._gcow_bf16`` itself.)"""
     sh = getattr(w, "_gcow_bf16", None)          # Python attributes live on the parameter object, not on a detached view
     if sh is None or sh.shape != w.shape or sh.device != w.device or w.dtype != torch.float32:
         w = w.detach()
