@@ -82,7 +82,7 @@ stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int64_t R, in
 // Sum the per-CTA partials of 32 channels with a 32 x 8 thread block: thread (cx, py)
 // adds partials py, py+8, ... of channel c (coalesced across cx), then the 8 rows are
 // added in a fixed order, so the result does not depend on scheduling.
-constexpr int kFinX = 32, kFinY = 8;
+constexpr int kFinX = 32, kFinY = 32;
 __device__ __forceinline__ void fold_partials(const float* __restrict__ part, int parts, int C, int c, double& s_out,
                                               double& q_out) {
   __shared__ double sm_s[kFinY][kFinX + 1], sm_q[kFinY][kFinX + 1];
