@@ -230,6 +230,28 @@ __global__ void reduce_partials_kernel(const float* __restrict__ part, float* __
   out[c] = s;
 }
 
+// The same for many partials of a short vector (LayerNorm's 444 x 2H): 32 x 32 threads per 32 columns, thread (cx, py)
+// adds partials py, py + 32, ..., then the 32 rows are added in a fixed order. One thread per column walking all the
+// partials serially took longer than the LayerNorm backward sweep it follows.
+__global__ void __launch_bounds__(1024)
+reduce_partials_tall_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int n) {
+  pdl_wait();
+  __shared__ float sm[32][33];
+  const int cx = threadIdx.x, py = threadIdx.y;
+  const int c = blockIdx.x * 32 + cx;
+  float s = 0;
+  if (c < n)
+    for (int p = py; p < parts; p += 32) s += part[(size_t)p * n + c];
+  sm[py][cx] = s;
+  __syncthreads();
+  if (py == 0 && c < n) {
+    float t = 0;
+#pragma unroll
+    for (int j = 0; j < 32; j++) t += sm[j][cx];
+    out[c] = t;
+  }
+}
+
 // ----------------------------------------------------------------------- GELU
 __device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 __device__ __forceinline__ float gelu_grad_f(float x) {
@@ -462,7 +484,7 @@ int gcow_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
     default: GCOW_LN_BWD(0); break;
   }
 #undef GCOW_LN_BWD
-  gcow::launch_dependent(reduce_partials_kernel, dim3((2 * H + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (const float*)part,
+  gcow::launch_dependent(reduce_partials_tall_kernel, dim3((2 * H + 31) / 32), dim3(32, 32), 0, (cudaStream_t)stream, (const float*)part,
                    dgamma_dbeta, parts, 2 * H);
   return (int)cudaGetLastError();
 }
@@ -492,8 +514,12 @@ int gcow_softmax_xent(void* logits, const int64_t* target, float* row_loss, cons
 // out[i] = sum_p part[p * n + i] in a fixed order (split-K partial products, bias partials).
 int gcow_reduce_partials(const float* part, float* out, int parts, int64_t n, void* stream) {
   if (n <= 0 || parts <= 0 || n > 0x7fffffff) return -1;
-  gcow::launch_dependent(reduce_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, part, out, parts,
-                   (int)n);
+  if (parts >= 64 && n <= 65536)
+    gcow::launch_dependent(reduce_partials_tall_kernel, dim3((unsigned)((n + 31) / 32)), dim3(32, 32), 0, (cudaStream_t)stream, part, out,
+                     parts, (int)n);
+  else
+    gcow::launch_dependent(reduce_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, part, out, parts,
+                     (int)n);
   return (int)cudaGetLastError();
 }
 
