@@ -550,8 +550,12 @@ int gcow_colsum(const void* g, float* part, float* out, int rows, int cols, int 
     dim3 grid((cols / 2 + 255) / 256, parts);
     colsum_partial_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)g, part, rows, cols, ld, rows_per);
   }
-  gcow::launch_dependent(reduce_partials_kernel, dim3((cols + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (const float*)part, out,
-                   parts, cols);
+  if (parts >= 64)
+    gcow::launch_dependent(reduce_partials_tall_kernel, dim3((cols + 31) / 32), dim3(32, 32), 0, (cudaStream_t)stream, (const float*)part,
+                     out, parts, cols);
+  else
+    gcow::launch_dependent(reduce_partials_kernel, dim3((cols + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (const float*)part, out,
+                     parts, cols);
   return (int)cudaGetLastError();
 }
 
