@@ -67,6 +67,7 @@ __device__ __forceinline__ void cta_fold(const float (&a)[8], const float (&b)[8
 __global__ void __launch_bounds__(kThreads)
 stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int64_t R, int C) {
   pdl_trigger();
+  pdl_wait();       // launched under the tail of the kernel that writes x
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll 4
@@ -140,6 +141,7 @@ apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, bf16
              uint8_t* __restrict__ mask, const float* __restrict__ scale, const float* __restrict__ shift, int64_t R,
              int C, int relu) {
   pdl_wait();
+  pdl_trigger();    // the consumer of y may set itself up meanwhile
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float sc[8], sh[8];
 #pragma unroll
@@ -177,6 +179,7 @@ bwd_reduce_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ dy2, con
                   const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ gmask_out,
                   float* __restrict__ part, int64_t R, int C, int relu) {
   pdl_trigger();
+  pdl_wait();
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float mu[8], rs[8], s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
@@ -225,6 +228,7 @@ bwd_dx_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ mask, con
               const float* __restrict__ dgamma, const float* __restrict__ dbeta, bf16* __restrict__ dx, int64_t R, int C,
               int relu) {
   pdl_wait();
+  pdl_trigger();
   const int groups = C / 8, g = threadIdx.x % groups, r0 = threadIdx.x / groups, rstep = kThreads / groups;
   float mu[8], rs[8], k0[8], k1[8], k2[8];
   const float invR = 1.0f / (float)R;
@@ -281,7 +285,7 @@ int gcow_bn_fwd_train(const void* x, const void* residual, void* y, void* mask, 
   cudaStream_t s = (cudaStream_t)stream;
   const int g = grid_for(R, C);
   float *mean = stats, *rstd = stats + C, *scale = stats + 2 * C, *shift = stats + 3 * C;
-  stats_kernel<<<g, kThreads, 0, s>>>((const bf16*)x, part, R, C);
+  gcow::launch_dependent(stats_kernel, dim3(g), dim3(kThreads), 0, s, (const bf16*)x, part, R, C);
   gcow::launch_dependent(finalize_fwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), 0, s, part, g, C, R, eps, momentum, gamma,
                    beta, mean, rstd, scale, shift, run_mean, run_var);
   gcow::launch_dependent(apply_kernel, dim3(g), dim3(kThreads), 0, s, (const bf16*)x, (const bf16*)residual, (bf16*)y, (uint8_t*)mask,
@@ -311,8 +315,8 @@ int gcow_bn_bwd3(const void* dy, const void* dy2, const void* mask, const void* 
   cudaStream_t s = (cudaStream_t)stream;
   const int g = grid_for(R, C);
   const float *mean = stats, *rstd = stats + C;
-  bwd_reduce_kernel<<<g, kThreads, 0, s>>>((const bf16*)dy, (const bf16*)dy2, (const uint8_t*)mask, (const bf16*)x, mean, rstd,
-                                           (bf16*)dres, part, R, C, relu);
+  gcow::launch_dependent(bwd_reduce_kernel, dim3(g), dim3(kThreads), 0, s, (const bf16*)dy, (const bf16*)dy2, (const uint8_t*)mask,
+                         (const bf16*)x, mean, rstd, (bf16*)dres, part, R, C, relu);
   gcow::launch_dependent(finalize_bwd_kernel, dim3((C + kFinX - 1) / kFinX), dim3(kFinX, kFinY), 0, s, (const float*)part, g, C, dgamma, dbeta);
   // the second sweep applies the mask again, or reads the masked gradient if it was written
   gcow::launch_dependent(bwd_dx_kernel, dim3(g), dim3(kThreads), 0, s, (const bf16*)(dres ? dres : dy), (const uint8_t*)mask, (const bf16*)x,

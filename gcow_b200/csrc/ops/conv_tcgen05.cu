@@ -41,6 +41,7 @@
 #include <string.h>
 #include <mutex>
 
+#include "pdl.cuh"
 #include "tc_common.cuh"
 
 namespace gcow {
@@ -129,6 +130,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   // a kernel launched as a programmatic dependent (the ordered sum of split partial results) may be scheduled
   // from here on; it waits for this grid to complete before it reads anything
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // this grid's own set-up ran under the tail of its predecessor; global memory only after that one has completed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // reduction length of a tile (wgrad: the pixel boxes of its split)
   auto tile_kblocks = [&](int tile) -> int {
@@ -573,8 +576,8 @@ static int conv_fwd_launch(const void* x, const void* w, void* y, const float* b
   const long long tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n * tiles_c;
   const int grid = (int)(tiles < sms ? tiles : sms);
   const size_t smem = smem_for(halves, p.bn_cols, p.stages);
-  if (halves == 2) conv_igemm_kernel<false, 2><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
-  else conv_igemm_kernel<false, 1><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
+  if (halves == 2) gcow::launch_dependent(conv_igemm_kernel<false, 2>, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, ma, mb, p);
+  else gcow::launch_dependent(conv_igemm_kernel<false, 1>, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, ma, mb, p);
   return (int)cudaGetLastError();
 }
 
@@ -672,8 +675,8 @@ int gcow_conv_wgrad_strided(const void* dy, const void* x, float* part, int N, i
   const long long tiles = (long long)q.split * ((Co + 128 * q.halves - 1) / (128 * q.halves)) * ((kh * kw * Ci + 255) / 256);
   const int grid = (int)(tiles < sms ? tiles : sms);
   const size_t smem = smem_for(q.halves, p.bn_cols, p.stages);
-  if (q.halves == 2) conv_igemm_kernel<true, 2><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
-  else conv_igemm_kernel<true, 1><<<grid, THREADS, smem, (cudaStream_t)stream>>>(ma, mb, p);
+  if (q.halves == 2) gcow::launch_dependent(conv_igemm_kernel<true, 2>, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, ma, mb, p);
+  else gcow::launch_dependent(conv_igemm_kernel<true, 1>, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, ma, mb, p);
   return (int)cudaGetLastError();
 }
 

@@ -129,6 +129,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   cluster_sync();            // both CTAs' barriers are initialised before either signals the other
   tc_fence_after();
   const uint32_t tmem_base = sm->tmem_base;
+  // programmatic dependent launch: the next kernel of the stream may set itself up from here on, and this one, when
+  // launched the same way, has set itself up under the tail of its predecessor; global memory only after that
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -361,10 +365,13 @@ int gcow_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = (cudaStream_t)stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr; cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  static const bool pdl = [] { const char* e = getenv("GCOW_PDL"); return !(e && e[0] == '0'); }();
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 2 : 1;
   if (b_mn) return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel<true>, ma, mb, p);
   return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel<false>, ma, mb, p);
 }

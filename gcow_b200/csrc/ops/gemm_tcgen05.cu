@@ -32,6 +32,7 @@
 #include <stdlib.h>
 #include <mutex>
 
+#include "pdl.cuh"
 #include "tc_common.cuh"
 
 namespace gcow {
@@ -131,6 +132,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // a kernel launched as a programmatic dependent (the ordered sum of split partial results) may be scheduled
   // from here on; it waits for this grid to complete before it reads anything
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // ... and this grid, when it was launched the same way, has come this far (barriers, tensor memory) under the tail
+  // of ITS predecessor: nothing in global memory is touched before that one has completed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -605,7 +609,7 @@ static int gemm_launch(const void* A, const void* B, void* C, int M, int N, int 
   int grid = tiles < sms ? tiles : sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   cudaStream_t st = (cudaStream_t)stream;
-#define GCOW_GEMM_LAUNCH(BM_, A, B) gemm_bf16_kernel<BM_, A, B><<<grid, Shape<BM_>::THREADS, smem_bytes<BM_>(), st>>>(ma, mb, mc, p)
+#define GCOW_GEMM_LAUNCH(BM_, A, B) gcow::launch_dependent(gemm_bf16_kernel<BM_, A, B>, dim3(grid), dim3(Shape<BM_>::THREADS), smem_bytes<BM_>(), st, ma, mb, mc, p)
   if (bm == 256) {
     if (!a_mn && !b_mn) GCOW_GEMM_LAUNCH(256, false, false);
     else if (!a_mn && b_mn) GCOW_GEMM_LAUNCH(256, false, true);

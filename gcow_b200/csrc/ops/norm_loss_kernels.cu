@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(128)
 layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                      bf16* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int rows, int H,
                      float eps) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   for (int r = blockIdx.x * 4 + (threadIdx.x >> 5); r < rows; r += gridDim.x * 4) {
     const bf16* xr = x + (size_t)r * H;
@@ -93,6 +95,7 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
                      const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ dx,
                      float* __restrict__ part, int rows, int H) {
   pdl_trigger();
+  pdl_wait();
   extern __shared__ float sm[];          // [4 warps][2][H]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* dg = sm + (size_t)warp * 2 * H;
@@ -223,6 +226,7 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, co
 // out[c] = sum_p part[p][c]  (fixed order)
 __global__ void reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int n) {
   pdl_wait();       // launched as a dependent of the kernel that writes `part`
+  pdl_trigger();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= n) return;
   float s = 0;
@@ -236,6 +240,7 @@ __global__ void reduce_partials_kernel(const float* __restrict__ part, float* __
 __global__ void __launch_bounds__(1024)
 reduce_partials_tall_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int n) {
   pdl_wait();
+  pdl_trigger();
   __shared__ float sm[32][33];
   const int cx = threadIdx.x, py = threadIdx.y;
   const int c = blockIdx.x * 32 + cx;
@@ -388,6 +393,7 @@ softmax_bwd_kernel(const bf16* __restrict__ dp, const bf16* __restrict__ p, bf16
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const bf16* __restrict__ g, float* __restrict__ part, int rows, int cols, int ld, int rows_per) {
   pdl_trigger();
+  pdl_wait();
   const int c = (blockIdx.x * 256 + threadIdx.x) * 2;
   if (c >= cols) return;
   const int r0 = blockIdx.y * rows_per, r1 = min(rows, r0 + rows_per);
@@ -406,6 +412,7 @@ colsum_partial_kernel(const bf16* __restrict__ g, float* __restrict__ part, int 
 __global__ void __launch_bounds__(256)
 colsum_partial8_kernel(const bf16* __restrict__ g, float* __restrict__ part, int rows, int cols, int ld, int rows_per) {
   pdl_trigger();
+  pdl_wait();
   __shared__ float red[8][256 + 8];
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;       // column group (8 columns), row lane
   const int c = blockIdx.x * 256 + cg * 8;
@@ -460,7 +467,7 @@ int gcow_layernorm_fwd(const void* x, const float* gamma, const float* beta, voi
                        int rows, int H, float eps, void* stream) {
   if (H % 8 || rows <= 0) return -1;
   int grid = (rows + 3) / 4; if (grid > 148 * 16) grid = 148 * 16;
-  layernorm_fwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const bf16*)x, gamma, beta, (bf16*)y, mean, rstd, rows, H, eps);
+  gcow::launch_dependent(layernorm_fwd_kernel, dim3(grid), dim3(128), 0, (cudaStream_t)stream, (const bf16*)x, gamma, beta, (bf16*)y, mean, rstd, rows, H, eps);
   return (int)cudaGetLastError();
 }
 
@@ -475,7 +482,7 @@ int gcow_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(layernorm_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4096 * 4); attr = true; }
   const int ch = (H + 255) / 256;
-#define GCOW_LN_BWD(CH) layernorm_bwd_kernel<CH><<<parts, 128, smem, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (bf16*)dx, part, rows, H)
+#define GCOW_LN_BWD(CH) gcow::launch_dependent(layernorm_bwd_kernel<CH>, dim3(parts), dim3(128), smem, (cudaStream_t)stream, (const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (bf16*)dx, part, rows, H)
   switch (ch) {
     case 1: GCOW_LN_BWD(1); break;
     case 2: GCOW_LN_BWD(2); break;
@@ -545,10 +552,10 @@ int gcow_colsum(const void* g, float* part, float* out, int rows, int cols, int 
   const int rows_per = (rows + parts - 1) / parts;
   if (cols % 8 == 0 && ld % 8 == 0 && ((uintptr_t)g & 15) == 0) {
     dim3 grid((cols + 255) / 256, parts);
-    colsum_partial8_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)g, part, rows, cols, ld, rows_per);
+    gcow::launch_dependent(colsum_partial8_kernel, grid, dim3(256), 0, (cudaStream_t)stream, (const bf16*)g, part, rows, cols, ld, rows_per);
   } else {
     dim3 grid((cols / 2 + 255) / 256, parts);
-    colsum_partial_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)g, part, rows, cols, ld, rows_per);
+    gcow::launch_dependent(colsum_partial_kernel, grid, dim3(256), 0, (cudaStream_t)stream, (const bf16*)g, part, rows, cols, ld, rows_per);
   }
   if (parts >= 64)
     gcow::launch_dependent(reduce_partials_tall_kernel, dim3((cols + 31) / 32), dim3(32, 32), 0, (cudaStream_t)stream, (const float*)part,

@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 namespace gcow {
 namespace pool {
 
@@ -39,6 +41,7 @@ __device__ __forceinline__ void split_index(int i, int groups, int& pix, int& g)
 __global__ void __launch_bounds__(256)
 maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ idx,
                    int N, int H, int W, int C, int OH, int OW) {
+  pdl_wait();
   const int groups = C / 8;
   const int oh = blockIdx.x % OH, n = blockIdx.x / OH;
   const bf16* xin = x + (int64_t)n * H * W * C;
@@ -68,6 +71,7 @@ maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __
 __global__ void __launch_bounds__(256)
 maxpool_bwd_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ idx, bf16* __restrict__ dx,
                    int N, int H, int W, int C, int OH, int OW) {
+  pdl_wait();
   const int groups = C / 8;
   const int ih = blockIdx.x % H, n = blockIdx.x / H;
   const int64_t obase = (int64_t)n * OH * OW * C;
@@ -150,16 +154,16 @@ int gcow_maxpool3x3s2_fwd(const void* x, void* y, void* idx, int N, int H, int W
   if (C % 8) return -1;
   const int OH = (H + 2 - 3) / 2 + 1, OW = (W + 2 - 3) / 2 + 1;
   if ((int64_t)N * OH > 0x7fffffffLL) return -1;
-  maxpool_fwd_kernel<<<(unsigned)(N * OH), 256, 0, (cudaStream_t)stream>>>(
-      (const bf16*)x, (bf16*)y, (uint8_t*)idx, N, H, W, C, OH, OW);
+  gcow::launch_dependent(maxpool_fwd_kernel, dim3((unsigned)(N * OH)), dim3(256), 0, (cudaStream_t)stream,
+                         (const bf16*)x, (bf16*)y, (uint8_t*)idx, N, H, W, C, OH, OW);
   return (int)cudaGetLastError();
 }
 int gcow_maxpool3x3s2_bwd(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, void* stream) {
   if (C % 8) return -1;
   const int OH = (H + 2 - 3) / 2 + 1, OW = (W + 2 - 3) / 2 + 1;
   if ((int64_t)N * H > 0x7fffffffLL) return -1;
-  maxpool_bwd_kernel<<<(unsigned)(N * H), 256, 0, (cudaStream_t)stream>>>(
-      (const bf16*)dy, (const uint8_t*)idx, (bf16*)dx, N, H, W, C, OH, OW);
+  gcow::launch_dependent(maxpool_bwd_kernel, dim3((unsigned)(N * H)), dim3(256), 0, (cudaStream_t)stream,
+                         (const bf16*)dy, (const uint8_t*)idx, (bf16*)dx, N, H, W, C, OH, OW);
   return (int)cudaGetLastError();
 }
 int gcow_avgpool_fwd(const void* x, void* y, int N, int HW, int C, void* stream) {
