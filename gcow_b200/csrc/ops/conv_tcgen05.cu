@@ -367,6 +367,192 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Weight-stationary forward for 64 -> 64 channels, 3x3, stride 1, padding 1 (the first stage of ResNet-50).
+// With 64 output channels as the MMA's N the instruction above uses a quarter of the array's width. Here the
+// roles are swapped: D[co][pixel] = sum_taps W_tap[co][ci] * X[pixel + tap][ci], the pixels are the 256-wide N
+// and the filter is the A operand. The 72 KB filter is fetched once per CTA and stays in shared memory. Per
+// tile ONE copy brings the pixel rows with their halo - (rows + 2) x (W + 2) pixels of 128 bytes, zero filled
+// outside the image - and the nine taps read it in place: pixel slot n = i * (W + 2) + j of the tile is smem row
+// n + r * (W + 2) + s for tap (r, s), so a tap is the same operand descriptor moved by whole 128-byte rows.
+// Slots with j >= W or i >= rows hold sums nobody needs and are not stored. Against nine copies per tile this
+// reads each pixel from L2 once (plus the halo) instead of nine times.
+// The MMA is M = 64 x N = 256: accumulator row r (an output channel) sits in lane (r / 16) * 32 + r % 16 of the
+// tensor memory, so each of the four lane quarters holds 16 channels and all eight epilogue warps have work
+// (measured: 80 us against 100 us with M = 128 and the upper 64 rows unused; an MMA takes about 150 cycles
+// either way). A descriptor whose start is not 1024-byte aligned needs no base offset: the 128-byte swizzle
+// is a function of the absolute shared-memory address, for the TMA's writes and the MMA's reads alike.
+struct WsParams {
+  __nv_bfloat16* out;   // [N, H, W, 64]
+  const float* bias;    // [64] or nullptr
+  int N, H, W;
+  int pitch;            // W + 2: pixel slots per image row
+  int rows;             // image rows per tile
+  int tiles_h;
+  int stages, stage_bytes;
+  uint32_t* error;
+};
+
+constexpr int WS_TAPS = 9, WS_W_BYTES = WS_TAPS * 64 * 128;
+constexpr int kWsSmemMax = 227 * 1024;
+
+struct WsSmem {
+  uint64_t full[4], empty[4], tmem_full[2], tmem_empty[2], wfull, drain;
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+conv_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const WsParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage0 = base + WS_W_BYTES;
+  WsSmem* sm = reinterpret_cast<WsSmem*>(stage0 + p.stages * p.stage_bytes);
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>(((uintptr_t)(sm + 1) + 15) & ~(uintptr_t)15);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.N * p.tiles_h;
+  const int STAGES = p.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&sm->tmem_full[a], 1); mbar_init(&sm->tmem_empty[a], EPI_WARPS * 32); }
+    mbar_init(&sm->wfull, 1);
+    mbar_init(&sm->drain, 1);
+    sm->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&sm->wfull, (uint32_t)WS_W_BYTES);
+      for (int tap = 0; tap < WS_TAPS; tap++)
+        tma_load_2d(smem_u32(base + tap * 8192), &map_w, smem_u32(&sm->wfull), tap * 64, 0);
+      const uint32_t tx = (uint32_t)(p.pitch * (p.rows + 2)) * 128u;
+      uint32_t s = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int n = tile / p.tiles_h, h0 = (tile - n * p.tiles_h) * p.rows;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->empty[s], phase ^ 1, p.error, 1))) break;
+        mbar_expect_tx(&sm->full[s], tx);
+        tma_load_4d(smem_u32(stage0 + s * p.stage_bytes), &map_x, smem_u32(&sm->full[s]), 0, -1, h0 - 1, n);
+        if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((64u >> 4) << 24);
+      bool ok = mbar_wait_abortable(&sm->abort, &sm->wfull, 0, p.error, 5);
+      tc_fence_after();
+      const uint32_t wsm = smem_u32(base);
+      uint32_t s = 0, phase = 0, t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+        const uint32_t buf = t & 1, use = t >> 1;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->full[s], phase, p.error, 3))) break;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->tmem_empty[buf], (use & 1) ^ 1, p.error, 2))) break;
+        tc_fence_after();
+        const uint32_t xs = smem_u32(stage0 + s * p.stage_bytes);
+        const uint32_t d_tmem = tmem_base + buf * 256;
+#pragma unroll 1
+        for (int tap = 0; tap < WS_TAPS; tap++) {
+          const int r = tap / 3, sx = tap - 3 * r;
+          const uint32_t xb = xs + (uint32_t)(r * p.pitch + sx) * 128u;
+          uint64_t db = smem_desc_sw128(xb);
+          const uint64_t da = smem_desc_sw128(wsm + tap * 8192);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++) tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (tap | k) != 0);
+        }
+        tc_commit(&sm->empty[s]);
+        tc_commit(&sm->tmem_full[buf]);
+        if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
+      }
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < kSpinLimit; it++) if (mbar_try_wait(&sm->drain, 0)) break;
+    }
+  } else {
+    // Lane = output channel, column = pixel slot, but memory wants the channels of a pixel side by side: every
+    // 32-slot chunk passes through the warp's staging buffer as [slot][channel] and leaves in 16-byte pieces.
+    const int q = warp & 3, ew = warp - 2, half = ew / 4;
+    constexpr int nco = 16;                        // channels this warp owns: lanes 0..15 of its quarter
+    const int co0 = q * nco;
+    const bool lane_useful = lane < nco;
+    const float bias = (lane_useful && p.bias) ? __ldg(p.bias + co0 + lane) : 0.0f;
+    uint8_t* stg = stage_base + ew * kStageWarpBytes;
+    constexpr int row_bytes = nco * 2;             // 32 bytes of one slot
+    constexpr int lanes_per_slot = row_bytes / 16, slots_per_pass = 32 / lanes_per_slot;
+    const int my_slot = lane / lanes_per_slot, my_piece = lane % lanes_per_slot;
+    uint32_t t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+      const uint32_t buf = t & 1, use = t >> 1;
+      ok = mbar_wait_abortable(&sm->abort, &sm->tmem_full[buf], use & 1, p.error, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int n = tile / p.tiles_h, h0 = (tile - n * p.tiles_h) * p.rows;
+      {
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * 128;
+        __nv_bfloat16* img = p.out + ((size_t)n * p.H + h0) * p.W * 64 + co0 + my_piece * 8;
+        // (i, j) of the first slot this lane stores
+        int i = (half * 128 + my_slot) / p.pitch, j = half * 128 + my_slot - i * p.pitch;
+        auto process = [&](const uint32_t (&r)[32]) {
+          if (lane_useful) {
+#pragma unroll
+            for (int e = 0; e < 32; e++)
+              *reinterpret_cast<__nv_bfloat16*>(stg + e * row_bytes + lane * 2) = __float2bfloat16(__uint_as_float(r[e]) + bias);
+          }
+          __syncwarp();
+          for (int e0 = 0; e0 < 32; e0 += slots_per_pass) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + (e0 + my_slot) * row_bytes + my_piece * 16);
+            if (j < p.W && i < p.rows && h0 + i < p.H) *reinterpret_cast<uint4*>(img + ((size_t)i * p.W + j) * 64) = v;
+            j += slots_per_pass;
+            while (j >= p.pitch) { j -= p.pitch; i++; }
+          }
+          __syncwarp();
+        };
+        // the next chunk's tensor-memory load is in flight while this one is staged and stored
+        uint32_t ra[32], rb[32];
+        tc_ld32(taddr, ra);
+        tc_wait_ld();
+        tc_ld32(taddr + 32, rb);
+        process(ra);
+        tc_wait_ld();
+        tc_ld32(taddr + 64, ra);
+        process(rb);
+        tc_wait_ld();
+        tc_ld32(taddr + 96, rb);
+        process(ra);
+        tc_wait_ld();
+        // everything of this accumulator is in registers: the MMA warp may overwrite it
+        tc_fence_before();
+        mbar_arrive(&sm->tmem_empty[buf]);
+        process(rb);
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // wt[ci][kh-1-r][kw-1-s][co] = w[co][r][s][ci]: the filter of the data-gradient convolution
 __global__ void flip_weights_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int kh,
                                     int kw, int Ci) {
@@ -484,6 +670,7 @@ static int device_sms() {
     cudaFuncSetAttribute(conv_igemm_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
     cudaFuncSetAttribute(conv_igemm_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
     cudaFuncSetAttribute(conv_igemm_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    cudaFuncSetAttribute(conv_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
   });
   return sms;
 }
@@ -596,6 +783,47 @@ int gcow_conv_fwd_strided(const void* x, const void* w, void* y, const float* bi
   if (stride < 1 || stride > 2) return -1;
   const int Ho = (Hin + 2 * pad_h - kh) / stride + 1, Wo = (Win + 2 * pad_w - kw) / stride + 1;
   return conv_fwd_launch(x, w, y, bias, N, Hin, Win, Ci, Co, kh, kw, pad_h, pad_w, stride, Ho, Wo, 1, 0, 0, Ho, Wo, error, stream);
+}
+
+// Whether gcow_conv_fwd_ws takes these extents (64 -> 64 channels, 3x3, stride 1, padding 1 are implied).
+int gcow_conv_ws_usable(int N, int H, int W) {
+  return N > 0 && H > 0 && W >= 6 && W + 2 <= 128;
+}
+
+// y[N,H,W,64] = conv3x3(x[N,H,W,64], w[64,3,3,64]) (+ bias), stride 1, padding 1, on the weight-stationary kernel
+// (pixels as the MMA's N). With w = the flipped filter [ci][2-r][2-s][co] and x = dY it is the input gradient.
+int gcow_conv_fwd_ws(const void* x, const void* w, void* y, const float* bias, int N, int H, int W, uint32_t* error,
+                     void* stream) {
+  if (!gcow_conv_ws_usable(N, H, W)) return -1;
+  if (((uintptr_t)y & 1) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return -1;
+  const int sms = device_sms();
+  WsParams p{};
+  p.out = (__nv_bfloat16*)y; p.bias = bias; p.N = N; p.H = H; p.W = W;
+  p.pitch = W + 2;
+  p.rows = 256 / p.pitch;
+  if (p.rows > H) p.rows = H;
+  p.tiles_h = (H + p.rows - 1) / p.rows;
+  // a stage holds the copied box; the taps of the last pixel slots read up to 2 * pitch + 2 rows further, into the
+  // next stage or the epilogue's staging buffers: sums of slots that are never stored
+  p.stage_bytes = (p.pitch * (p.rows + 2) * 128 + 1023) & ~1023;
+  const int tail = 16 + EPI_WARPS * kStageWarpBytes;
+  const int reach = (256 + 2 * p.pitch + 2) * 128 - tail;        // what the last stage itself must cover
+  if (p.stage_bytes < reach) p.stage_bytes = (reach + 1023) & ~1023;
+  int st = (kWsSmemMax - 1024 - WS_W_BYTES - (int)sizeof(WsSmem) - tail) / p.stage_bytes;
+  if (st > 4) st = 4;
+  if (st < 2) return -1;
+  p.stages = st;
+  p.error = error;
+  CUtensorMap mx, mw;
+  int rc = make_map_nhwc(&mx, x, (uint64_t)N, (uint64_t)H, (uint64_t)W, 64, (uint32_t)p.pitch, (uint32_t)(p.rows + 2), 1, 0);
+  if (rc) return rc;
+  rc = make_map_2d(&mw, w, 64, (uint64_t)WS_TAPS * 64, 64);
+  if (rc) return rc;
+  const long long tiles = (long long)N * p.tiles_h;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  const size_t smem = 1024 + WS_W_BYTES + (size_t)st * p.stage_bytes + sizeof(WsSmem) + tail;
+  gcow::launch_dependent(conv_ws_kernel, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, mx, mw, p);
+  return (int)cudaGetLastError();
 }
 
 // Input gradient of a 3x3, stride-2, padding-1 convolution with even input extents: dx[N,Hin,Win,Ci] from

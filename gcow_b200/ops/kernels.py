@@ -5,6 +5,8 @@ alignment); callers fall back to PyTorch otherwise.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _native
@@ -980,6 +982,21 @@ def embed3(ids, type_ids, tok, pos, typ):
 
 
 # ------------------------------------------------ implicit-GEMM convolution (stride 1)
+def conv_ws_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
+    """64 -> 64 channels, 3x3, stride 1, padding 1: the weight-stationary kernel (pixels as the MMA's N) applies."""
+    return (C == 64 and Co == 64 and KH == 3 and KW == 3 and pad_h == 1 and pad_w == 1
+            and os.environ.get("GCOW_CONV_WS", "1") != "0" and _have("gcow_conv_fwd_ws")
+            and bool(_native.cuda().gcow_conv_ws_usable(N, H, W)))
+
+
+def _conv_fwd_s1(lib, x_ptr, w_ptr, y_ptr, bias_ptr, N, H, W, C, Co, KH, KW, pad_h, pad_w, err, st, what):
+    """Stride-1 forward kernel for these extents: the weight-stationary one where it applies, else the general one."""
+    if conv_ws_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
+        _chk(lib.gcow_conv_fwd_ws(x_ptr, w_ptr, y_ptr, bias_ptr, N, H, W, err, st), what + " (ws)")
+    else:
+        _chk(lib.gcow_conv_fwd(x_ptr, w_ptr, y_ptr, bias_ptr, N, H, W, C, Co, KH, KW, pad_h, pad_w, err, st), what)
+
+
 class _ConvIgemmFn(torch.autograd.Function):
     """Stride-1 KxK convolution, channels-last bf16, as an implicit GEMM on the tcgen05 kernel
     (csrc/ops/conv_tcgen05.cu): forward, data gradient (the same kernel on dY with the flipped
@@ -997,9 +1014,9 @@ class _ConvIgemmFn(torch.autograd.Function):
         OH, OW = H + 2 * pad_h - KH + 1, W + 2 * pad_w - KW + 1
         y = torch.empty((N, Co, OH, OW), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
         bias = b.detach().float().contiguous() if b is not None else None
-        _chk(lib.gcow_conv_fwd(x.data_ptr(), wr.data_ptr(), y.data_ptr(), bias.data_ptr() if bias is not None else None,
-                               N, H, W, C, Co, KH, KW, pad_h, pad_w, _error_word(x.device).data_ptr(), _stream(x.device)),
-             "gcow_conv_fwd")
+        _conv_fwd_s1(lib, x.data_ptr(), wr.data_ptr(), y.data_ptr(), bias.data_ptr() if bias is not None else None,
+                     N, H, W, C, Co, KH, KW, pad_h, pad_w, _error_word(x.device).data_ptr(), _stream(x.device),
+                     "gcow_conv_fwd")
         _launches += 1
         ctx.save_for_backward(x, wr)
         ctx.meta = (N, C, H, W, Co, KH, KW, OH, OW, pad_h, pad_w, b is not None)
@@ -1020,8 +1037,8 @@ class _ConvIgemmFn(torch.autograd.Function):
             wt = torch.empty((C, KH, KW, Co), dtype=torch.bfloat16, device=dev)
             _chk(lib.gcow_conv_flip_weights(wr.data_ptr(), wt.data_ptr(), Co, KH, KW, C, st), "gcow_conv_flip_weights")
             gx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=dev, memory_format=torch.channels_last)
-            _chk(lib.gcow_conv_fwd(gy.data_ptr(), wt.data_ptr(), gx.data_ptr(), None, N, OH, OW, Co, C, KH, KW,
-                                   KH - 1 - pad_h, KW - 1 - pad_w, err, st), "gcow_conv_fwd (dgrad)")
+            _conv_fwd_s1(lib, gy.data_ptr(), wt.data_ptr(), gx.data_ptr(), None, N, OH, OW, Co, C, KH, KW,
+                         KH - 1 - pad_h, KW - 1 - pad_w, err, st, "gcow_conv_fwd (dgrad)")
             _launches += 2
         if ctx.needs_input_grad[1]:
             split = lib.gcow_conv_wgrad_split(N, H, W, C, Co, KH, KW, pad_h, pad_w)

@@ -17,6 +17,11 @@ CASES = [
     (2, 64, 11, 13, 64, 5, 5, 2, 2),
     (2, 64, 10, 10, 64, 2, 2, 1, 1),
     (2, 192, 8, 9, 64, 1, 3, 0, 1),
+    # 64 -> 64 channels, 3x3, padding 1: the weight-stationary kernel (several tiles per image, ragged last tile,
+    # an image smaller than one tile)
+    (2, 64, 56, 56, 64, 3, 3, 1, 1),
+    (3, 64, 30, 20, 64, 3, 3, 1, 1),
+    (1, 64, 7, 9, 64, 3, 3, 1, 1),
 ]
 
 
@@ -61,6 +66,26 @@ def test_conv_igemm_forward_and_gradients(case):
 
 
 # (N, Ci, H, W, Co): whole boxes, ragged pixel boxes, more output than input channels and the reverse
+def test_weight_stationary_kernel_serves_the_64_channel_layers_and_agrees_with_the_general_one(monkeypatch):
+    from gcow_b200.ops import kernels as K
+    N, H, W = 3, 56, 56
+    assert K.conv_ws_usable(N, H, W, 64, 64, 3, 3, 1, 1)
+    assert not K.conv_ws_usable(N, H, W, 64, 128, 3, 3, 1, 1) and not K.conv_ws_usable(N, H, W, 64, 64, 3, 3, 0, 0)
+    torch.manual_seed(5)
+    x, w, b = _mk(N, 64, H, W, 64, 3, 3)
+    gy = (torch.randn(N, 64, H, W, device="cuda") * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    outs = []
+    for ws in ("1", "0"):
+        monkeypatch.setenv("GCOW_CONV_WS", ws)
+        xo = x.clone().requires_grad_(True)
+        y = K.conv_igemm(xo, w.clone().requires_grad_(True), None, (1, 1))
+        y.backward(gy)
+        K.check_errors()
+        outs.append((y.detach().float(), xo.grad.float()))
+    # the same bf16 operands, fp32 accumulation in another order: equal up to the output rounding
+    assert _rel(outs[0][0], outs[1][0]) < 1e-2 and _rel(outs[0][1], outs[1][1]) < 1e-2
+
+
 S2_CASES = [(4, 64, 16, 16, 64), (3, 64, 10, 14, 128), (2, 128, 28, 28, 128), (5, 256, 6, 8, 64), (2, 64, 2, 2, 64)]
 
 
