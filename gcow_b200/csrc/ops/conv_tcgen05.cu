@@ -553,6 +553,156 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Weight gradient of the same layers (64 -> 64 channels, 3x3, stride 1, padding 1) from halo tiles.
+//   dW[co][(r, s), ci] = sum over pixels of dY[pixel][co] * X[pixel + (r - 1, s - 1)][ci]
+// A tile is four image rows in slots of pitch 64: one copy brings six rows of dY (rows h0-1 .. h0+4, columns
+// 0..63, zero filled past the image) and one copy six rows of X (the same rows, columns -1..62). With dY slot
+// d = (row - h0 + 1) * 64 + col the X pixel of tap (r, s) is slot d + (r - 1) * 64 + s. Both operands are
+// MN-major (a slot is a 128-byte row of 64 channels, slots are the reduction), so a tap is again a start
+// address moved by whole rows, and the descriptor's leading offset - the distance between consecutive 64-wide
+// blocks of M or N - does two more things:
+//   B: N = 192 = the three taps of a filter row, leading offset one slot (128 bytes): block n is tap s = n;
+//   A: M = 128 = dY and dY one image row further down (leading offset 64 slots): the upper 64 accumulator
+//      rows get the filter row r, the lower 64 the filter row r - 1 of the dY row below.
+// Two MMAs per 16 slots: {r = 1 above, r = 0 below} into columns 0..191 and {r = 2 above} into columns
+// 192..383 (its lower half repeats r = 1 and is not read). The lower half sees dY rows h0+1 .. h0+4; the
+// first tile of an image runs four more steps (slots of row h0-1, zero for the upper half) so that it also
+// sees row 0. Against the general kernel (one 8 KB copy of shifted X per tap and 64 pixels, three column
+// tiles that each re-read dY) a tile of 224 pixels costs two 48 KB copies and 32 MMAs.
+// Every CTA sums a contiguous range of tiles in tensor memory and writes one fp32 partial [64][576].
+struct WsWgradParams {
+  float* part;          // [gridDim.x][64][576]
+  int N, H, W;
+  int tiles_h, num_tiles, per;
+  uint32_t* error;
+};
+
+constexpr int WG_X_ROWS = 392, WG_DY_ROWS = 384, WG_STAGE_BYTES = (WG_X_ROWS + WG_DY_ROWS) * 128, WG_STAGES = 2;
+constexpr uint32_t WG_BOX_BYTES = 64 * 6 * 128;
+
+__device__ __forceinline__ uint64_t smem_desc_mn_lbo(uint32_t saddr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+conv_wgrad_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_dy,
+                     const WsWgradParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  WsSmem* sm = reinterpret_cast<WsSmem*>(base + WG_STAGES * WG_STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int first = blockIdx.x * p.per;
+  int last = first + p.per;
+  if (last > p.num_tiles) last = p.num_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WG_STAGES; s++) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
+    mbar_init(&sm->tmem_full[0], 1);
+    mbar_init(&sm->drain, 1);
+    sm->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // the eight rows behind each X box are read by the last taps against zero dY: they must hold finite numbers
+  if (threadIdx.x < WG_STAGES * 64) {
+    const int s = threadIdx.x / 64, i = threadIdx.x % 64;
+    *reinterpret_cast<uint4*>(base + s * WG_STAGE_BYTES + 384 * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t s = 0, phase = 0;
+      bool ok = true;
+      for (int tile = first; tile < last && ok; tile++) {
+        const int n = tile / p.tiles_h, h0 = (tile - n * p.tiles_h) * 4;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->empty[s], phase ^ 1, p.error, 1))) break;
+        mbar_expect_tx(&sm->full[s], 2 * WG_BOX_BYTES);
+        uint8_t* st = base + s * WG_STAGE_BYTES;
+        tma_load_4d(smem_u32(st), &map_x, smem_u32(&sm->full[s]), 0, -1, h0 - 1, n);
+        tma_load_4d(smem_u32(st + WG_X_ROWS * 128), &map_dy, smem_u32(&sm->full[s]), 0, 0, h0 - 1, n);
+        if (++s == WG_STAGES) { s = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // fp32 accumulate, bf16 x bf16, both operands MN-major, N = 192, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((192u >> 3) << 17) | ((128u >> 4) << 24);
+      uint32_t s = 0, phase = 0, acc = 0;
+      bool ok = true;
+      for (int tile = first; tile < last && ok; tile++) {
+        const int n = tile / p.tiles_h, h0 = (tile - n * p.tiles_h) * 4;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->full[s], phase, p.error, 3))) break;
+        tc_fence_after();
+        const uint32_t xs = smem_u32(base + s * WG_STAGE_BYTES), ds = xs + WG_X_ROWS * 128;
+#pragma unroll 1
+        for (int k = (h0 == 0 ? 0 : 4); k < 20; k++) {
+          const uint32_t off = (uint32_t)k * 16u * 128u;
+          const uint64_t da = smem_desc_mn_lbo(ds + off, 64u * 128u);
+          tc_mma(tmem_base, da, smem_desc_mn_lbo(xs + off, 128u), idesc, acc);
+          tc_mma(tmem_base + 192, da, smem_desc_mn_lbo(xs + off + 64u * 128u, 128u), idesc, acc);
+          acc = 1;
+        }
+        tc_commit(&sm->empty[s]);
+        if (++s == WG_STAGES) { s = 0; phase ^= 1; }
+      }
+      if (ok) tc_commit(&sm->tmem_full[0]);
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < kSpinLimit; it++) if (mbar_try_wait(&sm->drain, 0)) break;
+    }
+  } else {
+    const int q = warp & 3, ew = warp - 2, half = ew / 4;     // half 0: columns 0..191, half 1: columns 192..383
+    bool ok = mbar_wait_abortable(&sm->abort, &sm->tmem_full[0], 0, p.error, 4);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && !(half == 1 && q >= 2)) {
+      tc_fence_after();
+      const int row = q * 32 + lane;
+      const int co = row & 63;
+      const int r = half == 1 ? 2 : (row < 64 ? 1 : 0);        // filter row of this accumulator half
+      float* dst = p.part + ((size_t)blockIdx.x * 64 + co) * 576 + r * 192;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + half * 192;
+#pragma unroll 1
+      for (int c = 0; c < 6; c++) {
+        uint32_t v[32];
+        tc_ld32(taddr + c * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + c * 32 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                     __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // wt[ci][kh-1-r][kw-1-s][co] = w[co][r][s][ci]: the filter of the data-gradient convolution
 __global__ void flip_weights_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int kh,
                                     int kw, int Ci) {
@@ -671,6 +821,7 @@ static int device_sms() {
     cudaFuncSetAttribute(conv_igemm_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
     cudaFuncSetAttribute(conv_igemm_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
     cudaFuncSetAttribute(conv_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
+    cudaFuncSetAttribute(conv_wgrad_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
   });
   return sms;
 }
@@ -823,6 +974,37 @@ int gcow_conv_fwd_ws(const void* x, const void* w, void* y, const float* bias, i
   const int grid = (int)(tiles < sms ? tiles : sms);
   const size_t smem = 1024 + WS_W_BYTES + (size_t)st * p.stage_bytes + sizeof(WsSmem) + tail;
   gcow::launch_dependent(conv_ws_kernel, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, mx, mw, p);
+  return (int)cudaGetLastError();
+}
+
+// Whether gcow_conv_wgrad_ws takes these extents, and how many partial results it writes (0: not usable).
+int gcow_conv_wgrad_ws_split(int N, int H, int W) {
+  if (N <= 0 || H <= 0 || W < 1 || W + 2 > 64) return 0;
+  const int sms = device_sms();
+  const long long tiles = (long long)N * ((H + 3) / 4);
+  if (tiles > (1ll << 30)) return 0;
+  const int per = (int)((tiles + sms - 1) / sms);
+  return (int)((tiles + per - 1) / per);
+}
+
+// part[split][64][9 * 64] (fp32) = partial sums of dy[N,H,W,64]^T * shifted x[N,H,W,64] for a 3x3 filter with padding 1,
+// split = gcow_conv_wgrad_ws_split(N, H, W); the caller adds the slices (gcow_reduce_partials).
+int gcow_conv_wgrad_ws(const void* dy, const void* x, float* part, int N, int H, int W, uint32_t* error, void* stream) {
+  const int split = gcow_conv_wgrad_ws_split(N, H, W);
+  if (split <= 0 || ((uintptr_t)part & 15)) return -1;
+  WsWgradParams p{};
+  p.part = part; p.N = N; p.H = H; p.W = W;
+  p.tiles_h = (H + 3) / 4;
+  p.num_tiles = N * p.tiles_h;
+  p.per = (p.num_tiles + split - 1) / split;
+  p.error = error;
+  CUtensorMap mx, md;
+  int rc = make_map_nhwc(&mx, x, (uint64_t)N, (uint64_t)H, (uint64_t)W, 64, 64, 6, 1, 0);
+  if (rc) return rc;
+  rc = make_map_nhwc(&md, dy, (uint64_t)N, (uint64_t)H, (uint64_t)W, 64, 64, 6, 1, 0);
+  if (rc) return rc;
+  const size_t smem = 1024 + (size_t)WG_STAGES * WG_STAGE_BYTES + sizeof(WsSmem) + 64;
+  gcow::launch_dependent(conv_wgrad_ws_kernel, dim3(split), dim3(THREADS), smem, (cudaStream_t)stream, mx, md, p);
   return (int)cudaGetLastError();
 }
 

@@ -22,6 +22,9 @@ CASES = [
     (2, 64, 56, 56, 64, 3, 3, 1, 1),
     (3, 64, 30, 20, 64, 3, 3, 1, 1),
     (1, 64, 7, 9, 64, 3, 3, 1, 1),
+    # the widest rows the halo-tile weight gradient takes, and one column more (general weight gradient)
+    (5, 64, 13, 62, 64, 3, 3, 1, 1),
+    (2, 64, 5, 63, 64, 3, 3, 1, 1),
 ]
 
 
@@ -77,13 +80,18 @@ def test_weight_stationary_kernel_serves_the_64_channel_layers_and_agrees_with_t
     outs = []
     for ws in ("1", "0"):
         monkeypatch.setenv("GCOW_CONV_WS", ws)
+        monkeypatch.setenv("GCOW_CONV_WS_WGRAD", ws)
         xo = x.clone().requires_grad_(True)
-        y = K.conv_igemm(xo, w.clone().requires_grad_(True), None, (1, 1))
+        wo = w.clone().requires_grad_(True)
+        y = K.conv_igemm(xo, wo, None, (1, 1))
         y.backward(gy)
         K.check_errors()
-        outs.append((y.detach().float(), xo.grad.float()))
+        outs.append((y.detach().float(), xo.grad.float(), wo.grad.float()))
     # the same bf16 operands, fp32 accumulation in another order: equal up to the output rounding
     assert _rel(outs[0][0], outs[1][0]) < 1e-2 and _rel(outs[0][1], outs[1][1]) < 1e-2
+    assert _rel(outs[0][2], outs[1][2]) < 1e-4
+    lib = K._native.cuda()
+    assert lib.gcow_conv_wgrad_ws_split(N, H, W) > 1 and lib.gcow_conv_wgrad_ws_split(N, H, 63) == 0
 
 
 S2_CASES = [(4, 64, 16, 16, 64), (3, 64, 10, 14, 128), (2, 128, 28, 28, 128), (5, 256, 6, 8, 64), (2, 64, 2, 2, 64)]
