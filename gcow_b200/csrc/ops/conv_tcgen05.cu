@@ -71,6 +71,7 @@ struct Params {
   int b_chunks;         // wgrad: 64-channel groups of X fetched by one copy (1, 2 or 4)
   int flags;
   int stride;           // step of the input window per output pixel (forward) / per dY pixel (wgrad): 1 or 2
+  int swap;             // forward, two accumulators, 128 output channels: the channels are the MMA's M, the 256 pixels its N
   int out_step, out_off_h, out_off_w, out_H, out_W;   // forward: tile pixel (h, w) is stored at (h * out_step + out_off_h,
                                                       // w * out_step + out_off_w) of a [N, out_H, out_W, Co] tensor
   uint32_t* error;
@@ -218,6 +219,22 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           tc_fence_after();
           const uint32_t sa = smem_u32(base + s * stage_bytes), sb = sa + A_BYTES;
           const uint64_t db = WGRAD ? smem_desc_mn_sw128(sb) : smem_desc_sw128(sb);
+          if (!WGRAD && HALVES == 2 && p.swap) {
+            // D[co][pixel]: the filter tile is A, both pixel halves (contiguous in shared memory) are one 256-row B
+            if (kb == 0) {
+              for (int h = 0; h < 2 && ok; h++) ok = mbar_wait_abortable(&sm->abort, &sm->tmem_empty[buf * 2 + h], (use & 1) ^ 1, p.error, 2);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            const uint32_t idesc_swap = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+            const uint64_t dpix = smem_desc_sw128(sa);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; k++)
+              tc_mma(tmem_base + buf * 256, db + kstep * k, dpix + kstep * k, idesc_swap, (kb | k) != 0);
+            tc_commit(&sm->empty[s]);
+            if (++s == (uint32_t)STAGES) { s = 0; phase ^= 1; }
+            continue;
+          }
 #pragma unroll
           for (int h = 0; h < HALVES; h++) {
             if (kb == 0) {   // first write to this accumulator: its previous contents must have been read out
@@ -255,6 +272,54 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below need the whole warp
       if (!ok) break;
       tc_fence_after();
+      if (!WGRAD && HALVES == 2 && p.swap) {
+        // lane = output channel q * 32 + lane, column = tile pixel: 32-pixel chunks pass through the warp's staging
+        // buffer as [pixel][32 channels] and leave as 16-byte pieces, four lanes per pixel
+        const int tcn = tile % tiles_c, pt = tile / tiles_c;
+        const int w0 = (pt % p.tiles_w) * p.bw, h0 = ((pt / p.tiles_w) % p.tiles_h) * p.bh;
+        const int n0 = (pt / (p.tiles_w * p.tiles_h)) * p.bn;
+        const int co = tcn * p.bn_cols + q * 32;
+        const int hsel = ew / 4;
+        const float bias = (p.flags & kBias) && co + lane < p.Co ? __ldg(p.bias + co + lane) : 0.0f;
+        uint8_t* stg = stage_base + ew * kStageWarpBytes;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + hsel * 128;
+        __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(p.out) + co + (lane & 3) * 8;
+        const bool co_ok = co + (lane & 3) * 8 + 8 <= p.Co;
+        auto emit = [&](const uint32_t (&r)[32], int c) {
+#pragma unroll
+          for (int e = 0; e < 32; e++)
+            *reinterpret_cast<__nv_bfloat16*>(stg + e * 64 + lane * 2) = __float2bfloat16(__uint_as_float(r[e]) + bias);
+          __syncwarp();
+#pragma unroll
+          for (int e0 = 0; e0 < 32; e0 += 8) {
+            const int row = hsel * 128 + c * 32 + e0 + (lane >> 2);
+            const int iw = row % p.bw, ih = (row / p.bw) % p.bh, in = row / (p.bw * p.bh);
+            const int w = w0 + iw, hh = h0 + ih, n = n0 + in;
+            const int oh = hh * p.out_step + p.out_off_h, ow = w * p.out_step + p.out_off_w;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + (e0 + (lane >> 2)) * 64 + (lane & 3) * 16);
+            if (co_ok && in < p.bn && w < p.W && hh < p.H && n < p.N && oh < p.out_H && ow < p.out_W)
+              *reinterpret_cast<uint4*>(outp + (((size_t)n * p.out_H + oh) * p.out_W + ow) * (size_t)p.Co) = v;
+          }
+          __syncwarp();
+        };
+        uint32_t ra[32], rb[32];
+        tc_ld32(taddr, ra);
+        tc_wait_ld();
+        tc_ld32(taddr + 32, rb);
+        emit(ra, 0);
+        tc_wait_ld();
+        tc_ld32(taddr + 64, ra);
+        emit(rb, 1);
+        tc_wait_ld();
+        tc_ld32(taddr + 96, rb);
+        emit(ra, 2);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&sm->tmem_empty[buf * 2]);
+        mbar_arrive(&sm->tmem_empty[buf * 2 + 1]);
+        emit(rb, 3);
+        continue;
+      }
 #pragma unroll 1
       for (int h = 0; h < HALVES; h++) {
         const int row = h * 128 + q * 32 + lane;    // tile row of this thread
@@ -904,6 +969,7 @@ static int conv_fwd_launch(const void* x, const void* w, void* y, const float* b
   p.split = 1; p.chunks_per_split = 0; p.b_chunks = 1;
   p.flags = bias ? kBias : 0;
   p.stride = stride;
+  p.swap = (halves == 2 && p.bn_cols == 128 && Co % 8 == 0 && !getenv("GCOW_CONV_NOSWAP")) ? 1 : 0;
   p.out_step = out_step; p.out_off_h = out_off_h; p.out_off_w = out_off_w; p.out_H = out_H; p.out_W = out_W;
   p.error = error;
   CUtensorMap ma, mb;

@@ -25,6 +25,10 @@ CASES = [
     # the widest rows the halo-tile weight gradient takes, and one column more (general weight gradient)
     (5, 64, 13, 62, 64, 3, 3, 1, 1),
     (2, 64, 5, 63, 64, 3, 3, 1, 1),
+    # enough tiles for the two-accumulator forward tile with 128 output channels: the operand-swapped MMA
+    # (channels as M, 256 pixels as N); ragged 245-pixel boxes and whole ones
+    (40, 128, 28, 28, 128, 3, 3, 1, 1),
+    (48, 64, 20, 20, 128, 3, 3, 1, 1),
 ]
 
 
@@ -92,6 +96,25 @@ def test_weight_stationary_kernel_serves_the_64_channel_layers_and_agrees_with_t
     assert _rel(outs[0][2], outs[1][2]) < 1e-4
     lib = K._native.cuda()
     assert lib.gcow_conv_wgrad_ws_split(N, H, W) > 1 and lib.gcow_conv_wgrad_ws_split(N, H, 63) == 0
+
+
+def test_operand_swapped_forward_agrees_with_the_plain_one(monkeypatch):
+    import ctypes
+    from gcow_b200.ops import kernels as K
+    N, C, H, W, Co = 40, 128, 28, 28, 128
+    plan = (ctypes.c_int * 6)()
+    K._native.cuda().gcow_conv_fwd_plan(N, H, W, C, Co, 3, 3, 1, 1, 148, plan)
+    assert plan[0] == 2 and plan[1] == 128                        # the tile shape that swaps
+    torch.manual_seed(6)
+    x, w, b = _mk(N, C, H, W, Co, 3, 3)
+    outs = []
+    for noswap in ("", "1"):
+        if noswap:
+            monkeypatch.setenv("GCOW_CONV_NOSWAP", noswap)
+        y = K.conv_igemm(x, w, b, (1, 1))
+        K.check_errors()
+        outs.append(y.float())
+    assert _rel(outs[0], outs[1]) < 1e-2
 
 
 S2_CASES = [(4, 64, 16, 16, 64), (3, 64, 10, 14, 128), (2, 128, 28, 28, 128), (5, 256, 6, 8, 64), (2, 64, 2, 2, 64)]
