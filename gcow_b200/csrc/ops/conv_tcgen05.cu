@@ -619,6 +619,188 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Halo-tile forward for Ci -> 128 channels, 3x3, stride 1, padding 1 (Ci a multiple of 64): the same idea as the
+// weight-stationary kernel with the filter streamed instead of resident. The 128 output channels are the MMA's M,
+// the pixel slots (rows x (W + 2), rounded up to 16) its N. Per tile one halo box per 64-channel chunk of the input
+// (all chunks on one barrier) serves the nine taps; the filter tiles [128][64] of (chunk, tap) run through a ring
+// of their own. Against the general kernel (a 32 KB pixel box per tap and chunk) the pixel traffic from L2 falls
+// ninefold; the filter traffic per tile is the same.
+struct HaloParams {
+  __nv_bfloat16* out;   // [N, H, W, 128]
+  const float* bias;
+  int N, H, W, Ci;
+  int pitch, rows, tiles_h;
+  int nslots;           // N of the MMA: rows * pitch rounded up to 16
+  int chunk_bytes;      // shared-memory region of one 64-channel chunk of a tile (1024-byte multiple)
+  int a_stages, b_stages;
+  uint32_t* error;
+};
+
+struct HaloSmem {
+  uint64_t a_full[2], a_empty[2], b_full[8], b_empty[8], tmem_full[2], tmem_empty[2], drain;
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+};
+
+constexpr int HALO_B_BYTES = 128 * 64 * 2;
+
+__global__ void __launch_bounds__(THREADS, 1)
+conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const HaloParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int cchunks = p.Ci / 64;
+  const int a_stage_bytes = cchunks * p.chunk_bytes;
+  uint8_t* bring = base + p.a_stages * a_stage_bytes;
+  HaloSmem* sm = reinterpret_cast<HaloSmem*>(bring + p.b_stages * HALO_B_BYTES);
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>(((uintptr_t)(sm + 1) + 15) & ~(uintptr_t)15);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.N * p.tiles_h;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; s++) { mbar_init(&sm->a_full[s], 1); mbar_init(&sm->a_empty[s], 1); }
+    for (int s = 0; s < 8; s++) { mbar_init(&sm->b_full[s], 1); mbar_init(&sm->b_empty[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&sm->tmem_full[a], 1); mbar_init(&sm->tmem_empty[a], EPI_WARPS * 32); }
+    mbar_init(&sm->drain, 1);
+    sm->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t a_tx = (uint32_t)(cchunks * p.pitch * (p.rows + 2)) * 128u;
+      uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
+      bool ok = true;
+      auto load_a = [&](int tile) {
+        const int n = tile / p.tiles_h, h0 = (tile - n * p.tiles_h) * p.rows;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->a_empty[sa], pa ^ 1, p.error, 1))) return;
+        mbar_expect_tx(&sm->a_full[sa], a_tx);
+        for (int c = 0; c < cchunks; c++)
+          tma_load_4d(smem_u32(base + sa * a_stage_bytes + c * p.chunk_bytes), &map_x, smem_u32(&sm->a_full[sa]), c * 64, -1,
+                      h0 - 1, n);
+        if (++sa == (uint32_t)p.a_stages) { sa = 0; pa ^= 1; }
+      };
+      // the pixel tile of the next tile is requested in the middle of this tile's filter tiles
+      if (blockIdx.x < num_tiles) load_a(blockIdx.x);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < cchunks * WS_TAPS && ok; kb++) {
+          // once the ring has wrapped within this tile the previous tile's MMAs are done and its pixel stage is free
+          if (kb == p.b_stages && tile + (int)gridDim.x < num_tiles) { load_a(tile + gridDim.x); if (!ok) break; }
+          const int c = kb / WS_TAPS, tap = kb - c * WS_TAPS;
+          if (!(ok = mbar_wait_abortable(&sm->abort, &sm->b_empty[sb], pb ^ 1, p.error, 6))) break;
+          mbar_expect_tx(&sm->b_full[sb], (uint32_t)HALO_B_BYTES);
+          tma_load_2d(smem_u32(bring + sb * HALO_B_BYTES), &map_w, smem_u32(&sm->b_full[sb]), tap * p.Ci + c * 64, 0);
+          if (++sb == (uint32_t)p.b_stages) { sb = 0; pb ^= 1; }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.nslots >> 3) << 17) | ((128u >> 4) << 24);
+      uint32_t sa = 0, pa = 0, sb = 0, pb = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+        const uint32_t buf = t & 1, use = t >> 1;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->a_full[sa], pa, p.error, 3))) break;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->tmem_empty[buf], (use & 1) ^ 1, p.error, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * 256;
+        for (int kb = 0; kb < cchunks * WS_TAPS && ok; kb++) {
+          const int c = kb / WS_TAPS, tap = kb - c * WS_TAPS;
+          const int r = tap / 3, sx = tap - 3 * r;
+          if (!(ok = mbar_wait_abortable(&sm->abort, &sm->b_full[sb], pb, p.error, 7))) break;
+          tc_fence_after();
+          const uint64_t da = smem_desc_sw128(smem_u32(bring + sb * HALO_B_BYTES));
+          const uint64_t db = smem_desc_sw128(smem_u32(base + sa * a_stage_bytes + c * p.chunk_bytes) +
+                                              (uint32_t)(r * p.pitch + sx) * 128u);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++) tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          tc_commit(&sm->b_empty[sb]);
+          if (++sb == (uint32_t)p.b_stages) { sb = 0; pb ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&sm->a_empty[sa]);
+        tc_commit(&sm->tmem_full[buf]);
+        if (++sa == (uint32_t)p.a_stages) { sa = 0; pa ^= 1; }
+      }
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < kSpinLimit; it++) if (mbar_try_wait(&sm->drain, 0)) break;
+    }
+  } else {
+    // lane = output channel q * 32 + lane, column = pixel slot; 32-slot chunks turn around in the staging buffer
+    const int q = warp & 3, ew = warp - 2, half = ew / 4;
+    const int co0 = q * 32;
+    const float bias = p.bias ? __ldg(p.bias + co0 + lane) : 0.0f;
+    uint8_t* stg = stage_base + ew * kStageWarpBytes;
+    const int my_slot = lane >> 2, my_piece = lane & 3;
+    uint32_t t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+      const uint32_t buf = t & 1, use = t >> 1;
+      ok = mbar_wait_abortable(&sm->abort, &sm->tmem_full[buf], use & 1, p.error, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int n = tile / p.tiles_h, h0 = (tile - n * p.tiles_h) * p.rows;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * 128;
+      __nv_bfloat16* img = p.out + ((size_t)n * p.H + h0) * p.W * 128 + co0 + my_piece * 8;
+      int i = (half * 128 + my_slot) / p.pitch, j = half * 128 + my_slot - i * p.pitch;
+      auto process = [&](const uint32_t (&r)[32]) {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+          *reinterpret_cast<__nv_bfloat16*>(stg + e * 64 + lane * 2) = __float2bfloat16(__uint_as_float(r[e]) + bias);
+        __syncwarp();
+#pragma unroll
+        for (int e0 = 0; e0 < 32; e0 += 8) {
+          const uint4 v = *reinterpret_cast<const uint4*>(stg + (e0 + my_slot) * 64 + my_piece * 16);
+          if (j < p.W && i < p.rows && h0 + i < p.H) *reinterpret_cast<uint4*>(img + ((size_t)i * p.W + j) * 128) = v;
+          j += 8;
+          while (j >= p.pitch) { j -= p.pitch; i++; }
+        }
+        __syncwarp();
+      };
+      // columns at and past nslots were not written by the MMA: their slots lie past the tile's rows and are skipped
+      uint32_t ra[32], rb[32];
+      tc_ld32(taddr, ra);
+      tc_wait_ld();
+      tc_ld32(taddr + 32, rb);
+      process(ra);
+      tc_wait_ld();
+      tc_ld32(taddr + 64, ra);
+      process(rb);
+      tc_wait_ld();
+      tc_ld32(taddr + 96, rb);
+      process(ra);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sm->tmem_empty[buf]);
+      process(rb);
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Weight gradient of the same layers (64 -> 64 channels, 3x3, stride 1, padding 1) from halo tiles.
 //   dW[co][(r, s), ci] = sum over pixels of dY[pixel][co] * X[pixel + (r - 1, s - 1)][ci]
 // A tile is four image rows in slots of pitch 64: one copy brings six rows of dY (rows h0-1 .. h0+4, columns
@@ -887,6 +1069,7 @@ static int device_sms() {
     cudaFuncSetAttribute(conv_igemm_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
     cudaFuncSetAttribute(conv_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
     cudaFuncSetAttribute(conv_wgrad_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
+    cudaFuncSetAttribute(conv_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
   });
   return sms;
 }
@@ -1040,6 +1223,54 @@ int gcow_conv_fwd_ws(const void* x, const void* w, void* y, const float* bias, i
   const int grid = (int)(tiles < sms ? tiles : sms);
   const size_t smem = 1024 + WS_W_BYTES + (size_t)st * p.stage_bytes + sizeof(WsSmem) + tail;
   gcow::launch_dependent(conv_ws_kernel, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, mx, mw, p);
+  return (int)cudaGetLastError();
+}
+
+// Tile geometry of the halo-tile forward for Ci -> 128 channels; false when it does not apply or does not fit.
+static bool halo_plan(int N, int H, int W, int Ci, HaloParams* p) {
+  if (N <= 0 || H <= 0 || W < 6 || W + 2 > 128 || Ci < 64 || Ci % 64) return false;
+  p->N = N; p->H = H; p->W = W; p->Ci = Ci;
+  p->pitch = W + 2;
+  // image rows per tile: the fewest MMA columns over the whole image
+  long best = -1;
+  for (int rows = 1; rows * p->pitch <= 256 && rows <= H; rows++) {
+    const int ns = (rows * p->pitch + 15) & ~15;
+    const long cost = (long)((H + rows - 1) / rows) * ns;
+    if (best < 0 || cost <= best) { best = cost; p->rows = rows; p->nslots = ns; }
+  }
+  if (best < 0) return false;
+  p->tiles_h = (H + p->rows - 1) / p->rows;
+  p->chunk_bytes = ((p->nslots + 2 * p->pitch + 2) * 128 + 1023) & ~1023;
+  p->a_stages = 2;
+  const int fixed = 1024 + (int)sizeof(HaloSmem) + 16 + EPI_WARPS * kStageWarpBytes;
+  const int left = kWsSmemMax - fixed - p->a_stages * (Ci / 64) * p->chunk_bytes;
+  p->b_stages = left / HALO_B_BYTES;
+  if (p->b_stages > 8) p->b_stages = 8;
+  return p->b_stages >= 3;
+}
+
+int gcow_conv_halo_usable(int N, int H, int W, int Ci) {
+  HaloParams p{};
+  return halo_plan(N, H, W, Ci, &p) ? 1 : 0;
+}
+
+// y[N,H,W,128] = conv3x3(x[N,H,W,Ci], w[128,3,3,Ci]) (+ bias), stride 1, padding 1, on the halo-tile kernel.
+int gcow_conv_fwd_halo(const void* x, const void* w, void* y, const float* bias, int N, int H, int W, int Ci, uint32_t* error,
+                       void* stream) {
+  HaloParams p{};
+  if (!halo_plan(N, H, W, Ci, &p) || ((uintptr_t)y & 15)) return -1;
+  const int sms = device_sms();
+  p.out = (__nv_bfloat16*)y; p.bias = bias; p.error = error;
+  CUtensorMap mx, mw;
+  int rc = make_map_nhwc(&mx, x, (uint64_t)N, (uint64_t)H, (uint64_t)W, (uint64_t)Ci, (uint32_t)p.pitch, (uint32_t)(p.rows + 2), 1, 0);
+  if (rc) return rc;
+  rc = make_map_2d(&mw, w, 128, (uint64_t)WS_TAPS * Ci, 128);
+  if (rc) return rc;
+  const long long tiles = (long long)N * p.tiles_h;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  const size_t smem = 1024 + (size_t)p.a_stages * (Ci / 64) * p.chunk_bytes + (size_t)p.b_stages * HALO_B_BYTES +
+                      sizeof(HaloSmem) + 16 + EPI_WARPS * kStageWarpBytes;
+  gcow::launch_dependent(conv_halo_kernel, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, mx, mw, p);
   return (int)cudaGetLastError();
 }
 

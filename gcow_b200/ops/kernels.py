@@ -989,10 +989,20 @@ def conv_ws_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
             and bool(_native.cuda().gcow_conv_ws_usable(N, H, W)))
 
 
+def conv_halo_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
+    """Ci -> 128 channels, 3x3, stride 1, padding 1, tiles that fit the shared memory: the halo-tile kernel applies."""
+    return (Co == 128 and KH == 3 and KW == 3 and pad_h == 1 and pad_w == 1
+            and os.environ.get("GCOW_CONV_HALO", "1") != "0" and _have("gcow_conv_fwd_halo")
+            and bool(_native.cuda().gcow_conv_halo_usable(N, H, W, C)))
+
+
 def _conv_fwd_s1(lib, x_ptr, w_ptr, y_ptr, bias_ptr, N, H, W, C, Co, KH, KW, pad_h, pad_w, err, st, what):
-    """Stride-1 forward kernel for these extents: the weight-stationary one where it applies, else the general one."""
+    """Stride-1 forward kernel for these extents: the weight-stationary or halo-tile one where it applies, else the
+    general one."""
     if conv_ws_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
         _chk(lib.gcow_conv_fwd_ws(x_ptr, w_ptr, y_ptr, bias_ptr, N, H, W, err, st), what + " (ws)")
+    elif conv_halo_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
+        _chk(lib.gcow_conv_fwd_halo(x_ptr, w_ptr, y_ptr, bias_ptr, N, H, W, C, err, st), what + " (halo)")
     else:
         _chk(lib.gcow_conv_fwd(x_ptr, w_ptr, y_ptr, bias_ptr, N, H, W, C, Co, KH, KW, pad_h, pad_w, err, st), what)
 

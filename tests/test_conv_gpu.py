@@ -107,10 +107,29 @@ def test_operand_swapped_forward_agrees_with_the_plain_one(monkeypatch):
     assert plan[0] == 2 and plan[1] == 128                        # the tile shape that swaps
     torch.manual_seed(6)
     x, w, b = _mk(N, C, H, W, Co, 3, 3)
+    monkeypatch.setenv("GCOW_CONV_HALO", "0")                     # this shape would otherwise take the halo-tile kernel
     outs = []
     for noswap in ("", "1"):
         if noswap:
             monkeypatch.setenv("GCOW_CONV_NOSWAP", noswap)
+        y = K.conv_igemm(x, w, b, (1, 1))
+        K.check_errors()
+        outs.append(y.float())
+    assert _rel(outs[0], outs[1]) < 1e-2
+
+
+@pytest.mark.parametrize("shape", [(40, 128, 28, 28), (3, 64, 30, 20), (2, 128, 9, 11), (1, 192, 5, 6)])
+def test_halo_tile_forward_agrees_with_the_general_kernel(shape, monkeypatch):
+    from gcow_b200.ops import kernels as K
+    N, C, H, W = shape
+    assert K.conv_halo_usable(N, H, W, C, 128, 3, 3, 1, 1)
+    # other output widths, and tiles too large for two pixel stages, stay on the general kernel
+    assert not K.conv_halo_usable(N, H, W, C, 256, 3, 3, 1, 1) and not K.conv_halo_usable(2, 28, 28, 512, 128, 3, 3, 1, 1)
+    torch.manual_seed(7)
+    x, w, b = _mk(N, C, H, W, 128, 3, 3)
+    outs = []
+    for halo in ("1", "0"):
+        monkeypatch.setenv("GCOW_CONV_HALO", halo)
         y = K.conv_igemm(x, w, b, (1, 1))
         K.check_errors()
         outs.append(y.float())
