@@ -55,3 +55,26 @@ def test_forward_tile_choice_on_resnet_layers():
         halves, cols, bw, bh, bn, stages = list(out)
         assert (halves, cols) == want[ch], (ch, list(out))
         assert bw * bh * bn <= 128 * halves and 2 <= stages <= 8
+
+
+def test_special_3x3_kernels_take_the_shapes_they_fit():
+    """The weight-stationary, halo-tile weight-gradient and halo-tile forward kernels state on the host which extents
+    they take: rows that fit their slot pitch, tiles that fit the shared memory."""
+    lib = _lib()
+    if not hasattr(lib, "gcow_conv_halo_usable"):
+        pytest.skip("library built without the halo-tile kernels")
+    # weight-stationary forward (64 -> 64): any image whose rows plus halo fit 128 slots, at least 6 pixels wide
+    assert lib.gcow_conv_ws_usable(256, 56, 56) and lib.gcow_conv_ws_usable(1, 1, 6) and lib.gcow_conv_ws_usable(2, 9, 126)
+    assert not lib.gcow_conv_ws_usable(2, 9, 127) and not lib.gcow_conv_ws_usable(2, 9, 5) and not lib.gcow_conv_ws_usable(0, 9, 9)
+    # halo-tile weight gradient: slot pitch 64, one partial result per CTA, never more CTAs than SMs, none empty
+    assert lib.gcow_conv_wgrad_ws_split(2, 9, 63) == 0 and lib.gcow_conv_wgrad_ws_split(0, 9, 9) == 0
+    for (N, H, W) in ((256, 56, 56), (3, 30, 20), (1, 7, 9), (1, 1, 1), (1000, 5, 62)):
+        split = lib.gcow_conv_wgrad_ws_split(N, H, W)
+        tiles = N * -(-H // 4)
+        per = -(-tiles // split)
+        assert 1 <= split <= max(1, min(tiles, 148)) and (split - 1) * per < tiles <= split * per, (N, H, W, split)
+    # halo-tile forward (Ci -> 128): two pixel stages of all 64-channel chunks plus three filter stages must fit
+    assert lib.gcow_conv_halo_usable(256, 28, 28, 128) and lib.gcow_conv_halo_usable(256, 28, 28, 64)
+    assert lib.gcow_conv_halo_usable(1, 5, 6, 192)
+    assert not lib.gcow_conv_halo_usable(256, 28, 28, 512) and not lib.gcow_conv_halo_usable(256, 14, 14, 256)
+    assert not lib.gcow_conv_halo_usable(256, 28, 28, 96) and not lib.gcow_conv_halo_usable(4, 8, 127, 64)
