@@ -950,6 +950,145 @@ conv_wgrad_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Halo-tile weight gradient for 128 -> 128 channels, 3x3, stride 1, padding 1. The scheme of conv_wgrad_ws_kernel
+// with real channels in both halves of M: per tile of R image rows in slots of pitch P (32 or 64) one box of dY per
+// 64 output channels (rows h0 .. h0+R-1, columns 0..P-1) and one box of X per 64 input channels (rows h0-1 .. h0+R,
+// columns -1..P-2); X slot = dY slot + r * P + s. A: dY, M = 128 = the two channel boxes (leading offset = one
+// box); B: X of one channel chunk, N = 192 = the three taps of filter row r (leading offset one slot). The
+// accumulators of one filter row are 2 x 192 columns, so a CTA serves ONE filter row (blockIdx.y) over its range
+// of tiles; the three rows re-read the tiles, which are cheap (each tensor crosses L2 three times instead of nine).
+struct WgHaloParams {
+  float* part;          // [gridDim.x][128][9 * 128]
+  int N, H, W;
+  int P, R;             // slot pitch, image rows per tile
+  int tiles_h, num_tiles, per;
+  int x_chunk_bytes, dy_chunk_bytes;
+  uint32_t* error;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_dy,
+                       const WgHaloParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stage_bytes = 2 * p.x_chunk_bytes + 2 * p.dy_chunk_bytes;
+  WsSmem* sm = reinterpret_cast<WsSmem*>(base + WG_STAGES * stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int first = blockIdx.x * p.per;
+  int last = first + p.per;
+  if (last > p.num_tiles) last = p.num_tiles;
+  const int frow = blockIdx.y;                    // filter row of this CTA
+  const int x_box = p.P * (p.R + 2) * 128;        // bytes of one X box; the bytes behind it up to x_chunk_bytes are zero
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WG_STAGES; s++) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
+    mbar_init(&sm->tmem_full[0], 1);
+    mbar_init(&sm->drain, 1);
+    sm->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // the last taps read a few slots behind each X box against zero dY: those bytes must hold finite numbers
+  {
+    const int pad16 = (p.x_chunk_bytes - x_box) / 16;
+    for (int i = threadIdx.x; i < WG_STAGES * 2 * pad16; i += blockDim.x) {
+      const int region = i / pad16, j = i - region * pad16;
+      *reinterpret_cast<uint4*>(base + (region / 2) * stage_bytes + (region % 2) * p.x_chunk_bytes + x_box + j * 16) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t tx = 2u * (uint32_t)x_box + 2u * (uint32_t)(p.P * p.R * 128);
+      uint32_t s = 0, phase = 0;
+      bool ok = true;
+      for (int tile = first; tile < last && ok; tile++) {
+        const int n = tile / p.tiles_h, h0 = (tile - n * p.tiles_h) * p.R;
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->empty[s], phase ^ 1, p.error, 1))) break;
+        mbar_expect_tx(&sm->full[s], tx);
+        uint8_t* st = base + s * stage_bytes;
+        const uint32_t bar = smem_u32(&sm->full[s]);
+        for (int c = 0; c < 2; c++) {
+          tma_load_4d(smem_u32(st + c * p.x_chunk_bytes), &map_x, bar, c * 64, -1, h0 - 1, n);
+          tma_load_4d(smem_u32(st + 2 * p.x_chunk_bytes + c * p.dy_chunk_bytes), &map_dy, bar, c * 64, 0, h0, n);
+        }
+        if (++s == WG_STAGES) { s = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((192u >> 3) << 17) | ((128u >> 4) << 24);
+      const int ksteps = p.P * p.R / 16;
+      uint32_t s = 0, phase = 0, acc = 0;
+      bool ok = true;
+      for (int tile = first; tile < last && ok; tile++) {
+        if (!(ok = mbar_wait_abortable(&sm->abort, &sm->full[s], phase, p.error, 3))) break;
+        tc_fence_after();
+        const uint32_t xs = smem_u32(base + s * stage_bytes), ds = xs + 2 * p.x_chunk_bytes;
+#pragma unroll 1
+        for (int k = 0; k < ksteps; k++) {
+          const uint32_t off = (uint32_t)k * 16u * 128u;
+          const uint64_t da = smem_desc_mn_lbo(ds + off, (uint32_t)p.dy_chunk_bytes);
+          const uint32_t xo = off + (uint32_t)(frow * p.P) * 128u;
+          tc_mma(tmem_base, da, smem_desc_mn_lbo(xs + xo, 128u), idesc, acc);
+          tc_mma(tmem_base + 192, da, smem_desc_mn_lbo(xs + p.x_chunk_bytes + xo, 128u), idesc, acc);
+          acc = 1;
+        }
+        tc_commit(&sm->empty[s]);
+        if (++s == WG_STAGES) { s = 0; phase ^= 1; }
+      }
+      if (ok) tc_commit(&sm->tmem_full[0]);
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < kSpinLimit; it++) if (mbar_try_wait(&sm->drain, 0)) break;
+    }
+  } else {
+    const int q = warp & 3, ew = warp - 2, half = ew / 4;     // half = input-channel chunk: columns half * 192 ..
+    bool ok = mbar_wait_abortable(&sm->abort, &sm->tmem_full[0], 0, p.error, 4);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const int co = q * 32 + lane;
+      // column c * 32 + j of this half is tap s = (c * 32 + j) / 64, input channel half * 64 + (c * 32 + j) % 64
+      float* dst = p.part + ((size_t)blockIdx.x * 128 + co) * 1152 + (size_t)frow * 384 + half * 64;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + half * 192;
+#pragma unroll 1
+      for (int c = 0; c < 6; c++) {
+        uint32_t v[32];
+        tc_ld32(taddr + c * 32, v);
+        tc_wait_ld();
+        float* o = dst + (c >> 1) * 128 + (c & 1) * 32;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // wt[ci][kh-1-r][kw-1-s][co] = w[co][r][s][ci]: the filter of the data-gradient convolution
 __global__ void flip_weights_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int kh,
                                     int kw, int Ci) {
@@ -1070,6 +1209,7 @@ static int device_sms() {
     cudaFuncSetAttribute(conv_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
     cudaFuncSetAttribute(conv_wgrad_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
     cudaFuncSetAttribute(conv_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
+    cudaFuncSetAttribute(conv_wgrad_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemMax);
   });
   return sms;
 }
@@ -1302,6 +1442,47 @@ int gcow_conv_wgrad_ws(const void* dy, const void* x, float* part, int N, int H,
   if (rc) return rc;
   const size_t smem = 1024 + (size_t)WG_STAGES * WG_STAGE_BYTES + sizeof(WsSmem) + 64;
   gcow::launch_dependent(conv_wgrad_ws_kernel, dim3(split), dim3(THREADS), smem, (cudaStream_t)stream, mx, md, p);
+  return (int)cudaGetLastError();
+}
+
+// Geometry of the 128 -> 128 channel halo-tile weight gradient; split = 0: not usable.
+static int wgrad_halo_plan(int N, int H, int W, WgHaloParams* p) {
+  if (N <= 0 || H <= 0 || W < 1 || W + 2 > 64) return 0;
+  p->N = N; p->H = H; p->W = W;
+  p->P = W + 2 <= 32 ? 32 : 64;
+  p->R = p->P == 32 ? 4 : 2;
+  p->tiles_h = (H + p->R - 1) / p->R;
+  const long long tiles = (long long)N * p->tiles_h;
+  if (tiles > (1ll << 30)) return 0;
+  p->num_tiles = (int)tiles;
+  int groups = device_sms() / 3;                  // three filter rows per group of tiles
+  if (groups < 1) groups = 1;
+  p->per = (int)((tiles + groups - 1) / groups);
+  p->x_chunk_bytes = (p->P * (p->R + 2) * 128 + 256 + 1023) & ~1023;
+  p->dy_chunk_bytes = p->P * p->R * 128;
+  return (int)((tiles + p->per - 1) / p->per);
+}
+
+int gcow_conv_wgrad_halo_split(int N, int H, int W) {
+  WgHaloParams p{};
+  return wgrad_halo_plan(N, H, W, &p);
+}
+
+// part[split][128][9 * 128] (fp32) = partial sums of dy[N,H,W,128]^T * shifted x[N,H,W,128], 3x3, padding 1;
+// split = gcow_conv_wgrad_halo_split(N, H, W); the caller adds the slices.
+int gcow_conv_wgrad_halo(const void* dy, const void* x, float* part, int N, int H, int W, uint32_t* error, void* stream) {
+  WgHaloParams p{};
+  const int split = wgrad_halo_plan(N, H, W, &p);
+  if (split <= 0 || ((uintptr_t)part & 15)) return -1;
+  p.part = part; p.error = error;
+  CUtensorMap mx, md;
+  int rc = make_map_nhwc(&mx, x, (uint64_t)N, (uint64_t)H, (uint64_t)W, 128, (uint32_t)p.P, (uint32_t)(p.R + 2), 1, 0);
+  if (rc) return rc;
+  rc = make_map_nhwc(&md, dy, (uint64_t)N, (uint64_t)H, (uint64_t)W, 128, (uint32_t)p.P, (uint32_t)p.R, 1, 0);
+  if (rc) return rc;
+  const size_t smem = 1024 + (size_t)WG_STAGES * (2 * p.x_chunk_bytes + 2 * p.dy_chunk_bytes) + sizeof(WsSmem) + 64;
+  if (smem > (size_t)kWsSmemMax) return -1;
+  gcow::launch_dependent(conv_wgrad_halo_kernel, dim3(split, 3), dim3(THREADS), smem, (cudaStream_t)stream, mx, md, p);
   return (int)cudaGetLastError();
 }
 

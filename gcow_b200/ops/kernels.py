@@ -1054,13 +1054,21 @@ class _ConvIgemmFn(torch.autograd.Function):
             # 64 -> 64 channels, 3x3, padding 1: the halo-tile kernel, when the image rows fit its slot pitch
             ws_split = (lib.gcow_conv_wgrad_ws_split(N, H, W) if conv_ws_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w)
                         and os.environ.get("GCOW_CONV_WS_WGRAD", "1") != "0" and _have("gcow_conv_wgrad_ws") else 0)
-            split = ws_split if ws_split > 0 else lib.gcow_conv_wgrad_split(N, H, W, C, Co, KH, KW, pad_h, pad_w)
+            # 128 -> 128 channels, 3x3, padding 1: the halo-tile kernel with one CTA group per filter row
+            halo_split = (lib.gcow_conv_wgrad_halo_split(N, H, W) if C == 128 and Co == 128 and KH == 3 and KW == 3
+                          and pad_h == 1 and pad_w == 1 and os.environ.get("GCOW_CONV_HALO_WGRAD", "1") != "0"
+                          and _have("gcow_conv_wgrad_halo") else 0)
+            split = (ws_split if ws_split > 0 else halo_split if halo_split > 0 else
+                     lib.gcow_conv_wgrad_split(N, H, W, C, Co, KH, KW, pad_h, pad_w))
             flat, alias = _grad_target(ctx.grad_view, Co, KH * KW * C)
             # the partial sums are scratch when an ordered sum follows; a single part IS the result
             part = (_ws("conv_wgrad_part", (split, Co, KH * KW * C), torch.float32, dev) if split > 1 else
                     (flat.unsqueeze(0) if flat is not None else torch.empty((1, Co, KH * KW * C), dtype=torch.float32, device=dev)))
             if ws_split > 0:
                 _chk(lib.gcow_conv_wgrad_ws(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, err, st), "gcow_conv_wgrad_ws")
+            elif halo_split > 0:
+                _chk(lib.gcow_conv_wgrad_halo(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, err, st),
+                     "gcow_conv_wgrad_halo")
             else:
                 _chk(lib.gcow_conv_wgrad(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, KH, KW, pad_h, pad_w,
                                          err, st), "gcow_conv_wgrad")

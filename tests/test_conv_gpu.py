@@ -136,6 +136,27 @@ def test_halo_tile_forward_agrees_with_the_general_kernel(shape, monkeypatch):
     assert _rel(outs[0], outs[1]) < 1e-2
 
 
+@pytest.mark.parametrize("shape", [(40, 28, 28), (3, 10, 20), (2, 9, 40), (1, 3, 62), (2, 5, 1)])
+def test_halo_tile_weight_gradient_of_128_channel_layers(shape, monkeypatch):
+    from gcow_b200.ops import kernels as K
+    N, H, W = shape
+    assert K._native.cuda().gcow_conv_wgrad_halo_split(N, H, W) >= 1
+    assert K._native.cuda().gcow_conv_wgrad_halo_split(N, H, 63) == 0
+    torch.manual_seed(8)
+    x, w, _ = _mk(N, 128, H, W, 128, 3, 3)
+    gy = (torch.randn(N, 128, H, W, device="cuda") * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    wr = w.clone().requires_grad_(True)
+    F.conv2d(x.float(), wr, None, padding=1).backward(gy.float())
+    grads = []
+    for halo in ("1", "0"):
+        monkeypatch.setenv("GCOW_CONV_HALO_WGRAD", halo)
+        wo = w.clone().requires_grad_(True)
+        K.conv_igemm(x, wo, None, (1, 1)).backward(gy)
+        K.check_errors()
+        grads.append(wo.grad.float())
+    assert _rel(grads[0], wr.grad) < 5e-3 and _rel(grads[0], grads[1]) < 1e-4
+
+
 S2_CASES = [(4, 64, 16, 16, 64), (3, 64, 10, 14, 128), (2, 128, 28, 28, 128), (5, 256, 6, 8, 64), (2, 64, 2, 2, 64)]
 
 
