@@ -951,16 +951,17 @@ conv_wgrad_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Halo-tile weight gradient for 128 -> 128 channels, 3x3, stride 1, padding 1. The scheme of conv_wgrad_ws_kernel
-// with real channels in both halves of M: per tile of R image rows in slots of pitch P (32 or 64) one box of dY per
+// Halo-tile weight gradient for channel counts that are multiples of 128, 3x3, stride 1, padding 1. The scheme of
+// conv_wgrad_ws_kernel with real channels in both halves of M: per tile of R image rows in slots of pitch P (16, 32 or 64) one box of dY per
 // 64 output channels (rows h0 .. h0+R-1, columns 0..P-1) and one box of X per 64 input channels (rows h0-1 .. h0+R,
 // columns -1..P-2); X slot = dY slot + r * P + s. A: dY, M = 128 = the two channel boxes (leading offset = one
 // box); B: X of one channel chunk, N = 192 = the three taps of filter row r (leading offset one slot). The
-// accumulators of one filter row are 2 x 192 columns, so a CTA serves ONE filter row (blockIdx.y) over its range
-// of tiles; the three rows re-read the tiles, which are cheap (each tensor crosses L2 three times instead of nine).
+// accumulators of one filter row and 128 x 128 channels are 2 x 192 columns, so a CTA serves ONE (filter row, 128 input
+// channels, 128 output channels) group (blockIdx.y) over its range of tiles; the groups re-read the tiles, which are
+// cheap (with 128 channels each tensor crosses L2 three times instead of nine).
 struct WgHaloParams {
-  float* part;          // [gridDim.x][128][9 * 128]
-  int N, H, W;
+  float* part;          // [gridDim.x][Co][9 * Ci]
+  int N, H, W, Ci, Co;
   int P, R;             // slot pitch, image rows per tile
   int tiles_h, num_tiles, per;
   int x_chunk_bytes, dy_chunk_bytes;
@@ -978,7 +979,8 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   const int first = blockIdx.x * p.per;
   int last = first + p.per;
   if (last > p.num_tiles) last = p.num_tiles;
-  const int frow = blockIdx.y;                    // filter row of this CTA
+  const int frow = blockIdx.y % 3;                // filter row of this CTA,
+  const int cig = (blockIdx.y / 3) % (p.Ci / 128), cog = blockIdx.y / 3 / (p.Ci / 128);   // its 128 input and output channels
   const int x_box = p.P * (p.R + 2) * 128;        // bytes of one X box; the bytes behind it up to x_chunk_bytes are zero
 
   if (threadIdx.x == 0) {
@@ -1020,8 +1022,8 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         uint8_t* st = base + s * stage_bytes;
         const uint32_t bar = smem_u32(&sm->full[s]);
         for (int c = 0; c < 2; c++) {
-          tma_load_4d(smem_u32(st + c * p.x_chunk_bytes), &map_x, bar, c * 64, -1, h0 - 1, n);
-          tma_load_4d(smem_u32(st + 2 * p.x_chunk_bytes + c * p.dy_chunk_bytes), &map_dy, bar, c * 64, 0, h0, n);
+          tma_load_4d(smem_u32(st + c * p.x_chunk_bytes), &map_x, bar, cig * 128 + c * 64, -1, h0 - 1, n);
+          tma_load_4d(smem_u32(st + 2 * p.x_chunk_bytes + c * p.dy_chunk_bytes), &map_dy, bar, cog * 128 + c * 64, 0, h0, n);
         }
         if (++s == WG_STAGES) { s = 0; phase ^= 1; }
       }
@@ -1062,15 +1064,15 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     if (ok) {
       tc_fence_after();
       const int co = q * 32 + lane;
-      // column c * 32 + j of this half is tap s = (c * 32 + j) / 64, input channel half * 64 + (c * 32 + j) % 64
-      float* dst = p.part + ((size_t)blockIdx.x * 128 + co) * 1152 + (size_t)frow * 384 + half * 64;
+      // column c * 32 + j of this half is tap s = (c * 32 + j) / 64, input channel cig * 128 + half * 64 + (c * 32 + j) % 64
+      float* dst = p.part + ((size_t)blockIdx.x * p.Co + cog * 128 + co) * (size_t)(9 * p.Ci) + (size_t)frow * 3 * p.Ci + cig * 128 + half * 64;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + half * 192;
 #pragma unroll 1
       for (int c = 0; c < 6; c++) {
         uint32_t v[32];
         tc_ld32(taddr + c * 32, v);
         tc_wait_ld();
-        float* o = dst + (c >> 1) * 128 + (c & 1) * 32;
+        float* o = dst + (c >> 1) * p.Ci + (c & 1) * 32;
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
@@ -1445,17 +1447,19 @@ int gcow_conv_wgrad_ws(const void* dy, const void* x, float* part, int N, int H,
   return (int)cudaGetLastError();
 }
 
-// Geometry of the 128 -> 128 channel halo-tile weight gradient; split = 0: not usable.
-static int wgrad_halo_plan(int N, int H, int W, WgHaloParams* p) {
-  if (N <= 0 || H <= 0 || W < 1 || W + 2 > 64) return 0;
-  p->N = N; p->H = H; p->W = W;
-  p->P = W + 2 <= 32 ? 32 : 64;
-  p->R = p->P == 32 ? 4 : 2;
+// Geometry of the halo-tile weight gradient for channel counts that are multiples of 128; split = 0: not usable.
+static int wgrad_halo_plan(int N, int H, int W, int Ci, int Co, WgHaloParams* p) {
+  if (N <= 0 || H <= 0 || W < 1 || W + 2 > 64 || Ci < 128 || Ci % 128 || Co < 128 || Co % 128) return 0;
+  p->N = N; p->H = H; p->W = W; p->Ci = Ci; p->Co = Co;
+  p->P = W + 2 <= 16 ? 16 : (W + 2 <= 32 ? 32 : 64);
+  p->R = p->P == 16 ? 7 : (p->P == 32 ? 4 : 2);   // two stages of two X and two dY boxes fit the shared memory
   p->tiles_h = (H + p->R - 1) / p->R;
   const long long tiles = (long long)N * p->tiles_h;
   if (tiles > (1ll << 30)) return 0;
   p->num_tiles = (int)tiles;
-  int groups = device_sms() / 3;                  // three filter rows per group of tiles
+  const int per_tile = 3 * (Ci / 128) * (Co / 128);   // CTAs per range of tiles: filter rows x channel blocks
+  if (per_tile > 65535) return 0;
+  int groups = device_sms() / per_tile;
   if (groups < 1) groups = 1;
   p->per = (int)((tiles + groups - 1) / groups);
   p->x_chunk_bytes = (p->P * (p->R + 2) * 128 + 256 + 1023) & ~1023;
@@ -1463,26 +1467,27 @@ static int wgrad_halo_plan(int N, int H, int W, WgHaloParams* p) {
   return (int)((tiles + p->per - 1) / p->per);
 }
 
-int gcow_conv_wgrad_halo_split(int N, int H, int W) {
+int gcow_conv_wgrad_halo_split(int N, int H, int W, int Ci, int Co) {
   WgHaloParams p{};
-  return wgrad_halo_plan(N, H, W, &p);
+  return wgrad_halo_plan(N, H, W, Ci, Co, &p);
 }
 
-// part[split][128][9 * 128] (fp32) = partial sums of dy[N,H,W,128]^T * shifted x[N,H,W,128], 3x3, padding 1;
-// split = gcow_conv_wgrad_halo_split(N, H, W); the caller adds the slices.
-int gcow_conv_wgrad_halo(const void* dy, const void* x, float* part, int N, int H, int W, uint32_t* error, void* stream) {
+// part[split][Co][9 * Ci] (fp32) = partial sums of dy[N,H,W,Co]^T * shifted x[N,H,W,Ci], 3x3, padding 1;
+// split = gcow_conv_wgrad_halo_split(N, H, W, Ci, Co); the caller adds the slices.
+int gcow_conv_wgrad_halo(const void* dy, const void* x, float* part, int N, int H, int W, int Ci, int Co, uint32_t* error,
+                         void* stream) {
   WgHaloParams p{};
-  const int split = wgrad_halo_plan(N, H, W, &p);
+  const int split = wgrad_halo_plan(N, H, W, Ci, Co, &p);
   if (split <= 0 || ((uintptr_t)part & 15)) return -1;
   p.part = part; p.error = error;
   CUtensorMap mx, md;
-  int rc = make_map_nhwc(&mx, x, (uint64_t)N, (uint64_t)H, (uint64_t)W, 128, (uint32_t)p.P, (uint32_t)(p.R + 2), 1, 0);
+  int rc = make_map_nhwc(&mx, x, (uint64_t)N, (uint64_t)H, (uint64_t)W, (uint64_t)Ci, (uint32_t)p.P, (uint32_t)(p.R + 2), 1, 0);
   if (rc) return rc;
-  rc = make_map_nhwc(&md, dy, (uint64_t)N, (uint64_t)H, (uint64_t)W, 128, (uint32_t)p.P, (uint32_t)p.R, 1, 0);
+  rc = make_map_nhwc(&md, dy, (uint64_t)N, (uint64_t)H, (uint64_t)W, (uint64_t)Co, (uint32_t)p.P, (uint32_t)p.R, 1, 0);
   if (rc) return rc;
   const size_t smem = 1024 + (size_t)WG_STAGES * (2 * p.x_chunk_bytes + 2 * p.dy_chunk_bytes) + sizeof(WsSmem) + 64;
   if (smem > (size_t)kWsSmemMax) return -1;
-  gcow::launch_dependent(conv_wgrad_halo_kernel, dim3(split, 3), dim3(THREADS), smem, (cudaStream_t)stream, mx, md, p);
+  gcow::launch_dependent(conv_wgrad_halo_kernel, dim3(split, 3 * (Ci / 128) * (Co / 128)), dim3(THREADS), smem, (cudaStream_t)stream, mx, md, p);
   return (int)cudaGetLastError();
 }
 

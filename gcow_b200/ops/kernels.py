@@ -989,6 +989,9 @@ def conv_ws_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
             and bool(_native.cuda().gcow_conv_ws_usable(N, H, W)))
 
 
+_HALO_WGRAD_MIN_W = int(os.environ.get("GCOW_CONV_HALO_WGRAD_MIN_W", "15"))
+
+
 def conv_halo_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
     """Ci -> 128 channels, 3x3, stride 1, padding 1, tiles that fit the shared memory: the halo-tile kernel applies."""
     return (Co == 128 and KH == 3 and KW == 3 and pad_h == 1 and pad_w == 1
@@ -1054,10 +1057,13 @@ class _ConvIgemmFn(torch.autograd.Function):
             # 64 -> 64 channels, 3x3, padding 1: the halo-tile kernel, when the image rows fit its slot pitch
             ws_split = (lib.gcow_conv_wgrad_ws_split(N, H, W) if conv_ws_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w)
                         and os.environ.get("GCOW_CONV_WS_WGRAD", "1") != "0" and _have("gcow_conv_wgrad_ws") else 0)
-            # 128 -> 128 channels, 3x3, padding 1: the halo-tile kernel with one CTA group per filter row
-            halo_split = (lib.gcow_conv_wgrad_halo_split(N, H, W) if C == 128 and Co == 128 and KH == 3 and KW == 3
-                          and pad_h == 1 and pad_w == 1 and os.environ.get("GCOW_CONV_HALO_WGRAD", "1") != "0"
-                          and _have("gcow_conv_wgrad_halo") else 0)
+            # channel counts that are multiples of 128, 3x3, padding 1, rows of at least 15 pixels: the halo-tile kernel
+            # with one CTA group per (filter row, 128 x 128 channels). Measured at batch 256: 128 channels at 28 x 28 wins
+            # (layer 0.221 -> 0.189 ms), 256 channels at 14 x 14 ties with the general kernel, 512 channels at 7 x 7
+            # loses (slots of pitch 16 for rows of 7, 48 groups re-reading the tiles)
+            halo_split = (lib.gcow_conv_wgrad_halo_split(N, H, W, C, Co) if C % 128 == 0 and Co % 128 == 0 and KH == 3
+                          and KW == 3 and pad_h == 1 and pad_w == 1 and W >= _HALO_WGRAD_MIN_W
+                          and os.environ.get("GCOW_CONV_HALO_WGRAD", "1") != "0" and _have("gcow_conv_wgrad_halo") else 0)
             split = (ws_split if ws_split > 0 else halo_split if halo_split > 0 else
                      lib.gcow_conv_wgrad_split(N, H, W, C, Co, KH, KW, pad_h, pad_w))
             flat, alias = _grad_target(ctx.grad_view, Co, KH * KW * C)
@@ -1067,7 +1073,7 @@ class _ConvIgemmFn(torch.autograd.Function):
             if ws_split > 0:
                 _chk(lib.gcow_conv_wgrad_ws(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, err, st), "gcow_conv_wgrad_ws")
             elif halo_split > 0:
-                _chk(lib.gcow_conv_wgrad_halo(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, err, st),
+                _chk(lib.gcow_conv_wgrad_halo(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, err, st),
                      "gcow_conv_wgrad_halo")
             else:
                 _chk(lib.gcow_conv_wgrad(gy.data_ptr(), x.data_ptr(), part.data_ptr(), N, H, W, C, Co, KH, KW, pad_h, pad_w,

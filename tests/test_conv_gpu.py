@@ -136,15 +136,18 @@ def test_halo_tile_forward_agrees_with_the_general_kernel(shape, monkeypatch):
     assert _rel(outs[0], outs[1]) < 1e-2
 
 
-@pytest.mark.parametrize("shape", [(40, 28, 28), (3, 10, 20), (2, 9, 40), (1, 3, 62), (2, 5, 1)])
+@pytest.mark.parametrize("shape", [(40, 28, 28, 128, 128), (3, 10, 20, 128, 128), (2, 9, 40, 128, 128), (1, 3, 62, 128, 128),
+                                   (2, 5, 1, 128, 128), (9, 14, 14, 256, 256), (3, 13, 11, 128, 384), (2, 7, 12, 256, 128)])
 def test_halo_tile_weight_gradient_of_128_channel_layers(shape, monkeypatch):
     from gcow_b200.ops import kernels as K
-    N, H, W = shape
-    assert K._native.cuda().gcow_conv_wgrad_halo_split(N, H, W) >= 1
-    assert K._native.cuda().gcow_conv_wgrad_halo_split(N, H, 63) == 0
+    N, H, W, Ci, Co = shape
+    monkeypatch.setattr(K, "_HALO_WGRAD_MIN_W", 1)
+    assert K._native.cuda().gcow_conv_wgrad_halo_split(N, H, W, Ci, Co) >= 1
+    assert K._native.cuda().gcow_conv_wgrad_halo_split(N, H, 63, Ci, Co) == 0
+    assert K._native.cuda().gcow_conv_wgrad_halo_split(N, H, W, 64, Co) == 0
     torch.manual_seed(8)
-    x, w, _ = _mk(N, 128, H, W, 128, 3, 3)
-    gy = (torch.randn(N, 128, H, W, device="cuda") * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    x, w, _ = _mk(N, Ci, H, W, Co, 3, 3)
+    gy = (torch.randn(N, Co, H, W, device="cuda") * 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
     wr = w.clone().requires_grad_(True)
     F.conv2d(x.float(), wr, None, padding=1).backward(gy.float())
     grads = []
