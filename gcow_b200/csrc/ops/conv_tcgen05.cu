@@ -453,6 +453,7 @@ struct WsParams {
   int N, H, W;
   int pitch;            // W + 2: pixel slots per image row
   int rows;             // image rows per tile
+  int nslots;           // N of the MMA: rows * pitch rounded up to 16 (an MMA's time grows with its N)
   int tiles_h;
   int stages, stage_bytes;
   uint32_t* error;
@@ -518,7 +519,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((64u >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.nslots >> 3) << 17) | ((64u >> 4) << 24);
       bool ok = mbar_wait_abortable(&sm->abort, &sm->wfull, 0, p.error, 5);
       tc_fence_after();
       const uint32_t wsm = smem_u32(base);
@@ -1344,6 +1345,7 @@ int gcow_conv_fwd_ws(const void* x, const void* w, void* y, const float* bias, i
   p.pitch = W + 2;
   p.rows = 256 / p.pitch;
   if (p.rows > H) p.rows = H;
+  p.nslots = (p.rows * p.pitch + 15) & ~15;
   p.tiles_h = (H + p.rows - 1) / p.rows;
   // a stage holds the copied box; the taps of the last pixel slots read up to 2 * pitch + 2 rows further, into the
   // next stage or the epilogue's staging buffers: sums of slots that are never stored
