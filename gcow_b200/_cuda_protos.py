@@ -178,6 +178,7 @@ def _declare_conv(lib, proto):
     opt("gcow_conv_fwd_halo", i32, ptr, ptr, ptr, ptr, i32, i32, i32, i32, ptr, ptr)
     opt("gcow_conv_wgrad_halo_split", i32, i32, i32, i32, i32, i32)
     opt("gcow_conv_wgrad_halo", i32, ptr, ptr, ptr, i32, i32, i32, i32, i32, ptr, ptr)
+    opt("gcow_conv_set_swap", None, i32)
     opt("gcow_conv_fwd_plan", None, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, ptr)
     opt("gcow_embed3_fwd", i32, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, i32, ptr)
     opt("gcow_embed_type_parts", i32, i32)

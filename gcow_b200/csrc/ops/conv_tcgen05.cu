@@ -1273,6 +1273,11 @@ using namespace gcow::conv;
 
 extern "C" {
 
+// Whether forward tiles of 256 pixels x 128 channels take the operand-swapped MMA (default) or the plain one; the two
+// agree up to the order of the fp32 sums, which is what the tests use this for.
+static int g_swap_enabled = 1;
+void gcow_conv_set_swap(int on) { g_swap_enabled = on ? 1 : 0; }
+
 // The forward kernel in full generality: input window step `stride` (1 or 2), an output grid of Ho x Wo tile pixels
 // whose pixel (h, w) is stored at (h * out_step + out_off_h, w * out_step + out_off_w) of y [N, out_H, out_W, Co].
 static int conv_fwd_launch(const void* x, const void* w, void* y, const float* bias, int N, int Hin, int Win, int Ci, int Co,
@@ -1295,7 +1300,7 @@ static int conv_fwd_launch(const void* x, const void* w, void* y, const float* b
   p.split = 1; p.chunks_per_split = 0; p.b_chunks = 1;
   p.flags = bias ? kBias : 0;
   p.stride = stride;
-  p.swap = (halves == 2 && p.bn_cols == 128 && Co % 8 == 0 && !getenv("GCOW_CONV_NOSWAP")) ? 1 : 0;
+  p.swap = (halves == 2 && p.bn_cols == 128 && Co % 8 == 0 && g_swap_enabled) ? 1 : 0;
   p.out_step = out_step; p.out_off_h = out_off_h; p.out_off_w = out_off_w; p.out_H = out_H; p.out_W = out_W;
   p.error = error;
   CUtensorMap ma, mb;

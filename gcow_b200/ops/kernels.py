@@ -989,7 +989,7 @@ def conv_ws_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):
             and bool(_native.cuda().gcow_conv_ws_usable(N, H, W)))
 
 
-_HALO_WGRAD_MIN_W = int(os.environ.get("GCOW_CONV_HALO_WGRAD_MIN_W", "15"))
+_HALO_WGRAD_MIN_W = 15      # narrowest image rows the halo-tile weight gradient is routed for
 
 
 def conv_halo_usable(N, H, W, C, Co, KH, KW, pad_h, pad_w):

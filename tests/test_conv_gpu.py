@@ -109,12 +109,15 @@ def test_operand_swapped_forward_agrees_with_the_plain_one(monkeypatch):
     x, w, b = _mk(N, C, H, W, Co, 3, 3)
     monkeypatch.setenv("GCOW_CONV_HALO", "0")                     # this shape would otherwise take the halo-tile kernel
     outs = []
-    for noswap in ("", "1"):
-        if noswap:
-            monkeypatch.setenv("GCOW_CONV_NOSWAP", noswap)
-        y = K.conv_igemm(x, w, b, (1, 1))
-        K.check_errors()
-        outs.append(y.float())
+    lib = K._native.cuda()
+    try:
+        for swap in (1, 0):
+            lib.gcow_conv_set_swap(swap)
+            y = K.conv_igemm(x, w, b, (1, 1))
+            K.check_errors()
+            outs.append(y.float())
+    finally:
+        lib.gcow_conv_set_swap(1)
     assert _rel(outs[0], outs[1]) < 1e-2
 
 
